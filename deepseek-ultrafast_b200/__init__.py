@@ -1,0 +1,343 @@
+"""Host-side mirror of deepseek-ultrafast's kernel call surface over libdsuf_qmm (C ABI, include/dsuf_qmm.h).
+
+The reference's host side is Rust (crates/engine/src/ops.rs); no Rust toolchain exists in this build
+environment, so the same operator surface is mirrored here in Python over ctypes.  Names follow the reference:
+``gemv`` (ops.rs:331), ``moe_route_tokens`` / ``moe_perm`` / ``moe_gather_quant`` (cu/ops.cu:615, cu/tcmoe.cu:19,88),
+``moe_gemv`` (ops.rs:482), ``ffn`` (crates/engine/src/model.rs:3497).  PyTorch is used only to own device memory
+and streams; every computation happens in the library's CUDA kernels.  There is no fallback: if the shared
+library is missing or the device is not sm_100, construction fails.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+MODE_MX, MODE_DS = 0, 1
+FMT_FP8, FMT_FP4 = 0, 1
+SCORE_IDENTITY, SCORE_SOFTMAX, SCORE_SQRT_SOFTPLUS = 0, 1, 2
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libdsuf_qmm.so")
+_LIB = None
+
+
+class DsufError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"dsuf error {code}: {msg}")
+        self.code = code
+
+
+class WeightDesc(C.Structure):
+    _fields_ = [("fmt", C.c_int32), ("mode", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("n_experts", C.c_int32),
+                ("gate_up", C.c_int32), ("tiles", C.c_uint64), ("scales_ds", C.c_uint64)]
+
+
+class PlanStruct(C.Structure):
+    _fields_ = [("expert_off", C.c_uint64), ("row_pair", C.c_uint64), ("pair_row", C.c_uint64), ("row_w", C.c_uint64),
+                ("tiles", C.c_uint64), ("ntiles", C.c_uint64), ("scratch", C.c_uint64), ("p", C.c_int32),
+                ("n_exp", C.c_int32), ("tile_rows", C.c_int32), ("max_tiles", C.c_int32)]
+
+
+class DevStatus(C.Structure):
+    _fields_ = [("code", C.c_int32), ("kernel", C.c_int32), ("cta", C.c_int32), ("where", C.c_int32)]
+
+
+# name -> (restype, argtypes); also the list the symbol-export test walks
+ABI = {
+    "dsuf_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(C.c_void_p)]),
+    "dsuf_ctx_destroy": (C.c_int32, [C.c_void_p]),
+    "dsuf_last_error": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_size_t]),
+    "dsuf_ctx_set_pdl": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "dsuf_status_poll": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(DevStatus)]),
+    "dsuf_sm_count": (C.c_int32, [C.c_void_p]),
+    "dsuf_quant_fp8_weight_host": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "dsuf_quant_fp4_weight_host": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "dsuf_packed_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "dsuf_pack_fp8_weight": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "dsuf_pack_fp4_weight": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "dsuf_weight_create": (C.c_int32, [C.c_void_p, C.POINTER(WeightDesc), C.POINTER(C.c_void_p)]),
+    "dsuf_weight_destroy": (C.c_int32, [C.c_void_p]),
+    "dsuf_act_quant_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
+                                       C.c_uint64, C.c_uint64]),
+    "dsuf_gemm_workspace_bytes": (C.c_size_t, [C.c_void_p]),
+    "dsuf_workspace_init": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_size_t]),
+    "dsuf_gemm_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
+                                  C.c_int32, C.c_float, C.c_uint64]),
+    "dsuf_moe_route": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32,
+                                   C.c_int32, C.c_float, C.c_uint64, C.c_uint64]),
+    "dsuf_moe_plan_scratch_ints": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "dsuf_moe_permute_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.POINTER(PlanStruct)]),
+    "dsuf_moe_gather_quant": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
+                                          C.c_int32, C.POINTER(PlanStruct), C.c_uint64, C.c_uint64]),
+    "dsuf_moe_w13_swiglu": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(PlanStruct), C.c_uint64,
+                                        C.c_uint64, C.c_float, C.c_uint64]),
+    "dsuf_moe_w2": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(PlanStruct), C.c_uint64,
+                                C.c_uint64, C.c_uint64]),
+    "dsuf_moe_unpermute": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(PlanStruct), C.c_uint64, C.c_uint64, C.c_int32,
+                                       C.c_int32, C.c_int32, C.c_uint64, C.c_int32]),
+}
+
+
+def lib():
+    """Loads libdsuf_qmm.so; raises if it has not been built (there is deliberately no other code path)."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise DsufError(-2, f"{LIB_PATH} is missing: build it with `python deepseek-ultrafast_b200/build.py`")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in ABI.items():
+            f = getattr(L, name)
+            f.restype, f.argtypes = res, args
+        _LIB = L
+    return _LIB
+
+
+def _np_ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+# ------------------------------------------------------------------ host formats (no GPU)
+def quant_fp8_weight_host(mode, w_bf16):
+    w = np.ascontiguousarray(w_bf16, dtype=np.uint16)
+    n, k = w.shape
+    blk = 32 if mode == MODE_MX else 128
+    codes = np.empty((n, k), np.uint8)
+    scales = np.empty((n // blk, k // blk), np.uint8 if mode == MODE_MX else np.float32)
+    rc = lib().dsuf_quant_fp8_weight_host(mode, _np_ptr(w), n, k, _np_ptr(codes), _np_ptr(scales))
+    if rc:
+        raise DsufError(rc, "dsuf_quant_fp8_weight_host")
+    return codes, scales
+
+
+def quant_fp4_weight_host(w_bf16):
+    w = np.ascontiguousarray(w_bf16, dtype=np.uint16)
+    n, k = w.shape
+    codes = np.empty((n, k // 2), np.uint8)
+    scales = np.empty((n, k // 32), np.uint8)
+    rc = lib().dsuf_quant_fp4_weight_host(_np_ptr(w), n, k, _np_ptr(codes), _np_ptr(scales))
+    if rc:
+        raise DsufError(rc, "dsuf_quant_fp4_weight_host")
+    return codes, scales
+
+
+def pack_fp8_weight(mode, codes, scales):
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    n, k = codes.shape
+    out = np.empty(lib().dsuf_packed_bytes(FMT_FP8, mode, n, k), np.uint8)
+    sc = None if scales is None else np.ascontiguousarray(scales)
+    rc = lib().dsuf_pack_fp8_weight(mode, _np_ptr(codes), _np_ptr(sc), n, k, _np_ptr(out))
+    if rc:
+        raise DsufError(rc, "dsuf_pack_fp8_weight")
+    return out
+
+
+def pack_fp4_weight(codes, scales, gate_up):
+    codes = np.ascontiguousarray(codes, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    n, k = codes.shape[0], codes.shape[1] * 2
+    out = np.empty(lib().dsuf_packed_bytes(FMT_FP4, MODE_MX, n, k), np.uint8)
+    rc = lib().dsuf_pack_fp4_weight(_np_ptr(codes), _np_ptr(scales), n, k, int(bool(gate_up)), _np_ptr(out))
+    if rc:
+        raise DsufError(rc, "dsuf_pack_fp4_weight")
+    return out
+
+
+# ------------------------------------------------------------------ device side
+class Ctx:
+    """dsuf_ctx wrapper: one per device (Device::new + ops::hw(), crates/cuda/src/lib.rs:52, ops.rs:205)."""
+
+    def __init__(self, device=0, pdl=False):
+        import torch
+        self.torch = torch
+        self.device = torch.device("cuda", device)
+        h = C.c_void_p()
+        rc = lib().dsuf_ctx_create(device, C.byref(h))
+        if rc:
+            raise DsufError(rc, "dsuf_ctx_create failed (needs an sm_100 GPU)")
+        self.h = h
+        if pdl:
+            self.check(lib().dsuf_ctx_set_pdl(self.h, 1))
+        nbytes = lib().dsuf_gemm_workspace_bytes(self.h)
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.check(lib().dsuf_workspace_init(self.h, self.stream(), self.workspace.data_ptr(), nbytes))
+        self.sm_count = lib().dsuf_sm_count(self.h)
+
+    def stream(self):
+        return C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)
+
+    def check(self, rc):
+        if rc:
+            buf = C.create_string_buffer(512)
+            lib().dsuf_last_error(self.h, buf, 512)
+            raise DsufError(rc, buf.value.decode())
+
+    def status(self):
+        st = DevStatus()
+        self.check(lib().dsuf_status_poll(self.h, self.stream(), C.byref(st)))
+        return st
+
+    def close(self):
+        if self.h:
+            lib().dsuf_ctx_destroy(self.h)
+            self.h = None
+
+
+class Weight:
+    """Weight{fmt,w,s,n,k} / Experts (ops.rs:6-39, crates/engine/src/weights.rs:82-92) over a packed tile image."""
+
+    def __init__(self, ctx, fmt, mode, n, k, n_experts, gate_up, tiles, scales_ds=None):
+        self.ctx, self.fmt, self.mode, self.n, self.k = ctx, fmt, mode, n, k
+        self.n_experts, self.gate_up = n_experts, gate_up
+        self.tiles, self.scales_ds = tiles, scales_ds  # keep the device tensors alive
+        d = WeightDesc(fmt, mode, n, k, n_experts, int(bool(gate_up)), tiles.data_ptr(),
+                       scales_ds.data_ptr() if scales_ds is not None else 0)
+        h = C.c_void_p()
+        ctx.check(lib().dsuf_weight_create(ctx.h, C.byref(d), C.byref(h)))
+        self.h = h
+
+    @staticmethod
+    def dense_fp8(ctx, mode, codes, scales):
+        """codes u8 [n][k]; scales MX u8 [n/32][k/32] or DS f32 [n/128][k/128] (host arrays)."""
+        t = ctx.torch
+        n, k = codes.shape
+        tiles = t.from_numpy(pack_fp8_weight(mode, codes, scales if mode == MODE_MX else None)).to(ctx.device)
+        sds = t.from_numpy(np.ascontiguousarray(scales, np.float32)).to(ctx.device) if mode == MODE_DS else None
+        return Weight(ctx, FMT_FP8, mode, n, k, 1, False, tiles, sds)
+
+    @staticmethod
+    def experts_fp4(ctx, codes, scales, gate_up):
+        """codes u8 [E][n][k/2], scales u8 [E][n][k/32] (host arrays); gate_up: rows are [gate; up]."""
+        t = ctx.torch
+        e, n, kh = codes.shape
+        per = lib().dsuf_packed_bytes(FMT_FP4, MODE_MX, n, kh * 2)
+        tiles = t.empty(e * per, dtype=t.uint8, device=ctx.device)
+        for i in range(e):
+            tiles[i * per:(i + 1) * per].copy_(t.from_numpy(pack_fp4_weight(codes[i], scales[i], gate_up)))
+        return Weight(ctx, FMT_FP4, MODE_MX, n, kh * 2, e, gate_up, tiles)
+
+    @staticmethod
+    def experts_fp4_packed(ctx, tiles, n, k, n_experts, gate_up):
+        return Weight(ctx, FMT_FP4, MODE_MX, n, k, n_experts, gate_up, tiles)
+
+
+def act_quant(ctx, mode, x, q=None, s=None):
+    """tc_quant_rows (cu/tcgemm.cu:300): x bf16 [m][k] -> (codes u8 [m][k], scales)."""
+    t = ctx.torch
+    m, k = x.shape
+    blk = 32 if mode == MODE_MX else 128
+    if q is None:
+        q = t.empty((m, k), dtype=t.uint8, device=x.device)
+    if s is None:
+        s = t.empty((m, k // blk), dtype=t.uint8 if mode == MODE_MX else t.float32, device=x.device)
+    ctx.check(lib().dsuf_act_quant_fp8(ctx.h, ctx.stream(), mode, x.data_ptr(), x.stride(0), m, k, q.data_ptr(), s.data_ptr()))
+    return q, s
+
+
+def gemm_fp8(ctx, w, xq, xs, m, out=None, alpha=1.0):
+    t = ctx.torch
+    if out is None:
+        out = t.empty((m, w.n), dtype=t.bfloat16, device=xq.device)
+    ctx.check(lib().dsuf_gemm_fp8(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0),
+                                  alpha, ctx.workspace.data_ptr()))
+    return out
+
+
+def gemv(ctx, w, x, out=None, alpha=1.0):
+    """ops::gemv (ops.rs:331-474): bf16 activations in, bf16 out; quantizes once, then streams the weight."""
+    xq, xs = act_quant(ctx, w.mode, x)
+    return gemm_fp8(ctx, w, xq, xs, x.shape[0], out, alpha)
+
+
+class MoePlan:
+    """Caller-owned buffers of the permute plan (MpParams, ops.rs:1478-1491)."""
+
+    def __init__(self, ctx, tokens, topk, n_exp, tile_rows):
+        t = ctx.torch
+        dev = ctx.device
+        self.ctx, self.tokens, self.topk, self.n_exp, self.tile_rows = ctx, tokens, topk, n_exp, tile_rows
+        p = tokens * topk
+        self.p = p
+        self.max_tiles = p // tile_rows + n_exp
+        i32 = dict(dtype=t.int32, device=dev)
+        self.expert_off = t.zeros(n_exp + 1, **i32)
+        self.row_pair = t.zeros(max(p, 1), **i32)
+        self.pair_row = t.zeros(max(p, 1), **i32)
+        self.row_w = t.zeros(max(p, 1), dtype=t.float32, device=dev)
+        self.tiles = t.zeros((self.max_tiles, 4), **i32)
+        self.ntiles = t.zeros(2, **i32)
+        self.scratch = t.zeros(lib().dsuf_moe_plan_scratch_ints(p, n_exp), **i32)
+        self.c = PlanStruct(self.expert_off.data_ptr(), self.row_pair.data_ptr(), self.pair_row.data_ptr(),
+                            self.row_w.data_ptr(), self.tiles.data_ptr(), self.ntiles.data_ptr(), self.scratch.data_ptr(),
+                            p, n_exp, tile_rows, self.max_tiles)
+
+
+def moe_route_tokens(ctx, score_fn, scores, bias, topk, route_scale=1.0):
+    t = ctx.torch
+    tok, n_exp = scores.shape
+    ids = t.empty((tok, topk), dtype=t.int32, device=scores.device)
+    w = t.empty((tok, topk), dtype=t.float32, device=scores.device)
+    ctx.check(lib().dsuf_moe_route(ctx.h, ctx.stream(), score_fn, scores.data_ptr(), bias.data_ptr() if bias is not None else 0,
+                                   tok, n_exp, topk, route_scale, ids.data_ptr(), w.data_ptr()))
+    return ids, w
+
+
+def moe_perm(ctx, plan, ids, w, e_lo=0):
+    ctx.check(lib().dsuf_moe_permute_plan(ctx.h, ctx.stream(), ids.data_ptr(), w.data_ptr(), e_lo, C.byref(plan.c)))
+
+
+def moe_gather_quant(ctx, mode, plan, x, xq, xs):
+    tok, h = x.shape
+    ctx.check(lib().dsuf_moe_gather_quant(ctx.h, ctx.stream(), mode, x.data_ptr(), x.stride(0), tok, h, plan.topk,
+                                          C.byref(plan.c), xq.data_ptr(), xs.data_ptr()))
+
+
+def moe_w13_swiglu(ctx, w13, act_mode, plan, xq, xs, act_out, swiglu_limit=0.0):
+    ctx.check(lib().dsuf_moe_w13_swiglu(ctx.h, ctx.stream(), w13.h, act_mode, C.byref(plan.c), xq.data_ptr(), xs.data_ptr(),
+                                        swiglu_limit, act_out.data_ptr()))
+
+
+def moe_w2(ctx, w2, act_mode, plan, act_q, act_s, yrows):
+    ctx.check(lib().dsuf_moe_w2(ctx.h, ctx.stream(), w2.h, act_mode, C.byref(plan.c), act_q.data_ptr(), act_s.data_ptr(),
+                                yrows.data_ptr()))
+
+
+def moe_unpermute(ctx, plan, yrows, out, shared=None):
+    tok, h = out.shape
+    ctx.check(lib().dsuf_moe_unpermute(ctx.h, ctx.stream(), C.byref(plan.c), yrows.data_ptr(),
+                                       shared.data_ptr() if shared is not None else 0, tok, plan.topk, h, out.data_ptr(),
+                                       out.stride(0)))
+
+
+class MoeLayer:
+    """Routed-expert FFN of one layer = Rank::ffn / ffn_prefill (crates/engine/src/model.rs:3497, :3063) without the
+    model-specific parts: route -> plan -> gather+quant -> w13+SwiGLU -> quant -> w2 -> unpermute/combine.
+    All scratch is allocated once here; ``forward`` only launches kernels."""
+
+    def __init__(self, ctx, w13, w2, tokens, topk, act_mode, e_lo=0, tile_rows=None, swiglu_limit=0.0):
+        t = ctx.torch
+        dev = ctx.device
+        self.ctx, self.w13, self.w2, self.tokens, self.topk, self.act_mode = ctx, w13, w2, tokens, topk, act_mode
+        self.e_lo, self.swiglu_limit = e_lo, swiglu_limit
+        self.h, self.inter = w13.k, w13.n // 2
+        if tile_rows is None:
+            tile_rows = 8
+        self.plan = MoePlan(ctx, tokens, topk, w13.n_experts, tile_rows)
+        p = max(tokens * topk, 1)
+        blk = 32 if act_mode == MODE_MX else 128
+        sdt = t.uint8 if act_mode == MODE_MX else t.float32
+        self.xq = t.zeros((p, self.h), dtype=t.uint8, device=dev)
+        self.xs = t.zeros((p, self.h // blk), dtype=sdt, device=dev)
+        self.act = t.zeros((p, self.inter), dtype=t.bfloat16, device=dev)
+        self.act_q = t.zeros((p, self.inter), dtype=t.uint8, device=dev)
+        self.act_s = t.zeros((p, self.inter // blk), dtype=sdt, device=dev)
+        self.yrows = t.zeros((p, self.h), dtype=t.float32, device=dev)
+
+    def forward(self, x, ids, w, out, shared=None):
+        ctx, plan = self.ctx, self.plan
+        moe_perm(ctx, plan, ids, w, self.e_lo)
+        moe_gather_quant(ctx, self.act_mode, plan, x, self.xq, self.xs)
+        moe_w13_swiglu(ctx, self.w13, self.act_mode, plan, self.xq, self.xs, self.act, self.swiglu_limit)
+        act_quant(ctx, self.act_mode, self.act, self.act_q, self.act_s)
+        moe_w2(ctx, self.w2, self.act_mode, plan, self.act_q, self.act_s, self.yrows)
+        moe_unpermute(ctx, plan, self.yrows, out, shared)
+        return out

@@ -1,0 +1,92 @@
+// Host-side internals of libdsuf_qmm: context, error plumbing, the kernel launch helper and the prototypes of
+// the per-file launchers.  Nothing here is part of the exported C ABI (see include/dsuf_qmm.h).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/dsuf_qmm.h"
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+typedef CUresult (*dsuf_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                         const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                         CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct dsuf_ctx {
+    int device;
+    int sm_count;
+    int smem_optin;
+    int use_pdl;                   // launch with programmatic stream serialization
+    dsuf::DevStatus* dev_status;   // device word written by a kernel whose bounded wait expired
+    dsuf_encode_tiled_fn encode_tiled;
+    char err[512];
+};
+
+struct dsuf_weight {
+    dsuf_weight_desc d;
+    CUtensorMap tm_stream;   // tile records as bytes for the streaming (decode) kernels
+    CUtensorMap tm_tc;       // tile records for the tcgen05 kernels (FP4: 4-bit elements unpacked by TMA)
+    int rt, kt;              // row tiles per matrix, K tiles per row
+    int rec_bytes, codes_bytes;
+    long long tiles_total;
+};
+
+namespace dsuf {
+
+inline int fail(dsuf_ctx* ctx, int code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+inline int cuda_fail(dsuf_ctx* ctx, cudaError_t e, const char* what) {
+    return fail(ctx, (int)e > 0 ? (int)e : DSUF_E_BADARG, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define DSUF_REQUIRE(ctx, cond, ...) \
+    do { if (!(cond)) return ::dsuf::fail(ctx, DSUF_E_BADARG, __VA_ARGS__); } while (0)
+
+// One launch path for every kernel: asynchronous on the caller's stream, optional PDL attribute, no
+// allocation and no synchronisation (safe inside stream capture).
+template <typename... KArgs, typename... Args>
+int launch(dsuf_ctx* ctx, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "kernel launch");
+    return DSUF_OK;
+}
+
+// per-file launchers
+int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
+                     void* scales, const int* pair_row, int fanout, int sf_atoms);
+int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
+                        void* out, int ldo, float alpha, void* workspace);
+int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, int epi, int act_mode, const dsuf_moe_plan* plan,
+                      const void* xq, const void* xs, float swiglu_limit, void* out, int ldo);
+int launch_route(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp,
+                 int topk, float route_scale, int* ids, float* w);
+int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float* w, int e_lo, const dsuf_moe_plan* plan);
+int launch_unpermute(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
+                     int t, int topk, int h, void* out, int ldo);
+int stream_setup(dsuf_ctx* ctx);
+int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, long long rows, int box_rows);
+
+}  // namespace dsuf

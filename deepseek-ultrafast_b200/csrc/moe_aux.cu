@@ -1,0 +1,249 @@
+// Routing, permute plan and unpermute/combine of the routed-expert layer.
+//
+//   route_kernel        <- moe_route_tokens / route_token   (crates/kernels/cu/ops.cu:615-623, cu/route.cuh:3-56)
+//   plan_*_kernel       <- moe_perm                         (cu/tcmoe.cu:19-69; decode slots: cu/gemv.cu:715-776)
+//   unpermute_kernel    <- the nsum/src2 sum in comm_push   (cu/comm.cu:167-180)
+//
+// The reference builds its prefill plan in ONE 1024-thread CTA with shared-memory atomics (order inside an
+// expert depends on timing) and rebuilds the decode plan inside every GEMV CTA.  Here the plan is built once,
+// by a three-phase stable counting sort that scales over CTAs, and every consumer (decode or prefill) reads it.
+#include "internal.h"
+
+namespace dsuf {
+
+// ---------------------------------------------------------------- router
+constexpr int ROUTE_MAX_PER_LANE = 16;  // n_exp <= 512
+
+__global__ void __launch_bounds__(256) route_kernel(int score_fn, const float* scores, const float* bias, int t, int n_exp,
+                                                    int topk, float route_scale, int* ids, float* w) {
+    pdl_wait();
+    const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (tok >= t) return;
+    float sc[ROUTE_MAX_PER_LANE], key[ROUTE_MAX_PER_LANE];
+    const float* s = scores + (size_t)tok * n_exp;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        sc[i] = e < n_exp ? s[e] : -INFINITY;
+        mx = fmaxf(mx, sc[i]);
+    }
+    if (score_fn == DSUF_SCORE_SOFTMAX) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+            sc[i] = lane + 32 * i < n_exp ? expf(sc[i] - mx) : 0.f;
+            sum += sc[i];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) sc[i] = __fdiv_rn(sc[i], sum);
+    } else if (score_fn == DSUF_SCORE_SQRT_SOFTPLUS) {
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+            if (lane + 32 * i < n_exp) sc[i] = sqrtf(sc[i] > 20.f ? sc[i] : log1pf(expf(sc[i])));
+    }
+#pragma unroll
+    for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        key[i] = e < n_exp ? sc[i] + (bias ? bias[e] : 0.f) : -INFINITY;
+    }
+    float wsum = 0.f, myw = 0.f;
+    int myid = 0;
+    for (int j = 0; j < topk; ++j) {
+        // lane-local best (first maximum = lowest expert id among this lane's ties)
+        float bv = key[0];
+        int bi = 0;
+#pragma unroll
+        for (int i = 1; i < ROUTE_MAX_PER_LANE; ++i)
+            if (key[i] > bv) { bv = key[i]; bi = i; }
+        // order-preserving integer key so the warp reduction is exact
+        const unsigned u = __float_as_uint(bv);
+        const unsigned k32 = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        const unsigned kmax = __reduce_max_sync(0xffffffffu, k32);
+        const int cand = lane + 32 * bi;
+        const int win = (int)__reduce_min_sync(0xffffffffu, k32 == kmax ? (unsigned)cand : 0x7fffffffu);
+        float wv = 0.f;
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+            if (lane + 32 * i == win) { wv = sc[i]; key[i] = -INFINITY; }
+        wv = __shfl_sync(0xffffffffu, wv, win & 31);
+        wsum += wv;
+        if (lane == j) { myw = wv; myid = win; }
+    }
+    if (lane < topk) {
+        const float v = topk > 1 ? __fdiv_rn(myw, wsum + 1e-20f) : myw;
+        ids[(size_t)tok * topk + lane] = myid;
+        w[(size_t)tok * topk + lane] = v * route_scale;
+    }
+}
+
+int launch_route(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp,
+                 int topk, float route_scale, int* ids, float* w) {
+    if (t == 0) return DSUF_OK;
+    return launch(ctx, stream, route_kernel, dim3((t + 7) / 8), dim3(256), 0, score_fn, scores, bias, t, n_exp, topk,
+                  route_scale, ids, w);
+}
+
+// ---------------------------------------------------------------- permute plan
+// scratch layout (ints): block_cnt[nblk][n_exp] | local_rank[p]
+constexpr int PLAN_BLOCK = 1024;
+constexpr int PLAN_MAX_EXP = 512;
+
+struct PlanArgs {
+    const int* ids;
+    const float* w;
+    int e_lo, n_exp, p, tile_rows, max_tiles, nblk;
+    int* expert_off;
+    int* row_pair;
+    int* pair_row;
+    float* row_w;
+    int4* tiles;
+    int* ntiles;
+    int* block_cnt;
+    int* local_rank;
+    DevStatus* status;
+};
+
+// Phase A: per-block histogram and each pair's stable rank inside its block.
+__global__ void __launch_bounds__(PLAN_BLOCK) plan_count_kernel(const PlanArgs a) {
+    pdl_wait();
+    __shared__ unsigned short warp_hist[32][PLAN_MAX_EXP];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < 32 * PLAN_MAX_EXP; i += PLAN_BLOCK) (&warp_hist[0][0])[i] = 0;
+    __syncthreads();
+    const int i = blockIdx.x * PLAN_BLOCK + tid;
+    int e = -1;
+    if (i < a.p) {
+        e = a.ids[i] - a.e_lo;
+        if (e < 0 || e >= a.n_exp) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) warp_hist[warp][e] = (unsigned short)__popc(peers);
+    __syncthreads();
+    for (int x = tid; x < a.n_exp; x += PLAN_BLOCK) {
+        int run = 0;
+        for (int wv = 0; wv < 32; ++wv) {
+            const int c = warp_hist[wv][x];
+            warp_hist[wv][x] = (unsigned short)run;
+            run += c;
+        }
+        a.block_cnt[(size_t)blockIdx.x * a.n_exp + x] = run;
+    }
+    __syncthreads();
+    if (i < a.p) a.local_rank[i] = e >= 0 ? warp_hist[warp][e] + rank_in_warp : -1;
+}
+
+// Phase B (one CTA): scan blocks per expert, scan experts, emit the tile list.
+__global__ void __launch_bounds__(PLAN_MAX_EXP) plan_scan_kernel(const PlanArgs a) {
+    pdl_wait();
+    __shared__ int s_cnt[PLAN_MAX_EXP], s_off[PLAN_MAX_EXP + 1], s_toff[PLAN_MAX_EXP + 1];
+    const int e = threadIdx.x;
+    int total = 0;
+    if (e < a.n_exp) {
+        for (int b = 0; b < a.nblk; ++b) {
+            const int c = a.block_cnt[(size_t)b * a.n_exp + e];
+            a.block_cnt[(size_t)b * a.n_exp + e] = total;
+            total += c;
+        }
+    }
+    s_cnt[e] = e < a.n_exp ? total : 0;
+    __syncthreads();
+    if (e == 0) {
+        int run = 0, trun = 0;
+        for (int x = 0; x < a.n_exp; ++x) {
+            s_off[x] = run;
+            s_toff[x] = trun;
+            run += s_cnt[x];
+            trun += (s_cnt[x] + a.tile_rows - 1) / a.tile_rows;
+        }
+        s_off[a.n_exp] = run;
+        s_toff[a.n_exp] = trun;
+        a.ntiles[0] = trun <= a.max_tiles ? trun : a.max_tiles;
+        a.ntiles[1] = run;
+        if (trun > a.max_tiles) report(a.status, DEVERR_BAD_PLAN, 2, trun);
+    }
+    __syncthreads();
+    if (e <= a.n_exp) a.expert_off[e] = s_off[e];
+    if (e < a.n_exp) {
+        int ti = s_toff[e];
+        for (int r0 = 0; r0 < s_cnt[e]; r0 += a.tile_rows, ++ti)
+            if (ti < a.max_tiles) a.tiles[ti] = make_int4(e, s_off[e] + r0, min(a.tile_rows, s_cnt[e] - r0), 0);
+    }
+}
+
+// Phase C: place every pair.
+__global__ void __launch_bounds__(PLAN_BLOCK) plan_place_kernel(const PlanArgs a) {
+    pdl_wait();
+    const int i = blockIdx.x * PLAN_BLOCK + threadIdx.x;
+    if (i >= a.p) return;
+    const int lr = a.local_rank[i];
+    if (lr < 0) { a.pair_row[i] = -1; return; }
+    const int e = a.ids[i] - a.e_lo;
+    const int row = a.expert_off[e] + a.block_cnt[(size_t)blockIdx.x * a.n_exp + e] + lr;
+    a.row_pair[row] = i;
+    a.pair_row[i] = row;
+    a.row_w[row] = a.w[i];
+}
+
+int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float* w, int e_lo, const dsuf_moe_plan* plan) {
+    PlanArgs a;
+    a.ids = ids; a.w = w; a.e_lo = e_lo; a.n_exp = plan->n_exp; a.p = plan->p; a.tile_rows = plan->tile_rows;
+    a.max_tiles = plan->max_tiles;
+    a.nblk = (plan->p + PLAN_BLOCK - 1) / PLAN_BLOCK;
+    a.expert_off = (int*)plan->expert_off; a.row_pair = (int*)plan->row_pair; a.pair_row = (int*)plan->pair_row;
+    a.row_w = (float*)plan->row_w; a.tiles = (int4*)plan->tiles; a.ntiles = (int*)plan->ntiles;
+    a.block_cnt = (int*)plan->scratch;
+    a.local_rank = a.block_cnt + (size_t)a.nblk * a.n_exp;
+    a.status = ctx->dev_status;
+    int rc = launch(ctx, stream, plan_count_kernel, dim3(a.nblk > 0 ? a.nblk : 1), dim3(PLAN_BLOCK), 0, a);
+    if (rc) return rc;
+    rc = launch(ctx, stream, plan_scan_kernel, dim3(1), dim3(PLAN_MAX_EXP), 0, a);
+    if (rc) return rc;
+    if (a.nblk == 0) return DSUF_OK;
+    return launch(ctx, stream, plan_place_kernel, dim3(a.nblk), dim3(PLAN_BLOCK), 0, a);
+}
+
+// ---------------------------------------------------------------- unpermute / combine
+__global__ void __launch_bounds__(256) unpermute_kernel(const int* pair_row, const float* yrows, const bf16* shared, int topk,
+                                                        int h, bf16* out, int ldo) {
+    pdl_wait();
+    const int tok = blockIdx.x;
+    __shared__ int rows[16];
+    if (threadIdx.x < topk) rows[threadIdx.x] = pair_row[(size_t)tok * topk + threadIdx.x];
+    __syncthreads();
+    for (int c = (blockIdx.y * 256 + threadIdx.x) * 4; c < h; c += gridDim.y * 1024) {
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < topk; ++j) {
+            const int r = rows[j];
+            if (r < 0) continue;
+            const float4 v = __ldcs((const float4*)(yrows + (size_t)r * h + c));
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        if (shared) {
+            const uint2 raw = *(const uint2*)(shared + (size_t)tok * h + c);
+            const bf16* sh = (const bf16*)&raw;
+            s.x += __bfloat162float(sh[0]); s.y += __bfloat162float(sh[1]);
+            s.z += __bfloat162float(sh[2]); s.w += __bfloat162float(sh[3]);
+        }
+        uint2 o;
+        bf16* ob = (bf16*)&o;
+        ob[0] = __float2bfloat16(s.x); ob[1] = __float2bfloat16(s.y);
+        ob[2] = __float2bfloat16(s.z); ob[3] = __float2bfloat16(s.w);
+        *(uint2*)(out + (size_t)tok * ldo + c) = o;
+    }
+}
+
+int launch_unpermute(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
+                     int t, int topk, int h, void* out, int ldo) {
+    if (t == 0) return DSUF_OK;
+    const int gy = t >= 1024 ? 1 : (h + 1023) / 1024;
+    return launch(ctx, stream, unpermute_kernel, dim3(t, gy), dim3(256), 0, (const int*)plan->pair_row, yrows,
+                  (const bf16*)shared, topk, h, (bf16*)out, ldo);
+}
+
+}  // namespace dsuf

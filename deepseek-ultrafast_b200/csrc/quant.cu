@@ -1,0 +1,95 @@
+// FP8 (e4m3) activation quantization, stand-alone and fused with the routed-token scatter.
+//
+// Replaces tc_quant_rows (crates/kernels/cu/tcgemm.cu:300-340), the per-CTA quant_blocks8 staging of the decode
+// GEMVs (cu/quantblocks.cuh:7-57) and moe_gather_quant (cu/tcmoe.cu:88-133).  Activations are quantized ONCE per
+// token by this kernel; every GEMM consumer reads the codes.
+//   MX geometry: 1x32 blocks, scale 2^ceil(log2(max(amax,1e-4)/448)) stored as UE8M0, exact reciprocal by
+//                exponent flip (bit-identical to the reference).
+//   DS geometry: 1x128 blocks, fp32 scale = amax/448 (1 for an all-zero block), code = rne(x / scale) with IEEE
+//                division.
+// HBM-bound: reads 2 B and writes ~1.03 B (x fan-out for the scatter form) per element; 16-byte loads,
+// 8-byte stores, amax by warp shuffles.
+#include "internal.h"
+
+namespace dsuf {
+
+struct QuantArgs {
+    const bf16* x;        // [rows_in][ldx]
+    int ldx, rows_in, k;
+    uint8_t* q;           // [rows_out][k]
+    void* scales;         // MX: u8 [rows_out][k/32] (or 512-byte atoms), DS: f32 [rows_out][k/128]
+    const int* pair_row;  // scatter form: destination rows of token t are pair_row[t*fanout + j] (<0: skipped)
+    int fanout;           // 0: plain (row r -> row r)
+    int sf_atoms;         // MX only: write scales into 128-row x 128-K atoms instead of row-major
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
+    pdl_wait();
+    const int row = blockIdx.x;
+    const int k0 = (blockIdx.y * 256 + threadIdx.x) * 8;
+    const bool live = k0 < a.k;
+    float v[8];
+    if (live) {
+        const uint4 raw = *(const uint4*)(a.x + (size_t)row * a.ldx + k0);
+        const bf16* h = (const bf16*)&raw;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(h[e]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+    constexpr int LANES = MODE == DSUF_MODE_MX ? 4 : 16;  // lanes sharing one scale block
+#pragma unroll
+    for (int o = 1; o < LANES; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float sc;
+    uint2 out;
+    if (MODE == DSUF_MODE_MX) {
+        sc = round_scale_pow2(fmaxf(amax, 1e-4f), 1.0f / 448.0f);
+        const float inv = __uint_as_float(0x7f000000u - __float_as_uint(sc));
+        out.x = f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+        out.y = f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+    } else {
+        sc = amax == 0.f ? 1.0f : __fdiv_rn(amax, 448.0f);
+        out.x = f32x4_to_e4m3x4(__fdiv_rn(v[0], sc), __fdiv_rn(v[1], sc), __fdiv_rn(v[2], sc), __fdiv_rn(v[3], sc));
+        out.y = f32x4_to_e4m3x4(__fdiv_rn(v[4], sc), __fdiv_rn(v[5], sc), __fdiv_rn(v[6], sc), __fdiv_rn(v[7], sc));
+    }
+    pdl_launch_dependents();
+    if (!live) return;
+    const bool writes_scale = (threadIdx.x & (LANES - 1)) == 0;
+    const int nfan = a.fanout > 0 ? a.fanout : 1;
+    for (int j = 0; j < nfan; ++j) {
+        const int dst = a.fanout > 0 ? a.pair_row[(size_t)row * a.fanout + j] : row;
+        if (dst < 0) continue;
+        *(uint2*)(a.q + (size_t)dst * a.k + k0) = out;
+        if (writes_scale) {
+            if (MODE == DSUF_MODE_MX) {
+                const int kb = k0 >> 5;
+                const uint8_t b = (uint8_t)(__float_as_uint(sc) >> 23);
+                if (a.sf_atoms) {
+                    const int r = dst & 127;
+                    ((uint8_t*)a.scales)[((size_t)(dst >> 7) * (a.k >> 7) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = b;
+                } else {
+                    ((uint8_t*)a.scales)[(size_t)dst * (a.k >> 5) + kb] = b;
+                }
+            } else {
+                ((float*)a.scales)[(size_t)dst * (a.k >> 7) + (k0 >> 7)] = sc;
+            }
+        }
+    }
+}
+
+int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
+                     void* scales, const int* pair_row, int fanout, int sf_atoms) {
+    QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, sf_atoms};
+    if (rows_in == 0) return DSUF_OK;
+    dim3 grid(rows_in, (k + 2047) / 2048);
+    if (mode == DSUF_MODE_MX)
+        return launch(ctx, stream, act_quant_kernel<DSUF_MODE_MX>, grid, dim3(256), 0, a);
+    return launch(ctx, stream, act_quant_kernel<DSUF_MODE_DS>, grid, dim3(256), 0, a);
+}
+
+}  // namespace dsuf

@@ -1,0 +1,126 @@
+// Host launchers of the streaming (decode-shape) kernels: geometry checks, TMA descriptors for the activation
+// rows, instantiation table.  Launch contracts mirror ops::gemv (crates/engine/src/ops.rs:331-474: shape
+// preconditions returned as errors, never UB) and ops::moe_gemv (ops.rs:482-634).
+#include "internal.h"
+#include "stream_gemv.cuh"
+
+namespace dsuf {
+
+constexpr int WS_MAX_CTAS = 256;
+constexpr int WS_MAX_ROW_TILES = 8192;
+constexpr size_t WS_PARTIAL_BYTES = (size_t)WS_MAX_CTAS * 2 * 8 * 256 * sizeof(float);
+constexpr size_t WS_BYTES = WS_PARTIAL_BYTES + WS_MAX_ROW_TILES * sizeof(int);
+
+int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, long long rows, int box_rows) {
+    cuuint64_t dims[2] = {(cuuint64_t)k_bytes, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k_bytes};
+    cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+    cuuint32_t es[2] = {1u, 1u};
+    CUresult r = ctx->encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, DSUF_E_BADARG, "cuTensorMapEncodeTiled(activations) failed: %d", (int)r);
+    return DSUF_OK;
+}
+
+template <int FMT, int WMX, int AMX, int NT8, int EPI>
+static int set_attr(dsuf_ctx* ctx) {
+    cudaError_t e = cudaFuncSetAttribute(stream_gemv_kernel<FMT, WMX, AMX, NT8, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         StreamCfg<FMT>::SMEM);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(stream_gemv)");
+    return DSUF_OK;
+}
+
+int stream_setup(dsuf_ctx* ctx) {
+    int rc = 0;
+#define SA(...) if ((rc = set_attr<__VA_ARGS__>(ctx))) return rc
+    SA(FMT_FP8, 0, 0, 1, EPI_DENSE); SA(FMT_FP8, 0, 0, 2, EPI_DENSE);
+    SA(FMT_FP8, 1, 1, 1, EPI_DENSE); SA(FMT_FP8, 1, 1, 2, EPI_DENSE);
+    SA(FMT_FP4, 1, 0, 1, EPI_W13); SA(FMT_FP4, 1, 0, 2, EPI_W13);
+    SA(FMT_FP4, 1, 1, 1, EPI_W13); SA(FMT_FP4, 1, 1, 2, EPI_W13);
+    SA(FMT_FP4, 1, 0, 1, EPI_W2); SA(FMT_FP4, 1, 0, 2, EPI_W2);
+    SA(FMT_FP4, 1, 1, 1, EPI_W2); SA(FMT_FP4, 1, 1, 2, EPI_W2);
+#undef SA
+    return DSUF_OK;
+}
+
+static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
+    memset(&a, 0, sizeof(a));
+    a.tm_w = w->tm_stream;
+    a.wtiles = (const uint8_t*)w->d.tiles;
+    a.wscale_ds = (const float*)w->d.scales_ds;
+    a.status = ctx->dev_status;
+    a.RT = w->rt;
+    a.KT = w->kt;
+    a.rec_bytes = w->rec_bytes;
+    a.codes_bytes = w->codes_bytes;
+    a.n_rows = w->d.n;
+    a.alpha = 1.0f;
+}
+
+int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
+                        void* out, int ldo, float alpha, void* workspace) {
+    DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP8 && w->d.n_experts == 1, "dsuf_gemm_fp8: weight is not a dense FP8 weight");
+    DSUF_REQUIRE(ctx, m >= 1 && m <= 16, "dsuf_gemm_fp8: streaming path takes 1..16 token rows, got %d", m);
+    DSUF_REQUIRE(ctx, w->rt <= WS_MAX_ROW_TILES, "dsuf_gemm_fp8: too many row tiles (%d)", w->rt);
+    DSUF_REQUIRE(ctx, ldo >= w->d.n, "dsuf_gemm_fp8: ldo %d < n %d", ldo, w->d.n);
+    DSUF_REQUIRE(ctx, xq && xs && out && workspace, "dsuf_gemm_fp8: null pointer");
+    StreamArgs a;
+    fill_common(ctx, a, w);
+    const int nt8 = m <= 8 ? 1 : 2;
+    int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, 8 * nt8);
+    if (rc) return rc;
+    a.xscale = xs;
+    a.out = out;
+    a.partial = (float*)workspace;
+    a.counters = (int*)((uint8_t*)workspace + WS_PARTIAL_BYTES);
+    a.m = m;
+    a.x_rows = m;
+    a.ldo = ldo;
+    a.alpha = alpha;
+    const long long tot = (long long)w->rt * w->kt;
+    int grid = ctx->sm_count < WS_MAX_CTAS ? ctx->sm_count : WS_MAX_CTAS;
+    if (tot < grid) grid = (int)tot;
+    const size_t smem = StreamCfg<FMT_FP8>::SMEM;
+    const bool mx = w->d.mode == DSUF_MODE_MX;
+#define GO(WMX, AMX, NT) launch(ctx, stream, stream_gemv_kernel<FMT_FP8, WMX, AMX, NT, EPI_DENSE>, dim3(grid), dim3(STREAM_THREADS), smem, a)
+    if (mx) return nt8 == 1 ? GO(1, 1, 1) : GO(1, 1, 2);
+    return nt8 == 1 ? GO(0, 0, 1) : GO(0, 0, 2);
+#undef GO
+}
+
+int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, int epi, int act_mode, const dsuf_moe_plan* plan,
+                      const void* xq, const void* xs, float swiglu_limit, void* out, int ldo) {
+    DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP4, "grouped streaming GEMM: weight is not FP4");
+    DSUF_REQUIRE(ctx, plan->tile_rows == 8 || plan->tile_rows == 16, "grouped streaming GEMM: plan tile_rows must be 8 or 16");
+    DSUF_REQUIRE(ctx, xq && xs && out, "grouped streaming GEMM: null pointer");
+    DSUF_REQUIRE(ctx, epi != EPI_W13 || w->d.gate_up, "dsuf_moe_w13_swiglu: weight was not packed with gate_up=1");
+    StreamArgs a;
+    fill_common(ctx, a, w);
+    const int nt8 = plan->tile_rows / 8;
+    int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, plan->p, 8 * nt8);
+    if (rc) return rc;
+    a.xscale = xs;
+    a.slots = (const int4*)plan->tiles;
+    a.nslots = (const int*)plan->ntiles;
+    a.row_w = (const float*)plan->row_w;
+    a.out = out;
+    a.x_rows = plan->p;
+    a.ldo = ldo;
+    a.swiglu_limit = swiglu_limit;
+    const int grid = ctx->sm_count;
+    const size_t smem = StreamCfg<FMT_FP4>::SMEM;
+    const bool amx = act_mode == DSUF_MODE_MX;
+#define GO(AMX, NT, EPI) launch(ctx, stream, stream_gemv_kernel<FMT_FP4, 1, AMX, NT, EPI>, dim3(grid), dim3(STREAM_THREADS), smem, a)
+    if (epi == EPI_W13) {
+        if (amx) return nt8 == 1 ? GO(1, 1, EPI_W13) : GO(1, 2, EPI_W13);
+        return nt8 == 1 ? GO(0, 1, EPI_W13) : GO(0, 2, EPI_W13);
+    }
+    if (amx) return nt8 == 1 ? GO(1, 1, EPI_W2) : GO(1, 2, EPI_W2);
+    return nt8 == 1 ? GO(0, 1, EPI_W2) : GO(0, 2, EPI_W2);
+#undef GO
+}
+
+size_t stream_workspace_bytes() { return WS_BYTES; }
+
+}  // namespace dsuf

@@ -1,0 +1,172 @@
+/*
+ * dsuf_qmm.h -- C ABI of libdsuf_qmm, the B200 (sm_100a) implementation of deepseek-ultrafast's quantized
+ * matrix-product path: FP8 activation quantization, FP8 block-scaled GEMV/GEMM, grouped MXFP4 expert GEMMs
+ * (gate/up + SwiGLU, down) and the routed-token permute / unpermute around them.
+ *
+ * The reference has no C ABI: crates/engine/src/ops.rs fills #[repr(C)] parameter structs and launches cubin
+ * kernels by name through crates/cuda/src/lib.rs:630-664.  Each entry point below names the reference
+ * interface it stands in for, so crates/engine keeps its call surface and only the bodies of those functions
+ * turn into FFI calls.
+ *
+ * Conventions (mirroring crates/cuda + crates/engine):
+ *   - uint64_t arguments are device pointers; `stream` is a CUstream / cudaStream_t passed as void*.
+ *   - every function returns int32_t: 0 ok, >0 a CUDA error code, <0 a DSUF_E_* code; dsuf_last_error() gives
+ *     the message.  Preconditions are validated on the host and reported -- never undefined behaviour.
+ *   - hot calls are asynchronous on the caller's stream, allocate nothing, never synchronise and may be
+ *     recorded into a CUDA graph; functions marked (load-time) may allocate or synchronise.
+ *   - the caller owns all device memory, including scratch; sizes come from the *_bytes() queries.
+ *   - one context per device, used from the thread that has that device current; no global mutable state.
+ *   - bf16 data is raw uint16 bit patterns; FP8 codes are e4m3 bytes; FP4 codes are e2m1, two per byte,
+ *     low nibble = even k; UE8M0 scales are exponent bytes (2^(b-127)).
+ */
+#ifndef DSUF_QMM_H
+#define DSUF_QMM_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { DSUF_OK = 0, DSUF_E_BADARG = -1, DSUF_E_UNSUPPORTED = -2, DSUF_E_TIMEOUT = -3, DSUF_E_NCCL = -4, DSUF_E_NOMEM = -5 };
+
+/* Scale geometries.  MX = what the reference implements (1x32 activations, 32x32 FP8 weights, power-of-two
+ * UE8M0 scales: crates/kernels/cu/quantblocks.cuh:7-57, crates/model/src/formats.rs:59-84).
+ * DS = 1x128 activations / 128x128 FP8 weights with fp32 scales amax/448. */
+enum { DSUF_MODE_MX = 0, DSUF_MODE_DS = 1 };
+enum { DSUF_FMT_FP8 = 0, DSUF_FMT_FP4 = 1 };               /* WFmt, crates/engine/src/ops.rs:6-39 */
+enum { DSUF_SCORE_IDENTITY = 0, DSUF_SCORE_SOFTMAX = 1, DSUF_SCORE_SQRT_SOFTPLUS = 2 };
+
+typedef struct dsuf_ctx dsuf_ctx;
+typedef struct dsuf_weight dsuf_weight;
+
+typedef struct {
+    int32_t code;   /* 0 = no device-side error; 1 = a bounded wait expired; 2 = inconsistent plan */
+    int32_t kernel; /* kernel id */
+    int32_t cta;
+    int32_t where;
+} dsuf_dev_status;
+
+/* ---- context (load-time).  Stands in for Device::new + ops::hw() (crates/cuda/src/lib.rs:52-138,
+ * crates/engine/src/ops.rs:205-232): binds to the device's primary context, queries SM count and the
+ * shared-memory opt-in, raises the kernels' dynamic shared-memory limits. ---- */
+int32_t dsuf_ctx_create(int32_t device, dsuf_ctx** out);
+int32_t dsuf_ctx_destroy(dsuf_ctx* ctx);
+/* Copies the message of the last failing call on this context into buf (NUL-terminated). */
+int32_t dsuf_last_error(dsuf_ctx* ctx, char* buf, size_t len);
+/* Enables (1) or disables (0) programmatic dependent launch on every kernel of this context
+ * (Launch{pdl}, crates/cuda/src/lib.rs:633-638).  Default 0. */
+int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled);
+/* (synchronises `stream`) Reads and clears the device status word.  The reference's device waits are unbounded
+ * spins with no error reporting (cu/comm.cu:217-224); here every wait is bounded and reports through this. */
+int32_t dsuf_status_poll(dsuf_ctx* ctx, void* stream, dsuf_dev_status* out);
+int32_t dsuf_sm_count(dsuf_ctx* ctx);
+
+/* ---- host-side weight formats (load-time, no GPU).  Replace crates/model/src/formats.rs + packing.rs. ---- */
+
+/* quant_fp8_b32 twin (formats.rs:59-84) for MX; 128x128 fp32 amax/448 for DS.
+ * w bf16 [n][k] -> codes [n][k], scales MX: u8 [n/32][k/32], DS: f32 [n/128][k/128]. */
+int32_t dsuf_quant_fp8_weight_host(int32_t mode, const uint16_t* w, int32_t n, int32_t k, uint8_t* codes, void* scales);
+/* Synthetic MXFP4 quantizer following the reference's FP4 rule (cu/kv_fp4.cu:25-32):
+ * w bf16 [n][k] -> codes [n][k/2], scales u8 [n][k/32]. */
+int32_t dsuf_quant_fp4_weight_host(const uint16_t* w, int32_t n, int32_t k, uint8_t* codes, uint8_t* scales);
+
+/* Packed image = contiguous 128-row x 128-K tile records ordered [row tile][k tile], replacing tile_fp8 /
+ * tile_fp4 / tile_sf_blocks (formats.rs:96-228) and expert_shard (packing.rs:174-254).  One image feeds both the
+ * streaming decode kernels and the tcgen05 prefill kernels.
+ *   FP8 MX: 16384 B codes + 512 B scale atom;  FP8 DS: 16384 B codes (scales stay a separate f32 [n/128][k/128]);
+ *   FP4   :  8192 B codes + 512 B scale atom.
+ * n is padded up to a multiple of 128 with zero rows; k must be a multiple of 128. */
+size_t dsuf_packed_bytes(int32_t fmt, int32_t mode, int32_t n, int32_t k);
+int32_t dsuf_pack_fp8_weight(int32_t mode, const uint8_t* codes, const void* scales, int32_t n, int32_t k, uint8_t* out);
+/* gate_up != 0: codes/scales are [2*inter][k] with gate rows first, then up rows (n = 2*inter); rows are
+ * interleaved per 16-row group as 8 gate + the 8 matching up rows (the reference interleaves 32+32 per
+ * 64-row quad, packing.rs:237-241) so the SwiGLU epilogue finds both halves in one thread. */
+int32_t dsuf_pack_fp4_weight(const uint8_t* codes, const uint8_t* scales, int32_t n, int32_t k, int32_t gate_up, uint8_t* out);
+
+/* Weight descriptor = Weight{fmt,w,s,n,k} / Experts (ops.rs:6-39, weights.rs:82-92). */
+typedef struct {
+    int32_t fmt;             /* DSUF_FMT_* */
+    int32_t mode;            /* FP8: DSUF_MODE_*; FP4: ignored (always UE8M0 per 1x32) */
+    int32_t n, k;            /* rows and K of one matrix */
+    int32_t n_experts;       /* 1 for a dense weight */
+    int32_t gate_up;         /* rows packed with dsuf_pack_fp4_weight(gate_up=1) */
+    uint64_t tiles;          /* device: n_experts packed images back to back */
+    uint64_t scales_ds;      /* device: FP8 DS only, f32 [n_pad/128][k/128] */
+} dsuf_weight_desc;
+/* (load-time) Builds the TMA descriptors for a packed weight (tensor_map_u8_sw128 / tensor_map_fp4_unpack_*,
+ * crates/cuda/src/lib.rs:694-808, built by Loader::tc_copy, weights.rs:181-214). */
+int32_t dsuf_weight_create(dsuf_ctx* ctx, const dsuf_weight_desc* desc, dsuf_weight** out);
+int32_t dsuf_weight_destroy(dsuf_weight* w);
+
+/* ---- hot calls ---- */
+
+/* tc_quant_rows (cu/tcgemm.cu:300-340) and the in-GEMV quant_blocks8 staging (cu/quantblocks.cuh:7-57).
+ * x bf16 [m][ldx] -> q [m][k]; scales MX: u8 [m][k/32], DS: f32 [m][k/128].  k % 128 == 0, ldx % 8 == 0. */
+int32_t dsuf_act_quant_fp8(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t m, int32_t k,
+                           uint64_t q_out, uint64_t scale_out);
+
+/* Scratch of dsuf_gemm_fp8: stream-K partial sums and arrival counters.  Must be zeroed once with
+ * dsuf_workspace_init before first use; the kernels leave it zeroed.  Calls sharing one workspace must be
+ * stream-ordered. */
+size_t dsuf_gemm_workspace_bytes(dsuf_ctx* ctx);
+int32_t dsuf_workspace_init(dsuf_ctx* ctx, void* stream, uint64_t workspace, size_t bytes);
+
+/* ops::gemv (ops.rs:331-474) for m <= 16 token rows:
+ * out[m][n] (bf16, row stride ldo) = alpha * W . dequant(xq, xs).  Activations come pre-quantized from
+ * dsuf_act_quant_fp8 in the weight's geometry. */
+int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
+                      int32_t ldo, float alpha, uint64_t workspace);
+
+/* moe_route_tokens + route_token (cu/ops.cu:615-623, cu/route.cuh:3-56; RouteArgs ops.rs:124-135):
+ * top-k of score+bias, ties to the lower id, weights = score / sum(selected scores) * route_scale.
+ * scores f32 [t][n_exp] (logits when score_fn != IDENTITY), bias f32 [n_exp] or 0.
+ * ids_out i32 [t][topk], w_out f32 [t][topk].  n_exp <= 512, topk <= 16. */
+int32_t dsuf_moe_route(dsuf_ctx* ctx, void* stream, int32_t score_fn, uint64_t scores, uint64_t bias, int32_t t,
+                       int32_t n_exp, int32_t topk, float route_scale, uint64_t ids_out, uint64_t w_out);
+
+/* Permute plan = MpParams outputs (ops.rs:1478-1491) of moe_perm (cu/tcmoe.cu:19-69) and, with tile_rows = 8 or
+ * 16, the decode MoePlan slots (cu/gemv.cu:9-17,715-776).  All buffers caller-allocated. */
+typedef struct {
+    uint64_t expert_off; /* i32 [n_exp+1]  first permuted row of each local expert */
+    uint64_t row_pair;   /* i32 [p]        pair index (token*topk + j) of each permuted row */
+    uint64_t pair_row;   /* i32 [p]        permuted row of each pair, -1 when its expert is not local */
+    uint64_t row_w;      /* f32 [p]        routing weight of each permuted row */
+    uint64_t tiles;      /* i32x4 [max_tiles] (local expert, first row, rows <= tile_rows, 0) */
+    uint64_t ntiles;     /* i32 [2]        number of tiles, number of permuted rows */
+    uint64_t scratch;    /* i32 [dsuf_moe_plan_scratch_ints(p, n_exp)] */
+    int32_t p;           /* pairs = tokens * topk */
+    int32_t n_exp;       /* local experts */
+    int32_t tile_rows;   /* 8 / 16 (decode streaming) or 128 (tcgen05 prefill) */
+    int32_t max_tiles;   /* capacity of tiles[]: p / tile_rows + n_exp is always enough */
+} dsuf_moe_plan;
+size_t dsuf_moe_plan_scratch_ints(int32_t p, int32_t n_exp);
+/* Counting sort of the pairs by expert; rows of one expert are in ascending pair order (the reference's order
+ * inside an expert depends on atomicAdd timing, cu/tcmoe.cu:62).  Pairs whose expert is outside
+ * [e_lo, e_lo + n_exp) are dropped (expert-parallel shard). */
+int32_t dsuf_moe_permute_plan(dsuf_ctx* ctx, void* stream, uint64_t ids, uint64_t w, int32_t e_lo, const dsuf_moe_plan* plan);
+
+/* moe_gather_quant (cu/tcmoe.cu:88-133, MqParams ops.rs:1495-1509): quantize each token row once and write it
+ * to all of its permuted rows.  x bf16 [t][ldx] -> xq [p][h], xs MX u8 [p][h/32] / DS f32 [p][h/128]. */
+int32_t dsuf_moe_gather_quant(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t t, int32_t h,
+                              int32_t topk, const dsuf_moe_plan* plan, uint64_t xq_out, uint64_t xs_out);
+
+/* Grouped gate/up GEMM + SwiGLU: moe_fp4_swiglu (cu/gemv.cu:1016-1692 via ops::moe_gemv, ops.rs:482-634) for
+ * decode plans, tc_moe_w13 (cu/tcmoe.cu:184-588, TmParams ops.rs:1513-1534) for 128-row plans.
+ * act_out bf16 [p][inter] indexed by permuted row:
+ * bf16(silu(bf16 gate) * bf16 up * routing weight), optional clamp as cu/gemv.cu:470-483. */
+int32_t dsuf_moe_w13_swiglu(dsuf_ctx* ctx, void* stream, const dsuf_weight* w13, int32_t act_mode, const dsuf_moe_plan* plan,
+                            uint64_t xq, uint64_t xs, float swiglu_limit, uint64_t act_out);
+/* Grouped down GEMM: moe_fp4_store / moe_w2 / tc_moe_w2.  act_q [p][inter] + act_s from dsuf_act_quant_fp8 over
+ * act_out; yrows_out f32 [p][h] indexed by permuted row. */
+int32_t dsuf_moe_w2(dsuf_ctx* ctx, void* stream, const dsuf_weight* w2, int32_t act_mode, const dsuf_moe_plan* plan,
+                    uint64_t act_q, uint64_t act_s, uint64_t yrows_out);
+/* Unpermute + combine, the nsum/src2 part of comm_push (cu/comm.cu:167-180):
+ * out[t] = bf16(sum_j yrows[pair_row[t*topk+j]] (+ shared[t])), rows with pair_row < 0 skipped. */
+int32_t dsuf_moe_unpermute(dsuf_ctx* ctx, void* stream, const dsuf_moe_plan* plan, uint64_t yrows, uint64_t shared, int32_t t,
+                           int32_t topk, int32_t h, uint64_t out, int32_t ldo);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,40 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
+
+
+@pytest.fixture(scope="session")
+def pkg():
+    from __graft_entry__ import load_package
+    return load_package()
+
+
+@pytest.fixture(scope="session")
+def ctx(pkg):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no GPU")
+    c = pkg.Ctx(0)
+    yield c
+    c.close()
+
+
+def seeded(seed):
+    import torch
+    return torch.Generator().manual_seed(seed)
+
+
+def randn_bf16(gen, *shape, std=1.0):
+    """bf16 normal tensor as (torch bf16 tensor, uint16 numpy view)."""
+    import torch
+    t = (torch.randn(*shape, generator=gen) * std).bfloat16()
+    return t, t.view(torch.uint16).numpy()
