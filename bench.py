@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized matrix-product path on B200.
+
+Main line (one JSON object on stdout): the 4-layer expert-parallel MoE layer stack (hidden 7168, 256 experts top-8,
+expert intermediate 2048, MXFP4 expert weights, FP8 1x128 activations, one FP8 7168x7168 dense projection per
+layer) at a 64-token decode step, in tokens/s, on N GPUs.  The same object carries the decode FP8 GEMV sweep
+(GB/s per shape), the single-layer decode MoE, the HBM roofline of the dominant kernel, the end-to-end figure through
+host buffers and a CPU baseline timed on this box's host cores.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference        # the CPU restatement of the path, all host threads, same metric
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import load_package  # noqa: E402
+
+H, I, E, TOPK, LAYERS = 7168, 2048, 256, 8, 4
+DENSE_SHAPES = [(4096, 7168), (7168, 2048), (18432, 7168), (7168, 16384)]
+METRIC = "moe_layer_stack_decode_tokens_per_s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only queries)."""
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def expert_bytes():
+    """Algorithmic HBM bytes of one expert: FP4 codes + UE8M0/32 scales of w13 (2I x H) and w2 (H x I)."""
+    w13 = 2 * I * H // 2 + 2 * I * H // 32
+    w2 = H * I // 2 + H * I // 32
+    return w13, w2
+
+
+# ---------------------------------------------------------------------------------------------- CPU arm
+def cpu_sample(tokens_sample=2, seed=0):
+    """Times the CPU oracle on a bounded sample: `tokens_sample` tokens through ONE layer of the benchmark shape
+    (dense FP8 GEMV 7168x7168 + routed experts top-8 of 256), all host threads; returns tokens/s for the 4-layer stack."""
+    import oracle
+    import torch
+    rng = np.random.default_rng(seed)
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn(tokens_sample, H, generator=g)).bfloat16().view(torch.uint16).numpy()
+    # dense weight
+    wd = (torch.randn(H, H, generator=g) * 0.02).bfloat16().view(torch.uint16).numpy()
+    wq, ws = oracle.quant_fp8_weight(oracle.MODE_DS, wd)
+    # only the experts this sample routes to are materialised (ids drawn from the same softmax-of-N(0,1) routing)
+    logits = torch.randn(tokens_sample, E, generator=g).numpy()
+    ids, w = oracle.route(1, logits, None, TOPK)
+    used = sorted(set(ids.reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(used)}
+    ids_l = np.vectorize(remap.get)(ids).astype(np.int32)
+    c13 = np.empty((len(used), 2 * I, H // 2), np.uint8)
+    s13 = np.empty((len(used), 2 * I, H // 32), np.uint8)
+    c2 = np.empty((len(used), H, I // 2), np.uint8)
+    s2 = np.empty((len(used), H, I // 32), np.uint8)
+    for i in range(len(used)):
+        c13[i] = rng.integers(0, 256, c13[i].shape, dtype=np.uint8)
+        s13[i] = rng.integers(118, 122, s13[i].shape, dtype=np.uint8)
+        c2[i] = rng.integers(0, 256, c2[i].shape, dtype=np.uint8)
+        s2[i] = rng.integers(118, 122, s2[i].shape, dtype=np.uint8)
+    t0 = time.perf_counter()
+    xq, xs = oracle.act_quant(oracle.MODE_DS, x)
+    hb, _ = oracle.gemm_fp8(oracle.MODE_DS, wq, ws, xq, xs)
+    oracle.moe_layer(oracle.MODE_DS, hb, ids_l, w, c13, s13, c2, s2)
+    dt = time.perf_counter() - t0
+    return tokens_sample / (dt * LAYERS), dt, oracle.num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup):
+        cpu_sample(1)
+    nthreads = 1
+    sample_tokens = 2
+    t_all = time.perf_counter()
+    for s in range(args.steps):
+        v, dt, nthreads = cpu_sample(sample_tokens, seed=s)
+        vals.append(v)
+        if time.perf_counter() - t_all > 150:
+            break
+    v = float(np.median(vals))
+    sample = (f"{sample_tokens} tokens through one layer (FP8 7168x7168 dense + top-8 of 256 MXFP4 experts), scalar C oracle with "
+              f"OpenMP, extrapolated to {LAYERS} layers; median of {len(vals)} steps")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(vals),
+        "warmup": args.warmup, "ms_per_step": 1e3 * 64 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 x {fp8_e4m3, mxfp4_e2m1}, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "cfg4: 4 layers x (FP8 7168x7168 dense + 256-expert top-8 MXFP4 MoE), 64-token decode step"},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": nthreads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------------------------- GPU arm
+def time_events(torch, fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps  # ms per call
+
+
+def dense_sweep(pkg, ctx, torch, hbm_peak, quick):
+    """Decode FP8 GEMV sweep: GB/s of the weight-streaming kernel alone (activations pre-quantized), rotating over
+    enough weight copies that every launch reads its weights from HBM, not L2."""
+    synth = importlib.import_module(pkg.__name__ + ".synth")
+    out = []
+    for (n, k) in DENSE_SHAPES:
+        wbytes = n * k + 4 * (n // 128) * (k // 128)
+        copies = max(2, int(np.ceil(400e6 / wbytes)))
+        ws = []
+        for c in range(copies):
+            tiles, sds = synth.fp8_dense(torch, False, n, k, 0.02, 100 + c, ctx.device)
+            ws.append(pkg.Weight(ctx, 0, pkg.MODE_DS, n, k, 1, False, tiles, sds))
+        for m in ([1, 16] if quick else [1, 4, 8, 16]):
+            x = torch.randn(m, k, device=ctx.device).bfloat16()
+            xq, xs = pkg.act_quant(ctx, pkg.MODE_DS, x)
+            o = torch.empty(m, n, dtype=torch.bfloat16, device=ctx.device)
+            idx = [0]
+
+            def call():
+                pkg.gemm_fp8(ctx, ws[idx[0] % copies], xq, xs, m, o)
+                idx[0] += 1
+            ms = time_events(torch, call, 10 * copies, copies)
+            algo = wbytes + 2 * m * k + 2 * m * n
+            gbs = algo / (ms * 1e-3) / 1e9
+            out.append({"n": n, "k": k, "m": m, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1),
+                        "frac_of_measured_hbm": round(gbs / hbm_peak, 3), "frac_of_8tbs": round(gbs / 8000.0, 3)})
+        del ws
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = load_package()
+    stackmod = importlib.import_module(pkg.__name__ + ".stack")
+    ctx = pkg.Ctx(local, pdl=args.pdl)
+    hbm_peak, peak_src = peaks()
+    T = args.tokens
+    cfg = stackmod.StackConfig(hidden=H, inter=I, n_experts=E, topk=TOPK, layers=LAYERS, tokens=T)
+    if world > 1:
+        stack = stackmod.EpLayerStack(ctx, cfg, dist, rank, world)
+    else:
+        stack = stackmod.LayerStack(ctx, cfg)
+    t_local = T // world
+    g = torch.Generator().manual_seed(1234 + rank)
+    x_host = torch.randn(t_local, H, generator=g).bfloat16().pin_memory()
+    y_host = torch.empty(t_local, H, dtype=torch.bfloat16).pin_memory()
+    x_dev = x_host.cuda()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput ----
+    for _ in range(args.warmup):
+        stack.forward(x_dev)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    events = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        stack.forward(x_dev, events=events)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    # ---- end to end through host buffers ----
+    for _ in range(2):
+        x_dev.copy_(x_host, non_blocking=True)
+        y_host.copy_(stack.forward(x_dev), non_blocking=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        x_dev.copy_(x_host, non_blocking=True)
+        y = stack.forward(x_dev)
+        y_host.copy_(y, non_blocking=True)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    st = ctx.status()
+    if world > 1:
+        tms = torch.tensor([ms, ms_e2e], device="cuda")
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tms.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    # ---- roofline of the dominant kernel (grouped gate/up GEMM) ----
+    w13_b, w2_b = expert_bytes()
+    w13_ms = float(np.mean([a.elapsed_time(b) for a, b in events]))
+    n_local = E // world
+    ids_counts = []
+    for l in range(LAYERS):
+        ids, _ = pkg.moe_route_tokens(ctx, pkg.SCORE_SOFTMAX, stack.logits_full(l) if world > 1 else stack.logits[l], None, TOPK)
+        u = torch.unique(ids)
+        ids_counts.append(int(((u >= rank * n_local) & (u < (rank + 1) * n_local)).sum()))
+    e_act = float(np.mean(ids_counts))
+    algo_w13 = e_act * w13_b + T * TOPK * (H + H // 128 * 4) / world + T * TOPK * I * 2 / world
+    achieved = algo_w13 / (w13_ms * 1e-3) / 1e9
+    roofline = {"kernel": "stream_gemv_kernel<FP4,W13> (grouped gate/up + SwiGLU)", "bound": "hbm", "achieved": round(achieved, 1),
+                "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
+                "frac_of_8tbs": round(achieved / 8000.0, 4), "avg_launch_ms": round(w13_ms, 4), "active_experts_per_launch": e_act,
+                "algorithmic_bytes_per_launch": int(algo_w13), "traffic": args.traffic}
+    result = {
+        "metric": METRIC, "value": round(T / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "fp8_e4m3 x {fp8_e4m3, mxfp4_e2m1}, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": "cfg4: 4 layers x (FP8 7168x7168 dense + 256-expert top-8 MXFP4 MoE), %d-token decode step" % T,
+                   "tokens": T, "hidden": H, "experts": E, "topk": TOPK, "inter": I, "layers": LAYERS,
+                   "parallelism": "ep%d" % world, "l2": "weights read per step (>= 6 GB per GPU) exceed the 126 MB L2"},
+        "e2e": {"value": round(T / (ms_e2e * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": t_local * H * 2 * world,
+                "d2h_bytes_per_step": t_local * H * 2 * world, "ms_per_step": round(ms_e2e, 4)},
+        "gpu_launches": stack.count_launches() * args.steps,
+        "roofline": roofline, "clocks": clocks, "device_status": st.code,
+    }
+    if world == 1 and not args.skip_sub:
+        result["decode_gemv_sweep"] = dense_sweep(pkg, ctx, torch, hbm_peak, args.quick)
+        # single routed-expert layer (cfg2): tokens/s of one layer's MoE
+        layer0 = stack.moe[0]
+        ids, w = pkg.moe_route_tokens(ctx, pkg.SCORE_SOFTMAX, stack.logits[0], None, TOPK)
+        yb = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+        ms_l = time_events(torch, lambda: layer0.forward(x_dev, ids, w, yb), 20, 3)
+        e_act0 = int(torch.unique(ids).numel())
+        result["moe_decode_layer"] = {"tokens": T, "active_experts": e_act0, "ms": round(ms_l, 4), "tokens_per_s": round(T / (ms_l * 1e-3), 1),
+                                      "gbs": round(e_act0 * (w13_b + w2_b) / (ms_l * 1e-3) / 1e9, 1),
+                                      "note": "L2 holds 126 MB of the ~5 GB read per call; repeated calls on one layer are HBM-bound"}
+    if world == 1 and not args.skip_cpu:
+        v, dt, nthr = cpu_sample(2)
+        result["cpu_baseline"] = {"value": round(v, 3), "unit": "tokens/s", "cores": nthr, "kind": "port",
+                                  "sample": "2 tokens through one layer (FP8 7168x7168 dense + top-8 of 256 MXFP4 experts), scalar C "
+                                            "oracle with OpenMP (%.1f s), extrapolated to %d layers" % (dt, LAYERS)}
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--pdl", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="shorter GEMV sweep")
+    ap.add_argument("--skip-sub", action="store_true", help="main line only")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the dominant kernel, if captured")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -332,11 +332,18 @@ class MoeLayer:
         self.act_s = t.zeros((p, self.inter // blk), dtype=sdt, device=dev)
         self.yrows = t.zeros((p, self.h), dtype=t.float32, device=dev)
 
-    def forward(self, x, ids, w, out, shared=None):
+    def forward(self, x, ids, w, out, shared=None, events=None):
+        """``events``: optional list; (start, end) CUDA events around the gate/up kernel are appended (bench timing)."""
         ctx, plan = self.ctx, self.plan
         moe_perm(ctx, plan, ids, w, self.e_lo)
         moe_gather_quant(ctx, self.act_mode, plan, x, self.xq, self.xs)
+        if events is not None:
+            e0, e1 = ctx.torch.cuda.Event(enable_timing=True), ctx.torch.cuda.Event(enable_timing=True)
+            e0.record()
         moe_w13_swiglu(ctx, self.w13, self.act_mode, plan, self.xq, self.xs, self.act, self.swiglu_limit)
+        if events is not None:
+            e1.record()
+            events.append((e0, e1))
         act_quant(ctx, self.act_mode, self.act, self.act_q, self.act_s)
         moe_w2(ctx, self.w2, self.act_mode, plan, self.act_q, self.act_s, self.yrows)
         moe_unpermute(ctx, plan, self.yrows, out, shared)

@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, c = blockIdx.x;
     const int RT = a.RT, KT = a.KT;
+    bool dead = false;
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
@@ -123,7 +124,8 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
                     fresh = false;
                 }
                 const int s = n % S;
-                if (n >= S) mbar_wait(&empty_bar[s], ((n / S) - 1) & 1, a.status, KID_STREAM, 1);
+                // after the first expired wait nothing is waited for again: the loops stay finite and short
+                if (n >= S && !dead && !mbar_wait(&empty_bar[s], ((n / S) - 1) & 1, a.status, KID_STREAM, 1)) dead = true;
                 uint8_t* st = ring + (size_t)s * Cfg::STAGE;
                 const uint32_t bytes = Cfg::W_BYTES + NT8 * 1024 + (WMX ? 512 : 0);
                 mbar_expect_tx(&full_bar[s], bytes);
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
             if (!WMX) wds = __ldg(a.wscale_ds + (size_t)rt * KT + kt);
 
             const int s = n % S;
-            mbar_wait(&full_bar[s], (n / S) & 1, a.status, KID_STREAM, 2);
+            if (!dead && !mbar_wait(&full_bar[s], (n / S) & 1, a.status, KID_STREAM, 2)) dead = true;
             const uint8_t* st = ring + (size_t)s * Cfg::STAGE;
             uint32_t wsa = 0, wsb = 0;
             if (WMX) {

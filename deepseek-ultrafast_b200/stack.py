@@ -1,0 +1,77 @@
+"""The benchmark's layer stack: per layer one FP8 dense projection (hidden x hidden) followed by the routed-expert
+FFN (route -> plan -> gather+quant -> gate/up+SwiGLU -> quant -> down -> unpermute/combine).
+
+Single GPU: every expert is local.  Several GPUs (one process each, torch.distributed over NCCL): experts are
+sharded world-ways (rank r owns experts [r*E/W, (r+1)*E/W)), tokens are data parallel (rank r owns T/W of them);
+per layer the exchanges are
+    all-gather(x)                   tokens -> every rank, input of the K-sharded dense projection
+    reduce-scatter(dense partials)  the two halves of the tensor-parallel all-reduce (cf. comm_push2,
+                                    crates/kernels/cu/comm.cu:323-531)
+    all-to-all(dispatch)            FP8 token rows + scales + (expert, weight) to the ranks owning their experts
+    all-to-all(combine)             per-(token, rank) bf16 partial sums back to the token's owner
+The reference is tensor-parallel only and combines with its own push all-reduce (cu/comm.cu:134-279); the
+expert-parallel exchange here is this library's design.
+"""
+from . import (MODE_DS, MODE_MX, SCORE_SOFTMAX, MoeLayer, Weight, act_quant, gemm_fp8, moe_route_tokens)
+from . import synth
+
+
+class StackConfig:
+    def __init__(self, hidden=7168, inter=2048, n_experts=256, topk=8, layers=4, tokens=64, act_mode=MODE_DS,
+                 dense_mode=MODE_DS, std=0.02, seed=0):
+        self.hidden, self.inter, self.n_experts, self.topk = hidden, inter, n_experts, topk
+        self.layers, self.tokens, self.act_mode, self.dense_mode, self.std, self.seed = layers, tokens, act_mode, dense_mode, std, seed
+
+
+class LayerStack:
+    """Single-GPU stack (world size 1).  All buffers are allocated here; ``forward`` only launches kernels."""
+
+    def __init__(self, ctx, cfg):
+        t = ctx.torch
+        dev = ctx.device
+        self.ctx, self.cfg = ctx, cfg
+        H, I, E = cfg.hidden, cfg.inter, cfg.n_experts
+        self.dense, self.moe, self.logits = [], [], []
+        tile_rows = 8
+        for l in range(cfg.layers):
+            tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, H, cfg.std, cfg.seed + 1000 * l + 1, dev)
+            self.dense.append(Weight(ctx, 0, cfg.dense_mode, H, H, 1, False, tiles, sds))
+            w13 = synth.fp4_experts(t, E, 2 * I, H, cfg.std, cfg.seed + 1000 * l + 2, True, dev)
+            w2 = synth.fp4_experts(t, E, H, I, cfg.std, cfg.seed + 1000 * l + 3, False, dev)
+            W13 = Weight.experts_fp4_packed(ctx, w13, 2 * I, H, E, True)
+            W2 = Weight.experts_fp4_packed(ctx, w2, H, I, E, False)
+            self.moe.append(MoeLayer(ctx, W13, W2, cfg.tokens, cfg.topk, cfg.act_mode, tile_rows=tile_rows))
+            g = t.Generator(device=dev).manual_seed(cfg.seed + 1000 * l + 4)
+            self.logits.append(t.randn(cfg.tokens, E, generator=g, device=dev, dtype=t.float32))
+        blk = 32 if cfg.dense_mode == MODE_MX else 128
+        self.xq = t.empty((cfg.tokens, H), dtype=t.uint8, device=dev)
+        self.xs = t.empty((cfg.tokens, H // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
+        self.h = t.empty((cfg.tokens, H), dtype=t.bfloat16, device=dev)
+        self.y = [t.empty((cfg.tokens, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
+
+    def dense_forward(self, l, x, out):
+        """x bf16 [T][H] -> out bf16 [T][H]; T > 16 is processed in 16-row slabs by the streaming kernel."""
+        ctx, w = self.ctx, self.dense[l]
+        act_quant(ctx, w.mode, x, self.xq, self.xs)
+        T = x.shape[0]
+        for r0 in range(0, T, 16):
+            m = min(16, T - r0)
+            gemm_fp8(ctx, w, self.xq[r0:r0 + m], self.xs[r0:r0 + m], m, out[r0:r0 + m])
+        return out
+
+    def forward(self, x, events=None):
+        cfg = self.cfg
+        cur = x
+        for l in range(cfg.layers):
+            self.dense_forward(l, cur, self.h)
+            ids, w = moe_route_tokens(self.ctx, SCORE_SOFTMAX, self.logits[l], None, cfg.topk)
+            out = self.y[l & 1]
+            self.moe[l].forward(self.h, ids, w, out, events=events)
+            cur = out
+        return cur
+
+    def count_launches(self):
+        cfg = self.cfg
+        slabs = (cfg.tokens + 15) // 16
+        # act_quant + dense slabs + route + plan(3) + gather + w13 + quant + w2 + unpermute
+        return cfg.layers * (1 + slabs + 1 + 3 + 1 + 1 + 1 + 1 + 1)

@@ -1,0 +1,250 @@
+"""GPU parity: every kernel of the path, called through the C ABI, against the CPU oracle on identical seeded inputs.
+
+Bars: quantized codes, scales and all index work bit-exact; bf16/fp32 matrix-product outputs within 1e-2 relative
+Frobenius error of the oracle's fp32 dequantize-then-matmul (the tolerance the task states).
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import randn_bf16, seeded
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def rel(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / max(np.linalg.norm(b.astype(np.float64)), 1e-30))
+
+
+# ------------------------------------------------------------------ activation quantizer
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("m,k,ld", [(4, 2048, 2048), (16, 7168, 7168), (1, 128, 128), (3, 384, 512), (64, 2048, 2048)])
+def test_act_quant_bit_exact(pkg, ctx, mode, m, k, ld):
+    g = seeded(10 + m + k)
+    xt, _ = randn_bf16(g, m, ld)
+    xt[0, :128] = 0                                   # all-zero block
+    if m > 1:
+        xt[1, 5] = 3.0e4                              # outlier: neighbours underflow to tiny codes
+        xt[1, 200 % k] = -1.0e-3
+    xd = xt.cuda()[:, :k]
+    q, s = pkg.act_quant(ctx, mode, xd)
+    torch.cuda.synchronize()
+    qo, so = oracle.act_quant(mode, xt[:, :k].contiguous().view(torch.uint16).numpy())
+    assert (q.cpu().numpy() == qo).all()
+    assert (s.cpu().numpy() == so).all()
+
+
+def test_act_quant_rejects_bad_shapes(pkg, ctx):
+    x = torch.zeros(2, 100, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(pkg.DsufError):
+        pkg.act_quant(ctx, 0, x)                      # k % 128 != 0
+    q, s = pkg.act_quant(ctx, 1, torch.zeros(0, 128, dtype=torch.bfloat16, device="cuda"))  # empty input is fine
+    assert q.shape == (0, 128)
+
+
+# ------------------------------------------------------------------ dense FP8 GEMV
+def _dense_case(pkg, ctx, mode, n, k, m, seed, rows=None):
+    g = seeded(seed)
+    xt, xn = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, n, k, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(mode, wn)
+    xq, xs = oracle.act_quant(mode, xn)
+    w = pkg.Weight.dense_fp8(ctx, mode, wq, ws)
+    out = pkg.gemv(ctx, w, xt.cuda())
+    out2 = pkg.gemv(ctx, w, xt.cuda())
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    got = out.float().cpu().numpy()
+    assert (out.view(torch.uint16) == out2.view(torch.uint16)).all(), "stream-K result depends on timing"
+    if rows is None:
+        _, ref = oracle.gemm_fp8(mode, wq, ws, xq, xs)
+        deq = oracle.matmul_f32(oracle.dequant_fp8(mode, wq, ws), oracle.dequant_fp8(mode, xq, xs))
+        assert rel(got, ref) < TOL and rel(got, deq) < TOL
+        # bf16 rounding is the only difference left in most entries
+        assert np.abs(got - ref).max() <= np.abs(ref).max() * 2 ** -7
+    else:
+        blk = 32 if mode == 0 else 128
+        sel = np.sort(np.random.default_rng(seed).choice(n // blk, rows, replace=False))
+        ridx = (sel[:, None] * blk + np.arange(blk)[None]).reshape(-1)
+        _, ref = oracle.gemm_fp8(mode, wq[ridx], ws[sel], xq, xs)
+        assert rel(got[:, ridx], ref) < TOL
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+def test_dense_gemv_config0(pkg, ctx, mode, m):
+    """M=4 N=1024 K=2048 is the CPU-runnable configuration; the other M values are the decode sweep."""
+    _dense_case(pkg, ctx, mode, 1024, 2048, m, seed=0)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("n,k,m", [(128, 128, 1), (256, 512, 3), (4096, 7168, 16), (7168, 2048, 5), (384, 16384, 9)])
+def test_dense_gemv_shapes(pkg, ctx, mode, n, k, m):
+    _dense_case(pkg, ctx, mode, n, k, m, seed=n + k + m)
+
+
+@pytest.mark.parametrize("n,k", [(18432, 7168), (7168, 16384)])
+def test_dense_gemv_full_size_sampled_rows(pkg, ctx, n, k):
+    """The two largest decode shapes: oracle evaluated on a random sample of weight row blocks."""
+    _dense_case(pkg, ctx, 1, n, k, 16, seed=7, rows=4)
+
+
+def test_dense_gemv_linearity_and_alpha(pkg, ctx):
+    """Size-independent property: out(alpha) = alpha * out(1) up to bf16 rounding."""
+    g = seeded(3)
+    xt, xn = randn_bf16(g, 4, 2048)
+    _, wn = randn_bf16(g, 1024, 2048, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(1, wn)
+    w = pkg.Weight.dense_fp8(ctx, 1, wq, ws)
+    a = pkg.gemv(ctx, w, xt.cuda()).float()
+    b = pkg.gemv(ctx, w, xt.cuda(), alpha=0.5).float()
+    torch.cuda.synchronize()
+    assert torch.allclose(b, a * 0.5, rtol=2 ** -7, atol=1e-6)
+
+
+def test_dense_gemv_rejects_bad_arguments(pkg, ctx):
+    g = seeded(4)
+    _, wn = randn_bf16(g, 128, 128, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(1, wn)
+    w = pkg.Weight.dense_fp8(ctx, 1, wq, ws)
+    with pytest.raises(pkg.DsufError):
+        pkg.gemv(ctx, w, torch.zeros(17, 128, dtype=torch.bfloat16, device="cuda"))   # m > 16: not this path
+    xq = torch.zeros(1, 128, dtype=torch.uint8, device="cuda")
+    xs = torch.ones(1, 1, dtype=torch.float32, device="cuda")
+    with pytest.raises(pkg.DsufError):
+        pkg.gemm_fp8(ctx, w, xq, xs, 0)                                               # m = 0
+
+
+# ------------------------------------------------------------------ router, plan, gather
+@pytest.mark.parametrize("score_fn", [0, 1, 2])
+@pytest.mark.parametrize("t,e,k", [(64, 256, 8), (5, 8, 2), (1, 384, 6), (33, 512, 16)])
+def test_route_matches_oracle(pkg, ctx, score_fn, t, e, k):
+    g = seeded(t + e)
+    logits = torch.randn(t, e, generator=g)
+    if score_fn == 0:
+        logits = logits.abs() + 0.01
+    bias = torch.randn(e, generator=g) * 0.1
+    ids, w = pkg.moe_route_tokens(ctx, score_fn, logits.cuda(), bias.cuda(), k, route_scale=2.5)
+    torch.cuda.synchronize()
+    io, wo = oracle.route(score_fn, logits.numpy(), bias.numpy(), k, 2.5)
+    assert (ids.cpu().numpy() == io).all()
+    assert np.allclose(w.cpu().numpy(), wo, rtol=2e-5, atol=1e-7)
+
+
+def test_route_ties_go_to_the_lowest_id(pkg, ctx):
+    s = torch.full((3, 64), 0.25)
+    ids, w = pkg.moe_route_tokens(ctx, 0, s.cuda(), None, 4)
+    torch.cuda.synchronize()
+    assert ids.cpu().tolist() == [[0, 1, 2, 3]] * 3
+    assert torch.allclose(w.cpu(), torch.full((3, 4), 0.25))
+
+
+@pytest.mark.parametrize("t,k,e,tile,e_lo,n_loc", [(64, 8, 256, 8, 0, 256), (64, 8, 256, 16, 64, 64), (1, 1, 4, 8, 0, 4),
+                                                   (300, 6, 40, 128, 0, 40), (2000, 8, 256, 128, 128, 128)])
+def test_permute_plan_bit_exact(pkg, ctx, t, k, e, tile, e_lo, n_loc):
+    rng = np.random.default_rng(t)
+    ids = np.stack([rng.choice(e, k, replace=False) for _ in range(t)]).astype(np.int32)
+    w = rng.random((t, k)).astype(np.float32)
+    plan = pkg.MoePlan(ctx, t, k, n_loc, tile)
+    pkg.moe_perm(ctx, plan, torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda(), e_lo)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    # oracle on the local experts only: remap foreign experts to a sentinel bucket at the end
+    local = ids.reshape(-1) - e_lo
+    keep = (local >= 0) & (local < n_loc)
+    remap = np.where(keep, local, n_loc).astype(np.int32)
+    off, row_pair, pair_row, tiles = oracle.permute_plan(remap, n_loc + 1, tile)
+    nrows = int(keep.sum())
+    nt = int((tiles[:, 0] < n_loc).sum())
+    got_nt, got_rows = plan.ntiles.cpu().tolist()
+    assert (got_nt, got_rows) == (nt, nrows)
+    assert (plan.expert_off.cpu().numpy() == off[:n_loc + 1]).all()
+    assert (plan.row_pair.cpu().numpy()[:nrows] == row_pair[:nrows]).all()
+    want_pr = np.where(keep, pair_row, -1)
+    assert (plan.pair_row.cpu().numpy() == want_pr).all()
+    assert (plan.tiles.cpu().numpy()[:nt] == tiles[:nt]).all()
+    assert (plan.row_w.cpu().numpy()[:nrows] == w.reshape(-1)[row_pair[:nrows]]).all()
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_gather_quant_rows_equal_plain_quant(pkg, ctx, mode):
+    t, k, e, h = 24, 4, 16, 512
+    g = seeded(9)
+    xt, xn = randn_bf16(g, t, h)
+    rng = np.random.default_rng(1)
+    ids = np.stack([rng.choice(e, k, replace=False) for _ in range(t)]).astype(np.int32)
+    plan = pkg.MoePlan(ctx, t, k, e, 8)
+    pkg.moe_perm(ctx, plan, torch.from_numpy(ids).cuda(), torch.ones(t, k).cuda())
+    blk = 32 if mode == 0 else 128
+    xq = torch.zeros(t * k, h, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(t * k, h // blk, dtype=torch.uint8 if mode == 0 else torch.float32, device="cuda")
+    pkg.moe_gather_quant(ctx, mode, plan, xt.cuda(), xq, xs)
+    torch.cuda.synchronize()
+    qo, so = oracle.act_quant(mode, xn)
+    row_pair = plan.row_pair.cpu().numpy()
+    assert (xq.cpu().numpy() == qo[row_pair // k]).all()
+    assert (xs.cpu().numpy() == so[row_pair // k]).all()
+
+
+# ------------------------------------------------------------------ routed-expert layer
+def _moe_case(pkg, ctx, act_mode, T, H, I, E, K, tile_rows, seed, e_lo=0, n_loc=None, limit=0.0, shared=False):
+    n_loc = E if n_loc is None else n_loc
+    g = seeded(seed)
+    xt, xn = randn_bf16(g, T, H)
+    logits = torch.randn(T, E, generator=g)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    q13 = [oracle.quant_fp4_weight(w13[e]) for e in range(E)]
+    q2 = [oracle.quant_fp4_weight(w2[e]) for e in range(E)]
+    c13, s13 = np.stack([a for a, _ in q13]), np.stack([b for _, b in q13])
+    c2, s2 = np.stack([a for a, _ in q2]), np.stack([b for _, b in q2])
+    ids, rw = oracle.route(1, logits.numpy(), None, K)
+    sh_t, sh_n = randn_bf16(g, T, H, std=0.1) if shared else (None, None)
+    ref = oracle.moe_layer(act_mode, xn, ids, rw, c13, s13, c2, s2, swiglu_limit=limit, shared=sh_n, e_lo=e_lo,
+                           e_hi=e_lo + n_loc, want_act=True)
+    W13 = pkg.Weight.experts_fp4(ctx, c13[e_lo:e_lo + n_loc], s13[e_lo:e_lo + n_loc], True)
+    W2 = pkg.Weight.experts_fp4(ctx, c2[e_lo:e_lo + n_loc], s2[e_lo:e_lo + n_loc], False)
+    layer = pkg.MoeLayer(ctx, W13, W2, T, K, act_mode, e_lo=e_lo, tile_rows=tile_rows, swiglu_limit=limit)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    layer.forward(xt.cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(rw).cuda(), y,
+                  sh_t.cuda() if shared else None)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    # intermediate: SwiGLU activations per permuted row against the oracle's per-pair rows
+    nrows = int(layer.plan.ntiles.cpu()[1])
+    row_pair = layer.plan.row_pair.cpu().numpy()[:nrows]
+    act = layer.act.float().cpu().numpy()[:nrows]
+    act_ref = oracle.bf16_to_f32(ref["act_bf16"])[row_pair]
+    assert rel(act, act_ref) < TOL
+    got = y.float().cpu().numpy()
+    assert rel(got, ref["y_f32"]) < TOL
+    return layer
+
+
+@pytest.mark.parametrize("act_mode", [0, 1])
+@pytest.mark.parametrize("tile_rows", [8, 16])
+def test_moe_layer_small(pkg, ctx, act_mode, tile_rows):
+    _moe_case(pkg, ctx, act_mode, T=8, H=256, I=128, E=8, K=2, tile_rows=tile_rows, seed=1)
+
+
+@pytest.mark.parametrize("act_mode", [0, 1])
+def test_moe_layer_decode_shape_reduced(pkg, ctx, act_mode):
+    """64 tokens (8 seqs x 8-token draft block), top-8 of 32 experts, hidden 1024, inter 512: several experts get
+    more than 8 rows, so slots are split, and some get none."""
+    _moe_case(pkg, ctx, act_mode, T=64, H=1024, I=512, E=32, K=8, tile_rows=8, seed=2)
+
+
+def test_moe_layer_clamp_and_shared_expert_term(pkg, ctx):
+    _moe_case(pkg, ctx, 1, T=16, H=256, I=128, E=8, K=2, tile_rows=8, seed=3, limit=0.05, shared=True)
+
+
+def test_moe_layer_expert_parallel_shards_sum_to_whole(pkg, ctx):
+    """Two expert shards (experts 0-3 and 4-7) evaluated separately add up to the full layer (fp32, before rounding)."""
+    _moe_case(pkg, ctx, 1, T=16, H=256, I=128, E=8, K=2, tile_rows=8, seed=4, e_lo=0, n_loc=4)
+    _moe_case(pkg, ctx, 1, T=16, H=256, I=128, E=8, K=2, tile_rows=8, seed=4, e_lo=4, n_loc=4)
+
+
+def test_moe_single_token_single_expert(pkg, ctx):
+    _moe_case(pkg, ctx, 1, T=1, H=128, I=128, E=2, K=1, tile_rows=8, seed=5)
