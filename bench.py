@@ -183,12 +183,20 @@ def dense_sweep(pkg, ctx, torch, hbm_peak, quick):
             x = torch.randn(m, k, device=ctx.device).bfloat16()
             xq, xs = pkg.act_quant(ctx, pkg.MODE_DS, x)
             o = torch.empty(m, n, dtype=torch.bfloat16, device=ctx.device)
-            idx = [0]
-
-            def call():
-                pkg.gemm_fp8(ctx, ws[idx[0] % copies], xq, xs, m, o)
-                idx[0] += 1
-            ms = time_events(torch, call, 10 * copies, copies)
+            # one CUDA graph of `copies` launches (each on a different weight copy), replayed: GPU time, not launch rate
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for c in range(copies):
+                    pkg.gemm_fp8(ctx, ws[c], xq, xs, m, o)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for c in range(copies):
+                        pkg.gemm_fp8(ctx, ws[c], xq, xs, m, o)
+            torch.cuda.current_stream().wait_stream(side)
+            ms = time_events(torch, graph.replay, 10, 2) / copies
+            del graph
             algo = wbytes + 2 * m * k + 2 * m * n
             gbs = algo / (ms * 1e-3) / 1e9
             out.append({"n": n, "k": k, "m": m, "us": round(ms * 1e3, 2), "gbs": round(gbs, 1),

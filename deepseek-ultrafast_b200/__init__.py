@@ -48,6 +48,7 @@ ABI = {
     "dsuf_ctx_destroy": (C.c_int32, [C.c_void_p]),
     "dsuf_last_error": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_size_t]),
     "dsuf_ctx_set_pdl": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "dsuf_ctx_set_decode_path": (C.c_int32, [C.c_void_p, C.c_int32]),
     "dsuf_status_poll": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(DevStatus)]),
     "dsuf_sm_count": (C.c_int32, [C.c_void_p]),
     "dsuf_quant_fp8_weight_host": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
@@ -146,7 +147,7 @@ def pack_fp4_weight(codes, scales, gate_up):
 class Ctx:
     """dsuf_ctx wrapper: one per device (Device::new + ops::hw(), crates/cuda/src/lib.rs:52, ops.rs:205)."""
 
-    def __init__(self, device=0, pdl=False):
+    def __init__(self, device=0, pdl=False, tcgen05=True):
         import torch
         self.torch = torch
         self.device = torch.device("cuda", device)
@@ -157,10 +158,16 @@ class Ctx:
         self.h = h
         if pdl:
             self.check(lib().dsuf_ctx_set_pdl(self.h, 1))
+        self.set_decode_path(tcgen05)
         nbytes = lib().dsuf_gemm_workspace_bytes(self.h)
         self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
         self.check(lib().dsuf_workspace_init(self.h, self.stream(), self.workspace.data_ptr(), nbytes))
         self.sm_count = lib().dsuf_sm_count(self.h)
+
+    def set_decode_path(self, tcgen05):
+        """True: tcgen05 streaming kernels for decode shapes; False: the mma.sync streaming kernels."""
+        self.check(lib().dsuf_ctx_set_decode_path(self.h, 1 if tcgen05 else 0))
+        self.tcgen05 = bool(tcgen05)
 
     def stream(self):
         return C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)

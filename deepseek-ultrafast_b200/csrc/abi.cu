@@ -63,6 +63,12 @@ int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled) {
     return DSUF_OK;
 }
 
+int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05) {
+    if (!ctx) return DSUF_E_BADARG;
+    ctx->use_tc = tcgen05 ? 1 : 0;
+    return DSUF_OK;
+}
+
 int32_t dsuf_sm_count(dsuf_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 
 int32_t dsuf_status_poll(dsuf_ctx* ctx, void* stream, dsuf_dev_status* out) {
@@ -107,6 +113,17 @@ int32_t dsuf_weight_create(dsuf_ctx* ctx, const dsuf_weight_desc* d, dsuf_weight
                                    d->fmt == DSUF_FMT_FP4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { delete w; return fail(ctx, DSUF_E_BADARG, "cuTensorMapEncodeTiled(weight stream) failed: %d", (int)r); }
+    if (d->fmt == DSUF_FMT_FP4) {
+        // same bytes seen as 4-bit elements: TMA widens every 16 packed codes (8 bytes) to 16 bytes of shared memory
+        cuuint64_t edims[3] = {128, 128, (cuuint64_t)w->tiles_total};
+        cuuint32_t ebox[3] = {128, 128, 1};
+        r = ctx->encode_tiled(&w->tm_tc, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, (void*)d->tiles, edims, strides, ebox, es,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { delete w; return fail(ctx, DSUF_E_BADARG, "cuTensorMapEncodeTiled(weight fp4 unpack) failed: %d", (int)r); }
+    } else {
+        w->tm_tc = w->tm_stream;
+    }
     *out = w;
     return DSUF_OK;
 }
@@ -122,6 +139,7 @@ int32_t dsuf_act_quant_fp8(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x
     DSUF_REQUIRE(ctx, mode == DSUF_MODE_MX || mode == DSUF_MODE_DS, "act_quant: unknown mode %d", mode);
     DSUF_REQUIRE(ctx, m >= 0 && k > 0 && k % 128 == 0, "act_quant: k (%d) must be a positive multiple of 128", k);
     DSUF_REQUIRE(ctx, ldx >= k && ldx % 8 == 0, "act_quant: ldx (%d) must be >= k and a multiple of 8", ldx);
+    if (m == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, x && q_out && scale_out, "act_quant: null pointer");
     DSUF_REQUIRE(ctx, (x & 15) == 0 && (q_out & 7) == 0, "act_quant: x must be 16-byte and q_out 8-byte aligned");
     return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, m, k, (void*)q_out, (void*)scale_out, nullptr, 0, 0);

@@ -106,6 +106,14 @@ DSUF_DEV void tma_3d(void* dst, const void* tmap, int c0, int c1, int c2, uint64
         "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
+// 4-byte asynchronous copy (LDGSTS) and its completion hook: the mbarrier receives one arrival from this thread
+// once all of the thread's earlier cp.async copies have landed (the arrival must be part of the barrier's count).
+DSUF_DEV void cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+DSUF_DEV void cp_async_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 DSUF_DEV void prefetch_tmap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -157,5 +165,94 @@ DSUF_DEV float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)
 // Row permutation inside an 8-row group that makes 8-byte shared loads from 128-byte swizzled rows conflict free:
 // fragment row g reads tile row ROWMAP(g).
 DSUF_DEV int rowmap8(int g) { return ((g & 3) << 1) | (g >> 2); }
+
+
+// ---- tcgen05 (5th-generation tensor cores: operands in shared memory, accumulators in tensor memory) ----
+DSUF_DEV void tmem_alloc(uint32_t* slot_in_smem, uint32_t ncols) {   // whole warp; ncols a power of two >= 32
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(ncols) : "memory");
+}
+DSUF_DEV void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+DSUF_DEV void tmem_dealloc(uint32_t taddr, uint32_t ncols) {          // whole warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+DSUF_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+DSUF_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+DSUF_DEV void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// The mbarrier receives one arrival when every tcgen05 operation issued so far by this thread has completed.
+DSUF_DEV void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 512-byte scale-factor atom (32 rows x 16 bytes) from shared memory to 4 tensor-memory columns, all 4 lane quarters.
+DSUF_DEV void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem] with UE8M0 block scales from tensor memory; one K=32 step of 8-bit containers.
+DSUF_DEV void tc_mma_mx(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p; }" ::"r"(d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+// Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte units), descriptor
+// version 1 (bit 46), layout type (2 = 128-byte swizzle, 0 = none).
+DSUF_DEV uint64_t tc_smem_desc(const void* p, uint32_t lbo, uint32_t sbo, uint32_t layout) {
+    uint64_t d = (uint64_t)((smem_u32(p) & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)(layout & 7) << 61;
+    return d;
+}
+// Instruction descriptor of kind::mxf8f6f4 with M = 128: N>>3 at bit 17, UE8M0 scale type (bit 23), M>>4 at bit 24,
+// A format at bits 7-9 (0 = e4m3, 5 = e2m1), B format e4m3; scale-factor byte selectors (bits 4-5 for B, 29-30 for A)
+// are OR-ed in per K step.
+DSUF_DEV uint32_t tc_idesc_mx(int n, bool a_is_e2m1) {
+    return ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (a_is_e2m1 ? (5u << 7) : 0u);
+}
+DSUF_DEV uint32_t tc_idesc_sf(uint32_t idesc, uint32_t kc) { return idesc | (kc << 29) | (kc << 4); }
+
+// Accumulator read-back: this warp's 32 lanes x NCOL consecutive fp32 columns.
+template <int NCOL>
+DSUF_DEV void tmem_ld(uint32_t taddr, float* v);
+template <>
+DSUF_DEV void tmem_ld<8>(uint32_t taddr, float* v) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <>
+DSUF_DEV void tmem_ld<16>(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <>
+DSUF_DEV void tmem_ld<32>(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
 
 }  // namespace dsuf

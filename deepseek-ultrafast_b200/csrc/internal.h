@@ -21,6 +21,7 @@ struct dsuf_ctx {
     int sm_count;
     int smem_optin;
     int use_pdl;                   // launch with programmatic stream serialization
+    int use_tc;                    // decode shapes on the tcgen05 streaming kernel (1) or the mma.sync one (0)
     dsuf::DevStatus* dev_status;   // device word written by a kernel whose bounded wait expired
     dsuf_encode_tiled_fn encode_tiled;
     char err[512];

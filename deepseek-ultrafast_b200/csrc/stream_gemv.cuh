@@ -54,7 +54,9 @@ template <int FMT>
 struct StreamCfg {
     static constexpr int W_BYTES = FMT == FMT_FP8 ? 16384 : 8192;
     static constexpr int X_OFF = W_BYTES;
-    static constexpr int SF_OFF = W_BYTES + 2048;
+    static constexpr int SF_OFF = W_BYTES + 2048;   // 512-byte weight scale atom
+    static constexpr int XS_OFF = SF_OFF + 512;     // 16 activation block scales (4 bytes each)
+    static constexpr int WS_OFF = XS_OFF + 64;      // dense DS geometry: the tile's fp32 weight scale
     static constexpr int STAGE = W_BYTES + 2048 + 1024;
     static constexpr int STAGES = FMT == FMT_FP8 ? 10 : 16;
     static constexpr int SMEM = STAGE * STAGES + 1024;  // +1024: manual alignment of the ring
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(&full_bar[s], 1);
+            mbar_init(&full_bar[s], 1 + 32);  // expect_tx arrival + one cp.async arrival per producer lane
             mbar_init(&empty_bar[s], STREAM_CONSUMER_WARPS);
         }
         mbar_fence_init();
@@ -98,9 +100,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
 
     if (warp == STREAM_CONSUMER_WARPS) {
         // ================= producer =================
-        if (lane == 0 && beg < end) {
-            prefetch_tmap(&a.tm_w);
-            prefetch_tmap(&a.tm_x);
+        // lane 0 feeds the ring with TMA (weight tile, scale atom, activation tile); lanes 0..16 add the tile's
+        // activation / weight block scales with 4-byte asynchronous copies, so consumers never touch global memory.
+        if (beg < end) {
+            if (lane == 0) {
+                prefetch_tmap(&a.tm_w);
+                prefetch_tmap(&a.tm_x);
+            }
             const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
@@ -127,12 +133,22 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
                 // after the first expired wait nothing is waited for again: the loops stay finite and short
                 if (n >= S && !dead && !mbar_wait(&empty_bar[s], ((n / S) - 1) & 1, a.status, KID_STREAM, 1)) dead = true;
                 uint8_t* st = ring + (size_t)s * Cfg::STAGE;
-                const uint32_t bytes = Cfg::W_BYTES + NT8 * 1024 + (WMX ? 512 : 0);
-                mbar_expect_tx(&full_bar[s], bytes);
-                const long long tile = wbase + kt;
-                tma_3d(st, &a.tm_w, 0, 0, (int)tile, &full_bar[s], pol_w);
-                if (WMX) bulk_g2s(st + Cfg::SF_OFF, a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes, 512, &full_bar[s], pol_w);
-                tma_2d(st + Cfg::X_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                if (lane == 0) {
+                    const uint32_t bytes = Cfg::W_BYTES + NT8 * 1024 + (WMX ? 512 : 0);
+                    mbar_expect_tx(&full_bar[s], bytes);
+                    const long long tile = wbase + kt;
+                    tma_3d(st, &a.tm_w, 0, 0, (int)tile, &full_bar[s], pol_w);
+                    if (WMX) bulk_g2s(st + Cfg::SF_OFF, a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes, 512, &full_bar[s], pol_w);
+                    tma_2d(st + Cfg::X_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                }
+                if (lane < 8 * NT8) {
+                    const int r = min(xrow0 + lane, a.x_rows - 1);
+                    cp_async4(st + Cfg::XS_OFF + 4 * lane, (const uint32_t*)a.xscale + (size_t)r * KT + kt);
+                } else if (!WMX && lane == 16) {
+                    cp_async4(st + Cfg::WS_OFF, a.wscale_ds + (size_t)rt * KT + kt);
+                }
+                cp_async_arrive_noinc(&full_bar[s]);
+                __syncwarp();
                 if (++kt == KT) { kt = 0; ++q; fresh = true; }
             }
         }
@@ -168,26 +184,21 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
                 }
                 fresh = false;
             }
-            // activation / weight block scales of this tile (global, L2-resident)
+            const int s = n % S;
+            if (!dead && !mbar_wait(&full_bar[s], (n / S) & 1, a.status, KID_STREAM, 2)) dead = true;
+            const uint8_t* st = ring + (size_t)s * Cfg::STAGE;
+            // block scales of this tile, staged next to it by the producer warp
             float xsa[NT8], xsb[NT8];
             uint32_t xma[NT8], xmb[NT8];
 #pragma unroll
             for (int u = 0; u < NT8; ++u) {
-                const int r0 = min(xrow0 + 8 * u + ca, a.x_rows - 1), r1 = min(xrow0 + 8 * u + cb, a.x_rows - 1);
-                if (AMX) {
-                    xma[u] = __ldg((const uint32_t*)a.xscale + (size_t)r0 * KT + kt);
-                    xmb[u] = __ldg((const uint32_t*)a.xscale + (size_t)r1 * KT + kt);
-                } else {
-                    xsa[u] = __ldg((const float*)a.xscale + (size_t)r0 * KT + kt);
-                    xsb[u] = __ldg((const float*)a.xscale + (size_t)r1 * KT + kt);
-                }
+                xma[u] = *(const uint32_t*)(st + Cfg::XS_OFF + 4 * (8 * u + ca));
+                xmb[u] = *(const uint32_t*)(st + Cfg::XS_OFF + 4 * (8 * u + cb));
+                xsa[u] = __uint_as_float(xma[u]);
+                xsb[u] = __uint_as_float(xmb[u]);
             }
             float wds = 1.f;
-            if (!WMX) wds = __ldg(a.wscale_ds + (size_t)rt * KT + kt);
-
-            const int s = n % S;
-            if (!dead && !mbar_wait(&full_bar[s], (n / S) & 1, a.status, KID_STREAM, 2)) dead = true;
-            const uint8_t* st = ring + (size_t)s * Cfg::STAGE;
+            if (!WMX) wds = *(const float*)(st + Cfg::WS_OFF);
             uint32_t wsa = 0, wsb = 0;
             if (WMX) {
                 wsa = *(const uint32_t*)(st + Cfg::SF_OFF + (ra & 31) * 16 + (ra >> 5) * 4);

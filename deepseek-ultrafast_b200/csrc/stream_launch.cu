@@ -3,6 +3,7 @@
 // preconditions returned as errors, never UB) and ops::moe_gemv (ops.rs:482-634).
 #include "internal.h"
 #include "stream_gemv.cuh"
+#include "tc_stream.cuh"
 
 namespace dsuf {
 
@@ -20,6 +21,13 @@ int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, 
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ctx, DSUF_E_BADARG, "cuTensorMapEncodeTiled(activations) failed: %d", (int)r);
+    return DSUF_OK;
+}
+
+template <int FMT, int WMX, int AMX, int N, int EPI>
+static int set_attr_tc(dsuf_ctx* ctx) {
+    cudaError_t e = cudaFuncSetAttribute(tc_stream_kernel<FMT, WMX, AMX, N, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg::SMEM);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_stream)");
     return DSUF_OK;
 }
 
@@ -41,6 +49,14 @@ int stream_setup(dsuf_ctx* ctx) {
     SA(FMT_FP4, 1, 0, 1, EPI_W2); SA(FMT_FP4, 1, 0, 2, EPI_W2);
     SA(FMT_FP4, 1, 1, 1, EPI_W2); SA(FMT_FP4, 1, 1, 2, EPI_W2);
 #undef SA
+#define ST(...) if ((rc = set_attr_tc<__VA_ARGS__>(ctx))) return rc
+    ST(FMT_FP8, 0, 0, 8, EPI_DENSE); ST(FMT_FP8, 0, 0, 16, EPI_DENSE);
+    ST(FMT_FP8, 1, 1, 8, EPI_DENSE); ST(FMT_FP8, 1, 1, 16, EPI_DENSE);
+    ST(FMT_FP4, 1, 0, 8, EPI_W13); ST(FMT_FP4, 1, 0, 16, EPI_W13);
+    ST(FMT_FP4, 1, 1, 8, EPI_W13); ST(FMT_FP4, 1, 1, 16, EPI_W13);
+    ST(FMT_FP4, 1, 0, 8, EPI_W2); ST(FMT_FP4, 1, 0, 16, EPI_W2);
+    ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2);
+#undef ST
     return DSUF_OK;
 }
 
@@ -81,8 +97,15 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     const long long tot = (long long)w->rt * w->kt;
     int grid = ctx->sm_count < WS_MAX_CTAS ? ctx->sm_count : WS_MAX_CTAS;
     if (tot < grid) grid = (int)tot;
-    const size_t smem = StreamCfg<FMT_FP8>::SMEM;
     const bool mx = w->d.mode == DSUF_MODE_MX;
+    if (ctx->use_tc) {
+        a.tm_w = w->tm_tc;
+#define GT(WMX, AMX, NN) launch(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg::SMEM, a)
+        if (mx) return nt8 == 1 ? GT(1, 1, 8) : GT(1, 1, 16);
+        return nt8 == 1 ? GT(0, 0, 8) : GT(0, 0, 16);
+#undef GT
+    }
+    const size_t smem = StreamCfg<FMT_FP8>::SMEM;
 #define GO(WMX, AMX, NT) launch(ctx, stream, stream_gemv_kernel<FMT_FP8, WMX, AMX, NT, EPI_DENSE>, dim3(grid), dim3(STREAM_THREADS), smem, a)
     if (mx) return nt8 == 1 ? GO(1, 1, 1) : GO(1, 1, 2);
     return nt8 == 1 ? GO(0, 0, 1) : GO(0, 0, 2);
@@ -109,8 +132,19 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
     a.ldo = ldo;
     a.swiglu_limit = swiglu_limit;
     const int grid = ctx->sm_count;
-    const size_t smem = StreamCfg<FMT_FP4>::SMEM;
     const bool amx = act_mode == DSUF_MODE_MX;
+    if (ctx->use_tc) {
+        a.tm_w = w->tm_tc;
+#define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg::SMEM, a)
+        if (epi == EPI_W13) {
+            if (amx) return nt8 == 1 ? GT(1, 8, EPI_W13) : GT(1, 16, EPI_W13);
+            return nt8 == 1 ? GT(0, 8, EPI_W13) : GT(0, 16, EPI_W13);
+        }
+        if (amx) return nt8 == 1 ? GT(1, 8, EPI_W2) : GT(1, 16, EPI_W2);
+        return nt8 == 1 ? GT(0, 8, EPI_W2) : GT(0, 16, EPI_W2);
+#undef GT
+    }
+    const size_t smem = StreamCfg<FMT_FP4>::SMEM;
 #define GO(AMX, NT, EPI) launch(ctx, stream, stream_gemv_kernel<FMT_FP4, 1, AMX, NT, EPI>, dim3(grid), dim3(STREAM_THREADS), smem, a)
     if (epi == EPI_W13) {
         if (amx) return nt8 == 1 ? GO(1, 1, EPI_W13) : GO(1, 2, EPI_W13);

@@ -1,0 +1,325 @@
+// tcgen05 weight-streaming kernel for decode shapes ("swap-AB": the 128 weight rows of a tile are the MMA's M, the
+// few token rows its N), same work decomposition as stream_gemv.cuh but with ZERO per-weight-element instructions:
+//   * TMA lands the weight tile in shared memory in the tensor core's operand layout (FP4 tiles are widened to
+//     8-bit containers by the TMA unit itself, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B);
+//   * one thread issues tcgen05.mma kind::mxf8f6f4.block_scale (4 x K=32 per 128-K tile); UE8M0 weight scales are
+//     applied by the tensor core from tensor memory (tcgen05.cp of the tile record's 512-byte scale atom);
+//   * accumulators live in tensor memory; four epilogue warps read them back.  With MX (power-of-two) activation
+//     scales the whole K accumulates in tensor memory; with DS (fp32 per 128-K) activation / weight scales each
+//     128-K tile is promoted into fp32 registers with its scale pair, on a 4-deep ring of accumulators.
+// Replaces tc_gemv_fp8 (crates/kernels/cu/tcgemv.cu:33-241) and the mma.sync decode MoE
+// (cu/gemv.cu:1016-1692).  The reference's tcgen05 decode kernels load a CTA's whole K slice up front and then
+// drain it; here the ring is refilled continuously across row tiles and experts.
+#pragma once
+#include <cuda.h>
+#include "stream_gemv.cuh"
+
+namespace dsuf {
+
+constexpr int KID_TC = 3;
+constexpr int TC_THREADS = 192;  // warp 0: TMA producer (+ scale copies), warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int TC_EPI_THREADS = 128;
+
+struct TcCfg {
+    static constexpr int A_BYTES = 16384;
+    static constexpr int B_OFF = 16384;    // N x 128-byte activation rows (N <= 16)
+    static constexpr int SFA_OFF = 18432;  // weight scale atom (512)
+    static constexpr int SFB_OFF = 18944;  // activation scale atom (512), MX activations
+    static constexpr int XS_OFF = 19456;   // fp32 activation scales of the tile (DS activations)
+    static constexpr int WS_OFF = 19584;   // fp32 weight scale of the tile (DS weights)
+    static constexpr int STAGE = 20480;
+    static constexpr int STAGES = 10;
+    static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
+    static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
+    static constexpr int NB = 4;            // accumulator ring
+    static constexpr int ACC_COLS = 32;     // columns per accumulator
+    static constexpr int TM_SFA = 128, TM_SFB = 192, TM_COLS = 256;
+};
+
+template <int FMT, int WMX, int AMX, int N, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
+    using Cfg = TcCfg;
+    constexpr int S = Cfg::STAGES, NB = Cfg::NB;
+    constexpr bool PER_TILE = (AMX == 0);  // promote every 128-K tile with fp32 scales
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[NB], tempty_bar[NB];
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = gridDim.x, c = blockIdx.x;
+    const int RT = a.RT, KT = a.KT;
+    bool dead = false;
+
+    if (warp == 1) {
+        tmem_alloc(&s_tmem, Cfg::TM_COLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full_bar[s], 1 + 32);
+            mbar_init(&empty_bar[s], PER_TILE ? 1 + 4 : 1);
+        }
+        for (int b = 0; b < NB; ++b) {
+            mbar_init(&tfull_bar[b], 1);
+            mbar_init(&tempty_bar[b], 4);
+        }
+        mbar_fence_init();
+    }
+    if (tid >= 64) ((uint32_t*)(ring + Cfg::ONES_OFF))[tid - 64] = 0x7f7f7f7fu;  // 128 threads x 4 bytes = one atom of 1.0
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = s_tmem;
+    pdl_wait();
+
+    long long beg, end;
+    if (EPI == EPI_DENSE) {
+        const long long tot = (long long)RT * KT;
+        beg = (long long)c * tot / G;
+        end = (long long)(c + 1) * tot / G;
+    } else {
+        const long long q = (long long)(*a.nslots) * RT;
+        beg = ((long long)c * q / G) * KT;
+        end = ((long long)(c + 1) * q / G) * KT;
+    }
+
+    if (warp == 0) {
+        // ================= producer =================
+        if (beg < end) {
+            if (lane == 0) {
+                prefetch_tmap(&a.tm_w);
+                prefetch_tmap(&a.tm_x);
+            }
+            const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+            long long q = beg / KT;
+            int kt = (int)(beg - q * KT);
+            int rt = 0, xrow0 = 0;
+            long long wbase = 0;
+            bool fresh = true;
+            int n = 0;
+            for (long long i = beg; i < end; ++i, ++n) {
+                if (fresh) {
+                    if (EPI == EPI_DENSE) {
+                        rt = (int)q;
+                        wbase = (long long)rt * KT;
+                        xrow0 = 0;
+                    } else {
+                        const int slot = (int)(q / RT);
+                        rt = (int)(q - (long long)slot * RT);
+                        const int4 sl = a.slots[slot];
+                        wbase = ((long long)sl.x * RT + rt) * KT;
+                        xrow0 = sl.y;
+                    }
+                    fresh = false;
+                }
+                const int s = n % S;
+                if (n >= S && !dead && !mbar_wait(&empty_bar[s], ((n / S) - 1) & 1, a.status, KID_TC, 1)) dead = true;
+                uint8_t* st = ring + (size_t)s * Cfg::STAGE;
+                if (lane == 0) {
+                    // TMA counts the bytes it READS: a packed FP4 tile is 8192 bytes although it fills 16384 of shared memory
+                    const uint32_t bytes = (FMT == FMT_FP4 ? 8192 : 16384) + N * 128 + (WMX ? 512 : 0);
+                    mbar_expect_tx(&full_bar[s], bytes);
+                    const long long tile = wbase + kt;
+                    tma_3d(st, &a.tm_w, 0, 0, (int)tile, &full_bar[s], pol_w);
+                    if (WMX) bulk_g2s(st + Cfg::SFA_OFF, a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes, 512, &full_bar[s], pol_w);
+                    tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                }
+                if (lane < N) {
+                    const int r = min(xrow0 + lane, a.x_rows - 1);
+                    // MX: the token's 4 UE8M0 bytes go to its row of the scale atom; DS: its fp32 scale
+                    uint8_t* dst = AMX ? st + Cfg::SFB_OFF + (lane & 31) * 16 : st + Cfg::XS_OFF + 4 * lane;
+                    cp_async4(dst, (const uint32_t*)a.xscale + (size_t)r * KT + kt);
+                } else if (!WMX && lane == 16) {
+                    cp_async4(st + Cfg::WS_OFF, a.wscale_ds + (size_t)rt * KT + kt);
+                }
+                cp_async_arrive_noinc(&full_bar[s]);
+                __syncwarp();
+                if (++kt == KT) { kt = 0; ++q; fresh = true; }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer (one thread) =================
+        if (lane == 0 && beg < end) {
+            const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
+            const uint32_t ones_a = tm + Cfg::TM_SFA + 4 * S, ones_b = tm + Cfg::TM_SFB + 4 * S;
+            if (!WMX) tc_cp_sf(ones_a, tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+            if (!AMX) tc_cp_sf(ones_b, tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+            long long q = beg / KT;
+            int kt = (int)(beg - q * KT);
+            int n = 0, gidx = 0;
+            bool group_open = false;
+            for (long long i = beg; i < end; ++i, ++n) {
+                const int s = n % S;
+                if (!dead && !mbar_wait(&full_bar[s], (n / S) & 1, a.status, KID_TC, 2)) dead = true;
+                tc_fence_after();
+                if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
+                const int b = gidx % NB;
+                const bool first_of_group = !group_open;
+                if (!group_open) {
+                    if (gidx >= NB && !dead && !mbar_wait(&tempty_bar[b], ((gidx / NB) - 1) & 1, a.status, KID_TC, 3)) dead = true;
+                    tc_fence_after();
+                    group_open = true;
+                }
+                uint8_t* st = ring + (size_t)s * Cfg::STAGE;
+                uint32_t sfa = ones_a, sfb = ones_b;
+                if (WMX) { sfa = tm + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, tc_smem_desc(st + Cfg::SFA_OFF, 512, 128, 0)); }
+                if (AMX) { sfb = tm + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, tc_smem_desc(st + Cfg::SFB_OFF, 512, 128, 0)); }
+                const uint64_t ad = tc_smem_desc(st, 16, 1024, 2), bd = tc_smem_desc(st + Cfg::B_OFF, 16, 1024, 2);
+                const uint32_t d = tm + b * Cfg::ACC_COLS;
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc)
+                    tc_mma_mx(d, ad + (uint64_t)(kc * 2), bd + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
+                              (first_of_group && kc == 0) ? 0u : 1u);
+                tc_commit(&empty_bar[s]);
+                const bool item_end = (kt + 1 == KT) || (i + 1 == end);
+                if (PER_TILE || item_end) {
+                    tc_commit(&tfull_bar[b]);
+                    ++gidx;
+                    group_open = false;
+                }
+                if (++kt == KT) { kt = 0; ++q; }
+            }
+        }
+    } else {
+        // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
+        const int q4 = warp & 3;
+        const int r = 32 * q4 + lane;
+        const int etid = tid - 64;
+        const uint32_t lane_base = (uint32_t)(32 * q4) << 16;
+        float acc[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = 0.f;
+        long long q = beg / KT;
+        int kt = (int)(beg - q * KT);
+        int rt = 0, xrow0 = 0, cnt = 0;
+        bool fresh = true;
+        int n = 0, gidx = 0;
+        for (long long i = beg; i < end; ++i, ++n) {
+            if (fresh) {
+                if (EPI == EPI_DENSE) {
+                    rt = (int)q;
+                    xrow0 = 0;
+                    cnt = a.m;
+                } else {
+                    const int slot = (int)(q / RT);
+                    rt = (int)(q - (long long)slot * RT);
+                    const int4 sl = a.slots[slot];
+                    xrow0 = sl.y;
+                    cnt = sl.z;
+                }
+                fresh = false;
+            }
+            const bool item_end = (kt + 1 == KT) || (i + 1 == end);
+            if (PER_TILE || item_end) {
+                const int b = gidx % NB;
+                if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
+                tc_fence_after();
+                float v[N];
+                tmem_ld<N>(tm + lane_base + b * Cfg::ACC_COLS, v);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty_bar[b]);
+                ++gidx;
+                if (PER_TILE) {
+                    const int s = n % S;
+                    const uint8_t* st = ring + (size_t)s * Cfg::STAGE;
+                    const float wds = WMX ? 1.0f : *(const float*)(st + Cfg::WS_OFF);
+                    float xs[N];
+#pragma unroll
+                    for (int j = 0; j < N; j += 4) {
+                        const float4 t4 = *(const float4*)(st + Cfg::XS_OFF + 4 * j);
+                        xs[j] = t4.x; xs[j + 1] = t4.y; xs[j + 2] = t4.z; xs[j + 3] = t4.w;
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_bar[s]);
+#pragma unroll
+                    for (int j = 0; j < N; ++j) acc[j] = fmaf(v[j], wds * xs[j], acc[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) acc[j] = v[j];
+                }
+            }
+            if (item_end) {
+                // ---------------- flush the item ----------------
+                if (EPI == EPI_DENSE) {
+                    const long long it0 = q * KT;
+                    const bool whole = beg <= it0 && end >= it0 + KT;
+                    bool do_store = whole;
+                    if (!whole) {
+                        const int slot = (q == beg / KT) ? 0 : 1;
+                        float* pw = a.partial + ((size_t)(c * 2 + slot) * 16) * 128 + etid;
+#pragma unroll
+                        for (int j = 0; j < N; ++j) __stcg(pw + (size_t)j * 128, acc[j]);
+                        __threadfence();
+                        named_bar_sync(1, TC_EPI_THREADS);
+                        const long long tot = (long long)RT * KT;
+                        const int first = (int)(((it0 + 1) * G - 1) / tot);
+                        const int last = (int)(((it0 + KT) * G - 1) / tot);
+                        if (etid == 0) {
+                            const int old = atomicAdd(a.counters + q, 1);
+                            s_flag = (old == last - first);
+                            if (old == last - first) a.counters[q] = 0;  // self-resetting for the next launch
+                        }
+                        named_bar_sync(1, TC_EPI_THREADS);
+                        do_store = s_flag != 0;
+                        named_bar_sync(1, TC_EPI_THREADS);
+                        if (do_store) {
+                            __threadfence();
+#pragma unroll
+                            for (int j = 0; j < N; ++j) acc[j] = 0.f;
+                            for (int cc = first; cc <= last; ++cc) {  // fixed order: independent of arrival order
+                                const long long cbeg = (long long)cc * tot / G;
+                                const int cslot = (q == cbeg / KT) ? 0 : 1;
+                                const float* pr = a.partial + ((size_t)(cc * 2 + cslot) * 16) * 128 + etid;
+#pragma unroll
+                                for (int j = 0; j < N; ++j) acc[j] += __ldcg(pr + (size_t)j * 128);
+                            }
+                        }
+                    }
+                    if (do_store) {
+                        bf16* o = (bf16*)a.out;
+                        const int row = rt * 128 + r;
+#pragma unroll
+                        for (int j = 0; j < N; ++j)
+                            if (j < cnt && row < a.n_rows) o[(size_t)j * a.ldo + row] = __float2bfloat16(acc[j] * a.alpha);
+                    }
+                } else if (EPI == EPI_W13) {
+                    // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group)
+                    bf16* o = (bf16*)a.out;
+                    const float L = a.swiglu_limit;
+                    const bool is_gate = (r & 8) == 0;
+#pragma unroll
+                    for (int j = 0; j < N; ++j) {
+                        const float other = __shfl_xor_sync(0xffffffffu, acc[j], 8);
+                        if (is_gate && j < cnt) {
+                            const int row = xrow0 + j;
+                            float gt = bf16_round(acc[j]), up = bf16_round(other);
+                            if (L > 0.f) { up = fminf(fmaxf(up, -L), L); gt = fminf(gt, L); }
+                            const float val = gt / (1.0f + expf(-gt)) * up * __ldg(a.row_w + row);
+                            o[(size_t)row * a.ldo + rt * 64 + (r >> 4) * 8 + (r & 7)] = __float2bfloat16(val);
+                        }
+                    }
+                } else {
+                    float* o = (float*)a.out;
+                    const int col = rt * 128 + r;
+#pragma unroll
+                    for (int j = 0; j < N; ++j)
+                        if (j < cnt && col < a.n_rows) o[(size_t)(xrow0 + j) * a.ldo + col] = acc[j];
+                }
+#pragma unroll
+                for (int j = 0; j < N; ++j) acc[j] = 0.f;
+            }
+            if (++kt == KT) { kt = 0; ++q; fresh = true; }
+        }
+    }
+    pdl_launch_dependents();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tm, Cfg::TM_COLS);
+}
+
+}  // namespace dsuf

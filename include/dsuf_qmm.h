@@ -57,6 +57,10 @@ int32_t dsuf_last_error(dsuf_ctx* ctx, char* buf, size_t len);
 /* Enables (1) or disables (0) programmatic dependent launch on every kernel of this context
  * (Launch{pdl}, crates/cuda/src/lib.rs:633-638).  Default 0. */
 int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled);
+/* Decode-shape kernels: 1 = tcgen05 streaming kernel (TMA-unpacked FP4, block scales in tensor memory),
+ * 0 = mma.sync streaming kernel (the counterpart of the reference's cu/gemv.cu family).  Both compute the same
+ * function; the choice mirrors the reference's runtime switch between gemv and tc_gemv (model.rs:1523-1530). */
+int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05);
 /* (synchronises `stream`) Reads and clears the device status word.  The reference's device waits are unbounded
  * spins with no error reporting (cu/comm.cu:217-224); here every wait is bounded and reports through this. */
 int32_t dsuf_status_poll(dsuf_ctx* ctx, void* stream, dsuf_dev_status* out);

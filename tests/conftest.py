@@ -18,12 +18,13 @@ def pkg():
     return load_package()
 
 
-@pytest.fixture(scope="session")
-def ctx(pkg):
+@pytest.fixture(scope="session", params=["tcgen05", "mma"])
+def ctx(pkg, request):
+    """One context per decode path: the tcgen05 streaming kernels and the mma.sync streaming kernels."""
     import torch
     if not torch.cuda.is_available():
         pytest.skip("no GPU")
-    c = pkg.Ctx(0)
+    c = pkg.Ctx(0, tcgen05=request.param == "tcgen05")
     yield c
     c.close()
 
