@@ -220,7 +220,8 @@ def run_ours(args):
     ctx = pkg.Ctx(local, pdl=args.pdl)
     hbm_peak, peak_src = peaks()
     T = args.tokens
-    cfg = stackmod.StackConfig(hidden=H, inter=I, n_experts=E, topk=TOPK, layers=LAYERS, tokens=T)
+    amode = pkg.MODE_MX if args.act_mode == "mx" else pkg.MODE_DS
+    cfg = stackmod.StackConfig(hidden=H, inter=I, n_experts=E, topk=TOPK, layers=LAYERS, tokens=T, act_mode=amode, dense_mode=amode)
     if world > 1:
         stack = stackmod.EpLayerStack(ctx, cfg, dist, rank, world)
     else:
@@ -331,6 +332,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--pdl", action="store_true")
+    ap.add_argument("--act-mode", default="ds", choices=["ds", "mx"], help="scale geometry: ds = 1x128 fp32 (benchmark configs), mx = 1x32 UE8M0 (reference semantics)")
     ap.add_argument("--quick", action="store_true", help="shorter GEMV sweep")
     ap.add_argument("--skip-sub", action="store_true", help="main line only")
     ap.add_argument("--skip-cpu", action="store_true")

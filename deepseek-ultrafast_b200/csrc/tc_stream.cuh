@@ -7,6 +7,9 @@
 //   * accumulators live in tensor memory; four epilogue warps read them back.  With MX (power-of-two) activation
 //     scales the whole K accumulates in tensor memory; with DS (fp32 per 128-K) activation / weight scales each
 //     128-K tile is promoted into fp32 registers with its scale pair, on a 4-deep ring of accumulators.
+//     The four K=32 steps of a tile go to four separate sub-accumulators that the epilogue adds up: tcgen05.mma
+//     instructions that accumulate into the same columns serialise on the instruction's full latency, which for
+//     an 8- or 16-column N would leave the tensor pipe (and with it the whole stream) waiting.
 // Replaces tc_gemv_fp8 (crates/kernels/cu/tcgemv.cu:33-241) and the mma.sync decode MoE
 // (cu/gemv.cu:1016-1692).  The reference's tcgen05 decode kernels load a CTA's whole K slice up front and then
 // drain it; here the ring is refilled continuously across row tiles and experts.
@@ -17,7 +20,7 @@
 namespace dsuf {
 
 constexpr int KID_TC = 3;
-constexpr int TC_THREADS = 192;  // warp 0: TMA producer (+ scale copies), warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int TC_THREADS = 224;  // warp 0: weight producer, warp 1: MMA issuer, warps 2-5: epilogue, warp 6: activation producer
 constexpr int TC_EPI_THREADS = 128;
 
 struct TcCfg {
@@ -31,15 +34,14 @@ struct TcCfg {
     static constexpr int STAGES = 10;
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
-    static constexpr int NB = 4;            // accumulator ring
-    static constexpr int ACC_COLS = 32;     // columns per accumulator
-    static constexpr int TM_SFA = 128, TM_SFB = 192, TM_COLS = 256;
+    static constexpr int NB = 4;            // accumulator ring; every entry holds 4 sub-accumulators (one per K=32 step)
+    static constexpr int TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;
 };
 
 template <int FMT, int WMX, int AMX, int N, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
     using Cfg = TcCfg;
-    constexpr int S = Cfg::STAGES, NB = Cfg::NB;
+    constexpr int S = Cfg::STAGES, NB = Cfg::NB, ACC_COLS = 4 * N;
     constexpr bool PER_TILE = (AMX == 0);  // promote every 128-K tile with fp32 scales
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -51,6 +53,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     const int G = gridDim.x, c = blockIdx.x;
     const int RT = a.RT, KT = a.KT;
     bool dead = false;
+    long long t_tfull_out = 0, t_eall = 0;
 
     if (warp == 1) {
         tmem_alloc(&s_tmem, Cfg::TM_COLS);
@@ -58,7 +61,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     }
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(&full_bar[s], 1 + 32);
+            mbar_init(&full_bar[s], 2 + 32);  // weight expect_tx + activation expect_tx + 32 cp.async lanes
             mbar_init(&empty_bar[s], PER_TILE ? 1 + 4 : 1);
         }
         for (int b = 0; b < NB; ++b) {
@@ -87,56 +90,104 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     }
 
     if (warp == 0) {
-        // ================= producer =================
-        if (beg < end) {
-            if (lane == 0) {
-                prefetch_tmap(&a.tm_w);
-                prefetch_tmap(&a.tm_x);
-            }
-            const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
+        // ================= weight producer (one thread): tile codes + scale atom =================
+        // Kept to a dozen instructions per tile: one thread has to sustain a tile every ~150 cycles.
+        if (lane == 0 && beg < end) {
+            prefetch_tmap(&a.tm_w);
+            const uint64_t pol_w = policy_evict_first();
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
-            int rt = 0, xrow0 = 0;
-            long long wbase = 0;
+            int tile = 0;
+            const uint8_t* sf_src = nullptr;
             bool fresh = true;
-            int n = 0;
-            for (long long i = beg; i < end; ++i, ++n) {
+            int s = 0;
+            uint32_t ph = 0;
+            uint8_t* st = ring;
+            // TMA counts the bytes it READS: a packed FP4 tile is 8192 bytes although it fills 16384 of shared memory
+            constexpr uint32_t W_TX = (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0);
+            long long t_wait = 0;
+            const long long t_start = clock64();
+            for (long long i = beg; i < end; ++i) {
                 if (fresh) {
+                    long long wbase;
+                    if (EPI == EPI_DENSE) {
+                        wbase = q * KT;
+                    } else {
+                        const int slot = (int)(q / RT);
+                        const int rt = (int)(q - (long long)slot * RT);
+                        wbase = ((long long)a.slots[slot].x * RT + rt) * KT;
+                    }
+                    tile = (int)(wbase + kt);
+                    sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
+                    fresh = false;
+                }
+                const long long tw0 = clock64();
+                if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 1)) dead = true;
+                t_wait += clock64() - tw0;
+                mbar_expect_tx(&full_bar[s], (a.probe & 2) ? W_TX - (WMX ? 512 : 0) : W_TX);
+                if (a.probe & 8) {
+                    if (a.probe & 1) bulk_g2s_nh(st, sf_src - a.codes_bytes, FMT == FMT_FP4 ? 8192 : 16384, &full_bar[s]);
+                    else tma_3d_nh(st, &a.tm_w, 0, 0, tile, &full_bar[s]);
+                    if (WMX && !(a.probe & 2)) bulk_g2s_nh(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s]);
+                } else {
+                    if (a.probe & 1) bulk_g2s(st, sf_src - a.codes_bytes, FMT == FMT_FP4 ? 8192 : 16384, &full_bar[s], pol_w);
+                    else tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
+                    if (WMX && !(a.probe & 2)) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
+                }
+                ++tile;
+                sf_src += a.rec_bytes;
+                st += Cfg::STAGE;
+                if (++s == S) { s = 0; st = ring; ph ^= 1; }
+                if (++kt == KT) { kt = 0; ++q; fresh = true; }
+            }
+            if (a.dbg) { a.dbg[c * 8 + 0] = t_wait; a.dbg[c * 8 + 1] = clock64() - t_start; }
+        }
+    } else if (warp == 6) {
+        // ================= activation producer: token rows by TMA, their block scales by 4-byte async copies =================
+        if (beg < end) {
+            if (lane == 0) prefetch_tmap(&a.tm_x);
+            const uint64_t pol_x = policy_evict_last();
+            long long q = beg / KT;
+            int kt = (int)(beg - q * KT);
+            int xrow0 = 0;
+            const uint32_t* sc_src = nullptr;
+            bool fresh = true;
+            int s = 0;
+            uint32_t ph = 0;
+            uint8_t* st = ring;
+            for (long long i = beg; i < end; ++i) {
+                if (fresh) {
+                    int rt;
                     if (EPI == EPI_DENSE) {
                         rt = (int)q;
-                        wbase = (long long)rt * KT;
                         xrow0 = 0;
                     } else {
                         const int slot = (int)(q / RT);
                         rt = (int)(q - (long long)slot * RT);
-                        const int4 sl = a.slots[slot];
-                        wbase = ((long long)sl.x * RT + rt) * KT;
-                        xrow0 = sl.y;
+                        xrow0 = a.slots[slot].y;
                     }
+                    if (lane < N) sc_src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + lane, a.x_rows - 1) * KT;
+                    else if (!WMX && lane == 16) sc_src = (const uint32_t*)a.wscale_ds + (size_t)rt * KT;
                     fresh = false;
                 }
-                const int s = n % S;
-                if (n >= S && !dead && !mbar_wait(&empty_bar[s], ((n / S) - 1) & 1, a.status, KID_TC, 1)) dead = true;
-                uint8_t* st = ring + (size_t)s * Cfg::STAGE;
+                if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
                 if (lane == 0) {
-                    // TMA counts the bytes it READS: a packed FP4 tile is 8192 bytes although it fills 16384 of shared memory
-                    const uint32_t bytes = (FMT == FMT_FP4 ? 8192 : 16384) + N * 128 + (WMX ? 512 : 0);
-                    mbar_expect_tx(&full_bar[s], bytes);
-                    const long long tile = wbase + kt;
-                    tma_3d(st, &a.tm_w, 0, 0, (int)tile, &full_bar[s], pol_w);
-                    if (WMX) bulk_g2s(st + Cfg::SFA_OFF, a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes, 512, &full_bar[s], pol_w);
-                    tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                    if (a.probe & 4) mbar_arrive(&full_bar[s]);
+                    else {
+                        mbar_expect_tx(&full_bar[s], N * 128);
+                        if (a.probe & 8) tma_2d_nh(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s]);
+                        else tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                    }
                 }
                 if (lane < N) {
-                    const int r = min(xrow0 + lane, a.x_rows - 1);
                     // MX: the token's 4 UE8M0 bytes go to its row of the scale atom; DS: its fp32 scale
-                    uint8_t* dst = AMX ? st + Cfg::SFB_OFF + (lane & 31) * 16 : st + Cfg::XS_OFF + 4 * lane;
-                    cp_async4(dst, (const uint32_t*)a.xscale + (size_t)r * KT + kt);
+                    cp_async4(AMX ? st + Cfg::SFB_OFF + lane * 16 : st + Cfg::XS_OFF + 4 * lane, sc_src + kt);
                 } else if (!WMX && lane == 16) {
-                    cp_async4(st + Cfg::WS_OFF, a.wscale_ds + (size_t)rt * KT + kt);
+                    cp_async4(st + Cfg::WS_OFF, sc_src + kt);
                 }
                 cp_async_arrive_noinc(&full_bar[s]);
-                __syncwarp();
+                st += Cfg::STAGE;
+                if (++s == S) { s = 0; st = ring; ph ^= 1; }
                 if (++kt == KT) { kt = 0; ++q; fresh = true; }
             }
         }
@@ -149,30 +200,36 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             if (!AMX) tc_cp_sf(ones_b, tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
-            int n = 0, gidx = 0;
+            int gidx = 0, s = 0;
+            uint32_t ph = 0;
             bool group_open = false;
-            for (long long i = beg; i < end; ++i, ++n) {
-                const int s = n % S;
-                if (!dead && !mbar_wait(&full_bar[s], (n / S) & 1, a.status, KID_TC, 2)) dead = true;
+            uint8_t* st = ring;
+            long long t_full = 0, t_tempty = 0;
+            const long long t_start = clock64();
+            for (long long i = beg; i < end; ++i) {
+                const long long tw0 = clock64();
+                if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TC, 2)) dead = true;
+                t_full += clock64() - tw0;
                 tc_fence_after();
                 if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                 const int b = gidx % NB;
                 const bool first_of_group = !group_open;
                 if (!group_open) {
+                    const long long tw1 = clock64();
                     if (gidx >= NB && !dead && !mbar_wait(&tempty_bar[b], ((gidx / NB) - 1) & 1, a.status, KID_TC, 3)) dead = true;
+                    t_tempty += clock64() - tw1;
                     tc_fence_after();
                     group_open = true;
                 }
-                uint8_t* st = ring + (size_t)s * Cfg::STAGE;
                 uint32_t sfa = ones_a, sfb = ones_b;
-                if (WMX) { sfa = tm + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, tc_smem_desc(st + Cfg::SFA_OFF, 512, 128, 0)); }
-                if (AMX) { sfb = tm + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, tc_smem_desc(st + Cfg::SFB_OFF, 512, 128, 0)); }
+                if (WMX) { sfa = tm + Cfg::TM_SFA + 4 * s; if (!(a.probe & 32)) tc_cp_sf(sfa, tc_smem_desc(st + Cfg::SFA_OFF, 512, 128, 0)); }
+                if (AMX) { sfb = tm + Cfg::TM_SFB + 4 * s; if (!(a.probe & 32)) tc_cp_sf(sfb, tc_smem_desc(st + Cfg::SFB_OFF, 512, 128, 0)); }
                 const uint64_t ad = tc_smem_desc(st, 16, 1024, 2), bd = tc_smem_desc(st + Cfg::B_OFF, 16, 1024, 2);
-                const uint32_t d = tm + b * Cfg::ACC_COLS;
+                const uint32_t d = tm + b * ACC_COLS;
 #pragma unroll
                 for (int kc = 0; kc < 4; ++kc)
-                    tc_mma_mx(d, ad + (uint64_t)(kc * 2), bd + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
-                              (first_of_group && kc == 0) ? 0u : 1u);
+                    if (kc == 0 || !(a.probe & 16)) tc_mma_mx(d + kc * N, ad + (uint64_t)(kc * 2), bd + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
+                              first_of_group ? 0u : 1u);
                 tc_commit(&empty_bar[s]);
                 const bool item_end = (kt + 1 == KT) || (i + 1 == end);
                 if (PER_TILE || item_end) {
@@ -180,10 +237,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     ++gidx;
                     group_open = false;
                 }
+                st += Cfg::STAGE;
+                if (++s == S) { s = 0; st = ring; ph ^= 1; }
                 if (++kt == KT) { kt = 0; ++q; }
             }
+            if (a.dbg) { a.dbg[c * 8 + 2] = t_full; a.dbg[c * 8 + 3] = t_tempty; a.dbg[c * 8 + 4] = clock64() - t_start; a.dbg[c * 8 + 5] = end - beg; }
         }
-    } else {
+    } else if (warp < 6) {
         // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
         const int q4 = warp & 3;
         const int r = 32 * q4 + lane;
@@ -196,8 +256,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
         int kt = (int)(beg - q * KT);
         int rt = 0, xrow0 = 0, cnt = 0;
         bool fresh = true;
-        int n = 0, gidx = 0;
-        for (long long i = beg; i < end; ++i, ++n) {
+        int gidx = 0, es = 0;
+        const uint8_t* est = ring;
+        long long t_tfull = 0;
+        const long long t_estart = clock64();
+        for (long long i = beg; i < end; ++i) {
             if (fresh) {
                 if (EPI == EPI_DENSE) {
                     rt = (int)q;
@@ -215,17 +278,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             const bool item_end = (kt + 1 == KT) || (i + 1 == end);
             if (PER_TILE || item_end) {
                 const int b = gidx % NB;
+                const long long tw0 = clock64();
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
+                t_tfull += clock64() - tw0;
                 tc_fence_after();
                 float v[N];
-                tmem_ld<N>(tm + lane_base + b * Cfg::ACC_COLS, v);
+                {
+                    float r4[ACC_COLS];
+#pragma unroll
+                    for (int c0 = 0; c0 < ACC_COLS; c0 += 32) tmem_ld<32>(tm + lane_base + b * ACC_COLS + c0, r4 + c0);
+#pragma unroll
+                    for (int j = 0; j < N; ++j) v[j] = (r4[j] + r4[N + j]) + (r4[2 * N + j] + r4[3 * N + j]);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty_bar[b]);
                 ++gidx;
                 if (PER_TILE) {
-                    const int s = n % S;
-                    const uint8_t* st = ring + (size_t)s * Cfg::STAGE;
+                    const int s = es;
+                    const uint8_t* st = est;
                     const float wds = WMX ? 1.0f : *(const float*)(st + Cfg::WS_OFF);
                     float xs[N];
 #pragma unroll
@@ -312,9 +383,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
 #pragma unroll
                 for (int j = 0; j < N; ++j) acc[j] = 0.f;
             }
+            est += Cfg::STAGE;
+            if (++es == S) { es = 0; est = ring; }
             if (++kt == KT) { kt = 0; ++q; fresh = true; }
         }
+        t_tfull_out = t_tfull;
+        t_eall = clock64() - t_estart;
     }
+    if (a.dbg && tid == 64) { a.dbg[c * 8 + 6] = t_tfull_out; a.dbg[c * 8 + 7] = t_eall; }
     pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
