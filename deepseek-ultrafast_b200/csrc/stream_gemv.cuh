@@ -48,7 +48,6 @@ struct StreamArgs {
     int ldo;
     float alpha;
     float swiglu_limit;
-    int probe;
     long long* dbg;   // optional [grid][8] cycle counters (debug builds of the bench only)
 };
 

@@ -73,8 +73,9 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
     a.codes_bytes = w->codes_bytes;
     a.n_rows = w->d.n;
     a.alpha = 1.0f;
-    a.probe = getenv("DSUF_PROBE") ? atoi(getenv("DSUF_PROBE")) : 0;
+#ifdef DSUF_TC_TIMING
     a.dbg = getenv("DSUF_DBG_PTR") ? (long long*)strtoull(getenv("DSUF_DBG_PTR"), nullptr, 0) : nullptr;
+#endif
 }
 
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
@@ -137,7 +138,7 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
     const int grid = ctx->sm_count;
     const bool amx = act_mode == DSUF_MODE_MX;
     if (ctx->use_tc) {
-        a.tm_w = getenv("DSUF_PROBE_NOUNPACK") ? w->tm_stream : w->tm_tc;
+        a.tm_w = w->tm_tc;
 #define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg::SMEM, a)
         if (epi == EPI_W13) {
             if (amx) return nt8 == 1 ? GT(1, 8, EPI_W13) : GT(1, 16, EPI_W13);

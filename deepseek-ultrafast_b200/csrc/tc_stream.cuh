@@ -2,14 +2,16 @@
 // few token rows its N), same work decomposition as stream_gemv.cuh but with ZERO per-weight-element instructions:
 //   * TMA lands the weight tile in shared memory in the tensor core's operand layout (FP4 tiles are widened to
 //     8-bit containers by the TMA unit itself, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B);
-//   * one thread issues tcgen05.mma kind::mxf8f6f4.block_scale (4 x K=32 per 128-K tile); UE8M0 weight scales are
-//     applied by the tensor core from tensor memory (tcgen05.cp of the tile record's 512-byte scale atom);
+//   * tcgen05.mma kind::mxf8f6f4.block_scale, 4 x K=32 per 128-K tile; UE8M0 weight scales are applied by the tensor
+//     core from tensor memory (tcgen05.cp of the tile record's 512-byte scale atom);
 //   * accumulators live in tensor memory; four epilogue warps read them back.  With MX (power-of-two) activation
 //     scales the whole K accumulates in tensor memory; with DS (fp32 per 128-K) activation / weight scales each
 //     128-K tile is promoted into fp32 registers with its scale pair, on a 4-deep ring of accumulators.
-//     The four K=32 steps of a tile go to four separate sub-accumulators that the epilogue adds up: tcgen05.mma
-//     instructions that accumulate into the same columns serialise on the instruction's full latency, which for
-//     an 8- or 16-column N would leave the tensor pipe (and with it the whole stream) waiting.
+//   * The four K=32 steps of a tile go to four separate sub-accumulators that the epilogue adds up, so no two
+//     MMAs of a tile depend on each other.
+//   * Measured on B200: the thread that issues the tcgen05 instructions is the serial resource of this kernel
+//     (~75 cycles per MMA of issue back-pressure plus the scale copy and the commit).  In the per-tile (DS) mode
+//     two warps therefore issue alternate tiles, each into its own accumulator-ring entries.
 // Replaces tc_gemv_fp8 (crates/kernels/cu/tcgemv.cu:33-241) and the mma.sync decode MoE
 // (cu/gemv.cu:1016-1692).  The reference's tcgen05 decode kernels load a CTA's whole K slice up front and then
 // drain it; here the ring is refilled continuously across row tiles and experts.
@@ -20,7 +22,8 @@
 namespace dsuf {
 
 constexpr int KID_TC = 3;
-constexpr int TC_THREADS = 224;  // warp 0: weight producer, warp 1: MMA issuer, warps 2-5: epilogue, warp 6: activation producer
+// warp 0: weight producer, warp 1: MMA issuer A, warps 2-5: epilogue, warp 6: activation producer, warp 7: MMA issuer B
+constexpr int TC_THREADS = 256;
 constexpr int TC_EPI_THREADS = 128;
 
 struct TcCfg {
@@ -31,18 +34,27 @@ struct TcCfg {
     static constexpr int XS_OFF = 19456;   // fp32 activation scales of the tile (DS activations)
     static constexpr int WS_OFF = 19584;   // fp32 weight scale of the tile (DS weights)
     static constexpr int STAGE = 20480;
-    static constexpr int STAGES = 10;
+    static constexpr int STAGES = 10;      // even: two issuers walk the ring in steps of two
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
-    static constexpr int NB = 4;            // accumulator ring; every entry holds 4 sub-accumulators (one per K=32 step)
-    static constexpr int TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;
+    static constexpr int NB = 4;           // accumulator ring; every entry holds 4 sub-accumulators (one per K=32 step)
+    static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
 };
+
+#ifdef DSUF_TC_TIMING
+#define DSUF_T0(v) const long long v = clock64()
+#define DSUF_TACC(acc, v) acc += clock64() - v
+#else
+#define DSUF_T0(v)
+#define DSUF_TACC(acc, v)
+#endif
 
 template <int FMT, int WMX, int AMX, int N, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
     using Cfg = TcCfg;
     constexpr int S = Cfg::STAGES, NB = Cfg::NB, ACC_COLS = 4 * N;
-    constexpr bool PER_TILE = (AMX == 0);  // promote every 128-K tile with fp32 scales
+    constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
+    constexpr int NI = PER_TILE ? 2 : 1;    // MMA-issuing warps
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[NB], tempty_bar[NB];
@@ -52,8 +64,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, c = blockIdx.x;
     const int RT = a.RT, KT = a.KT;
-    bool dead = false;
-    long long t_tfull_out = 0, t_eall = 0;
+    bool dead = false;  // set by the first expired wait: nothing is waited for again, the loops stay finite
 
     if (warp == 1) {
         tmem_alloc(&s_tmem, Cfg::TM_COLS);
@@ -62,7 +73,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full_bar[s], 2 + 32);  // weight expect_tx + activation expect_tx + 32 cp.async lanes
-            mbar_init(&empty_bar[s], PER_TILE ? 1 + 4 : 1);
+            mbar_init(&empty_bar[s], PER_TILE ? 4 : 1);  // epilogue warps (they read the stage's scales) / MMA commit
         }
         for (int b = 0; b < NB; ++b) {
             mbar_init(&tfull_bar[b], 1);
@@ -70,7 +81,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
         }
         mbar_fence_init();
     }
-    if (tid >= 64) ((uint32_t*)(ring + Cfg::ONES_OFF))[tid - 64] = 0x7f7f7f7fu;  // 128 threads x 4 bytes = one atom of 1.0
+    if (tid >= 64 && tid < 192) ((uint32_t*)(ring + Cfg::ONES_OFF))[tid - 64] = 0x7f7f7f7fu;  // one atom of UE8M0 1.0
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -78,6 +89,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     const uint32_t tm = s_tmem;
     pdl_wait();
 
+    // ---- this CTA's span of the global tile sequence (see stream_gemv.cuh) ----
     long long beg, end;
     if (EPI == EPI_DENSE) {
         const long long tot = (long long)RT * KT;
@@ -91,7 +103,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
 
     if (warp == 0) {
         // ================= weight producer (one thread): tile codes + scale atom =================
-        // Kept to a dozen instructions per tile: one thread has to sustain a tile every ~150 cycles.
         if (lane == 0 && beg < end) {
             prefetch_tmap(&a.tm_w);
             const uint64_t pol_w = policy_evict_first();
@@ -105,8 +116,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             uint8_t* st = ring;
             // TMA counts the bytes it READS: a packed FP4 tile is 8192 bytes although it fills 16384 of shared memory
             constexpr uint32_t W_TX = (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0);
-            long long t_wait = 0;
-            const long long t_start = clock64();
             for (long long i = beg; i < end; ++i) {
                 if (fresh) {
                     long long wbase;
@@ -121,26 +130,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
                     fresh = false;
                 }
-                const long long tw0 = clock64();
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 1)) dead = true;
-                t_wait += clock64() - tw0;
-                mbar_expect_tx(&full_bar[s], (a.probe & 2) ? W_TX - (WMX ? 512 : 0) : W_TX);
-                if (a.probe & 8) {
-                    if (a.probe & 1) bulk_g2s_nh(st, sf_src - a.codes_bytes, FMT == FMT_FP4 ? 8192 : 16384, &full_bar[s]);
-                    else tma_3d_nh(st, &a.tm_w, 0, 0, tile, &full_bar[s]);
-                    if (WMX && !(a.probe & 2)) bulk_g2s_nh(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s]);
-                } else {
-                    if (a.probe & 1) bulk_g2s(st, sf_src - a.codes_bytes, FMT == FMT_FP4 ? 8192 : 16384, &full_bar[s], pol_w);
-                    else tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
-                    if (WMX && !(a.probe & 2)) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
-                }
+                mbar_expect_tx(&full_bar[s], W_TX);
+                tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
+                if (WMX) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
                 ++tile;
                 sf_src += a.rec_bytes;
                 st += Cfg::STAGE;
                 if (++s == S) { s = 0; st = ring; ph ^= 1; }
                 if (++kt == KT) { kt = 0; ++q; fresh = true; }
             }
-            if (a.dbg) { a.dbg[c * 8 + 0] = t_wait; a.dbg[c * 8 + 1] = clock64() - t_start; }
         }
     } else if (warp == 6) {
         // ================= activation producer: token rows by TMA, their block scales by 4-byte async copies =================
@@ -172,12 +171,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 }
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
                 if (lane == 0) {
-                    if (a.probe & 4) mbar_arrive(&full_bar[s]);
-                    else {
-                        mbar_expect_tx(&full_bar[s], N * 128);
-                        if (a.probe & 8) tma_2d_nh(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s]);
-                        else tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
-                    }
+                    mbar_expect_tx(&full_bar[s], N * 128);
+                    tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
                 }
                 if (lane < N) {
                     // MX: the token's 4 UE8M0 bytes go to its row of the scale atom; DS: its fp32 scale
@@ -191,60 +186,83 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 if (++kt == KT) { kt = 0; ++q; fresh = true; }
             }
         }
-    } else if (warp == 1) {
-        // ================= MMA issuer (one thread) =================
-        if (lane == 0 && beg < end) {
+    } else if (warp == 1 || warp == 7) {
+        // ================= MMA issuers (one thread each; issuer B only in the per-tile mode) =================
+        const int j = warp == 1 ? 0 : 1;
+        if (lane == 0 && j < NI && beg + j < end) {
             const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
-            const uint32_t ones_a = tm + Cfg::TM_SFA + 4 * S, ones_b = tm + Cfg::TM_SFB + 4 * S;
+            const uint32_t ones_a = tm + Cfg::TM_SFA + 4 * (S + j), ones_b = tm + Cfg::TM_SFB + 4 * (S + j);
             if (!WMX) tc_cp_sf(ones_a, tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
             if (!AMX) tc_cp_sf(ones_b, tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+            // descriptors of stage 0; a stage is selected by adding its byte offset / 16 to the address field
+            const uint64_t ad0 = tc_smem_desc(ring, 16, 1024, 2), bd0 = tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2);
+            const uint64_t fa0 = tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0), fb0 = tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0);
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
-            int gidx = 0, s = 0;
+            int s = j, gidx = 0;
             uint32_t ph = 0;
             bool group_open = false;
-            uint8_t* st = ring;
-            long long t_full = 0, t_tempty = 0;
-            const long long t_start = clock64();
-            for (long long i = beg; i < end; ++i) {
-                const long long tw0 = clock64();
+            DSUF_T0(t_start);
+            long long t_full = 0, t_tempty = 0, t_issue = 0;
+            for (long long i = beg + j; i < end; i += NI) {
+                DSUF_T0(t0);
                 if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TC, 2)) dead = true;
-                t_full += clock64() - tw0;
+                DSUF_TACC(t_full, t0);
                 tc_fence_after();
                 if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
-                const int b = gidx % NB;
-                const bool first_of_group = !group_open;
-                if (!group_open) {
-                    const long long tw1 = clock64();
-                    if (gidx >= NB && !dead && !mbar_wait(&tempty_bar[b], ((gidx / NB) - 1) & 1, a.status, KID_TC, 3)) dead = true;
-                    t_tempty += clock64() - tw1;
+                int b;
+                bool first_of_group;
+                DSUF_T0(t1);
+                if (PER_TILE) {
+                    const int n = (int)(i - beg);
+                    b = n & (NB - 1);
+                    first_of_group = true;
+                    if (n >= NB && !dead && !mbar_wait(&tempty_bar[b], ((n / NB) - 1) & 1, a.status, KID_TC, 3)) dead = true;
                     tc_fence_after();
-                    group_open = true;
+                } else {
+                    b = gidx % NB;
+                    first_of_group = !group_open;
+                    if (!group_open) {
+                        if (gidx >= NB && !dead && !mbar_wait(&tempty_bar[b], ((gidx / NB) - 1) & 1, a.status, KID_TC, 3)) dead = true;
+                        tc_fence_after();
+                        group_open = true;
+                    }
                 }
+                DSUF_TACC(t_tempty, t1);
+                DSUF_T0(t2);
+                const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
                 uint32_t sfa = ones_a, sfb = ones_b;
-                if (WMX) { sfa = tm + Cfg::TM_SFA + 4 * s; if (!(a.probe & 32)) tc_cp_sf(sfa, tc_smem_desc(st + Cfg::SFA_OFF, 512, 128, 0)); }
-                if (AMX) { sfb = tm + Cfg::TM_SFB + 4 * s; if (!(a.probe & 32)) tc_cp_sf(sfb, tc_smem_desc(st + Cfg::SFB_OFF, 512, 128, 0)); }
-                const uint64_t ad = tc_smem_desc(st, 16, 1024, 2), bd = tc_smem_desc(st + Cfg::B_OFF, 16, 1024, 2);
+                if (WMX) { sfa = tm + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
+                if (AMX) { sfb = tm + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
                 const uint32_t d = tm + b * ACC_COLS;
 #pragma unroll
                 for (int kc = 0; kc < 4; ++kc)
-                    if (kc == 0 || !(a.probe & 16)) tc_mma_mx(d + kc * N, ad + (uint64_t)(kc * 2), bd + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
+                    tc_mma_mx(d + kc * N, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
                               first_of_group ? 0u : 1u);
-                tc_commit(&empty_bar[s]);
-                const bool item_end = (kt + 1 == KT) || (i + 1 == end);
-                if (PER_TILE || item_end) {
-                    tc_commit(&tfull_bar[b]);
-                    ++gidx;
-                    group_open = false;
+                if (PER_TILE) {
+                    tc_commit(&tfull_bar[b]);  // the epilogue warps release the stage after reading its scales
+                } else {
+                    tc_commit(&empty_bar[s]);
+                    if (kt + 1 == KT || i + 1 == end) {
+                        tc_commit(&tfull_bar[b]);
+                        ++gidx;
+                        group_open = false;
+                    }
+                    if (++kt == KT) { kt = 0; ++q; }
                 }
-                st += Cfg::STAGE;
-                if (++s == S) { s = 0; st = ring; ph ^= 1; }
-                if (++kt == KT) { kt = 0; ++q; }
+                DSUF_TACC(t_issue, t2);
+                s += NI;
+                if (s >= S) { s -= S; ph ^= 1; }
             }
-            if (a.dbg) { a.dbg[c * 8 + 2] = t_full; a.dbg[c * 8 + 3] = t_tempty; a.dbg[c * 8 + 4] = clock64() - t_start; a.dbg[c * 8 + 5] = end - beg; }
+#ifdef DSUF_TC_TIMING
+            if (a.dbg && j == 0) {
+                a.dbg[c * 8 + 0] = t_full; a.dbg[c * 8 + 1] = t_tempty; a.dbg[c * 8 + 2] = t_issue;
+                a.dbg[c * 8 + 3] = clock64() - t_start; a.dbg[c * 8 + 4] = (end - beg + NI - 1) / NI;
+            }
+#endif
         }
-    } else if (warp < 6) {
-        // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
+    } else {
+        // ================= epilogue warps 2..5 (thread = weight row of the tile = tensor-memory lane) =================
         const int q4 = warp & 3;
         const int r = 32 * q4 + lane;
         const int etid = tid - 64;
@@ -258,8 +276,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
         bool fresh = true;
         int gidx = 0, es = 0;
         const uint8_t* est = ring;
-        long long t_tfull = 0;
-        const long long t_estart = clock64();
         for (long long i = beg; i < end; ++i) {
             if (fresh) {
                 if (EPI == EPI_DENSE) {
@@ -278,9 +294,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             const bool item_end = (kt + 1 == KT) || (i + 1 == end);
             if (PER_TILE || item_end) {
                 const int b = gidx % NB;
-                const long long tw0 = clock64();
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
-                t_tfull += clock64() - tw0;
                 tc_fence_after();
                 float v[N];
                 {
@@ -295,17 +309,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 if (lane == 0) mbar_arrive(&tempty_bar[b]);
                 ++gidx;
                 if (PER_TILE) {
-                    const int s = es;
-                    const uint8_t* st = est;
-                    const float wds = WMX ? 1.0f : *(const float*)(st + Cfg::WS_OFF);
+                    const float wds = WMX ? 1.0f : *(const float*)(est + Cfg::WS_OFF);
                     float xs[N];
 #pragma unroll
                     for (int j = 0; j < N; j += 4) {
-                        const float4 t4 = *(const float4*)(st + Cfg::XS_OFF + 4 * j);
+                        const float4 t4 = *(const float4*)(est + Cfg::XS_OFF + 4 * j);
                         xs[j] = t4.x; xs[j + 1] = t4.y; xs[j + 2] = t4.z; xs[j + 3] = t4.w;
                     }
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty_bar[s]);
+                    if (lane == 0) mbar_arrive(&empty_bar[es]);  // MMAs of this stage are complete and its scales are read
 #pragma unroll
                     for (int j = 0; j < N; ++j) acc[j] = fmaf(v[j], wds * xs[j], acc[j]);
                 } else {
@@ -358,7 +370,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                             if (j < cnt && row < a.n_rows) o[(size_t)j * a.ldo + row] = __float2bfloat16(acc[j] * a.alpha);
                     }
                 } else if (EPI == EPI_W13) {
-                    // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group)
+                    // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group);
+                    // SwiGLU as crates/kernels/cu/gemv.cu:470-483: bf16 rounds, optional clamp, routing weight folded in
                     bf16* o = (bf16*)a.out;
                     const float L = a.swiglu_limit;
                     const bool is_gate = (r & 8) == 0;
@@ -387,10 +400,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             if (++es == S) { es = 0; est = ring; }
             if (++kt == KT) { kt = 0; ++q; fresh = true; }
         }
-        t_tfull_out = t_tfull;
-        t_eall = clock64() - t_estart;
     }
-    if (a.dbg && tid == 64) { a.dbg[c * 8 + 6] = t_tfull_out; a.dbg[c * 8 + 7] = t_eall; }
     pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
