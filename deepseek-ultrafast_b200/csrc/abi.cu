@@ -159,7 +159,6 @@ int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_
                       int32_t ldo, float alpha, uint64_t workspace) {
     if (!ctx || !w) return DSUF_E_BADARG;
     DSUF_REQUIRE(ctx, (xq & 15) == 0, "dsuf_gemm_fp8: xq must be 16-byte aligned");
-    if (m > 16) return fail(ctx, DSUF_E_UNSUPPORTED, "dsuf_gemm_fp8: m = %d > 16 needs the tcgen05 path, which this build does not carry yet", m);
     return launch_stream_dense(ctx, (cudaStream_t)stream, w, (const void*)xq, (const void*)xs, m, (void*)out, ldo, alpha, (void*)workspace);
 }
 
@@ -216,7 +215,6 @@ int32_t dsuf_moe_w13_swiglu(dsuf_ctx* ctx, void* stream, const dsuf_weight* w13,
     int rc = check_plan(ctx, plan);
     if (rc) return rc;
     DSUF_REQUIRE(ctx, (xq & 15) == 0, "moe_w13: xq must be 16-byte aligned");
-    if (plan->tile_rows == 128) return fail(ctx, DSUF_E_UNSUPPORTED, "moe_w13: 128-row plans need the tcgen05 path, which this build does not carry yet");
     return launch_stream_moe(ctx, (cudaStream_t)stream, w13, EPI_W13, act_mode, plan, (const void*)xq, (const void*)xs, swiglu_limit,
                              (void*)act_out, w13->d.n / 2);
 }
@@ -227,7 +225,6 @@ int32_t dsuf_moe_w2(dsuf_ctx* ctx, void* stream, const dsuf_weight* w2, int32_t 
     int rc = check_plan(ctx, plan);
     if (rc) return rc;
     DSUF_REQUIRE(ctx, (act_q & 15) == 0, "moe_w2: act_q must be 16-byte aligned");
-    if (plan->tile_rows == 128) return fail(ctx, DSUF_E_UNSUPPORTED, "moe_w2: 128-row plans need the tcgen05 path, which this build does not carry yet");
     return launch_stream_moe(ctx, (cudaStream_t)stream, w2, EPI_W2, act_mode, plan, (const void*)act_q, (const void*)act_s, 0.f,
                              (void*)yrows_out, w2->d.n);
 }

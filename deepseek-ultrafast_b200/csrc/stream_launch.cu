@@ -10,7 +10,7 @@ namespace dsuf {
 
 constexpr int WS_MAX_CTAS = 256;
 constexpr int WS_MAX_ROW_TILES = 8192;
-constexpr size_t WS_PARTIAL_BYTES = (size_t)WS_MAX_CTAS * 2 * 8 * 256 * sizeof(float);
+constexpr size_t WS_PARTIAL_BYTES = (size_t)WS_MAX_CTAS * 2 * 64 * 128 * sizeof(float);  // [cta][head/tail][<=64 tokens][128 rows]
 constexpr size_t WS_BYTES = WS_PARTIAL_BYTES + WS_MAX_ROW_TILES * sizeof(int);
 
 int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, long long rows, int box_rows) {
@@ -27,7 +27,7 @@ int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, 
 
 template <int FMT, int WMX, int AMX, int N, int EPI>
 static int set_attr_tc(dsuf_ctx* ctx) {
-    cudaError_t e = cudaFuncSetAttribute(tc_stream_kernel<FMT, WMX, AMX, N, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(tc_stream_kernel<FMT, WMX, AMX, N, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<N>::SMEM);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_stream)");
     return DSUF_OK;
 }
@@ -51,12 +51,12 @@ int stream_setup(dsuf_ctx* ctx) {
     SA(FMT_FP4, 1, 1, 1, EPI_W2); SA(FMT_FP4, 1, 1, 2, EPI_W2);
 #undef SA
 #define ST(...) if ((rc = set_attr_tc<__VA_ARGS__>(ctx))) return rc
-    ST(FMT_FP8, 0, 0, 8, EPI_DENSE); ST(FMT_FP8, 0, 0, 16, EPI_DENSE);
-    ST(FMT_FP8, 1, 1, 8, EPI_DENSE); ST(FMT_FP8, 1, 1, 16, EPI_DENSE);
-    ST(FMT_FP4, 1, 0, 8, EPI_W13); ST(FMT_FP4, 1, 0, 16, EPI_W13);
-    ST(FMT_FP4, 1, 1, 8, EPI_W13); ST(FMT_FP4, 1, 1, 16, EPI_W13);
-    ST(FMT_FP4, 1, 0, 8, EPI_W2); ST(FMT_FP4, 1, 0, 16, EPI_W2);
-    ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2);
+    ST(FMT_FP8, 0, 0, 8, EPI_DENSE); ST(FMT_FP8, 0, 0, 16, EPI_DENSE); ST(FMT_FP8, 0, 0, 32, EPI_DENSE); ST(FMT_FP8, 0, 0, 64, EPI_DENSE);
+    ST(FMT_FP8, 1, 1, 8, EPI_DENSE); ST(FMT_FP8, 1, 1, 16, EPI_DENSE); ST(FMT_FP8, 1, 1, 32, EPI_DENSE); ST(FMT_FP8, 1, 1, 64, EPI_DENSE);
+    ST(FMT_FP4, 1, 0, 8, EPI_W13); ST(FMT_FP4, 1, 0, 16, EPI_W13); ST(FMT_FP4, 1, 0, 128, EPI_W13);
+    ST(FMT_FP4, 1, 1, 8, EPI_W13); ST(FMT_FP4, 1, 1, 16, EPI_W13); ST(FMT_FP4, 1, 1, 128, EPI_W13);
+    ST(FMT_FP4, 1, 0, 8, EPI_W2); ST(FMT_FP4, 1, 0, 16, EPI_W2); ST(FMT_FP4, 1, 0, 128, EPI_W2);
+    ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2); ST(FMT_FP4, 1, 1, 128, EPI_W2);
 #undef ST
     return DSUF_OK;
 }
@@ -81,14 +81,16 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
                         void* out, int ldo, float alpha, void* workspace) {
     DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP8 && w->d.n_experts == 1, "dsuf_gemm_fp8: weight is not a dense FP8 weight");
-    DSUF_REQUIRE(ctx, m >= 1 && m <= 16, "dsuf_gemm_fp8: streaming path takes 1..16 token rows, got %d", m);
+    const int m_max = ctx->use_tc ? 64 : 16;
+    DSUF_REQUIRE(ctx, m >= 1 && m <= m_max, "dsuf_gemm_fp8: this decode path takes 1..%d token rows per call, got %d", m_max, m);
     DSUF_REQUIRE(ctx, w->rt <= WS_MAX_ROW_TILES, "dsuf_gemm_fp8: too many row tiles (%d)", w->rt);
     DSUF_REQUIRE(ctx, ldo >= w->d.n, "dsuf_gemm_fp8: ldo %d < n %d", ldo, w->d.n);
     DSUF_REQUIRE(ctx, xq && xs && out && workspace, "dsuf_gemm_fp8: null pointer");
     StreamArgs a;
     fill_common(ctx, a, w);
     const int nt8 = m <= 8 ? 1 : 2;
-    int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, 8 * nt8);
+    const int ntok = m <= 8 ? 8 : m <= 16 ? 16 : m <= 32 ? 32 : 64;
+    int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, ntok);
     if (rc) return rc;
     a.xscale = xs;
     a.out = out;
@@ -104,9 +106,9 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     const bool mx = w->d.mode == DSUF_MODE_MX;
     if (ctx->use_tc) {
         a.tm_w = w->tm_tc;
-#define GT(WMX, AMX, NN) launch(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg::SMEM, a)
-        if (mx) return nt8 == 1 ? GT(1, 1, 8) : GT(1, 1, 16);
-        return nt8 == 1 ? GT(0, 0, 8) : GT(0, 0, 16);
+#define GT(WMX, AMX, NN) launch(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg<NN>::SMEM, a)
+        if (mx) return ntok == 8 ? GT(1, 1, 8) : ntok == 16 ? GT(1, 1, 16) : ntok == 32 ? GT(1, 1, 32) : GT(1, 1, 64);
+        return ntok == 8 ? GT(0, 0, 8) : ntok == 16 ? GT(0, 0, 16) : ntok == 32 ? GT(0, 0, 32) : GT(0, 0, 64);
 #undef GT
     }
     const size_t smem = StreamCfg<FMT_FP8>::SMEM;
@@ -119,13 +121,14 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
 int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, int epi, int act_mode, const dsuf_moe_plan* plan,
                       const void* xq, const void* xs, float swiglu_limit, void* out, int ldo) {
     DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP4, "grouped streaming GEMM: weight is not FP4");
-    DSUF_REQUIRE(ctx, plan->tile_rows == 8 || plan->tile_rows == 16, "grouped streaming GEMM: plan tile_rows must be 8 or 16");
+    DSUF_REQUIRE(ctx, plan->tile_rows == 8 || plan->tile_rows == 16 || (plan->tile_rows == 128 && ctx->use_tc),
+                 "grouped GEMM: plan tile_rows must be 8 or 16 (any decode path) or 128 (tcgen05 path)");
     DSUF_REQUIRE(ctx, xq && xs && out, "grouped streaming GEMM: null pointer");
     DSUF_REQUIRE(ctx, epi != EPI_W13 || w->d.gate_up, "dsuf_moe_w13_swiglu: weight was not packed with gate_up=1");
     StreamArgs a;
     fill_common(ctx, a, w);
     const int nt8 = plan->tile_rows / 8;
-    int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, plan->p, 8 * nt8);
+    int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, plan->p, plan->tile_rows);
     if (rc) return rc;
     a.xscale = xs;
     a.slots = (const int4*)plan->tiles;
@@ -139,13 +142,14 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
     const bool amx = act_mode == DSUF_MODE_MX;
     if (ctx->use_tc) {
         a.tm_w = w->tm_tc;
-#define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg::SMEM, a)
+#define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg<NN>::SMEM, a)
+        const int tr = plan->tile_rows;
         if (epi == EPI_W13) {
-            if (amx) return nt8 == 1 ? GT(1, 8, EPI_W13) : GT(1, 16, EPI_W13);
-            return nt8 == 1 ? GT(0, 8, EPI_W13) : GT(0, 16, EPI_W13);
+            if (amx) return tr == 8 ? GT(1, 8, EPI_W13) : tr == 16 ? GT(1, 16, EPI_W13) : GT(1, 128, EPI_W13);
+            return tr == 8 ? GT(0, 8, EPI_W13) : tr == 16 ? GT(0, 16, EPI_W13) : GT(0, 128, EPI_W13);
         }
-        if (amx) return nt8 == 1 ? GT(1, 8, EPI_W2) : GT(1, 16, EPI_W2);
-        return nt8 == 1 ? GT(0, 8, EPI_W2) : GT(0, 16, EPI_W2);
+        if (amx) return tr == 8 ? GT(1, 8, EPI_W2) : tr == 16 ? GT(1, 16, EPI_W2) : GT(1, 128, EPI_W2);
+        return tr == 8 ? GT(0, 8, EPI_W2) : tr == 16 ? GT(0, 16, EPI_W2) : GT(0, 128, EPI_W2);
 #undef GT
     }
     const size_t smem = StreamCfg<FMT_FP4>::SMEM;

@@ -26,19 +26,25 @@ constexpr int KID_TC = 3;
 constexpr int TC_THREADS = 256;
 constexpr int TC_EPI_THREADS = 128;
 
+template <int N>
 struct TcCfg {
     static constexpr int A_BYTES = 16384;
-    static constexpr int B_OFF = 16384;    // N x 128-byte activation rows (N <= 16)
-    static constexpr int SFA_OFF = 18432;  // weight scale atom (512)
-    static constexpr int SFB_OFF = 18944;  // activation scale atom (512), MX activations
-    static constexpr int XS_OFF = 19456;   // fp32 activation scales of the tile (DS activations)
-    static constexpr int WS_OFF = 19584;   // fp32 weight scale of the tile (DS weights)
-    static constexpr int STAGE = 20480;
-    static constexpr int STAGES = 10;      // even: two issuers walk the ring in steps of two
+    static constexpr int B_BYTES = N * 128 < 1024 ? 1024 : N * 128;  // N token rows of 128 bytes
+    static constexpr int B_OFF = A_BYTES;
+    static constexpr int SFA_OFF = B_OFF + B_BYTES;  // weight scale atom (512)
+    static constexpr int SFB_OFF = SFA_OFF + 512;    // MX activations: activation scale atom (512)
+    static constexpr int XS_OFF = SFA_OFF + 512;     // DS activations: N fp32 scales (same bytes as the atom)
+    static constexpr int WS_OFF = XS_OFF + 4 * N;    // DS weights: fp32 scale of the tile (N <= 64 there)
+    static constexpr int STAGE = A_BYTES + B_BYTES + 1024;
+    static constexpr int S_FIT = (226 * 1024 - 2048) / STAGE;
+    static constexpr int STAGES = (S_FIT > 12 ? 12 : S_FIT) & ~1;  // even: two issuers walk the ring in steps of two
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
-    static constexpr int NB = 4;           // accumulator ring; every entry holds 4 sub-accumulators (one per K=32 step)
+    static constexpr int SUB = N <= 16 ? 4 : 1;      // sub-accumulators per ring entry (one per K=32 step for small N)
+    static constexpr int ACC_COLS = SUB * N;
+    static constexpr int NB = ACC_COLS <= 64 ? 4 : 2;  // accumulator ring
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
+    static_assert(NB * ACC_COLS <= 256 && STAGES >= 4 && N <= 128, "tensor-memory / shared-memory budget");
 };
 
 #ifdef DSUF_TC_TIMING
@@ -51,8 +57,8 @@ struct TcCfg {
 
 template <int FMT, int WMX, int AMX, int N, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
-    using Cfg = TcCfg;
-    constexpr int S = Cfg::STAGES, NB = Cfg::NB, ACC_COLS = 4 * N;
+    using Cfg = TcCfg<N>;
+    constexpr int S = Cfg::STAGES, NB = Cfg::NB, ACC_COLS = Cfg::ACC_COLS, SUB = Cfg::SUB;
     constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
     constexpr int NI = PER_TILE ? 2 : 1;    // MMA-issuing warps
     extern __shared__ uint8_t smem_raw[];
@@ -149,7 +155,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
             int xrow0 = 0;
-            const uint32_t* sc_src = nullptr;
+            const float* ws_src = nullptr;
             bool fresh = true;
             int s = 0;
             uint32_t ph = 0;
@@ -165,8 +171,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                         rt = (int)(q - (long long)slot * RT);
                         xrow0 = a.slots[slot].y;
                     }
-                    if (lane < N) sc_src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + lane, a.x_rows - 1) * KT;
-                    else if (!WMX && lane == 16) sc_src = (const uint32_t*)a.wscale_ds + (size_t)rt * KT;
+                    ws_src = (!WMX && lane == 31) ? a.wscale_ds + (size_t)rt * KT : nullptr;
                     fresh = false;
                 }
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
@@ -174,12 +179,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     mbar_expect_tx(&full_bar[s], N * 128);
                     tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
                 }
-                if (lane < N) {
+#pragma unroll
+                for (int n = lane; n < N; n += 32) {
                     // MX: the token's 4 UE8M0 bytes go to its row of the scale atom; DS: its fp32 scale
-                    cp_async4(AMX ? st + Cfg::SFB_OFF + lane * 16 : st + Cfg::XS_OFF + 4 * lane, sc_src + kt);
-                } else if (!WMX && lane == 16) {
-                    cp_async4(st + Cfg::WS_OFF, sc_src + kt);
+                    const uint32_t* src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + n, a.x_rows - 1) * KT + kt;
+                    cp_async4(AMX ? st + Cfg::SFB_OFF + (n & 31) * 16 + (n >> 5) * 4 : st + Cfg::XS_OFF + 4 * n, src);
                 }
+                if (!WMX && lane == 31) cp_async4(st + Cfg::WS_OFF, ws_src + kt);
                 cp_async_arrive_noinc(&full_bar[s]);
                 st += Cfg::STAGE;
                 if (++s == S) { s = 0; st = ring; ph ^= 1; }
@@ -237,8 +243,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 const uint32_t d = tm + b * ACC_COLS;
 #pragma unroll
                 for (int kc = 0; kc < 4; ++kc)
-                    tc_mma_mx(d + kc * N, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
-                              first_of_group ? 0u : 1u);
+                    tc_mma_mx(d + (SUB == 4 ? kc * N : 0), ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
+                              tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && (SUB == 4 || kc == 0)) ? 0u : 1u);
                 if (PER_TILE) {
                     tc_commit(&tfull_bar[b]);  // the epilogue warps release the stage after reading its scales
                 } else {
@@ -296,34 +302,54 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 const int b = gidx % NB;
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
                 tc_fence_after();
-                float v[N];
-                {
-                    float r4[ACC_COLS];
+                if (SUB == 4) {
+                    float v[N], r4[ACC_COLS];
 #pragma unroll
                     for (int c0 = 0; c0 < ACC_COLS; c0 += 32) tmem_ld<32>(tm + lane_base + b * ACC_COLS + c0, r4 + c0);
 #pragma unroll
                     for (int j = 0; j < N; ++j) v[j] = (r4[j] + r4[N + j]) + (r4[2 * N + j] + r4[3 * N + j]);
+                    if (PER_TILE) {
+                        const float wds = WMX ? 1.0f : *(const float*)(est + Cfg::WS_OFF);
+#pragma unroll
+                        for (int j = 0; j < N; j += 4) {
+                            const float4 t4 = *(const float4*)(est + Cfg::XS_OFF + 4 * j);
+                            acc[j] = fmaf(v[j], wds * t4.x, acc[j]);
+                            acc[j + 1] = fmaf(v[j + 1], wds * t4.y, acc[j + 1]);
+                            acc[j + 2] = fmaf(v[j + 2], wds * t4.z, acc[j + 2]);
+                            acc[j + 3] = fmaf(v[j + 3], wds * t4.w, acc[j + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < N; ++j) acc[j] = v[j];
+                    }
+                } else {
+                    const float wds = (PER_TILE && !WMX) ? *(const float*)(est + Cfg::WS_OFF) : 1.0f;
+#pragma unroll
+                    for (int c0 = 0; c0 < N; c0 += 32) {
+                        float v[32];
+                        tmem_ld<32>(tm + lane_base + b * ACC_COLS + c0, v);
+                        if (PER_TILE) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 t4 = *(const float4*)(est + Cfg::XS_OFF + 4 * (c0 + j));
+                                acc[c0 + j] = fmaf(v[j], wds * t4.x, acc[c0 + j]);
+                                acc[c0 + j + 1] = fmaf(v[j + 1], wds * t4.y, acc[c0 + j + 1]);
+                                acc[c0 + j + 2] = fmaf(v[j + 2], wds * t4.z, acc[c0 + j + 2]);
+                                acc[c0 + j + 3] = fmaf(v[j + 3], wds * t4.w, acc[c0 + j + 3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) acc[c0 + j] = v[j];
+                        }
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&tempty_bar[b]);
-                ++gidx;
-                if (PER_TILE) {
-                    const float wds = WMX ? 1.0f : *(const float*)(est + Cfg::WS_OFF);
-                    float xs[N];
-#pragma unroll
-                    for (int j = 0; j < N; j += 4) {
-                        const float4 t4 = *(const float4*)(est + Cfg::XS_OFF + 4 * j);
-                        xs[j] = t4.x; xs[j + 1] = t4.y; xs[j + 2] = t4.z; xs[j + 3] = t4.w;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty_bar[es]);  // MMAs of this stage are complete and its scales are read
-#pragma unroll
-                    for (int j = 0; j < N; ++j) acc[j] = fmaf(v[j], wds * xs[j], acc[j]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < N; ++j) acc[j] = v[j];
+                if (lane == 0) {
+                    mbar_arrive(&tempty_bar[b]);
+                    if (PER_TILE) mbar_arrive(&empty_bar[es]);  // MMAs of this stage are complete and its scales are read
                 }
+                ++gidx;
             }
             if (item_end) {
                 // ---------------- flush the item ----------------
@@ -333,7 +359,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     bool do_store = whole;
                     if (!whole) {
                         const int slot = (q == beg / KT) ? 0 : 1;
-                        float* pw = a.partial + ((size_t)(c * 2 + slot) * 16) * 128 + etid;
+                        float* pw = a.partial + ((size_t)(c * 2 + slot) * 64) * 128 + etid;
 #pragma unroll
                         for (int j = 0; j < N; ++j) __stcg(pw + (size_t)j * 128, acc[j]);
                         __threadfence();
@@ -356,7 +382,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                             for (int cc = first; cc <= last; ++cc) {  // fixed order: independent of arrival order
                                 const long long cbeg = (long long)cc * tot / G;
                                 const int cslot = (q == cbeg / KT) ? 0 : 1;
-                                const float* pr = a.partial + ((size_t)(cc * 2 + cslot) * 16) * 128 + etid;
+                                const float* pr = a.partial + ((size_t)(cc * 2 + cslot) * 64) * 128 + etid;
 #pragma unroll
                                 for (int j = 0; j < N; ++j) acc[j] += __ldcg(pr + (size_t)j * 128);
                             }

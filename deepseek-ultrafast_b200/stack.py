@@ -50,12 +50,13 @@ class LayerStack:
         self.y = [t.empty((cfg.tokens, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
 
     def dense_forward(self, l, x, out):
-        """x bf16 [T][H] -> out bf16 [T][H]; T > 16 is processed in 16-row slabs by the streaming kernel."""
+        """x bf16 [T][H] -> out bf16 [T][H]; processed in slabs of the decode kernel's row limit (64 tcgen05, 16 mma.sync)."""
         ctx, w = self.ctx, self.dense[l]
         act_quant(ctx, w.mode, x, self.xq, self.xs)
         T = x.shape[0]
-        for r0 in range(0, T, 16):
-            m = min(16, T - r0)
+        slab = 64 if ctx.tcgen05 else 16
+        for r0 in range(0, T, slab):
+            m = min(slab, T - r0)
             gemm_fp8(ctx, w, self.xq[r0:r0 + m], self.xs[r0:r0 + m], m, out[r0:r0 + m])
         return out
 
@@ -72,6 +73,7 @@ class LayerStack:
 
     def count_launches(self):
         cfg = self.cfg
-        slabs = (cfg.tokens + 15) // 16
+        slab = 64 if self.ctx.tcgen05 else 16
+        slabs = (cfg.tokens + slab - 1) // slab
         # act_quant + dense slabs + route + plan(3) + gather + w13 + quant + w2 + unpermute
         return cfg.layers * (1 + slabs + 1 + 3 + 1 + 1 + 1 + 1 + 1)

@@ -91,6 +91,15 @@ def test_dense_gemv_full_size_sampled_rows(pkg, ctx, n, k):
     _dense_case(pkg, ctx, 1, n, k, 16, seed=7, rows=4)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("n,k,m", [(1024, 2048, 17), (512, 1024, 33), (7168, 7168, 64)])
+def test_dense_gemv_up_to_64_rows_on_tcgen05(pkg, ctx, mode, n, k, m):
+    """The tcgen05 decode kernel takes up to 64 token rows per call (one pass over the weight)."""
+    if not ctx.tcgen05:
+        pytest.skip("the mma.sync decode kernel takes at most 16 rows per call")
+    _dense_case(pkg, ctx, mode, n, k, m, seed=n + m)
+
+
 def test_dense_gemv_linearity_and_alpha(pkg, ctx):
     """Size-independent property: out(alpha) = alpha * out(1) up to bf16 rounding."""
     g = seeded(3)
@@ -110,7 +119,7 @@ def test_dense_gemv_rejects_bad_arguments(pkg, ctx):
     wq, ws = oracle.quant_fp8_weight(1, wn)
     w = pkg.Weight.dense_fp8(ctx, 1, wq, ws)
     with pytest.raises(pkg.DsufError):
-        pkg.gemv(ctx, w, torch.zeros(17, 128, dtype=torch.bfloat16, device="cuda"))   # m > 16: not this path
+        pkg.gemv(ctx, w, torch.zeros(65, 128, dtype=torch.bfloat16, device="cuda"))   # more rows than one call takes
     xq = torch.zeros(1, 128, dtype=torch.uint8, device="cuda")
     xs = torch.ones(1, 1, dtype=torch.float32, device="cuda")
     with pytest.raises(pkg.DsufError):
@@ -234,6 +243,15 @@ def test_moe_layer_decode_shape_reduced(pkg, ctx, act_mode):
     """64 tokens (8 seqs x 8-token draft block), top-8 of 32 experts, hidden 1024, inter 512: several experts get
     more than 8 rows, so slots are split, and some get none."""
     _moe_case(pkg, ctx, act_mode, T=64, H=1024, I=512, E=32, K=8, tile_rows=8, seed=2)
+
+
+@pytest.mark.parametrize("act_mode", [0, 1])
+@pytest.mark.parametrize("T,E,K", [(200, 4, 2), (96, 2, 2), (700, 8, 3)])
+def test_moe_layer_prefill_tiles_of_128_rows(pkg, ctx, act_mode, T, E, K):
+    """128-row plans (prefill): experts with fewer rows than a tile, exactly full tiles and several tiles."""
+    if not ctx.tcgen05:
+        pytest.skip("128-row plans run on the tcgen05 path only")
+    _moe_case(pkg, ctx, act_mode, T=T, H=256, I=128, E=E, K=K, tile_rows=128, seed=T)
 
 
 def test_moe_layer_clamp_and_shared_expert_term(pkg, ctx):
