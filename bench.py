@@ -206,6 +206,46 @@ def dense_sweep(pkg, ctx, torch, hbm_peak, quick):
     return out
 
 
+def zipf_routing(torch, tokens, n_exp, topk, seed, device):
+    """cfg3 routing: expert popularity Zipf(s=1.1) over a seeded permutation; each token draws `topk` distinct experts
+    without replacement in proportion to popularity (Gumbel top-k); weights = softmax of `topk` fresh N(0,1) logits."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    perm = torch.randperm(n_exp, generator=g, device=device)
+    p = 1.0 / torch.arange(1, n_exp + 1, device=device, dtype=torch.float32) ** 1.1
+    logp = torch.empty(n_exp, device=device)
+    logp[perm] = torch.log(p / p.sum())
+    u = torch.rand(tokens, n_exp, generator=g, device=device).clamp_min(1e-20)
+    ids = (logp[None, :] - torch.log(-torch.log(u))).topk(topk, dim=1).indices.to(torch.int32)
+    w = torch.softmax(torch.randn(tokens, topk, generator=g, device=device), dim=1)
+    return ids.contiguous(), w.contiguous()
+
+
+def prefill_moe(pkg, ctx, torch, stack, tokens):
+    """cfg3: one routed-expert layer over `tokens` tokens with Zipf-skewed routing on 128-row plans (tcgen05 path);
+    TFLOPS = 6 * pairs * inter * hidden / time of the two grouped GEMMs (+ the whole layer's time alongside)."""
+    w13, w2 = stack.moe[0].w13, stack.moe[0].w2
+    layer = pkg.MoeLayer(ctx, w13, w2, tokens, TOPK, stack.cfg.act_mode, tile_rows=128)
+    ids, w = zipf_routing(torch, tokens, E, TOPK, 7, ctx.device)
+    x = torch.randn(tokens, H, device=ctx.device).bfloat16()
+    y = torch.empty(tokens, H, dtype=torch.bfloat16, device=ctx.device)
+    ms_layer = time_events(torch, lambda: layer.forward(x, ids, w, y), 3, 2)
+    plan = layer.plan
+
+    def gemms():
+        pkg.moe_w13_swiglu(ctx, w13, layer.act_mode, plan, layer.xq, layer.xs, layer.act, 0.0)
+        pkg.moe_w2(ctx, w2, layer.act_mode, plan, layer.act_q, layer.act_s, layer.yrows)
+    ms_g = time_events(torch, gemms, 3, 1)
+    flops = 6.0 * tokens * TOPK * I * H
+    cnt = torch.bincount(ids.reshape(-1).long(), minlength=E)
+    st = ctx.status()
+    del layer
+    return {"tokens": tokens, "pairs": tokens * TOPK, "ms_grouped_gemms": round(ms_g, 3), "tflops": round(flops / (ms_g * 1e-3) / 1e12, 1),
+            "frac_of_fp8_dense_peak_4500": round(flops / (ms_g * 1e-3) / 4.5e15, 4), "ms_layer": round(ms_layer, 3),
+            "layer_tokens_per_s": round(tokens / (ms_layer * 1e-3), 1),
+            "tokens_per_expert": {"max": int(cnt.max()), "median": int(cnt.median()), "min": int(cnt.min())},
+            "routing": "Zipf(1.1) popularity, Gumbel top-8 without replacement", "device_status": st.code}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -314,6 +354,8 @@ def run_ours(args):
         result["moe_decode_layer"] = {"tokens": T, "active_experts": e_act0, "ms": round(ms_l, 4), "tokens_per_s": round(T / (ms_l * 1e-3), 1),
                                       "gbs": round(e_act0 * (w13_b + w2_b) / (ms_l * 1e-3) / 1e9, 1),
                                       "note": "L2 holds 126 MB of the ~5 GB read per call; repeated calls on one layer are HBM-bound"}
+    if world == 1 and not args.skip_sub and not args.quick:
+        result["prefill_moe"] = prefill_moe(pkg, ctx, torch, stack, args.prefill_tokens)
     if world == 1 and not args.skip_cpu:
         v, dt, nthr = cpu_sample(2)
         result["cpu_baseline"] = {"value": round(v, 3), "unit": "tokens/s", "cores": nthr, "kind": "port",
@@ -336,6 +378,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="shorter GEMV sweep")
     ap.add_argument("--skip-sub", action="store_true", help="main line only")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--prefill-tokens", type=int, default=16384)
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the dominant kernel, if captured")
     args = ap.parse_args()
     if args.impl == "reference":

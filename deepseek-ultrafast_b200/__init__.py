@@ -342,6 +342,8 @@ class MoeLayer:
     def forward(self, x, ids, w, out, shared=None, events=None):
         """``events``: optional list; (start, end) CUDA events around the gate/up kernel are appended (bench timing)."""
         ctx, plan = self.ctx, self.plan
+        if events is None:
+            events = getattr(self, "events", None)
         moe_perm(ctx, plan, ids, w, self.e_lo)
         moe_gather_quant(ctx, self.act_mode, plan, x, self.xq, self.xs)
         if events is not None:

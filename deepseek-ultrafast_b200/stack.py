@@ -77,3 +77,92 @@ class LayerStack:
         slabs = (cfg.tokens + slab - 1) // slab
         # act_quant + dense slabs + route + plan(3) + gather + w13 + quant + w2 + unpermute
         return cfg.layers * (1 + slabs + 1 + 3 + 1 + 1 + 1 + 1 + 1)
+
+
+class _KernelCompute:
+    """The three compute steps of ep.ep_layer_forward on this library's CUDA kernels."""
+
+    def __init__(self, stack, l):
+        self.s, self.l = stack, l
+
+    def dense_partial(self, x_all):
+        s, w = self.s, self.s.dense[self.l]
+        ctx = s.ctx
+        k0, k1 = s.kslice
+        act_quant(ctx, w.mode, x_all[:, k0:k1], s.xq, s.xs)
+        T = x_all.shape[0]
+        slab = 64 if ctx.tcgen05 else 16
+        for r0 in range(0, T, slab):
+            m = min(slab, T - r0)
+            gemm_fp8(ctx, w, s.xq[r0:r0 + m], s.xs[r0:r0 + m], m, s.partial[r0:r0 + m])
+        return s.partial
+
+    def route(self, h_local):
+        s = self.s
+        return moe_route_tokens(s.ctx, SCORE_SOFTMAX, s.logits[self.l][s.t0:s.t1], None, s.cfg.topk)
+
+    def experts_partial(self, h_all, ids_all, w_all):
+        s = self.s
+        return s.moe[self.l].forward(h_all, ids_all, w_all, s.y_part)
+
+
+class EpLayerStack:
+    """The layer stack on `world` GPUs, one process each (see ep.py for the sharding and the four exchanges)."""
+
+    def __init__(self, ctx, cfg, dist, rank, world):
+        from . import ep
+        t = ctx.torch
+        dev = ctx.device
+        self.ctx, self.cfg, self.rank, self.world = ctx, cfg, rank, world
+        self.xch = ep.Exchange(dist, rank, world)
+        H, I, E, T = cfg.hidden, cfg.inter, cfg.n_experts, cfg.tokens
+        self.kslice = ep.shard_bounds(H, world, rank)
+        if (self.kslice[1] - self.kslice[0]) % 128:
+            raise ValueError("hidden / world must be a multiple of 128")
+        self.e_lo, e_hi = ep.shard_bounds(E, world, rank)
+        self.t0, self.t1 = ep.shard_bounds(T, world, rank)
+        n_loc, kloc = e_hi - self.e_lo, self.kslice[1] - self.kslice[0]
+        self.dense, self.moe, self.logits = [], [], []
+        for l in range(cfg.layers):
+            base = cfg.seed + 1000 * l + 100000 * rank   # random-init weights: every shard draws its own
+            tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, kloc, cfg.std, base + 1, dev)
+            self.dense.append(Weight(ctx, 0, cfg.dense_mode, H, kloc, 1, False, tiles, sds))
+            w13 = synth.fp4_experts(t, n_loc, 2 * I, H, cfg.std, base + 2, True, dev)
+            w2 = synth.fp4_experts(t, n_loc, H, I, cfg.std, base + 3, False, dev)
+            W13 = Weight.experts_fp4_packed(ctx, w13, 2 * I, H, n_loc, True)
+            W2 = Weight.experts_fp4_packed(ctx, w2, H, I, n_loc, False)
+            self.moe.append(MoeLayer(ctx, W13, W2, T, cfg.topk, cfg.act_mode, e_lo=self.e_lo, tile_rows=8))
+            g = t.Generator(device=dev).manual_seed(cfg.seed + 1000 * l + 4)   # same logits on every rank
+            self.logits.append(t.randn(T, E, generator=g, device=dev, dtype=t.float32))
+        blk = 32 if cfg.dense_mode == MODE_MX else 128
+        tl = self.t1 - self.t0
+        self.xq = t.empty((T, kloc), dtype=t.uint8, device=dev)
+        self.xs = t.empty((T, kloc // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
+        self.partial = t.empty((T, H), dtype=t.bfloat16, device=dev)
+        self.y_part = t.empty((T, H), dtype=t.bfloat16, device=dev)
+        self.bufs = {"x_all": t.empty((T, H), dtype=t.bfloat16, device=dev),
+                     "h_local": t.empty((tl, H), dtype=t.bfloat16, device=dev),
+                     "h_all": t.empty((T, H), dtype=t.bfloat16, device=dev),
+                     "ids_all": t.empty((T, cfg.topk), dtype=t.int32, device=dev),
+                     "w_all": t.empty((T, cfg.topk), dtype=t.float32, device=dev),
+                     "y_local": None}
+        self.y = [t.empty((tl, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
+        self.compute = [_KernelCompute(self, l) for l in range(cfg.layers)]
+
+    def logits_full(self, l):
+        return self.logits[l]
+
+    def forward(self, x_local, events=None):
+        from . import ep
+        cur = x_local
+        for l in range(self.cfg.layers):
+            self.bufs["y_local"] = self.y[l & 1]
+            self.moe[l].events = events
+            cur = ep.ep_layer_forward(self.xch, self.compute[l], cur, self.bufs)
+        return cur
+
+    def count_launches(self):
+        cfg = self.cfg
+        slab = 64 if self.ctx.tcgen05 else 16
+        slabs = (cfg.tokens + slab - 1) // slab
+        return cfg.layers * (1 + slabs + 1 + 3 + 1 + 1 + 1 + 1 + 1)

@@ -1,0 +1,120 @@
+"""Expert-parallel exchange on CPU: two gloo ranks run ep.ep_layer_forward with the oracle as the compute steps and must
+reproduce the single-rank layer (K-sharded dense + reduce-scatter, dispatch by all-gather, expert shard, combine)."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+T, H, I, E, K = 8, 256, 128, 8, 2
+
+
+def _inputs():
+    import oracle
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    logits = torch.randn(T, E, generator=g)
+    wd = (torch.randn(H, H, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    q13 = [oracle.quant_fp4_weight(w13[e]) for e in range(E)]
+    q2 = [oracle.quant_fp4_weight(w2[e]) for e in range(E)]
+    return dict(x=x, logits=logits, wd=wd, c13=np.stack([a for a, _ in q13]), s13=np.stack([b for _, b in q13]),
+                c2=np.stack([a for a, _ in q2]), s2=np.stack([b for _, b in q2]))
+
+
+class OracleCompute:
+    def __init__(self, inp, rank, world):
+        import oracle
+        from __graft_entry__ import load_package
+        import importlib
+        self.o, self.inp, self.rank, self.world = oracle, inp, rank, world
+        ep = importlib.import_module(load_package().__name__ + ".ep")
+        self.k0, self.k1 = ep.shard_bounds(H, world, rank)
+        self.e0, self.e1 = ep.shard_bounds(E, world, rank)
+        self.t0, self.t1 = ep.shard_bounds(T, world, rank)
+        self.wq, self.ws = oracle.quant_fp8_weight(oracle.MODE_DS, np.ascontiguousarray(inp["wd"][:, self.k0:self.k1]))
+
+    def dense_partial(self, x_all):
+        o = self.o
+        xs = np.ascontiguousarray(x_all.view(torch.uint16).numpy()[:, self.k0:self.k1])
+        xq, xsc = o.act_quant(o.MODE_DS, xs)
+        ob, _ = o.gemm_fp8(o.MODE_DS, self.wq, self.ws, xq, xsc)
+        return torch.from_numpy(ob.view(np.int16)).view(torch.bfloat16)
+
+    def route(self, h_local):
+        ids, w = self.o.route(1, self.inp["logits"][self.t0:self.t1].numpy(), None, K)
+        return torch.from_numpy(ids), torch.from_numpy(w)
+
+    def experts_partial(self, h_all, ids_all, w_all):
+        o, inp = self.o, self.inp
+        r = o.moe_layer(o.MODE_DS, h_all.view(torch.uint16).numpy(), ids_all.numpy(), w_all.numpy(), inp["c13"], inp["s13"],
+                        inp["c2"], inp["s2"], e_lo=self.e0, e_hi=self.e1)
+        return torch.from_numpy(r["y_bf16"].view(np.int16)).view(torch.bfloat16)
+
+
+def _bufs(world):
+    tl = T // world
+    return {"x_all": torch.empty(T, H, dtype=torch.bfloat16), "h_local": torch.empty(tl, H, dtype=torch.bfloat16),
+            "h_all": torch.empty(T, H, dtype=torch.bfloat16), "ids_all": torch.empty(T, K, dtype=torch.int32),
+            "w_all": torch.empty(T, K, dtype=torch.float32), "y_local": torch.empty(tl, H, dtype=torch.bfloat16)}
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    import importlib
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ep = importlib.import_module(load_package().__name__ + ".ep")
+    inp = _inputs()
+    xch = ep.Exchange(dist, rank, world)
+    t0, t1 = ep.shard_bounds(T, world, rank)
+    bufs = _bufs(world)
+    y = ep.ep_layer_forward(xch, OracleCompute(inp, rank, world), inp["x"][t0:t1].contiguous(), bufs)
+    torch.save((bufs["h_local"].clone(), y.clone()), os.path.join(out_dir, f"y{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_layer_equals_single_rank(tmp_path):
+    sys.path.insert(0, ROOT)
+    import importlib
+    from __graft_entry__ import load_package
+    ep = importlib.import_module(load_package().__name__ + ".ep")
+    inp = _inputs()
+    bufs1 = _bufs(1)
+    one = OracleCompute(inp, 0, 1)
+    ep.ep_layer_forward(ep.Exchange(None, 0, 1), one, inp["x"], bufs1)
+    ref_h = bufs1["h_local"].float()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    parts = [torch.load(os.path.join(tmp_path, f"y{r}.pt")) for r in range(2)]
+    h2 = torch.cat([p[0] for p in parts])
+    y2 = torch.cat([p[1] for p in parts]).float()
+    # 1) K-sharded dense + reduce-scatter: equal to the unsharded projection up to bf16 rounding of the two partials
+    assert (h2.float() - ref_h).norm() / ref_h.norm() < 5e-3
+    # 2) dispatch / expert shards / combine: equal to the unsharded expert layer evaluated on the SAME h
+    #    (FP8 re-quantization makes the layer discontinuous in h, so the comparison must not mix the two h's)
+    ids, w = one.route(None)
+    y_ref = one.experts_partial(h2, ids, w).float()
+    err = (y2 - y_ref).norm() / y_ref.norm()
+    assert err < 5e-3, err
+    assert y_ref.abs().max() > 0
+
+
+def test_shard_bounds_reject_uneven_splits():
+    sys.path.insert(0, ROOT)
+    import importlib
+    from __graft_entry__ import load_package
+    ep = importlib.import_module(load_package().__name__ + ".ep")
+    assert ep.shard_bounds(256, 8, 3) == (96, 128)
+    with pytest.raises(ValueError):
+        ep.shard_bounds(10, 4, 0)
