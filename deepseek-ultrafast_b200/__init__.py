@@ -64,6 +64,8 @@ ABI = {
     "dsuf_workspace_init": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_size_t]),
     "dsuf_gemm_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
                                   C.c_int32, C.c_float, C.c_uint64]),
+    "dsuf_gemm_fp8_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
+                                         C.c_int32, C.c_float]),
     "dsuf_moe_route": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32,
                                    C.c_int32, C.c_float, C.c_uint64, C.c_uint64]),
     "dsuf_moe_plan_scratch_ints": (C.c_size_t, [C.c_int32, C.c_int32]),
@@ -246,6 +248,16 @@ def gemm_fp8(ctx, w, xq, xs, m, out=None, alpha=1.0):
         out = t.empty((m, w.n), dtype=t.bfloat16, device=xq.device)
     ctx.check(lib().dsuf_gemm_fp8(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0),
                                   alpha, ctx.workspace.data_ptr()))
+    return out
+
+
+def gemm_fp8_static(ctx, w, xq, xs, m, out=None, alpha=1.0):
+    """dsuf_gemm_fp8 without a caller workspace (scratch is a fixed array inside the library); see include/dsuf_qmm.h."""
+    t = ctx.torch
+    if out is None:
+        out = t.empty((m, w.n), dtype=t.bfloat16, device=xq.device)
+    ctx.check(lib().dsuf_gemm_fp8_static(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0),
+                                         alpha))
     return out
 
 

@@ -79,7 +79,7 @@ int launch(dsuf_ctx* ctx, cudaStream_t stream, void (*kernel)(KArgs...), dim3 gr
 int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
                      void* scales, const int* pair_row, int fanout, int sf_atoms);
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
-                        void* out, int ldo, float alpha, void* workspace);
+                        void* out, int ldo, float alpha, void* workspace, int* counters_at = nullptr);
 int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, int epi, int act_mode, const dsuf_moe_plan* plan,
                       const void* xq, const void* xs, float swiglu_limit, void* out, int ldo);
 int launch_route(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp,

@@ -79,7 +79,7 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
 }
 
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
-                        void* out, int ldo, float alpha, void* workspace) {
+                        void* out, int ldo, float alpha, void* workspace, int* counters_at) {
     DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP8 && w->d.n_experts == 1, "dsuf_gemm_fp8: weight is not a dense FP8 weight");
     const int m_max = ctx->use_tc ? 64 : 16;
     DSUF_REQUIRE(ctx, m >= 1 && m <= m_max, "dsuf_gemm_fp8: this decode path takes 1..%d token rows per call, got %d", m_max, m);
@@ -95,7 +95,7 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     a.xscale = xs;
     a.out = out;
     a.partial = (float*)workspace;
-    a.counters = (int*)((uint8_t*)workspace + WS_PARTIAL_BYTES);
+    a.counters = counters_at ? counters_at : (int*)((uint8_t*)workspace + WS_PARTIAL_BYTES);
     a.m = m;
     a.x_rows = m;
     a.ldo = ldo;

@@ -122,6 +122,21 @@ int32_t dsuf_workspace_init(dsuf_ctx* ctx, void* stream, uint64_t workspace, siz
 int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
                       int32_t ldo, float alpha, uint64_t workspace);
 
+/* No counterpart in the reference.  Same function as dsuf_gemm_fp8 for callers that cannot allocate device memory
+ * (an engine that spent its device budget on one start-up arena, a plugin without its own allocator, a caller for which
+ * an allocation would synchronise the device): the stream-K scratch is a fixed array inside the library's device image
+ * instead of a caller workspace.  Limits and rules:
+ *   - about 10 MB per GPU that loads the library, held until the process exits;
+ *   - weights of at most 131072 rows (1024 row tiles) on GPUs of at most 160 SMs; anything larger returns
+ *     DSUF_E_BADARG with a message that says so;
+ *   - all calls share the one array: calls that overlap on the GPU race, so keep them stream-ordered; its arrival
+ *     counters are cleared on the stream before each launch, nothing else carries over between calls;
+ *   - the first call on a device resolves the array's device address (that device must be current); make that call
+ *     before any stream capture starts.
+ * Calls no cudaMalloc / cudaFree and no allocating library routine. */
+int32_t dsuf_gemm_fp8_static(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m,
+                             uint64_t out, int32_t ldo, float alpha);
+
 /* moe_route_tokens + route_token (cu/ops.cu:615-623, cu/route.cuh:3-56; RouteArgs ops.rs:124-135):
  * top-k of score+bias, ties to the lower id, weights = score / sum(selected scores) * route_scale.
  * scores f32 [t][n_exp] (logits when score_fn != IDENTITY), bias f32 [n_exp] or 0.
