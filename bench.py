@@ -327,7 +327,7 @@ def run_ours(args):
     e_act = float(np.mean(ids_counts))
     algo_w13 = e_act * w13_b + T * TOPK * (H + H // 128 * 4) / world + T * TOPK * I * 2 / world
     achieved = algo_w13 / (w13_ms * 1e-3) / 1e9
-    roofline = {"kernel": "stream_gemv_kernel<FP4,W13> (grouped gate/up + SwiGLU)", "bound": "hbm", "achieved": round(achieved, 1),
+    roofline = {"kernel": ("tc_stream_kernel" if ctx.tcgen05 else "stream_gemv_kernel") + "<FP4,W13> (grouped gate/up + SwiGLU)", "bound": "hbm", "achieved": round(achieved, 1),
                 "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                 "frac_of_8tbs": round(achieved / 8000.0, 4), "avg_launch_ms": round(w13_ms, 4), "active_experts_per_launch": e_act,
                 "algorithmic_bytes_per_launch": int(algo_w13), "traffic": args.traffic}

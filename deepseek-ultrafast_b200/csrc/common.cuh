@@ -138,6 +138,10 @@ DSUF_DEV bool elect_one() {
     asm volatile("{ .reg .pred e; elect.sync _|e, 0xffffffff; selp.u32 %0, 1, 0, e; }" : "=r"(pred));
     return pred != 0;
 }
+// Warp-uniform broadcasts: tcgen05 / TMA instructions take their descriptors from uniform registers; values the
+// compiler cannot prove uniform cost a register-file round trip per operand on every issue.
+DSUF_DEV uint32_t uni32(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
+DSUF_DEV uint64_t uni64(uint64_t v) { return ((uint64_t)uni32((uint32_t)(v >> 32)) << 32) | uni32((uint32_t)v); }
 DSUF_DEV void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
 
 // ---- codecs ----

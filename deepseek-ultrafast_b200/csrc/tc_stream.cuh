@@ -108,9 +108,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     }
 
     if (warp == 0) {
-        // ================= weight producer (one thread): tile codes + scale atom =================
-        if (lane == 0 && beg < end) {
-            prefetch_tmap(&a.tm_w);
+        // ================= weight producer: tile codes + scale atom =================
+        // The whole warp runs the loop (so every value stays warp-uniform and the TMA descriptors live in uniform
+        // registers); one elected lane issues.
+        if (beg < end) {
+            if (lane == 0) prefetch_tmap(&a.tm_w);
             const uint64_t pol_w = policy_evict_first();
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
@@ -137,9 +139,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     fresh = false;
                 }
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 1)) dead = true;
-                mbar_expect_tx(&full_bar[s], W_TX);
-                tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
-                if (WMX) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
+                if (elect_one()) {
+                    mbar_expect_tx(&full_bar[s], W_TX);
+                    tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
+                    if (WMX) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
+                }
+                __syncwarp();
                 ++tile;
                 sf_src += a.rec_bytes;
                 st += Cfg::STAGE;
@@ -175,10 +180,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     fresh = false;
                 }
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
-                if (lane == 0) {
+                if (elect_one()) {
                     mbar_expect_tx(&full_bar[s], N * 128);
                     tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
                 }
+                __syncwarp();
 #pragma unroll
                 for (int n = lane; n < N; n += 32) {
                     // MX: the token's 4 UE8M0 bytes go to its row of the scale atom; DS: its fp32 scale
@@ -195,14 +201,22 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
     } else if (warp == 1 || warp == 7) {
         // ================= MMA issuers (one thread each; issuer B only in the per-tile mode) =================
         const int j = warp == 1 ? 0 : 1;
-        if (lane == 0 && j < NI && beg + j < end) {
+        // The whole warp runs the loop and one elected lane issues: tcgen05 operands are uniform-register operands,
+        // and a loop run by a single lane of a diverged warp pays a register-file round trip for each of them.
+        if (j < NI && beg + j < end) {
+            const uint32_t tmu = uni32(tm);
             const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
-            const uint32_t ones_a = tm + Cfg::TM_SFA + 4 * (S + j), ones_b = tm + Cfg::TM_SFB + 4 * (S + j);
-            if (!WMX) tc_cp_sf(ones_a, tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
-            if (!AMX) tc_cp_sf(ones_b, tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+            const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
+            const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+            if (elect_one()) {
+                if (!WMX) tc_cp_sf(ones_a, ones_d);
+                if (!AMX) tc_cp_sf(ones_b, ones_d);
+            }
+            __syncwarp();
             // descriptors of stage 0; a stage is selected by adding its byte offset / 16 to the address field
-            const uint64_t ad0 = tc_smem_desc(ring, 16, 1024, 2), bd0 = tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2);
-            const uint64_t fa0 = tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0), fb0 = tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0);
+            const uint64_t ad0 = uni64(tc_smem_desc(ring, 16, 1024, 2)), bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
+            const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0)),
+                           fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
             int s = j, gidx = 0;
@@ -237,23 +251,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 DSUF_TACC(t_tempty, t1);
                 DSUF_T0(t2);
                 const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
-                uint32_t sfa = ones_a, sfb = ones_b;
-                if (WMX) { sfa = tm + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
-                if (AMX) { sfb = tm + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
-                const uint32_t d = tm + b * ACC_COLS;
+                const bool group_end = PER_TILE || kt + 1 == KT || i + 1 == end;
+                if (elect_one()) {
+                    uint32_t sfa = ones_a, sfb = ones_b;
+                    if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
+                    if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
+                    const uint32_t d = tmu + b * ACC_COLS;
 #pragma unroll
-                for (int kc = 0; kc < 4; ++kc)
-                    tc_mma_mx(d + (SUB == 4 ? kc * N : 0), ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
-                              tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && (SUB == 4 || kc == 0)) ? 0u : 1u);
-                if (PER_TILE) {
-                    tc_commit(&tfull_bar[b]);  // the epilogue warps release the stage after reading its scales
-                } else {
-                    tc_commit(&empty_bar[s]);
-                    if (kt + 1 == KT || i + 1 == end) {
-                        tc_commit(&tfull_bar[b]);
-                        ++gidx;
-                        group_open = false;
-                    }
+                    for (int kc = 0; kc < 4; ++kc)
+                        tc_mma_mx(d + (SUB == 4 ? kc * N : 0), ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
+                                  tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && (SUB == 4 || kc == 0)) ? 0u : 1u);
+                    // per-tile mode: the epilogue warps release the stage after reading its scales
+                    if (!PER_TILE) tc_commit(&empty_bar[s]);
+                    if (group_end) tc_commit(&tfull_bar[b]);
+                }
+                __syncwarp();
+                if (!PER_TILE) {
+                    if (group_end) { ++gidx; group_open = false; }
                     if (++kt == KT) { kt = 0; ++q; }
                 }
                 DSUF_TACC(t_issue, t2);
@@ -261,7 +275,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 if (s >= S) { s -= S; ph ^= 1; }
             }
 #ifdef DSUF_TC_TIMING
-            if (a.dbg && j == 0) {
+            if (a.dbg && j == 0 && lane == 0) {
                 a.dbg[c * 8 + 0] = t_full; a.dbg[c * 8 + 1] = t_tempty; a.dbg[c * 8 + 2] = t_issue;
                 a.dbg[c * 8 + 3] = clock64() - t_start; a.dbg[c * 8 + 4] = (end - beg + NI - 1) / NI;
             }
