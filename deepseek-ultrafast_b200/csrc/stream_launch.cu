@@ -106,7 +106,7 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     const bool mx = w->d.mode == DSUF_MODE_MX;
     if (ctx->use_tc) {
         a.tm_w = w->tm_tc;
-#define GT(WMX, AMX, NN) launch(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg<NN>::SMEM, a)
+#define GT(WMX, AMX, NN) launch(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, a)
         if (mx) return ntok == 8 ? GT(1, 1, 8) : ntok == 16 ? GT(1, 1, 16) : ntok == 32 ? GT(1, 1, 32) : GT(1, 1, 64);
         return ntok == 8 ? GT(0, 0, 8) : ntok == 16 ? GT(0, 0, 16) : ntok == 32 ? GT(0, 0, 32) : GT(0, 0, 64);
 #undef GT
@@ -142,7 +142,7 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
     const bool amx = act_mode == DSUF_MODE_MX;
     if (ctx->use_tc) {
         a.tm_w = w->tm_tc;
-#define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TC_THREADS), (size_t)TcCfg<NN>::SMEM, a)
+#define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, a)
         const int tr = plan->tile_rows;
         if (epi == EPI_W13) {
             if (amx) return tr == 8 ? GT(1, 8, EPI_W13) : tr == 16 ? GT(1, 16, EPI_W13) : GT(1, 128, EPI_W13);

@@ -22,8 +22,8 @@
 namespace dsuf {
 
 constexpr int KID_TC = 3;
-// warp 0: weight producer, warp 1: MMA issuer A, warps 2-5: epilogue, warp 6: activation producer, warp 7: MMA issuer B
-constexpr int TC_THREADS = 256;
+// warp 0: weight producer, 1: MMA issuer A, 2-5: epilogue, 6: activation producer, 7: MMA issuer B,
+// 8 / 9: second weight / activation producer (token tiles up to 64 columns)
 constexpr int TC_EPI_THREADS = 128;
 
 template <int N>
@@ -36,13 +36,17 @@ struct TcCfg {
     static constexpr int XS_OFF = SFA_OFF + 512;     // DS activations: N fp32 scales (same bytes as the atom)
     static constexpr int WS_OFF = XS_OFF + 4 * N;    // DS weights: fp32 scale of the tile (N <= 64 there)
     static constexpr int STAGE = A_BYTES + B_BYTES + 1024;
-    static constexpr int S_FIT = (226 * 1024 - 2048) / STAGE;
+    static constexpr int NE = N <= 16 ? 2 : 1;        // epilogue warp groups (per-tile mode: alternate tiles)
+    static constexpr int RED_BYTES = NE == 2 ? 2 * N * 128 * 4 : 0;  // static shared memory of the group combine
+    static constexpr int S_FIT = (226 * 1024 - 2048 - RED_BYTES) / STAGE;
     static constexpr int STAGES = (S_FIT > 12 ? 12 : S_FIT) & ~1;  // even: two issuers walk the ring in steps of two
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
-    static constexpr int SUB = N <= 16 ? 4 : 1;      // sub-accumulators per ring entry (one per K=32 step for small N)
-    static constexpr int ACC_COLS = SUB * N;
-    static constexpr int NB = ACC_COLS <= 64 ? 4 : 2;  // accumulator ring
+    static constexpr int SUB = 1;                    // sub-accumulators per ring entry (4 = one per K=32 step; measured: no gain)
+    static constexpr int ACC_COLS = SUB * N < 32 ? 32 : SUB * N;
+    static constexpr int NB = ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
+    static constexpr int NP = N <= 64 ? 2 : 1;        // producer warps per kind (weights / activations), alternate tiles
+    static constexpr int THREADS = 256 + 64 * (NP - 1) + 128 * (NE - 1);  // warps 8, 9: second producers; 10-13: second epilogue group
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
     static_assert(NB * ACC_COLS <= 256 && STAGES >= 4 && N <= 128, "tensor-memory / shared-memory budget");
 };
@@ -56,16 +60,20 @@ struct TcCfg {
 #endif
 
 template <int FMT, int WMX, int AMX, int N, int EPI>
-__global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
     using Cfg = TcCfg<N>;
     constexpr int S = Cfg::STAGES, NB = Cfg::NB, ACC_COLS = Cfg::ACC_COLS, SUB = Cfg::SUB;
     constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
     constexpr int NI = PER_TILE ? 2 : 1;    // MMA-issuing warps
+    constexpr int NP = Cfg::NP;
+    constexpr int NE = (PER_TILE && Cfg::NE == 2) ? 2 : 1;  // epilogue groups actually working
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[NB], tempty_bar[NB];
+    static_assert((NB & (NB - 1)) == 0, "accumulator ring size must be a power of two");
     __shared__ uint32_t s_tmem;
     __shared__ int s_flag;
+    __shared__ float s_red[Cfg::NE == 2 ? 2 * N * 128 : 1];  // second epilogue group -> first, double buffered by item
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, c = blockIdx.x;
@@ -107,24 +115,27 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
         end = ((long long)(c + 1) * q / G) * KT;
     }
 
-    if (warp == 0) {
-        // ================= weight producer: tile codes + scale atom =================
+    if (warp == 0 || warp == 8) {
+        // ================= weight producers (warp 8 takes the odd tiles when NP == 2): tile codes + scale atom =================
+        const int pj = warp == 0 ? 0 : 1;
         // The whole warp runs the loop (so every value stays warp-uniform and the TMA descriptors live in uniform
         // registers); one elected lane issues.
-        if (beg < end) {
+        if (pj < NP && beg + pj < end) {
             if (lane == 0) prefetch_tmap(&a.tm_w);
             const uint64_t pol_w = policy_evict_first();
-            long long q = beg / KT;
-            int kt = (int)(beg - q * KT);
+            long long q = (beg + pj) / KT;
+            int kt = (int)(beg + pj - q * KT);
             int tile = 0;
             const uint8_t* sf_src = nullptr;
             bool fresh = true;
-            int s = 0;
+            int s = pj;
             uint32_t ph = 0;
-            uint8_t* st = ring;
+            uint8_t* st = ring + pj * Cfg::STAGE;
             // TMA counts the bytes it READS: a packed FP4 tile is 8192 bytes although it fills 16384 of shared memory
             constexpr uint32_t W_TX = (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0);
-            for (long long i = beg; i < end; ++i) {
+            long long tw_wait = 0;
+            DSUF_T0(tw_start);
+            for (long long i = beg + pj; i < end; i += NP) {
                 if (fresh) {
                     long long wbase;
                     if (EPI == EPI_DENSE) {
@@ -138,34 +149,44 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
                     fresh = false;
                 }
+                DSUF_T0(tw0);
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 1)) dead = true;
+                DSUF_TACC(tw_wait, tw0);
                 if (elect_one()) {
                     mbar_expect_tx(&full_bar[s], W_TX);
                     tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
                     if (WMX) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
                 }
                 __syncwarp();
-                ++tile;
-                sf_src += a.rec_bytes;
-                st += Cfg::STAGE;
-                if (++s == S) { s = 0; st = ring; ph ^= 1; }
-                if (++kt == KT) { kt = 0; ++q; fresh = true; }
+                tile += NP;
+                sf_src += (size_t)NP * a.rec_bytes;
+                s += NP;
+                st += NP * Cfg::STAGE;
+                if (s >= S) { s -= S; st -= S * Cfg::STAGE; ph ^= 1; }
+                kt += NP;
+                while (kt >= KT) { kt -= KT; ++q; fresh = true; }
             }
+#ifdef DSUF_TC_TIMING
+            if (a.dbg && lane == 0 && pj == 0) a.dbg[c * 8 + 5] = clock64() - tw_start - tw_wait;
+#endif
         }
-    } else if (warp == 6) {
-        // ================= activation producer: token rows by TMA, their block scales by 4-byte async copies =================
-        if (beg < end) {
+    } else if (warp == 6 || warp == 9) {
+        // ================= activation producers: token rows by TMA, their block scales by 4-byte async copies =================
+        const int pj = warp == 6 ? 0 : 1;
+        if (pj < NP && beg + pj < end) {
             if (lane == 0) prefetch_tmap(&a.tm_x);
             const uint64_t pol_x = policy_evict_last();
-            long long q = beg / KT;
-            int kt = (int)(beg - q * KT);
+            long long q = (beg + pj) / KT;
+            int kt = (int)(beg + pj - q * KT);
             int xrow0 = 0;
             const float* ws_src = nullptr;
             bool fresh = true;
-            int s = 0;
+            int s = pj;
             uint32_t ph = 0;
-            uint8_t* st = ring;
-            for (long long i = beg; i < end; ++i) {
+            uint8_t* st = ring + pj * Cfg::STAGE;
+            long long tx_wait = 0;
+            DSUF_T0(tx_start);
+            for (long long i = beg + pj; i < end; i += NP) {
                 if (fresh) {
                     int rt;
                     if (EPI == EPI_DENSE) {
@@ -179,7 +200,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     ws_src = (!WMX && lane == 31) ? a.wscale_ds + (size_t)rt * KT : nullptr;
                     fresh = false;
                 }
+                DSUF_T0(tx0);
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
+                DSUF_TACC(tx_wait, tx0);
                 if (elect_one()) {
                     mbar_expect_tx(&full_bar[s], N * 128);
                     tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
@@ -193,10 +216,15 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 }
                 if (!WMX && lane == 31) cp_async4(st + Cfg::WS_OFF, ws_src + kt);
                 cp_async_arrive_noinc(&full_bar[s]);
-                st += Cfg::STAGE;
-                if (++s == S) { s = 0; st = ring; ph ^= 1; }
-                if (++kt == KT) { kt = 0; ++q; fresh = true; }
+                s += NP;
+                st += NP * Cfg::STAGE;
+                if (s >= S) { s -= S; st -= S * Cfg::STAGE; ph ^= 1; }
+                kt += NP;
+                while (kt >= KT) { kt -= KT; ++q; fresh = true; }
             }
+#ifdef DSUF_TC_TIMING
+            if (a.dbg && lane == 0 && pj == 0) a.dbg[c * 8 + 6] = clock64() - tx_start - tx_wait;
+#endif
         }
     } else if (warp == 1 || warp == 7) {
         // ================= MMA issuers (one thread each; issuer B only in the per-tile mode) =================
@@ -281,11 +309,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             }
 #endif
         }
-    } else {
-        // ================= epilogue warps 2..5 (thread = weight row of the tile = tensor-memory lane) =================
+    } else if ((warp >= 2 && warp <= 5) || (NE == 2 && warp >= 10)) {
+        // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
+        // per-tile mode with narrow token tiles: two groups of four warps take alternate tiles and add up at item end
+        const int eg = warp >= 10 ? 1 : 0;
         const int q4 = warp & 3;
         const int r = 32 * q4 + lane;
-        const int etid = tid - 64;
+        const int etid = ((warp - 2) & 3) * 32 + lane;
         const uint32_t lane_base = (uint32_t)(32 * q4) << 16;
         float acc[N];
 #pragma unroll
@@ -294,8 +324,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
         int kt = (int)(beg - q * KT);
         int rt = 0, xrow0 = 0, cnt = 0;
         bool fresh = true;
-        int gidx = 0, es = 0;
+        int gidx = 0, es = 0, items_done = 0;
         const uint8_t* est = ring;
+        long long te_wait = 0;
+        DSUF_T0(te_start);
         for (long long i = beg; i < end; ++i) {
             if (fresh) {
                 if (EPI == EPI_DENSE) {
@@ -312,9 +344,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 fresh = false;
             }
             const bool item_end = (kt + 1 == KT) || (i + 1 == end);
-            if (PER_TILE || item_end) {
+            const bool mine = NE == 1 || ((int)(i - beg) & 1) == eg;
+            if (!mine) ++gidx;
+            if ((PER_TILE || item_end) && mine) {
                 const int b = gidx % NB;
+                DSUF_T0(te0);
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
+                DSUF_TACC(te_wait, te0);
                 tc_fence_after();
                 if (SUB == 4) {
                     float v[N], r4[ACC_COLS];
@@ -338,13 +374,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     }
                 } else {
                     const float wds = (PER_TILE && !WMX) ? *(const float*)(est + Cfg::WS_OFF) : 1.0f;
+                    constexpr int CH = N < 32 ? N : 32;
 #pragma unroll
-                    for (int c0 = 0; c0 < N; c0 += 32) {
-                        float v[32];
-                        tmem_ld<32>(tm + lane_base + b * ACC_COLS + c0, v);
+                    for (int c0 = 0; c0 < N; c0 += CH) {
+                        float v[CH];
+                        tmem_ld<CH>(tm + lane_base + b * ACC_COLS + c0, v);
                         if (PER_TILE) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
+                            for (int j = 0; j < CH; j += 4) {
                                 const float4 t4 = *(const float4*)(est + Cfg::XS_OFF + 4 * (c0 + j));
                                 acc[c0 + j] = fmaf(v[j], wds * t4.x, acc[c0 + j]);
                                 acc[c0 + j + 1] = fmaf(v[j + 1], wds * t4.y, acc[c0 + j + 1]);
@@ -353,7 +390,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                             }
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) acc[c0 + j] = v[j];
+                            for (int j = 0; j < CH; ++j) acc[c0 + j] = v[j];
                         }
                     }
                 }
@@ -365,7 +402,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                 }
                 ++gidx;
             }
-            if (item_end) {
+            if (item_end && NE == 2) {
+                float* red = s_red + (items_done & 1) * (N * 128);
+                if (eg == 1) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) red[j * 128 + r] = acc[j];
+                }
+                named_bar_sync(2, 256);
+                if (eg == 0) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) acc[j] += red[j * 128 + r];
+                }
+                ++items_done;
+            }
+            if (item_end && eg == 0) {
                 // ---------------- flush the item ----------------
                 if (EPI == EPI_DENSE) {
                     const long long it0 = q * KT;
@@ -433,6 +483,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
                     for (int j = 0; j < N; ++j)
                         if (j < cnt && col < a.n_rows) o[(size_t)(xrow0 + j) * a.ldo + col] = acc[j];
                 }
+            }
+            if (item_end) {
 #pragma unroll
                 for (int j = 0; j < N; ++j) acc[j] = 0.f;
             }
@@ -440,6 +492,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tc_stream_kernel(const __grid_c
             if (++es == S) { es = 0; est = ring; }
             if (++kt == KT) { kt = 0; ++q; fresh = true; }
         }
+#ifdef DSUF_TC_TIMING
+        if (a.dbg && tid == 64) a.dbg[c * 8 + 7] = clock64() - te_start - te_wait;
+#endif
     }
     pdl_launch_dependents();
     tc_fence_before();
