@@ -246,6 +246,19 @@ def prefill_moe(pkg, ctx, torch, stack, tokens):
             "routing": "Zipf(1.1) popularity, Gumbel top-8 without replacement", "device_status": st.code}
 
 
+def finish(torch, dist, world, graph):
+    """Multi-rank exit: tearing the NCCL communicator down while a captured graph still references it can block, so the
+    ranks drop the graph, meet at a barrier and leave without the communicator's destructor."""
+    del graph
+    sys.stdout.flush()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stderr.flush()
+        os._exit(0)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -277,34 +290,60 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident throughput ----
+    # ---- the step as one CUDA graph (kernels + collectives), as the reference replays its decode step (model.rs:3956) ----
     for _ in range(args.warmup):
         stack.forward(x_dev)
+    barrier()
+    graph = None
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            stack.forward(x_dev)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                y_static = stack.forward(x_dev)
+        torch.cuda.current_stream().wait_stream(side)
+
+    def step():
+        if graph is not None:
+            graph.replay()
+            return y_static
+        return stack.forward(x_dev)
+
+    for _ in range(args.warmup):
+        step()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    events = []
+    # ---- device-resident throughput ----
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        stack.forward(x_dev, events=events)
+        step()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
-    # ---- end to end through host buffers ----
+    # ---- end to end through host buffers: H2D of the step's tokens, the step, D2H of its result ----
     for _ in range(2):
         x_dev.copy_(x_host, non_blocking=True)
-        y_host.copy_(stack.forward(x_dev), non_blocking=True)
+        y_host.copy_(step(), non_blocking=True)
     barrier()
     e0.record()
     for _ in range(args.steps):
         x_dev.copy_(x_host, non_blocking=True)
-        y = stack.forward(x_dev)
+        y = step()
         y_host.copy_(y, non_blocking=True)
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps
+    # ---- dominant kernel: the same steps launched eagerly with CUDA events around every gate/up launch ----
+    events = []
+    for _ in range(args.steps):
+        stack.forward(x_dev, events=events)
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
     st = ctx.status()
     if world > 1:
@@ -312,8 +351,7 @@ def run_ours(args):
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
         ms, ms_e2e = tms.tolist()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        finish(torch, dist, world, graph)
         return
     # ---- roofline of the dominant kernel (grouped gate/up GEMM) ----
     w13_b, w2_b = expert_bytes()
@@ -337,7 +375,7 @@ def run_ours(args):
         "dtype": "fp8_e4m3 x {fp8_e4m3, mxfp4_e2m1}, fp32 accumulate", "data": "synthetic",
         "config": {"workload": "cfg4: 4 layers x (FP8 7168x7168 dense + 256-expert top-8 MXFP4 MoE), %d-token decode step" % T,
                    "tokens": T, "hidden": H, "experts": E, "topk": TOPK, "inter": I, "layers": LAYERS,
-                   "parallelism": "ep%d" % world, "l2": "weights read per step (>= 6 GB per GPU) exceed the 126 MB L2"},
+                   "parallelism": "ep%d" % world, "step_launch": "eager" if args.no_graph else "cuda_graph", "l2": "weights read per step (>= 6 GB per GPU) exceed the 126 MB L2"},
         "e2e": {"value": round(T / (ms_e2e * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": t_local * H * 2 * world,
                 "d2h_bytes_per_step": t_local * H * 2 * world, "ms_per_step": round(ms_e2e, 4)},
         "gpu_launches": stack.count_launches() * args.steps,
@@ -362,8 +400,7 @@ def run_ours(args):
                                   "sample": "2 tokens through one layer (FP8 7168x7168 dense + top-8 of 256 MXFP4 experts), scalar C "
                                             "oracle with OpenMP (%.1f s), extrapolated to %d layers" % (dt, LAYERS)}
     print(json.dumps(result))
-    if world > 1:
-        dist.destroy_process_group()
+    finish(torch, dist, world, graph)
 
 
 def main():
@@ -374,6 +411,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--pdl", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--act-mode", default="ds", choices=["ds", "mx"], help="scale geometry: ds = 1x128 fp32 (benchmark configs), mx = 1x32 UE8M0 (reference semantics)")
     ap.add_argument("--quick", action="store_true", help="shorter GEMV sweep")
     ap.add_argument("--skip-sub", action="store_true", help="main line only")

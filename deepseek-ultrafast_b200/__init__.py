@@ -290,11 +290,13 @@ class MoePlan:
                             p, n_exp, tile_rows, self.max_tiles)
 
 
-def moe_route_tokens(ctx, score_fn, scores, bias, topk, route_scale=1.0):
+def moe_route_tokens(ctx, score_fn, scores, bias, topk, route_scale=1.0, ids=None, w=None):
     t = ctx.torch
     tok, n_exp = scores.shape
-    ids = t.empty((tok, topk), dtype=t.int32, device=scores.device)
-    w = t.empty((tok, topk), dtype=t.float32, device=scores.device)
+    if ids is None:
+        ids = t.empty((tok, topk), dtype=t.int32, device=scores.device)
+    if w is None:
+        w = t.empty((tok, topk), dtype=t.float32, device=scores.device)
     ctx.check(lib().dsuf_moe_route(ctx.h, ctx.stream(), score_fn, scores.data_ptr(), bias.data_ptr() if bias is not None else 0,
                                    tok, n_exp, topk, route_scale, ids.data_ptr(), w.data_ptr()))
     return ids, w

@@ -4,14 +4,19 @@ Sharding (world size W, rank r):
     tokens   data parallel: rank r owns rows [r*T/W, (r+1)*T/W) of every activation
     dense    K-sharded FP8 projection: rank r holds W_dense[:, r*H/W:(r+1)*H/W]; partial products are summed across ranks
     experts  rank r owns experts [r*E/W, (r+1)*E/W)
-Per layer, four fixed-size collectives, none of which needs a host-side count (so the step stays graph-capturable):
-    all_gather(x)            every rank sees all T token rows for its K-slice of the dense projection
-    reduce_scatter(partial)  the tensor-parallel all-reduce, split so each rank keeps only its own token rows
-    all_gather(h, ids, w)    dispatch: token rows + routing to the expert owners (a token travels once per rank)
-    reduce_scatter(y)        combine: per-rank partial sums over local experts back to the token owners
-The last two are the dense, padded form of the dispatch/combine all-to-all: at decode sizes (64 tokens, top-8 of 256
-over <= 8 ranks) a token reaches 5.25 of 8 ranks on average, so padding costs < 40 % of a sub-megabyte message and
-removes the count exchange.  The reference has no expert parallelism (tensor parallel + its own push all-reduce,
+Per layer, two fixed-size collectives, neither of which needs a host-side count (so the step stays graph-capturable):
+    all_reduce(dense partials)   the tensor-parallel all-reduce of the K-sharded projection; every rank ends up with all
+                                 T rows of h, which IS the dispatch: the token rows are now at every expert owner
+    all_reduce(y partials)       combine: per-rank partial sums over local experts; the result doubles as the next
+                                 layer's gathered input
+i.e. reduce-scatter + all-gather pairs of the token-parallel formulation (reduce-scatter the dense output to the token
+owners, all-gather it again for dispatch; reduce-scatter the expert output, all-gather it for the next dense layer) are
+fused into one all-reduce each.  At decode sizes (64 tokens x 7168 x bf16 = 0.9 MB) this is the dense, padded form of
+the dispatch/combine all-to-all: with top-8 of 256 experts over <= 8 ranks a token reaches 5.25 of 8 ranks on average,
+so sending every row everywhere costs < 40 % extra on a sub-megabyte message and removes the count exchange and two
+collective launches per layer.  Routing is evaluated redundantly on every rank from the gathered rows (64 x 256 scores).
+Token ownership only matters at the ends of the stack: one all-gather going in, a slice coming out.
+The reference has no expert parallelism (tensor parallel + its own push all-reduce,
 crates/kernels/cu/comm.cu:134-279); this exchange is this library's design.
 
 The compute steps are injected (``compute``) so the same exchange code runs on the CUDA kernels (stack.EpLayerStack)
@@ -33,19 +38,11 @@ class Exchange:
         self.dist.all_gather_into_tensor(out, local.contiguous(), group=self.group)
         return out
 
-    def reduce_scatter_rows(self, out, full):
-        """out [n][...] <- this rank's row block of the element-wise sum over ranks of full [W*n][...]."""
-        if self.world == 1:
-            out.copy_(full)
-            return out
-        if self.dist.get_backend(self.group) == "gloo":  # gloo has no reduce_scatter: reduce everywhere, keep own rows
-            tmp = full.clone()
-            self.dist.all_reduce(tmp, group=self.group)
-            n = out.shape[0]
-            out.copy_(tmp[self.rank * n:(self.rank + 1) * n])
-            return out
-        self.dist.reduce_scatter_tensor(out, full.contiguous(), group=self.group)
-        return out
+    def all_reduce(self, t):
+        """In-place element-wise sum over ranks."""
+        if self.world > 1:
+            self.dist.all_reduce(t, group=self.group)
+        return t
 
 
 def shard_bounds(total, world, rank):
@@ -56,18 +53,12 @@ def shard_bounds(total, world, rank):
     return rank * n, (rank + 1) * n
 
 
-def ep_layer_forward(xch, compute, x_local, bufs):
-    """One layer on one rank.  ``compute`` provides
-         dense_partial(x_all) -> partial [T][H]   (this rank's K-slice of the projection, all tokens)
-         route(h_local) -> (ids [T/W][k], w [T/W][k])
-         experts_partial(h_all, ids_all, w_all) -> y partial [T][H] over this rank's experts only
-    ``bufs`` holds preallocated tensors: x_all, partial, h_local, h_all, ids_all, w_all, y_local."""
-    x_all = xch.all_gather_rows(bufs["x_all"], x_local)
-    partial = compute.dense_partial(x_all)
-    h_local = xch.reduce_scatter_rows(bufs["h_local"], partial)
-    ids, w = compute.route(h_local)
-    h_all = xch.all_gather_rows(bufs["h_all"], h_local)
-    ids_all = xch.all_gather_rows(bufs["ids_all"], ids)
-    w_all = xch.all_gather_rows(bufs["w_all"], w)
-    y_part = compute.experts_partial(h_all, ids_all, w_all)
-    return xch.reduce_scatter_rows(bufs["y_local"], y_part)
+def ep_layer_forward(xch, compute, x_all):
+    """One layer on one rank; x_all [T][H] holds ALL token rows (identical on every rank).  ``compute`` provides
+         dense_partial(x_all) -> partial [T][H]   (this rank's K-slice of the projection, all tokens; overwritten in place)
+         route(h_all) -> (ids [T][k], w [T][k])
+         experts_partial(h_all, ids, w) -> y partial [T][H] over this rank's experts only (overwritten in place)
+    Returns y [T][H], again identical on every rank."""
+    h_all = xch.all_reduce(compute.dense_partial(x_all))
+    ids, w = compute.route(h_all)
+    return xch.all_reduce(compute.experts_partial(h_all, ids, w))

@@ -3,12 +3,9 @@ FFN (route -> plan -> gather+quant -> gate/up+SwiGLU -> quant -> down -> unpermu
 
 Single GPU: every expert is local.  Several GPUs (one process each, torch.distributed over NCCL): experts are
 sharded world-ways (rank r owns experts [r*E/W, (r+1)*E/W)), tokens are data parallel (rank r owns T/W of them);
-per layer the exchanges are
-    all-gather(x)                   tokens -> every rank, input of the K-sharded dense projection
-    reduce-scatter(dense partials)  the two halves of the tensor-parallel all-reduce (cf. comm_push2,
-                                    crates/kernels/cu/comm.cu:323-531)
-    all-to-all(dispatch)            FP8 token rows + scales + (expert, weight) to the ranks owning their experts
-    all-to-all(combine)             per-(token, rank) bf16 partial sums back to the token's owner
+per layer the exchanges are two all-reduces of the [tokens][hidden] bf16 activations (ep.py): the tensor-parallel sum
+of the K-sharded dense projection, which also delivers every token row to every expert owner (dispatch), and the sum of
+the per-rank expert outputs (combine), which also is the next layer's gathered input.
 The reference is tensor-parallel only and combines with its own push all-reduce (cu/comm.cu:134-279); the
 expert-parallel exchange here is this library's design.
 """
@@ -97,17 +94,17 @@ class _KernelCompute:
             gemm_fp8(ctx, w, s.xq[r0:r0 + m], s.xs[r0:r0 + m], m, s.partial[r0:r0 + m])
         return s.partial
 
-    def route(self, h_local):
+    def route(self, h_all):
         s = self.s
-        return moe_route_tokens(s.ctx, SCORE_SOFTMAX, s.logits[self.l][s.t0:s.t1], None, s.cfg.topk)
+        return moe_route_tokens(s.ctx, SCORE_SOFTMAX, s.logits[self.l], None, s.cfg.topk, ids=s.ids, w=s.w)
 
     def experts_partial(self, h_all, ids_all, w_all):
         s = self.s
-        return s.moe[self.l].forward(h_all, ids_all, w_all, s.y_part)
+        return s.moe[self.l].forward(h_all, ids_all, w_all, s.y_part[self.l & 1])
 
 
 class EpLayerStack:
-    """The layer stack on `world` GPUs, one process each (see ep.py for the sharding and the four exchanges)."""
+    """The layer stack on `world` GPUs, one process each (see ep.py for the sharding and the exchanges)."""
 
     def __init__(self, ctx, cfg, dist, rank, world):
         from . import ep
@@ -135,31 +132,26 @@ class EpLayerStack:
             g = t.Generator(device=dev).manual_seed(cfg.seed + 1000 * l + 4)   # same logits on every rank
             self.logits.append(t.randn(T, E, generator=g, device=dev, dtype=t.float32))
         blk = 32 if cfg.dense_mode == MODE_MX else 128
-        tl = self.t1 - self.t0
         self.xq = t.empty((T, kloc), dtype=t.uint8, device=dev)
         self.xs = t.empty((T, kloc // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
         self.partial = t.empty((T, H), dtype=t.bfloat16, device=dev)
-        self.y_part = t.empty((T, H), dtype=t.bfloat16, device=dev)
-        self.bufs = {"x_all": t.empty((T, H), dtype=t.bfloat16, device=dev),
-                     "h_local": t.empty((tl, H), dtype=t.bfloat16, device=dev),
-                     "h_all": t.empty((T, H), dtype=t.bfloat16, device=dev),
-                     "ids_all": t.empty((T, cfg.topk), dtype=t.int32, device=dev),
-                     "w_all": t.empty((T, cfg.topk), dtype=t.float32, device=dev),
-                     "y_local": None}
-        self.y = [t.empty((tl, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
+        self.y_part = [t.empty((T, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
+        self.x_all = t.empty((T, H), dtype=t.bfloat16, device=dev)
+        self.ids = t.empty((T, cfg.topk), dtype=t.int32, device=dev)
+        self.w = t.empty((T, cfg.topk), dtype=t.float32, device=dev)
         self.compute = [_KernelCompute(self, l) for l in range(cfg.layers)]
 
     def logits_full(self, l):
         return self.logits[l]
 
     def forward(self, x_local, events=None):
+        """x_local bf16 [T/W][H] (this rank's tokens) -> this rank's rows of the stack output."""
         from . import ep
-        cur = x_local
+        cur = self.xch.all_gather_rows(self.x_all, x_local)
         for l in range(self.cfg.layers):
-            self.bufs["y_local"] = self.y[l & 1]
             self.moe[l].events = events
-            cur = ep.ep_layer_forward(self.xch, self.compute[l], cur, self.bufs)
-        return cur
+            cur = ep.ep_layer_forward(self.xch, self.compute[l], cur)
+        return cur[self.t0:self.t1]
 
     def count_launches(self):
         cfg = self.cfg
