@@ -6,7 +6,8 @@
 //
 // The reference builds its prefill plan in ONE 1024-thread CTA with shared-memory atomics (order inside an
 // expert depends on timing) and rebuilds the decode plan inside every GEMV CTA.  Here the plan is built once,
-// by a three-phase stable counting sort that scales over CTAs, and every consumer (decode or prefill) reads it.
+// by a stable counting sort (one fused launch for decode-sized plans, three phases that scale over CTAs above
+// that), and every consumer (decode or prefill) reads it.
 #include "internal.h"
 
 namespace dsuf {
@@ -17,6 +18,7 @@ constexpr int ROUTE_MAX_PER_LANE = 16;  // n_exp <= 512
 __global__ void __launch_bounds__(256) route_kernel(int score_fn, const float* scores, const float* bias, int t, int n_exp,
                                                     int topk, float route_scale, int* ids, float* w) {
     pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
     const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (tok >= t) return;
     float sc[ROUTE_MAX_PER_LANE], key[ROUTE_MAX_PER_LANE];
@@ -108,9 +110,40 @@ struct PlanArgs {
     DevStatus* status;
 };
 
+// Exclusive scan of one value per thread over a block of up to 1024 threads (two values scanned together).
+__device__ __forceinline__ void block_exscan2(int a, int b, int& ea, int& eb, int& ta, int& tb, int* s_wa, int* s_wb) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    int ia = a, ib = b;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int ua = __shfl_up_sync(0xffffffffu, ia, o), ub = __shfl_up_sync(0xffffffffu, ib, o);
+        if (lane >= o) { ia += ua; ib += ub; }
+    }
+    if (lane == 31) { s_wa[warp] = ia; s_wb[warp] = ib; }
+    __syncthreads();
+    if (warp == 0) {
+        int wa = lane < nw ? s_wa[lane] : 0, wb = lane < nw ? s_wb[lane] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int ua = __shfl_up_sync(0xffffffffu, wa, o), ub = __shfl_up_sync(0xffffffffu, wb, o);
+            if (lane >= o) { wa += ua; wb += ub; }
+        }
+        s_wa[lane] = wa;  // inclusive warp totals
+        s_wb[lane] = wb;
+    }
+    __syncthreads();
+    const int ba = warp ? s_wa[warp - 1] : 0, bb = warp ? s_wb[warp - 1] : 0;
+    ea = ba + ia - a;
+    eb = bb + ib - b;
+    ta = s_wa[nw - 1];
+    tb = s_wb[nw - 1];
+    __syncthreads();
+}
+
 // Phase A: per-block histogram and each pair's stable rank inside its block.
 __global__ void __launch_bounds__(PLAN_BLOCK) plan_count_kernel(const PlanArgs a) {
     pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
     __shared__ unsigned short warp_hist[32][PLAN_MAX_EXP];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int i = tid; i < 32 * PLAN_MAX_EXP; i += PLAN_BLOCK) (&warp_hist[0][0])[i] = 0;
@@ -141,7 +174,8 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_count_kernel(const PlanArgs a
 // Phase B (one CTA): scan blocks per expert, scan experts, emit the tile list.
 __global__ void __launch_bounds__(PLAN_MAX_EXP) plan_scan_kernel(const PlanArgs a) {
     pdl_wait();
-    __shared__ int s_cnt[PLAN_MAX_EXP], s_off[PLAN_MAX_EXP + 1], s_toff[PLAN_MAX_EXP + 1];
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+    __shared__ int s_cnt[32], s_off[32];
     const int e = threadIdx.x;
     int total = 0;
     if (e < a.n_exp) {
@@ -151,34 +185,28 @@ __global__ void __launch_bounds__(PLAN_MAX_EXP) plan_scan_kernel(const PlanArgs 
             total += c;
         }
     }
-    s_cnt[e] = e < a.n_exp ? total : 0;
-    __syncthreads();
+    const int cnt = e < a.n_exp ? total : 0;
+    const int ntile = (cnt + a.tile_rows - 1) / a.tile_rows;
+    int off, toff, rows, tiles_total;
+    block_exscan2(cnt, ntile, off, toff, rows, tiles_total, s_cnt, s_off);
     if (e == 0) {
-        int run = 0, trun = 0;
-        for (int x = 0; x < a.n_exp; ++x) {
-            s_off[x] = run;
-            s_toff[x] = trun;
-            run += s_cnt[x];
-            trun += (s_cnt[x] + a.tile_rows - 1) / a.tile_rows;
-        }
-        s_off[a.n_exp] = run;
-        s_toff[a.n_exp] = trun;
-        a.ntiles[0] = trun <= a.max_tiles ? trun : a.max_tiles;
-        a.ntiles[1] = run;
-        if (trun > a.max_tiles) report(a.status, DEVERR_BAD_PLAN, 2, trun);
+        a.expert_off[a.n_exp] = rows;
+        a.ntiles[0] = tiles_total <= a.max_tiles ? tiles_total : a.max_tiles;
+        a.ntiles[1] = rows;
+        if (tiles_total > a.max_tiles) report(a.status, DEVERR_BAD_PLAN, 2, tiles_total);
     }
-    __syncthreads();
-    if (e <= a.n_exp) a.expert_off[e] = s_off[e];
     if (e < a.n_exp) {
-        int ti = s_toff[e];
-        for (int r0 = 0; r0 < s_cnt[e]; r0 += a.tile_rows, ++ti)
-            if (ti < a.max_tiles) a.tiles[ti] = make_int4(e, s_off[e] + r0, min(a.tile_rows, s_cnt[e] - r0), 0);
+        a.expert_off[e] = off;
+        int ti = toff;
+        for (int r0 = 0; r0 < cnt; r0 += a.tile_rows, ++ti)
+            if (ti < a.max_tiles) a.tiles[ti] = make_int4(e, off + r0, min(a.tile_rows, cnt - r0), 0);
     }
 }
 
 // Phase C: place every pair.
 __global__ void __launch_bounds__(PLAN_BLOCK) plan_place_kernel(const PlanArgs a) {
     pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
     const int i = blockIdx.x * PLAN_BLOCK + threadIdx.x;
     if (i >= a.p) return;
     const int lr = a.local_rank[i];
@@ -188,6 +216,63 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_place_kernel(const PlanArgs a
     a.row_pair[row] = i;
     a.pair_row[i] = row;
     a.row_w[row] = a.w[i];
+}
+
+
+// Decode-sized plans (all pairs fit one block): histogram, scans, tile list and placement in ONE launch.
+// Same result as the three-phase path, bit for bit (the order inside an expert is the pair order either way).
+__global__ void __launch_bounds__(PLAN_BLOCK) plan_small_kernel(const PlanArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+    __shared__ unsigned short warp_hist[32][PLAN_MAX_EXP];
+    __shared__ int s_off[PLAN_MAX_EXP + 1], s_wa[32], s_wb[32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < 32 * PLAN_MAX_EXP; i += PLAN_BLOCK) (&warp_hist[0][0])[i] = 0;
+    __syncthreads();
+    int e = -1;
+    if (tid < a.p) {
+        e = a.ids[tid] - a.e_lo;
+        if (e < 0 || e >= a.n_exp) e = -1;
+    }
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank_in_warp == 0) warp_hist[warp][e] = (unsigned short)__popc(peers);
+    __syncthreads();
+    int cnt = 0;
+    if (tid < a.n_exp) {
+        for (int wv = 0; wv < 32; ++wv) {
+            const int c = warp_hist[wv][tid];
+            warp_hist[wv][tid] = (unsigned short)cnt;
+            cnt += c;
+        }
+    }
+    const int ntile = (cnt + a.tile_rows - 1) / a.tile_rows;
+    int off, toff, rows, tiles_total;
+    block_exscan2(cnt, ntile, off, toff, rows, tiles_total, s_wa, s_wb);
+    if (tid < a.n_exp) {
+        s_off[tid] = off;
+        a.expert_off[tid] = off;
+        int ti = toff;
+        for (int r0 = 0; r0 < cnt; r0 += a.tile_rows, ++ti)
+            if (ti < a.max_tiles) a.tiles[ti] = make_int4(tid, off + r0, min(a.tile_rows, cnt - r0), 0);
+    }
+    if (tid == 0) {
+        a.expert_off[a.n_exp] = rows;
+        a.ntiles[0] = tiles_total <= a.max_tiles ? tiles_total : a.max_tiles;
+        a.ntiles[1] = rows;
+        if (tiles_total > a.max_tiles) report(a.status, DEVERR_BAD_PLAN, 2, tiles_total);
+    }
+    __syncthreads();
+    if (tid < a.p) {
+        if (e < 0) {
+            a.pair_row[tid] = -1;
+        } else {
+            const int row = s_off[e] + warp_hist[warp][e] + rank_in_warp;
+            a.row_pair[row] = tid;
+            a.pair_row[tid] = row;
+            a.row_w[row] = a.w[tid];
+        }
+    }
 }
 
 int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float* w, int e_lo, const dsuf_moe_plan* plan) {
@@ -200,6 +285,7 @@ int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float*
     a.block_cnt = (int*)plan->scratch;
     a.local_rank = a.block_cnt + (size_t)a.nblk * a.n_exp;
     a.status = ctx->dev_status;
+    if (a.nblk <= 1) return launch(ctx, stream, plan_small_kernel, dim3(1), dim3(PLAN_BLOCK), 0, a);
     int rc = launch(ctx, stream, plan_count_kernel, dim3(a.nblk > 0 ? a.nblk : 1), dim3(PLAN_BLOCK), 0, a);
     if (rc) return rc;
     rc = launch(ctx, stream, plan_scan_kernel, dim3(1), dim3(PLAN_MAX_EXP), 0, a);
@@ -212,6 +298,7 @@ int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float*
 __global__ void __launch_bounds__(256) unpermute_kernel(const int* pair_row, const float* yrows, const bf16* shared, int topk,
                                                         int h, bf16* out, int ldo) {
     pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
     const int tok = blockIdx.x;
     __shared__ int rows[16];
     if (threadIdx.x < topk) rows[threadIdx.x] = pair_row[(size_t)tok * topk + threadIdx.x];

@@ -26,6 +26,7 @@ struct QuantArgs {
 template <int MODE>
 __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
     pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
     const int row = blockIdx.x;
     const int k0 = (blockIdx.y * 256 + threadIdx.x) * 8;
     const bool live = k0 < a.k;
@@ -57,7 +58,6 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
         out.x = f32x4_to_e4m3x4(__fdiv_rn(v[0], sc), __fdiv_rn(v[1], sc), __fdiv_rn(v[2], sc), __fdiv_rn(v[3], sc));
         out.y = f32x4_to_e4m3x4(__fdiv_rn(v[4], sc), __fdiv_rn(v[5], sc), __fdiv_rn(v[6], sc), __fdiv_rn(v[7], sc));
     }
-    pdl_launch_dependents();
     if (!live) return;
     const bool writes_scale = (threadIdx.x & (LANES - 1)) == 0;
     const int nfan = a.fanout > 0 ? a.fanout : 1;

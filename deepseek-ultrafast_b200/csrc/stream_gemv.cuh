@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
     }
     __syncthreads();
     pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
 
     // ---- this CTA's span of the global tile sequence ----
     long long beg, end;
@@ -362,7 +363,6 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
             }
         }
     }
-    pdl_launch_dependents();
 }
 
 }  // namespace dsuf

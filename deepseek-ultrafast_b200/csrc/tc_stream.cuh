@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     tc_fence_after();
     const uint32_t tm = s_tmem;
     pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
 
     // ---- this CTA's span of the global tile sequence (see stream_gemv.cuh) ----
     long long beg, end;
@@ -496,7 +497,6 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         if (a.dbg && tid == 64) a.dbg[c * 8 + 7] = clock64() - te_start - te_wait;
 #endif
     }
-    pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

@@ -72,8 +72,9 @@ class LayerStack:
         cfg = self.cfg
         slab = 64 if self.ctx.tcgen05 else 16
         slabs = (cfg.tokens + slab - 1) // slab
-        # act_quant + dense slabs + route + plan(3) + gather + w13 + quant + w2 + unpermute
-        return cfg.layers * (1 + slabs + 1 + 3 + 1 + 1 + 1 + 1 + 1)
+        # act_quant + dense slabs + route + plan (1 launch up to 1024 pairs, else 3) + gather + w13 + quant + w2 + unpermute
+        plan = 1 if cfg.tokens * cfg.topk <= 1024 else 3
+        return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1)
 
 
 class _KernelCompute:
@@ -157,4 +158,5 @@ class EpLayerStack:
         cfg = self.cfg
         slab = 64 if self.ctx.tcgen05 else 16
         slabs = (cfg.tokens + slab - 1) // slab
-        return cfg.layers * (1 + slabs + 1 + 3 + 1 + 1 + 1 + 1 + 1)
+        plan = 1 if cfg.tokens * cfg.topk <= 1024 else 3
+        return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1)
