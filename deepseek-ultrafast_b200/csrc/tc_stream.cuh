@@ -33,8 +33,6 @@ struct TcCfg {
     static constexpr int B_OFF = A_BYTES;
     static constexpr int SFA_OFF = B_OFF + B_BYTES;  // weight scale atom (512)
     static constexpr int SFB_OFF = SFA_OFF + 512;    // MX activations: activation scale atom (512)
-    static constexpr int XS_OFF = SFA_OFF + 512;     // DS activations: N fp32 scales (same bytes as the atom)
-    static constexpr int WS_OFF = XS_OFF + 4 * N;    // DS weights: fp32 scale of the tile (N <= 64 there)
     static constexpr int STAGE = A_BYTES + B_BYTES + 1024;
     static constexpr int NE = N <= 16 ? 2 : 1;        // epilogue warp groups (per-tile mode: alternate tiles)
     static constexpr int RED_BYTES = NE == 2 ? 2 * N * 128 * 4 : 0;  // static shared memory of the group combine
@@ -43,8 +41,9 @@ struct TcCfg {
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
     static constexpr int SUB = 1;                    // sub-accumulators per ring entry (4 = one per K=32 step; measured: no gain)
-    static constexpr int ACC_COLS = SUB * N < 32 ? 32 : SUB * N;
-    static constexpr int NB = ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
+    static constexpr int ACC_COLS = SUB * N;
+    static constexpr int NB = ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
+    static constexpr int XS_ENTRY = 4 * N + 16;      // per-tile fp32 scales: N activation scales + the weight scale, one entry per accumulator
     static constexpr int NP = N <= 64 ? 2 : 1;        // producer warps per kind (weights / activations), alternate tiles
     static constexpr int THREADS = 256 + 64 * (NP - 1) + 128 * (NE - 1);  // warps 8, 9: second producers; 10-13: second epilogue group
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
@@ -73,6 +72,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     static_assert((NB & (NB - 1)) == 0, "accumulator ring size must be a power of two");
     __shared__ uint32_t s_tmem;
     __shared__ int s_flag;
+    __shared__ __align__(16) uint8_t s_xs[NB * Cfg::XS_ENTRY];  // DS scales travel with the accumulator, not with the stage
     __shared__ float s_red[Cfg::NE == 2 ? 2 * N * 128 : 1];  // second epilogue group -> first, double buffered by item
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
             mbar_init(&full_bar[s], 2 + 32);  // weight expect_tx + activation expect_tx + 32 cp.async lanes
-            mbar_init(&empty_bar[s], PER_TILE ? 4 : 1);  // epilogue warps (they read the stage's scales) / MMA commit
+            mbar_init(&empty_bar[s], 1);  // tcgen05.commit: the tensor core has finished reading the stage
         }
         for (int b = 0; b < NB; ++b) {
             mbar_init(&tfull_bar[b], 1);
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 while (kt >= KT) { kt -= KT; ++q; fresh = true; }
             }
 #ifdef DSUF_TC_TIMING
-            if (a.dbg && lane == 0 && pj == 0) a.dbg[c * 8 + 5] = clock64() - tw_start - tw_wait;
+
 #endif
         }
     } else if (warp == 6 || warp == 9) {
@@ -209,13 +209,20 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
                 }
                 __syncwarp();
+                uint8_t* xe = nullptr;
+                if (PER_TILE) {
+                    // fp32 scales go to the entry of the accumulator this tile will use, free once the epilogue released it
+                    const int tn = (int)(i - beg), tb = tn & (NB - 1);
+                    if (tn >= NB && !dead && !mbar_wait(&tempty_bar[tb], ((tn / NB) - 1) & 1, a.status, KID_TC, 6)) dead = true;
+                    xe = s_xs + tb * Cfg::XS_ENTRY;
+                }
 #pragma unroll
                 for (int n = lane; n < N; n += 32) {
                     // MX: the token's 4 UE8M0 bytes go to its row of the scale atom; DS: its fp32 scale
                     const uint32_t* src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + n, a.x_rows - 1) * KT + kt;
-                    cp_async4(AMX ? st + Cfg::SFB_OFF + (n & 31) * 16 + (n >> 5) * 4 : st + Cfg::XS_OFF + 4 * n, src);
+                    cp_async4(AMX ? st + Cfg::SFB_OFF + (n & 31) * 16 + (n >> 5) * 4 : xe + 4 * n, src);
                 }
-                if (!WMX && lane == 31) cp_async4(st + Cfg::WS_OFF, ws_src + kt);
+                if (!WMX && lane == 31) cp_async4(xe + 4 * N, ws_src + kt);
                 cp_async_arrive_noinc(&full_bar[s]);
                 s += NP;
                 st += NP * Cfg::STAGE;
@@ -224,7 +231,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 while (kt >= KT) { kt -= KT; ++q; fresh = true; }
             }
 #ifdef DSUF_TC_TIMING
-            if (a.dbg && lane == 0 && pj == 0) a.dbg[c * 8 + 6] = clock64() - tx_start - tx_wait;
+
 #endif
         }
     } else if (warp == 1 || warp == 7) {
@@ -290,8 +297,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     for (int kc = 0; kc < 4; ++kc)
                         tc_mma_mx(d + (SUB == 4 ? kc * N : 0), ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
                                   tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && (SUB == 4 || kc == 0)) ? 0u : 1u);
-                    // per-tile mode: the epilogue warps release the stage after reading its scales
-                    if (!PER_TILE) tc_commit(&empty_bar[s]);
+                    tc_commit(&empty_bar[s]);
                     if (group_end) tc_commit(&tfull_bar[b]);
                 }
                 __syncwarp();
@@ -305,7 +311,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             }
 #ifdef DSUF_TC_TIMING
             if (a.dbg && j == 0 && lane == 0) {
-                a.dbg[c * 8 + 0] = t_full; a.dbg[c * 8 + 1] = t_tempty; a.dbg[c * 8 + 2] = t_issue;
+                a.dbg[c * 8 + 0] = t_full; a.dbg[c * 8 + 2] = t_issue;
                 a.dbg[c * 8 + 3] = clock64() - t_start; a.dbg[c * 8 + 4] = (end - beg + NI - 1) / NI;
             }
 #endif
@@ -327,7 +333,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         bool fresh = true;
         int gidx = 0, es = 0, items_done = 0;
         const uint8_t* est = ring;
-        long long te_wait = 0;
+        long long te_wait = 0, te_ld = 0, te_arr = 0, te_flush = 0;
         DSUF_T0(te_start);
         for (long long i = beg; i < end; ++i) {
             if (fresh) {
@@ -352,6 +358,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 DSUF_T0(te0);
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
                 DSUF_TACC(te_wait, te0);
+                DSUF_T0(tl0);
                 tc_fence_after();
                 if (SUB == 4) {
                     float v[N], r4[ACC_COLS];
@@ -360,10 +367,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 #pragma unroll
                     for (int j = 0; j < N; ++j) v[j] = (r4[j] + r4[N + j]) + (r4[2 * N + j] + r4[3 * N + j]);
                     if (PER_TILE) {
-                        const float wds = WMX ? 1.0f : *(const float*)(est + Cfg::WS_OFF);
+                        const float wds = WMX ? 1.0f : *(const float*)(s_xs + b * Cfg::XS_ENTRY + 4 * N);
 #pragma unroll
                         for (int j = 0; j < N; j += 4) {
-                            const float4 t4 = *(const float4*)(est + Cfg::XS_OFF + 4 * j);
+                            const float4 t4 = *(const float4*)(s_xs + b * Cfg::XS_ENTRY + 4 * j);
                             acc[j] = fmaf(v[j], wds * t4.x, acc[j]);
                             acc[j + 1] = fmaf(v[j + 1], wds * t4.y, acc[j + 1]);
                             acc[j + 2] = fmaf(v[j + 2], wds * t4.z, acc[j + 2]);
@@ -374,7 +381,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         for (int j = 0; j < N; ++j) acc[j] = v[j];
                     }
                 } else {
-                    const float wds = (PER_TILE && !WMX) ? *(const float*)(est + Cfg::WS_OFF) : 1.0f;
+                    const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + b * Cfg::XS_ENTRY + 4 * N) : 1.0f;
                     constexpr int CH = N < 32 ? N : 32;
 #pragma unroll
                     for (int c0 = 0; c0 < N; c0 += CH) {
@@ -383,7 +390,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         if (PER_TILE) {
 #pragma unroll
                             for (int j = 0; j < CH; j += 4) {
-                                const float4 t4 = *(const float4*)(est + Cfg::XS_OFF + 4 * (c0 + j));
+                                const float4 t4 = *(const float4*)(s_xs + b * Cfg::XS_ENTRY + 4 * (c0 + j));
                                 acc[c0 + j] = fmaf(v[j], wds * t4.x, acc[c0 + j]);
                                 acc[c0 + j + 1] = fmaf(v[j + 1], wds * t4.y, acc[c0 + j + 1]);
                                 acc[c0 + j + 2] = fmaf(v[j + 2], wds * t4.z, acc[c0 + j + 2]);
@@ -395,14 +402,17 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         }
                     }
                 }
+                DSUF_TACC(te_ld, tl0);
+                DSUF_T0(ta0);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&tempty_bar[b]);
-                    if (PER_TILE) mbar_arrive(&empty_bar[es]);  // MMAs of this stage are complete and its scales are read
                 }
                 ++gidx;
+                DSUF_TACC(te_arr, ta0);
             }
+            DSUF_T0(tf0);
             if (item_end && NE == 2) {
                 float* red = s_red + (items_done & 1) * (N * 128);
                 if (eg == 1) {
@@ -489,12 +499,13 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 #pragma unroll
                 for (int j = 0; j < N; ++j) acc[j] = 0.f;
             }
+            DSUF_TACC(te_flush, tf0);
             est += Cfg::STAGE;
             if (++es == S) { es = 0; est = ring; }
             if (++kt == KT) { kt = 0; ++q; fresh = true; }
         }
 #ifdef DSUF_TC_TIMING
-        if (a.dbg && tid == 64) a.dbg[c * 8 + 7] = clock64() - te_start - te_wait;
+        if (a.dbg && tid == 64) { a.dbg[c * 8 + 7] = clock64() - te_start - te_wait; a.dbg[c * 8 + 5] = te_ld; a.dbg[c * 8 + 6] = te_arr; a.dbg[c * 8 + 1] = te_flush; }
 #endif
     }
     tc_fence_before();
