@@ -65,7 +65,8 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
     constexpr int NI = PER_TILE ? 2 : 1;    // MMA-issuing warps
     constexpr int NP = Cfg::NP;
-    constexpr int NE = (PER_TILE && Cfg::NE == 2) ? 2 : 1;  // epilogue groups actually working
+    // epilogue groups actually working: the second group pays off where tiles are 8.7 KB (FP4 experts), not for dense FP8
+    constexpr int NE = (PER_TILE && Cfg::NE == 2 && EPI != EPI_DENSE) ? 2 : 1;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[NB], tempty_bar[NB];
