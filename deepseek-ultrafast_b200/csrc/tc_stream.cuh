@@ -45,7 +45,7 @@ struct TcCfg {
     static constexpr int NB = ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
     static constexpr int XS_ENTRY = 4 * N + 16;      // per-tile fp32 scales: N activation scales + the weight scale, one entry per accumulator
     static constexpr int NP = N <= 64 ? 2 : 1;        // producer warps per kind (weights / activations), alternate tiles
-    static constexpr int THREADS = 256 + 64 * (NP - 1) + 128 * (NE - 1);  // warps 8, 9: second producers; 10-13: second epilogue group
+    static constexpr int THREADS = 256 + 64 * (NP - 1) + 128;  // second producers (NP == 2), then the second epilogue group
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
     static_assert(NB * ACC_COLS <= 256 && STAGES >= 4 && N <= 128, "tensor-memory / shared-memory budget");
 };
@@ -67,6 +67,11 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     constexpr int NP = Cfg::NP;
     // epilogue groups actually working: the second group pays off where tiles are 8.7 KB (FP4 experts), not for dense FP8
     constexpr int NE = (PER_TILE && Cfg::NE == 2 && EPI != EPI_DENSE) ? 2 : 1;
+    // wide token tiles: the two epilogue groups split the token COLUMNS of every accumulator instead
+    constexpr bool CSPLIT = N >= 32;
+    constexpr int NC = CSPLIT ? N / 2 : N;            // columns per epilogue thread
+    constexpr int EG1 = 8 + 2 * (NP - 1);             // first warp of the second epilogue group
+    constexpr int EPI_BAR = CSPLIT ? 256 : 128;       // threads meeting at the dense stream-K fix-up
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[NB], tempty_bar[NB];
@@ -92,7 +97,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         }
         for (int b = 0; b < NB; ++b) {
             mbar_init(&tfull_bar[b], 1);
-            mbar_init(&tempty_bar[b], 4);
+            mbar_init(&tempty_bar[b], CSPLIT ? 8 : 4);
         }
         mbar_fence_init();
     }
@@ -117,7 +122,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         end = ((long long)(c + 1) * q / G) * KT;
     }
 
-    if (warp == 0 || warp == 8) {
+    if (warp == 0 || (NP == 2 && warp == 8)) {
         // ================= weight producers (warp 8 takes the odd tiles when NP == 2): tile codes + scale atom =================
         const int pj = warp == 0 ? 0 : 1;
         // The whole warp runs the loop (so every value stays warp-uniform and the TMA descriptors live in uniform
@@ -172,7 +177,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 
 #endif
         }
-    } else if (warp == 6 || warp == 9) {
+    } else if (warp == 6 || (NP == 2 && warp == 9)) {
         // ================= activation producers: token rows by TMA, their block scales by 4-byte async copies =================
         const int pj = warp == 6 ? 0 : 1;
         if (pj < NP && beg + pj < end) {
@@ -317,17 +322,18 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             }
 #endif
         }
-    } else if ((warp >= 2 && warp <= 5) || (NE == 2 && warp >= 10)) {
+    } else if ((warp >= 2 && warp <= 5) || ((NE == 2 || CSPLIT) && warp >= EG1)) {
         // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
         // per-tile mode with narrow token tiles: two groups of four warps take alternate tiles and add up at item end
-        const int eg = warp >= 10 ? 1 : 0;
+        const int eg = warp >= EG1 ? 1 : 0;
+        const int cb = CSPLIT ? eg * NC : 0;              // first token column this thread owns
         const int q4 = warp & 3;
         const int r = 32 * q4 + lane;
-        const int etid = ((warp - 2) & 3) * 32 + lane;
+        const int etid = (warp >= EG1 ? warp - EG1 : warp - 2) * 32 + lane;
         const uint32_t lane_base = (uint32_t)(32 * q4) << 16;
-        float acc[N];
+        float acc[NC];
 #pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] = 0.f;
+        for (int j = 0; j < NC; ++j) acc[j] = 0.f;
         long long q = beg / KT;
         int kt = (int)(beg - q * KT);
         int rt = 0, xrow0 = 0, cnt = 0;
@@ -361,37 +367,17 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 DSUF_TACC(te_wait, te0);
                 DSUF_T0(tl0);
                 tc_fence_after();
-                if (SUB == 4) {
-                    float v[N], r4[ACC_COLS];
-#pragma unroll
-                    for (int c0 = 0; c0 < ACC_COLS; c0 += 32) tmem_ld<32>(tm + lane_base + b * ACC_COLS + c0, r4 + c0);
-#pragma unroll
-                    for (int j = 0; j < N; ++j) v[j] = (r4[j] + r4[N + j]) + (r4[2 * N + j] + r4[3 * N + j]);
-                    if (PER_TILE) {
-                        const float wds = WMX ? 1.0f : *(const float*)(s_xs + b * Cfg::XS_ENTRY + 4 * N);
-#pragma unroll
-                        for (int j = 0; j < N; j += 4) {
-                            const float4 t4 = *(const float4*)(s_xs + b * Cfg::XS_ENTRY + 4 * j);
-                            acc[j] = fmaf(v[j], wds * t4.x, acc[j]);
-                            acc[j + 1] = fmaf(v[j + 1], wds * t4.y, acc[j + 1]);
-                            acc[j + 2] = fmaf(v[j + 2], wds * t4.z, acc[j + 2]);
-                            acc[j + 3] = fmaf(v[j + 3], wds * t4.w, acc[j + 3]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < N; ++j) acc[j] = v[j];
-                    }
-                } else {
+                {
                     const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + b * Cfg::XS_ENTRY + 4 * N) : 1.0f;
-                    constexpr int CH = N < 32 ? N : 32;
+                    constexpr int CH = NC < 32 ? NC : 32;
 #pragma unroll
-                    for (int c0 = 0; c0 < N; c0 += CH) {
+                    for (int c0 = 0; c0 < NC; c0 += CH) {
                         float v[CH];
-                        tmem_ld<CH>(tm + lane_base + b * ACC_COLS + c0, v);
+                        tmem_ld<CH>(tm + lane_base + b * ACC_COLS + cb + c0, v);
                         if (PER_TILE) {
 #pragma unroll
                             for (int j = 0; j < CH; j += 4) {
-                                const float4 t4 = *(const float4*)(s_xs + b * Cfg::XS_ENTRY + 4 * (c0 + j));
+                                const float4 t4 = *(const float4*)(s_xs + b * Cfg::XS_ENTRY + 4 * (cb + c0 + j));
                                 acc[c0 + j] = fmaf(v[j], wds * t4.x, acc[c0 + j]);
                                 acc[c0 + j + 1] = fmaf(v[j + 1], wds * t4.y, acc[c0 + j + 1]);
                                 acc[c0 + j + 2] = fmaf(v[j + 2], wds * t4.z, acc[c0 + j + 2]);
@@ -427,40 +413,40 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 }
                 ++items_done;
             }
-            if (item_end && eg == 0) {
-                // ---------------- flush the item ----------------
+            if (item_end && (eg == 0 || CSPLIT)) {
+                // ---------------- flush the item (column-split groups each flush their own token columns) ----------------
                 if (EPI == EPI_DENSE) {
                     const long long it0 = q * KT;
                     const bool whole = beg <= it0 && end >= it0 + KT;
                     bool do_store = whole;
                     if (!whole) {
                         const int slot = (q == beg / KT) ? 0 : 1;
-                        float* pw = a.partial + ((size_t)(c * 2 + slot) * 64) * 128 + etid;
+                        float* pw = a.partial + ((size_t)(c * 2 + slot) * 64 + cb) * 128 + etid;
 #pragma unroll
-                        for (int j = 0; j < N; ++j) __stcg(pw + (size_t)j * 128, acc[j]);
+                        for (int j = 0; j < NC; ++j) __stcg(pw + (size_t)j * 128, acc[j]);
                         __threadfence();
-                        named_bar_sync(1, TC_EPI_THREADS);
+                        named_bar_sync(1, EPI_BAR);
                         const long long tot = (long long)RT * KT;
                         const int first = (int)(((it0 + 1) * G - 1) / tot);
                         const int last = (int)(((it0 + KT) * G - 1) / tot);
-                        if (etid == 0) {
+                        if (etid == 0 && eg == 0) {
                             const int old = atomicAdd(a.counters + q, 1);
                             s_flag = (old == last - first);
                             if (old == last - first) a.counters[q] = 0;  // self-resetting for the next launch
                         }
-                        named_bar_sync(1, TC_EPI_THREADS);
+                        named_bar_sync(1, EPI_BAR);
                         do_store = s_flag != 0;
-                        named_bar_sync(1, TC_EPI_THREADS);
+                        named_bar_sync(1, EPI_BAR);
                         if (do_store) {
                             __threadfence();
 #pragma unroll
-                            for (int j = 0; j < N; ++j) acc[j] = 0.f;
+                            for (int j = 0; j < NC; ++j) acc[j] = 0.f;
                             for (int cc = first; cc <= last; ++cc) {  // fixed order: independent of arrival order
                                 const long long cbeg = (long long)cc * tot / G;
                                 const int cslot = (q == cbeg / KT) ? 0 : 1;
-                                const float* pr = a.partial + ((size_t)(cc * 2 + cslot) * 64) * 128 + etid;
+                                const float* pr = a.partial + ((size_t)(cc * 2 + cslot) * 64 + cb) * 128 + etid;
 #pragma unroll
-                                for (int j = 0; j < N; ++j) acc[j] += __ldcg(pr + (size_t)j * 128);
+                                for (int j = 0; j < NC; ++j) acc[j] += __ldcg(pr + (size_t)j * 128);
                             }
                         }
                     }
@@ -468,8 +454,8 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         bf16* o = (bf16*)a.out;
                         const int row = rt * 128 + r;
 #pragma unroll
-                        for (int j = 0; j < N; ++j)
-                            if (j < cnt && row < a.n_rows) o[(size_t)j * a.ldo + row] = __float2bfloat16(acc[j] * a.alpha);
+                        for (int j = 0; j < NC; ++j)
+                            if (cb + j < cnt && row < a.n_rows) o[(size_t)(cb + j) * a.ldo + row] = __float2bfloat16(acc[j] * a.alpha);
                     }
                 } else if (EPI == EPI_W13) {
                     // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group);
@@ -478,10 +464,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     const float L = a.swiglu_limit;
                     const bool is_gate = (r & 8) == 0;
 #pragma unroll
-                    for (int j = 0; j < N; ++j) {
+                    for (int j = 0; j < NC; ++j) {
                         const float other = __shfl_xor_sync(0xffffffffu, acc[j], 8);
-                        if (is_gate && j < cnt) {
-                            const int row = xrow0 + j;
+                        if (is_gate && cb + j < cnt) {
+                            const int row = xrow0 + cb + j;
                             float gt = bf16_round(acc[j]), up = bf16_round(other);
                             if (L > 0.f) { up = fminf(fmaxf(up, -L), L); gt = fminf(gt, L); }
                             const float val = gt / (1.0f + expf(-gt)) * up * __ldg(a.row_w + row);
@@ -492,13 +478,13 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     float* o = (float*)a.out;
                     const int col = rt * 128 + r;
 #pragma unroll
-                    for (int j = 0; j < N; ++j)
-                        if (j < cnt && col < a.n_rows) o[(size_t)(xrow0 + j) * a.ldo + col] = acc[j];
+                    for (int j = 0; j < NC; ++j)
+                        if (cb + j < cnt && col < a.n_rows) o[(size_t)(xrow0 + cb + j) * a.ldo + col] = acc[j];
                 }
             }
             if (item_end) {
 #pragma unroll
-                for (int j = 0; j < N; ++j) acc[j] = 0.f;
+                for (int j = 0; j < NC; ++j) acc[j] = 0.f;
             }
             DSUF_TACC(te_flush, tf0);
             est += Cfg::STAGE;
