@@ -48,6 +48,7 @@ struct StreamArgs {
     int ldo;
     float alpha;
     float swiglu_limit;
+    int whole_items;  // dense: give every CTA whole row tiles (no stream-K partials) when that costs no extra wave
     long long* dbg;   // optional [grid][8] cycle counters (debug builds of the bench only)
 };
 
@@ -90,7 +91,10 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
 
     // ---- this CTA's span of the global tile sequence ----
     long long beg, end;
-    if (EPI == EPI_DENSE) {
+    if (EPI == EPI_DENSE && a.whole_items) {
+        beg = ((long long)c * RT / G) * KT;
+        end = ((long long)(c + 1) * RT / G) * KT;
+    } else if (EPI == EPI_DENSE) {
         const long long tot = (long long)RT * KT;
         beg = (long long)c * tot / G;
         end = (long long)(c + 1) * tot / G;

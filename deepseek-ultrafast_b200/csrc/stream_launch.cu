@@ -103,6 +103,10 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     const long long tot = (long long)w->rt * w->kt;
     int grid = ctx->sm_count < WS_MAX_CTAS ? ctx->sm_count : WS_MAX_CTAS;
     if (tot < grid) grid = (int)tot;
+    // Stream-K balances to one tile but pays a partial-sum exchange per split row tile (a few microseconds on a kernel
+    // of tens); whole row tiles per CTA are preferred when they need no more tile-steps than that.
+    const long long steps_streamk = (tot + grid - 1) / grid + 6, steps_whole = (long long)((w->rt + grid - 1) / grid) * w->kt;
+    a.whole_items = steps_whole <= steps_streamk ? 1 : 0;
     const bool mx = w->d.mode == DSUF_MODE_MX;
     if (ctx->use_tc) {
         a.tm_w = w->tm_tc;

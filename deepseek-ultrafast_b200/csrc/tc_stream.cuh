@@ -112,7 +112,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 
     // ---- this CTA's span of the global tile sequence (see stream_gemv.cuh) ----
     long long beg, end;
-    if (EPI == EPI_DENSE) {
+    if (EPI == EPI_DENSE && a.whole_items) {
+        beg = ((long long)c * RT / G) * KT;
+        end = ((long long)(c + 1) * RT / G) * KT;
+    } else if (EPI == EPI_DENSE) {
         const long long tot = (long long)RT * KT;
         beg = (long long)c * tot / G;
         end = (long long)(c + 1) * tot / G;
