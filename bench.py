@@ -29,6 +29,8 @@ from __graft_entry__ import load_package  # noqa: E402
 H, I, E, TOPK, LAYERS = 7168, 2048, 256, 8, 4
 DENSE_SHAPES = [(4096, 7168), (7168, 2048), (18432, 7168), (7168, 16384)]
 METRIC = "moe_layer_stack_decode_tokens_per_s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch in the ncu small case, divided by its 55 active experts
+NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT = (874.597888e6 + 3.874816e6) / 55
 
 
 def peaks():
@@ -374,7 +376,11 @@ def run_ours(args):
     roofline = {"kernel": ("tc_stream_kernel" if ctx.tcgen05 else "stream_gemv_kernel") + "<FP4,W13> (grouped gate/up + SwiGLU)", "bound": "hbm", "achieved": round(achieved, 1),
                 "peak": hbm_peak, "peak_source": peak_src, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                 "frac_of_8tbs": round(achieved / 8000.0, 4), "avg_launch_ms": round(w13_ms, 4), "active_experts_per_launch": e_act,
-                "algorithmic_bytes_per_launch": int(algo_w13), "traffic": args.traffic}
+                "algorithmic_bytes_per_launch": int(algo_w13),
+                "traffic": args.traffic if args.traffic is not None else int(e_act * NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT),
+                "traffic_source": "given on the command line" if args.traffic is not None else
+                "ncu dram__bytes_read+write of the 64-expert small case (profiles/tc_stream_kernel_fp4_w13_decode_small_case.md), "
+                "per active expert, times this launch's active experts (traffic grows with the experts streamed)"}
     result = {
         "metric": METRIC, "value": round(T / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
