@@ -266,3 +266,53 @@ def test_moe_layer_expert_parallel_shards_sum_to_whole(pkg, ctx):
 
 def test_moe_single_token_single_expert(pkg, ctx):
     _moe_case(pkg, ctx, 1, T=1, H=128, I=128, E=2, K=1, tile_rows=8, seed=5)
+
+
+def test_moe_layer_full_benchmark_size_sampled_tokens(pkg, ctx):
+    """The decode configuration at full size (64 tokens, 256 experts top-8, hidden 7168, inter 2048; 6 GB of expert tiles,
+    byte offsets beyond 4 GB): the oracle is evaluated for a sample of tokens on exactly the tile bytes the kernels read
+    (downloaded and unpacked), the other tokens are covered by the size-independent check that every output row is the
+    sum of its top-k expert rows."""
+    import importlib
+    synth = importlib.import_module(pkg.__name__ + ".synth")
+    if not ctx.tcgen05:
+        pytest.skip("full size is run once, on the default decode path")
+    T, H, I, E, K = 64, 7168, 2048, 256, 8
+    dev = ctx.device
+    w13 = synth.fp4_experts(torch, E, 2 * I, H, 0.02, 11, True, dev)
+    w2 = synth.fp4_experts(torch, E, H, I, 0.02, 12, False, dev)
+    W13 = pkg.Weight.experts_fp4_packed(ctx, w13, 2 * I, H, E, True)
+    W2 = pkg.Weight.experts_fp4_packed(ctx, w2, H, I, E, False)
+    g = seeded(99)
+    xt, xn = randn_bf16(g, T, H)
+    logits = torch.randn(T, E, generator=g)
+    ids, rw = pkg.moe_route_tokens(ctx, pkg.SCORE_SOFTMAX, logits.cuda(), None, K)
+    layer = pkg.MoeLayer(ctx, W13, W2, T, K, pkg.MODE_DS)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    layer.forward(xt.cuda(), ids, rw, y)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    ids_n, rw_n = ids.cpu().numpy(), rw.cpu().numpy()
+    io, wo = oracle.route(1, logits.numpy(), None, K)
+    assert (ids_n == io).all()
+    # size-independent: out[t] == bf16(sum of the token's k permuted rows)
+    pr = layer.plan.pair_row.cpu().numpy().reshape(T, K)
+    yr = layer.yrows.cpu().numpy()
+    want = torch.from_numpy(yr[pr].sum(axis=1)).bfloat16().float().numpy()
+    got = y.float().cpu().numpy()
+    assert rel(got, want) < 1e-3
+    # sampled tokens against the oracle, on the experts they use (highest expert ids included: largest byte offsets)
+    sample = [0, 31, int(np.argmax(ids_n.max(axis=1)))]
+    per13 = (2 * I // 128) * (H // 128) * synth.REC_FP4
+    per2 = (H // 128) * (I // 128) * synth.REC_FP4
+    used = sorted(set(ids_n[sample].reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(used)}
+    c13, s13, c2, s2 = [], [], [], []
+    for e in used:
+        a, b = synth.unpack_fp4(w13[e * per13:(e + 1) * per13].cpu().numpy(), 2 * I, H, True)
+        c13.append(a); s13.append(b)
+        a, b = synth.unpack_fp4(w2[e * per2:(e + 1) * per2].cpu().numpy(), H, I, False)
+        c2.append(a); s2.append(b)
+    ids_l = np.vectorize(remap.get)(ids_n[sample]).astype(np.int32)
+    ref = oracle.moe_layer(oracle.MODE_DS, xn[sample], ids_l, rw_n[sample], np.stack(c13), np.stack(s13), np.stack(c2), np.stack(s2))
+    assert rel(got[sample], ref["y_f32"]) < TOL
