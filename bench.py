@@ -228,11 +228,12 @@ def zipf_routing(torch, tokens, n_exp, topk, seed, device):
     return ids.contiguous(), w.contiguous()
 
 
-def prefill_moe(pkg, ctx, torch, stack, tokens):
+def prefill_moe(pkg, ctx, torch, stack, tokens, act_mode=None):
     """cfg3: one routed-expert layer over `tokens` tokens with Zipf-skewed routing on 128-row plans (tcgen05 path);
     TFLOPS = 6 * pairs * inter * hidden / time of the two grouped GEMMs (+ the whole layer's time alongside)."""
     w13, w2 = stack.moe[0].w13, stack.moe[0].w2
-    layer = pkg.MoeLayer(ctx, w13, w2, tokens, TOPK, stack.cfg.act_mode, tile_rows=128)
+    act_mode = stack.cfg.act_mode if act_mode is None else act_mode
+    layer = pkg.MoeLayer(ctx, w13, w2, tokens, TOPK, act_mode, tile_rows=128)
     ids, w = zipf_routing(torch, tokens, E, TOPK, 7, ctx.device)
     x = torch.randn(tokens, H, device=ctx.device).bfloat16()
     y = torch.empty(tokens, H, dtype=torch.bfloat16, device=ctx.device)
@@ -406,6 +407,14 @@ def run_ours(args):
                                       "note": "L2 holds 126 MB of the ~5 GB read per call; repeated calls on one layer are HBM-bound"}
     if world == 1 and not args.skip_sub and not args.quick:
         result["prefill_moe"] = prefill_moe(pkg, ctx, torch, stack, args.prefill_tokens)
+        if stack.cfg.act_mode == pkg.MODE_DS:
+            # the same two workloads with the reference's own activation geometry (1x32, UE8M0 scales: block scaling in hardware)
+            lmx = pkg.MoeLayer(ctx, stack.moe[0].w13, stack.moe[0].w2, T, TOPK, pkg.MODE_MX)
+            ms_mx = time_events(torch, lambda: lmx.forward(x_dev, ids, w, yb), 20, 3)
+            result["mx_geometry"] = {"moe_decode_layer": {"ms": round(ms_mx, 4), "tokens_per_s": round(T / (ms_mx * 1e-3), 1),
+                                                          "gbs": round(e_act0 * (w13_b + w2_b) / (ms_mx * 1e-3) / 1e9, 1)},
+                                     "prefill_moe": prefill_moe(pkg, ctx, torch, stack, args.prefill_tokens, pkg.MODE_MX)}
+            del lmx
     if world == 1 and not args.skip_cpu:
         p = cpu_prepare()
         vals, dts, t_all = [], [], time.perf_counter()

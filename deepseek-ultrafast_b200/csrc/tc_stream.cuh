@@ -61,9 +61,15 @@ struct TcCfg {
 template <int FMT, int WMX, int AMX, int N, int EPI>
 __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
     using Cfg = TcCfg<N>;
-    constexpr int S = Cfg::STAGES, NB = Cfg::NB, ACC_COLS = Cfg::ACC_COLS, SUB = Cfg::SUB;
+    constexpr int S = Cfg::STAGES, ACC_COLS = Cfg::ACC_COLS, SUB = Cfg::SUB;
     constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
-    constexpr int NI = PER_TILE ? 2 : 1;    // MMA-issuing warps
+    constexpr int NI = PER_TILE ? 2 : 1;    // MMA-issuing warps of the per-tile mode
+    // whole-K mode with token tiles up to 64 columns: two issuers as well, alternate tiles, each accumulating into its
+    // own half of the ring entry; the epilogue adds the halves
+    constexpr bool DUAL_WHOLE = !PER_TILE && N <= 64;
+    constexpr int ACCW = DUAL_WHOLE ? 2 * ACC_COLS : ACC_COLS;  // tensor-memory columns of one ring entry
+    constexpr int NB = Cfg::NB * ACCW > 256 ? Cfg::NB / 2 : Cfg::NB;  // ring entries in use
+    static_assert(NB * ACCW <= 256, "accumulator ring overlaps the scale columns");
     constexpr int NP = Cfg::NP;
     // epilogue groups actually working: the second group pays off where tiles are 8.7 KB (FP4 experts), not for dense FP8
     constexpr int NE = (PER_TILE && Cfg::NE == 2 && EPI != EPI_DENSE) ? 2 : 1;
@@ -96,7 +102,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             mbar_init(&empty_bar[s], 1);  // tcgen05.commit: the tensor core has finished reading the stage
         }
         for (int b = 0; b < NB; ++b) {
-            mbar_init(&tfull_bar[b], 1);
+            mbar_init(&tfull_bar[b], DUAL_WHOLE ? 2 : 1);
             mbar_init(&tempty_bar[b], CSPLIT ? 8 : 4);
         }
         mbar_fence_init();
@@ -248,7 +254,67 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         const int j = warp == 1 ? 0 : 1;
         // The whole warp runs the loop and one elected lane issues: tcgen05 operands are uniform-register operands,
         // and a loop run by a single lane of a diverged warp pays a register-file round trip for each of them.
-        if (j < NI && beg + j < end) {
+        if (DUAL_WHOLE) {
+            if (beg < end) {
+                // Both issuers walk every tile of the span (so both know the group boundaries); issuer j issues the
+                // tiles of parity j into columns [j*N, (j+1)*N) of the ring entry.  tfull needs both: a commit from an
+                // issuer that contributed MMAs, a plain arrival from one that did not.
+                const uint32_t tmu = uni32(tm);
+                const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
+                const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
+                const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+                if (elect_one()) {
+                    if (!WMX) tc_cp_sf(ones_a, ones_d);
+                    if (!AMX) tc_cp_sf(ones_b, ones_d);
+                }
+                __syncwarp();
+                const uint64_t ad0 = uni64(tc_smem_desc(ring, 16, 1024, 2)), bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
+                const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0)),
+                               fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
+                int kt = (int)(beg % KT);
+                int s = 0, gidx = 0;
+                uint32_t ph = 0;
+                bool issued = false, entry_free = false;
+                for (long long i = beg; i < end; ++i) {
+                    const bool mine = ((int)(i - beg) & 1) == j;
+                    const bool group_end = kt + 1 == KT || i + 1 == end;
+                    const int b = gidx & (NB - 1);
+                    if ((mine || group_end) && !entry_free) {
+                        // also before a bare arrival: the entry's previous phase must be complete before this one is fed
+                        if (gidx >= NB && !dead && !mbar_wait(&tempty_bar[b], ((gidx / NB) - 1) & 1, a.status, KID_TC, 3)) dead = true;
+                        entry_free = true;
+                    }
+                    if (mine) {
+                        if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TC, 2)) dead = true;
+                        tc_fence_after();
+                        if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
+                        const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
+                        if (elect_one()) {
+                            uint32_t sfa = ones_a, sfb = ones_b;
+                            if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
+                            if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
+                            const uint32_t d = tmu + b * ACCW + j * N;
+#pragma unroll
+                            for (int kc = 0; kc < 4; ++kc)
+                                tc_mma_mx(d, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc),
+                                          sfa, sfb, (!issued && kc == 0) ? 0u : 1u);
+                            tc_commit(&empty_bar[s]);
+                            if (group_end) tc_commit(&tfull_bar[b]);
+                        }
+                        issued = true;
+                    } else if (group_end) {
+                        if (elect_one()) {
+                            if (issued) tc_commit(&tfull_bar[b]);
+                            else mbar_arrive(&tfull_bar[b]);
+                        }
+                    }
+                    __syncwarp();
+                    if (group_end) { ++gidx; issued = false; entry_free = false; }
+                    if (++kt == KT) kt = 0;
+                    if (++s == S) { s = 0; ph ^= 1; }
+                }
+            }
+        } else if (j < NI && beg + j < end) {
             const uint32_t tmu = uni32(tm);
             const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
             const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
@@ -344,6 +410,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         int gidx = 0, es = 0, items_done = 0;
         const uint8_t* est = ring;
         long long te_wait = 0, te_ld = 0, te_arr = 0, te_flush = 0;
+        long long g0 = beg;  // first tile of the current accumulation group
         DSUF_T0(te_start);
         for (long long i = beg; i < end; ++i) {
             if (fresh) {
@@ -373,10 +440,19 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 {
                     const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + b * Cfg::XS_ENTRY + 4 * N) : 1.0f;
                     constexpr int CH = NC < 32 ? NC : 32;
+                    // two issuers in the whole-K mode: which halves of the entry hold this group's sums
+                    const bool lone = DUAL_WHOLE && i == g0;
+                    const bool has0 = !lone || (((int)(g0 - beg) & 1) == 0);
 #pragma unroll
                     for (int c0 = 0; c0 < NC; c0 += CH) {
                         float v[CH];
-                        tmem_ld<CH>(tm + lane_base + b * ACC_COLS + cb + c0, v);
+                        tmem_ld<CH>(tm + lane_base + b * ACCW + (has0 ? 0 : N) + cb + c0, v);
+                        if (DUAL_WHOLE && !lone) {
+                            float v2[CH];
+                            tmem_ld<CH>(tm + lane_base + b * ACCW + N + cb + c0, v2);
+#pragma unroll
+                            for (int j = 0; j < CH; ++j) v[j] += v2[j];
+                        }
                         if (PER_TILE) {
 #pragma unroll
                             for (int j = 0; j < CH; j += 4) {
@@ -488,6 +564,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             if (item_end) {
 #pragma unroll
                 for (int j = 0; j < NC; ++j) acc[j] = 0.f;
+                g0 = i + 1;
             }
             DSUF_TACC(te_flush, tf0);
             est += Cfg::STAGE;
