@@ -5,6 +5,7 @@
 #include "internal.h"
 #include "stream_gemv.cuh"
 #include "tc_stream.cuh"
+#include "tc_prefill.cuh"
 
 namespace dsuf {
 
@@ -58,6 +59,10 @@ int stream_setup(dsuf_ctx* ctx) {
     ST(FMT_FP4, 1, 0, 8, EPI_W2); ST(FMT_FP4, 1, 0, 16, EPI_W2); ST(FMT_FP4, 1, 0, 128, EPI_W2);
     ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2); ST(FMT_FP4, 1, 1, 128, EPI_W2);
 #undef ST
+    for (const void* f : {(const void*)tc_prefill_kernel<EPI_W13>, (const void*)tc_prefill_kernel<EPI_W2>}) {
+        cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, TcpCfg::SMEM);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_prefill)");
+    }
     return DSUF_OK;
 }
 
@@ -75,6 +80,7 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
     a.alpha = 1.0f;
 #ifdef DSUF_TC_TIMING
     a.dbg = getenv("DSUF_DBG_PTR") ? (long long*)strtoull(getenv("DSUF_DBG_PTR"), nullptr, 0) : nullptr;
+    a.probe = getenv("DSUF_PROBE") ? atoi(getenv("DSUF_PROBE")) : 0;
 #endif
 }
 
@@ -148,6 +154,12 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
         a.tm_w = w->tm_tc;
 #define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, a)
         const int tr = plan->tile_rows;
+        if (tr == 128 && amx && (w->rt & 1) == 0) {
+            // prefill-size token tiles with MX scales on both sides: two row tiles per step, two issuers
+            if (epi == EPI_W13)
+                return launch(ctx, stream, tc_prefill_kernel<EPI_W13>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a);
+            return launch(ctx, stream, tc_prefill_kernel<EPI_W2>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a);
+        }
         if (epi == EPI_W13) {
             if (amx) return tr == 8 ? GT(1, 8, EPI_W13) : tr == 16 ? GT(1, 16, EPI_W13) : GT(1, 128, EPI_W13);
             return tr == 8 ? GT(0, 8, EPI_W13) : tr == 16 ? GT(0, 16, EPI_W13) : GT(0, 128, EPI_W13);

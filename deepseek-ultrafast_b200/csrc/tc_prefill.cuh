@@ -1,0 +1,227 @@
+// tcgen05 grouped GEMM for prefill-size token tiles: 128 tokens x TWO 128-row weight tiles per CTA step, MX
+// (power-of-two) scales on both operands applied by the tensor core.
+//
+// Measured on B200 with the decode kernel (tc_stream.cuh) at 128-token tiles: a tcgen05.mma occupies its issuing
+// thread for about as long as it occupies the tensor pipe (97 cycles at N = 128), and everything else that thread
+// does per tile (the wait on the stage, fences, scale copies, the commit: ~350 cycles) is added serially, so one
+// issuer keeps the pipe barely half busy; the ring of six 33 KB stages also covers too little latency.  Here
+//   * a stage holds one activation tile (128 tokens x 128 K) and the tiles of two adjacent weight row tiles, so
+//     every activation byte brought into shared memory feeds 256 weight rows (a third less ingest per flop);
+//   * two issuer warps each own one of the two row tiles and one accumulator (128 lanes x 128 columns of tensor
+//     memory): the bookkeeping of one overlaps the MMAs of the other, and the summation order of every output is
+//     fixed (results do not depend on timing);
+//   * sixteen epilogue warps drain both accumulators into registers in one go (64 columns per thread), release
+//     the tensor memory, and run the SwiGLU / store epilogue while the next item's MMAs proceed.
+// Replaces tc_moe_w13 / tc_moe_w2 (crates/kernels/cu/tcmoe.cu:184-588) for MX activations; the weights come
+// straight from the tile records (no in-kernel re-layout warps, cu/tcmoe.cu:412-456).
+#pragma once
+#include "tc_stream.cuh"
+
+namespace dsuf {
+
+constexpr int KID_TCP = 4;
+
+struct TcpCfg {
+    static constexpr int A_BYTES = 16384;            // one weight tile, FP4 widened to 8-bit containers by TMA
+    static constexpr int B_OFF = 2 * A_BYTES;        // 128 token rows of 128 bytes
+    static constexpr int SFA_OFF = B_OFF + 16384;    // two weight scale atoms (512 bytes each)
+    static constexpr int SFB_OFF = SFA_OFF + 1024;   // activation scale atom
+    static constexpr int STAGE = SFB_OFF + 1024;     // 51200: a multiple of 1024
+    static constexpr int STAGES = 4;
+    static constexpr int SMEM = STAGE * STAGES + 1024;
+    static constexpr int EPI_WARP0 = 4;              // warps 4..19: four groups of four (accumulator x column half)
+    static constexpr int THREADS = (EPI_WARP0 + 16) * 32;
+    static constexpr int TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;
+};
+
+// warp 0 / 2: producers (weight row tile 0 + activation tile / weight row tile 1 + activation scales),
+// 1 / 3: MMA issuers (accumulator 0 / 1), 4..19: epilogue (640 threads: 96 registers each)
+template <int EPI>
+__global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __grid_constant__ StreamArgs a) {
+    using Cfg = TcpCfg;
+    constexpr int S = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[2], tempty_bar[2];
+    __shared__ uint32_t s_tmem;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = gridDim.x, c = blockIdx.x;
+    const int RT = a.RT, KT = a.KT, RP = RT >> 1;  // row-tile pairs per expert (RT is even: checked by the launcher)
+    bool dead = false;  // set by the first expired wait: nothing is waited for again, the loops stay finite
+
+    if (warp == 1) {
+        tmem_alloc(&s_tmem, Cfg::TM_COLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full_bar[s], 2 + 32);  // one expect_tx per producer warp + 32 cp.async lanes
+            mbar_init(&empty_bar[s], 2);      // one tcgen05.commit per issuer
+        }
+        for (int j = 0; j < 2; ++j) {
+            mbar_init(&tfull_bar[j], 1);
+            mbar_init(&tempty_bar[j], 8);     // the eight epilogue warps of the accumulator
+        }
+        mbar_fence_init();
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tm = s_tmem;
+    pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+
+    // items = (slot, row-tile pair); every CTA takes a contiguous range
+    const long long nitems = (long long)(*a.nslots) * RP;
+    const long long ibeg = (long long)c * nitems / G, iend = (long long)(c + 1) * nitems / G;
+
+    if (warp == 0 || warp == 2) {
+        // ================= producers =================
+        // warp 0: weight row tile 2*rp (codes + scale atom) and the activation tile;
+        // warp 2: weight row tile 2*rp + 1 and the activation scales (4-byte async copies into the scale atom)
+        const int j = warp >> 1;
+        if (ibeg < iend) {
+            if (lane == 0) { prefetch_tmap(&a.tm_w); prefetch_tmap(&a.tm_x); }
+            const uint64_t pol = policy_evict_last();  // scale atoms and token rows; the weight tiles take the default policy
+            int s = 0;
+            uint32_t ph = 0;
+            long long n = 0;
+            for (long long it = ibeg; it < iend; ++it) {
+                const int slot = (int)(it / RP), rp = (int)(it - (long long)slot * RP);
+                const int4 sl = a.slots[slot];
+                const int xrow0 = sl.y;
+                int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
+                const uint8_t* sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
+                for (int kt = 0; kt < KT; ++kt, ++n) {
+                    if (n >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TCP, 1 + j)) dead = true;
+                    uint8_t* st = ring + s * Cfg::STAGE;
+                    if (elect_one()) {
+                        // TMA counts the bytes it reads: 8192 for a packed FP4 tile that fills 16384 of shared memory
+                        mbar_expect_tx(&full_bar[s], 8192 + 512 + (j == 0 ? 16384 : 0));
+                        tma_3d_nh(st + j * Cfg::A_BYTES, &a.tm_w, 0, 0, tile, &full_bar[s]);
+                        bulk_g2s(st + Cfg::SFA_OFF + j * 512, sf_src, 512, &full_bar[s], pol);
+                        if (j == 0) tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol);
+                    }
+                    __syncwarp();
+                    if (j == 1) {
+#pragma unroll
+                        for (int t = lane; t < 128; t += 32) {
+                            // the token's 4 UE8M0 bytes of this K tile go to its row of the scale atom
+                            const uint32_t* src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + t, a.x_rows - 1) * KT + kt;
+                            cp_async4(st + Cfg::SFB_OFF + (t & 31) * 16 + (t >> 5) * 4, src);
+                        }
+                        cp_async_arrive_noinc(&full_bar[s]);
+                    }
+                    ++tile;
+                    sf_src += a.rec_bytes;
+                    if (++s == S) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1 || warp == 3) {
+        // ================= MMA issuers: issuer j multiplies row tile j of every stage into accumulator j =================
+        // The whole warp runs the loop and one elected lane issues (tcgen05 operands are uniform-register operands).
+        const int j = warp >> 1;
+        if (ibeg < iend) {
+            const uint32_t tmu = uni32(tm);
+            const uint32_t idesc = tc_idesc_mx(128, true);
+            const uint64_t ad0 = uni64(tc_smem_desc(ring + j * Cfg::A_BYTES, 16, 1024, 2)),
+                           bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
+            const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF + j * 512, 512, 128, 0)),
+                           fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
+            const uint32_t d = tmu + j * 128;
+            int s = 0;
+            uint32_t ph = 0;
+            long long nit = 0;
+            for (long long it = ibeg; it < iend; ++it, ++nit) {
+                // the accumulator is single-buffered: wait until the epilogue has drained the previous item
+                if (nit > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
+                tc_fence_after();
+                for (int kt = 0; kt < KT; ++kt) {
+                    if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TCP, 4)) dead = true;
+                    fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
+                    const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
+                    if (elect_one()) {
+                        // each issuer keeps its own copy of the stage's scales in tensor memory
+                        const uint32_t sfa = tmu + Cfg::TM_SFA + 4 * (2 * s + j), sfb = tmu + Cfg::TM_SFB + 4 * (2 * s + j);
+                        tc_cp_sf(sfa, fa0 + so);
+                        tc_cp_sf(sfb, fb0 + so);
+#pragma unroll
+                        for (int kc = 0; kc < 4; ++kc)
+                            tc_mma_mx(d, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
+                                      (kt == 0 && kc == 0) ? 0u : 1u);
+                        tc_commit(&empty_bar[s]);
+                        if (kt + 1 == KT) tc_commit(&tfull_bar[j]);
+                    }
+                    __syncwarp();
+                    if (++s == S) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp >= Cfg::EPI_WARP0) {
+        // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
+        const int e = warp - Cfg::EPI_WARP0;
+        const int ga = e >> 3;                 // accumulator = row tile of the pair
+        const int cb = ((e >> 2) & 1) * 64;    // first of this thread's 64 token columns
+        const int q4 = warp & 3;               // tensor-memory lane quadrant this warp may read
+        const int r = 32 * q4 + lane;
+        const uint32_t taddr = tm + ((uint32_t)(32 * q4) << 16) + ga * 128 + cb;
+        float acc[64];
+        long long nit = 0;
+        for (long long it = ibeg; it < iend; ++it, ++nit) {
+            const int slot = (int)(it / RP), rp = (int)(it - (long long)slot * RP);
+            const int rt = 2 * rp + ga;
+            const int4 sl = a.slots[slot];
+            const int xrow0 = sl.y, cnt = sl.z;
+            float rw0 = 0.f, rw1 = 0.f;
+            if (EPI == EPI_W13) {
+                // routing weights of this thread's token columns, one per lane, fetched while the item's MMAs run
+                rw0 = (cb + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + lane) : 0.f;
+                rw1 = (cb + 32 + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 + lane) : 0.f;
+            }
+            if (!dead && !mbar_wait(&tfull_bar[ga], (uint32_t)(nit & 1), a.status, KID_TCP, 5)) dead = true;
+            tc_fence_after();
+            tmem_ld<32>(taddr, acc);
+            tmem_ld<32>(taddr + 32, acc + 32);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[ga]);
+            if (EPI == EPI_W13) {
+                // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group); after the
+                // exchange the gate lane finishes column j, the up lane column j + 1.
+                // SwiGLU as crates/kernels/cu/gemv.cu:470-483: bf16 rounds, optional clamp, routing weight folded in
+                bf16* ocol = (bf16*)a.out + rt * 64 + (r >> 4) * 8 + (r & 7);
+                const float L = a.swiglu_limit;
+                const bool is_gate = (r & 8) == 0;
+#pragma unroll
+                for (int j = 0; j < 64; j += 2) {
+                    const float o0 = __shfl_xor_sync(0xffffffffu, acc[j], 8);
+                    const float o1 = __shfl_xor_sync(0xffffffffu, acc[j + 1], 8);
+                    const int col = is_gate ? j : j + 1;
+                    const float rw = __shfl_sync(0xffffffffu, j < 32 ? rw0 : rw1, col & 31);
+                    if (cb + col < cnt) {
+                        const int row = xrow0 + cb + col;
+                        float gt = bf16_round(is_gate ? acc[j] : o1), up = bf16_round(is_gate ? o0 : acc[j + 1]);
+                        if (L > 0.f) { up = fminf(fmaxf(up, -L), L); gt = fminf(gt, L); }
+                        const float val = gt / (1.0f + expf(-gt)) * up * rw;
+                        ocol[(size_t)row * a.ldo] = __float2bfloat16(val);
+                    }
+                }
+            } else {
+                float* o = (float*)a.out;
+                const int col = rt * 128 + r;
+#pragma unroll
+                for (int j = 0; j < 64; ++j)
+                    if (cb + j < cnt && col < a.n_rows) o[(size_t)(xrow0 + cb + j) * a.ldo + col] = acc[j];
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tm, Cfg::TM_COLS);
+}
+
+}  // namespace dsuf

@@ -44,7 +44,7 @@ struct TcCfg {
     static constexpr int ACC_COLS = SUB * N;
     static constexpr int NB = ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
     static constexpr int XS_ENTRY = 4 * N + 16;      // per-tile fp32 scales: N activation scales + the weight scale, one entry per accumulator
-    static constexpr int NP = N <= 64 ? 2 : 1;        // producer warps per kind (weights / activations), alternate tiles
+    static constexpr int NP = 2;                      // producer warps per kind (weights / activations), alternate tiles
     static constexpr int THREADS = 256 + 64 * (NP - 1) + 128;  // second producers (NP == 2), then the second epilogue group
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
     static_assert(NB * ACC_COLS <= 256 && STAGES >= 4 && N <= 128, "tensor-memory / shared-memory budget");
@@ -53,9 +53,14 @@ struct TcCfg {
 #ifdef DSUF_TC_TIMING
 #define DSUF_T0(v) const long long v = clock64()
 #define DSUF_TACC(acc, v) acc += clock64() - v
+#define DSUF_PROBE(bit) (a.probe & (bit))
+// event trace of CTA 0, tiles [256, 320): [tile][16] clock values behind the [grid][8] counters
+#define DSUF_TRACE(i, k) do { const long long tn_ = (i) - beg; if (a.dbg && c == 0 && tn_ >= 256 && tn_ < 320 && lane == 0) a.dbg[(long long)G * 8 + (tn_ - 256) * 16 + (k)] = clock64(); } while (0)
 #else
+#define DSUF_TRACE(i, k)
 #define DSUF_T0(v)
 #define DSUF_TACC(acc, v)
+#define DSUF_PROBE(bit) false
 #endif
 
 template <int FMT, int WMX, int AMX, int N, int EPI>
@@ -166,14 +171,21 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     fresh = false;
                 }
                 DSUF_T0(tw0);
+                DSUF_TRACE(i, 0);
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 1)) dead = true;
+                DSUF_TRACE(i, 1);
                 DSUF_TACC(tw_wait, tw0);
                 if (elect_one()) {
-                    mbar_expect_tx(&full_bar[s], W_TX);
-                    tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
+                    if (DSUF_PROBE(2)) {
+                        mbar_expect_tx(&full_bar[s], WMX ? 512 : 0);
+                    } else {
+                        mbar_expect_tx(&full_bar[s], W_TX);
+                        tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
+                    }
                     if (WMX) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
                 }
                 __syncwarp();
+                DSUF_TRACE(i, 2);
                 tile += NP;
                 sf_src += (size_t)NP * a.rec_bytes;
                 s += NP;
@@ -217,11 +229,17 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     fresh = false;
                 }
                 DSUF_T0(tx0);
+                DSUF_TRACE(i, 3);
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
+                DSUF_TRACE(i, 4);
                 DSUF_TACC(tx_wait, tx0);
                 if (elect_one()) {
-                    mbar_expect_tx(&full_bar[s], N * 128);
-                    tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                    if (DSUF_PROBE(1)) {
+                        mbar_arrive(&full_bar[s]);
+                    } else {
+                        mbar_expect_tx(&full_bar[s], N * 128);
+                        tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                    }
                 }
                 __syncwarp();
                 uint8_t* xe = nullptr;
@@ -239,6 +257,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 }
                 if (!WMX && lane == 31) cp_async4(xe + 4 * N, ws_src + kt);
                 cp_async_arrive_noinc(&full_bar[s]);
+                DSUF_TRACE(i, 5);
                 s += NP;
                 st += NP * Cfg::STAGE;
                 if (s >= S) { s -= S; st -= S * Cfg::STAGE; ph ^= 1; }
@@ -334,13 +353,18 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             uint32_t ph = 0;
             bool group_open = false;
             DSUF_T0(t_start);
+#ifdef DSUF_TC_TIMING
+            unsigned long long gt0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
+#endif
             long long t_full = 0, t_tempty = 0, t_issue = 0;
             for (long long i = beg + j; i < end; i += NI) {
                 DSUF_T0(t0);
+                DSUF_TRACE(i, 6);
                 if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TC, 2)) dead = true;
+                DSUF_TRACE(i, 7);
                 DSUF_TACC(t_full, t0);
                 tc_fence_after();
-                if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
+                if (AMX && !DSUF_PROBE(4)) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                 int b;
                 bool first_of_group;
                 DSUF_T0(t1);
@@ -370,6 +394,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     const uint32_t d = tmu + b * ACC_COLS;
 #pragma unroll
                     for (int kc = 0; kc < 4; ++kc)
+                        if (!DSUF_PROBE(8) || kc == 0)
                         tc_mma_mx(d + (SUB == 4 ? kc * N : 0), ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
                                   tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && (SUB == 4 || kc == 0)) ? 0u : 1u);
                     tc_commit(&empty_bar[s]);
@@ -381,6 +406,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     if (++kt == KT) { kt = 0; ++q; }
                 }
                 DSUF_TACC(t_issue, t2);
+                DSUF_TRACE(i, 8);
                 s += NI;
                 if (s >= S) { s -= S; ph ^= 1; }
             }
@@ -388,6 +414,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             if (a.dbg && j == 0 && lane == 0) {
                 a.dbg[c * 8 + 0] = t_full; a.dbg[c * 8 + 2] = t_issue;
                 a.dbg[c * 8 + 3] = clock64() - t_start; a.dbg[c * 8 + 4] = (end - beg + NI - 1) / NI;
+                unsigned long long gt1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1)); a.dbg[c * 8 + 6] = (long long)(gt1 - gt0);
             }
 #endif
         }
@@ -411,6 +438,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         const uint8_t* est = ring;
         long long te_wait = 0, te_ld = 0, te_arr = 0, te_flush = 0;
         long long g0 = beg;  // first tile of the current accumulation group
+        float rwreg[(NC + 31) / 32] = {};
         DSUF_T0(te_start);
         for (long long i = beg; i < end; ++i) {
             if (fresh) {
@@ -424,6 +452,12 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     const int4 sl = a.slots[slot];
                     xrow0 = sl.y;
                     cnt = sl.z;
+                    if (EPI == EPI_W13) {
+                        // routing weights of this thread's token columns, one per lane, fetched while the item's MMAs run
+#pragma unroll
+                        for (int k = 0; k < (NC + 31) / 32; ++k)
+                            rwreg[k] = (cb + 32 * k + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 * k + lane) : 0.f;
+                    }
                 }
                 fresh = false;
             }
@@ -542,15 +576,21 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     bf16* o = (bf16*)a.out;
                     const float L = a.swiglu_limit;
                     const bool is_gate = (r & 8) == 0;
+                    bf16* ocol = o + rt * 64 + (r >> 4) * 8 + (r & 7);
+                    // After the exchange both lanes of a pair hold (gate, up) of two token columns: the gate lane
+                    // finishes column j, the up lane column j + 1, so every lane evaluates one SwiGLU per column pair.
 #pragma unroll
-                    for (int j = 0; j < NC; ++j) {
-                        const float other = __shfl_xor_sync(0xffffffffu, acc[j], 8);
-                        if (is_gate && cb + j < cnt) {
-                            const int row = xrow0 + cb + j;
-                            float gt = bf16_round(acc[j]), up = bf16_round(other);
+                    for (int j = 0; j < NC; j += 2) {
+                        const float o0 = __shfl_xor_sync(0xffffffffu, acc[j], 8);
+                        const float o1 = __shfl_xor_sync(0xffffffffu, acc[j + 1], 8);
+                        const int col = is_gate ? j : j + 1;
+                        const float rw = __shfl_sync(0xffffffffu, rwreg[col >> 5], col & 31);
+                        if (cb + col < cnt) {
+                            const int row = xrow0 + cb + col;
+                            float gt = bf16_round(is_gate ? acc[j] : o1), up = bf16_round(is_gate ? o0 : acc[j + 1]);
                             if (L > 0.f) { up = fminf(fmaxf(up, -L), L); gt = fminf(gt, L); }
-                            const float val = gt / (1.0f + expf(-gt)) * up * __ldg(a.row_w + row);
-                            o[(size_t)row * a.ldo + rt * 64 + (r >> 4) * 8 + (r & 7)] = __float2bfloat16(val);
+                            const float val = gt / (1.0f + expf(-gt)) * up * rw;
+                            ocol[(size_t)row * a.ldo] = __float2bfloat16(val);
                         }
                     }
                 } else {
@@ -572,7 +612,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             if (++kt == KT) { kt = 0; ++q; fresh = true; }
         }
 #ifdef DSUF_TC_TIMING
-        if (a.dbg && tid == 64) { a.dbg[c * 8 + 7] = clock64() - te_start - te_wait; a.dbg[c * 8 + 5] = te_ld; a.dbg[c * 8 + 6] = te_arr; a.dbg[c * 8 + 1] = te_flush; }
+        if (a.dbg && tid == 64) { a.dbg[c * 8 + 7] = clock64() - te_start - te_wait; a.dbg[c * 8 + 5] = te_ld; a.dbg[c * 8 + 1] = te_flush; }
 #endif
     }
     tc_fence_before();
