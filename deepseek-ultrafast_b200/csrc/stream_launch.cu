@@ -59,7 +59,8 @@ int stream_setup(dsuf_ctx* ctx) {
     ST(FMT_FP4, 1, 0, 8, EPI_W2); ST(FMT_FP4, 1, 0, 16, EPI_W2); ST(FMT_FP4, 1, 0, 128, EPI_W2);
     ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2); ST(FMT_FP4, 1, 1, 128, EPI_W2);
 #undef ST
-    for (const void* f : {(const void*)tc_prefill_kernel<EPI_W13>, (const void*)tc_prefill_kernel<EPI_W2>}) {
+    for (const void* f : {(const void*)tc_prefill_kernel<EPI_W13, 1>, (const void*)tc_prefill_kernel<EPI_W2, 1>,
+                          (const void*)tc_prefill_kernel<EPI_W13, 0>, (const void*)tc_prefill_kernel<EPI_W2, 0>}) {
         cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, TcpCfg::SMEM);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_prefill)");
     }
@@ -154,11 +155,12 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
         a.tm_w = w->tm_tc;
 #define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, a)
         const int tr = plan->tile_rows;
-        if (tr == 128 && amx && (w->rt & 1) == 0) {
-            // prefill-size token tiles with MX scales on both sides: two row tiles per step, two issuers
-            if (epi == EPI_W13)
-                return launch(ctx, stream, tc_prefill_kernel<EPI_W13>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a);
-            return launch(ctx, stream, tc_prefill_kernel<EPI_W2>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a);
+        if (tr == 128 && (w->rt & 1) == 0) {
+            // prefill-size token tiles: two row tiles per step, two issuers
+#define GP(EPI, AMX) launch(ctx, stream, tc_prefill_kernel<EPI, AMX>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a)
+            if (epi == EPI_W13) return amx ? GP(EPI_W13, 1) : GP(EPI_W13, 0);
+            return amx ? GP(EPI_W2, 1) : GP(EPI_W2, 0);
+#undef GP
         }
         if (epi == EPI_W13) {
             if (amx) return tr == 8 ? GT(1, 8, EPI_W13) : tr == 16 ? GT(1, 16, EPI_W13) : GT(1, 128, EPI_W13);

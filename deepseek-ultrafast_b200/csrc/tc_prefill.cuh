@@ -28,7 +28,8 @@ struct TcpCfg {
     static constexpr int SFB_OFF = SFA_OFF + 1024;   // activation scale atom
     static constexpr int STAGE = SFB_OFF + 1024;     // 51200: a multiple of 1024
     static constexpr int STAGES = 4;
-    static constexpr int SMEM = STAGE * STAGES + 1024;
+    static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0 (DS activations)
+    static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
     static constexpr int EPI_WARP0 = 4;              // warps 4..19: four groups of four (accumulator x column half)
     static constexpr int THREADS = (EPI_WARP0 + 16) * 32;
     static constexpr int TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;
@@ -36,10 +37,16 @@ struct TcpCfg {
 
 // warp 0 / 2: producers (weight row tile 0 + activation tile / weight row tile 1 + activation scales),
 // 1 / 3: MMA issuers (accumulator 0 / 1), 4..19: epilogue (640 threads: 96 registers each)
-template <int EPI>
+// AMX = 1: UE8M0 activation scales per 1x32, applied by the tensor core; the whole K accumulates in tensor memory.
+// AMX = 0: fp32 activation scales per 1x128 (DS geometry): every 128-K tile is promoted into fp32 registers with
+//          its scales.  The accumulators stay single-buffered: while the epilogue reads accumulator j, the other
+//          issuer's MMAs keep the tensor pipe busy.
+template <int EPI, int AMX>
 __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __grid_constant__ StreamArgs a) {
     using Cfg = TcpCfg;
     constexpr int S = Cfg::STAGES;
+    constexpr int XR = 8;  // ring of fp32 activation scales (DS): outlives the stage, read after the MMAs completed
+    __shared__ __align__(16) float s_xs[AMX ? 4 : XR * 128];
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[2], tempty_bar[2];
@@ -65,6 +72,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         }
         mbar_fence_init();
     }
+    if (!AMX && tid >= 64 && tid < 192) ((uint32_t*)(ring + Cfg::ONES_OFF))[tid - 64] = 0x7f7f7f7fu;  // one atom of UE8M0 1.0
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -74,8 +82,8 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
     pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
 
     // items = (slot, row-tile pair); every CTA takes a contiguous range
-    const long long nitems = (long long)(*a.nslots) * RP;
-    const long long ibeg = (long long)c * nitems / G, iend = (long long)(c + 1) * nitems / G;
+    const long long nitems = (long long)(*a.nslots) * RP;  // far below 2^31: slots <= permuted rows / 128 + experts
+    const int ibeg = (int)((long long)c * nitems / G), iend = (int)((long long)(c + 1) * nitems / G);
 
     if (warp == 0 || warp == 2) {
         // ================= producers =================
@@ -87,9 +95,9 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             const uint64_t pol = policy_evict_last();  // scale atoms and token rows; the weight tiles take the default policy
             int s = 0;
             uint32_t ph = 0;
-            long long n = 0;
-            for (long long it = ibeg; it < iend; ++it) {
-                const int slot = (int)(it / RP), rp = (int)(it - (long long)slot * RP);
+            int n = 0;
+            for (int it = ibeg; it < iend; ++it) {
+                const int slot = it / RP, rp = it - slot * RP;
                 const int4 sl = a.slots[slot];
                 const int xrow0 = sl.y;
                 int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
@@ -108,9 +116,10 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     if (j == 1) {
 #pragma unroll
                         for (int t = lane; t < 128; t += 32) {
-                            // the token's 4 UE8M0 bytes of this K tile go to its row of the scale atom
+                            // MX: the token's 4 UE8M0 bytes of this K tile go to its row of the scale atom; DS: its fp32 scale
                             const uint32_t* src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + t, a.x_rows - 1) * KT + kt;
-                            cp_async4(st + Cfg::SFB_OFF + (t & 31) * 16 + (t >> 5) * 4, src);
+                            if (AMX) cp_async4(st + Cfg::SFB_OFF + (t & 31) * 16 + (t >> 5) * 4, src);
+                            else cp_async4(s_xs + (n & (XR - 1)) * 128 + t, src);
                         }
                         cp_async_arrive_noinc(&full_bar[s]);
                     }
@@ -132,28 +141,43 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF + j * 512, 512, 128, 0)),
                            fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
             const uint32_t d = tmu + j * 128;
+            const uint32_t ones_b = tmu + Cfg::TM_SFB + 4 * (2 * S + j);
+            if (!AMX) {
+                const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));  // shuffles: outside the election
+                if (elect_one()) tc_cp_sf(ones_b, ones_d);
+                __syncwarp();
+            }
             int s = 0;
             uint32_t ph = 0;
-            long long nit = 0;
-            for (long long it = ibeg; it < iend; ++it, ++nit) {
-                // the accumulator is single-buffered: wait until the epilogue has drained the previous item
-                if (nit > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
-                tc_fence_after();
-                for (int kt = 0; kt < KT; ++kt) {
+            int nit = 0, n = 0;
+            for (int it = ibeg; it < iend; ++it, ++nit) {
+                if (AMX) {
+                    // the accumulator is single-buffered: wait until the epilogue has drained the previous item
+                    if (nit > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
+                    tc_fence_after();
+                }
+                for (int kt = 0; kt < KT; ++kt, ++n) {
                     if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TCP, 4)) dead = true;
-                    fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
+                    if (AMX) {
+                        fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
+                    } else {
+                        // per-tile promotion: the epilogue must have read the previous tile out of the accumulator
+                        if (n > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((n - 1) & 1), a.status, KID_TCP, 3)) dead = true;
+                        tc_fence_after();
+                    }
                     const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
                     if (elect_one()) {
                         // each issuer keeps its own copy of the stage's scales in tensor memory
-                        const uint32_t sfa = tmu + Cfg::TM_SFA + 4 * (2 * s + j), sfb = tmu + Cfg::TM_SFB + 4 * (2 * s + j);
+                        const uint32_t sfa = tmu + Cfg::TM_SFA + 4 * (2 * s + j);
+                        uint32_t sfb = ones_b;
                         tc_cp_sf(sfa, fa0 + so);
-                        tc_cp_sf(sfb, fb0 + so);
+                        if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * (2 * s + j); tc_cp_sf(sfb, fb0 + so); }
 #pragma unroll
                         for (int kc = 0; kc < 4; ++kc)
                             tc_mma_mx(d, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
-                                      (kt == 0 && kc == 0) ? 0u : 1u);
+                                      ((!AMX || kt == 0) && kc == 0) ? 0u : 1u);
                         tc_commit(&empty_bar[s]);
-                        if (kt + 1 == KT) tc_commit(&tfull_bar[j]);
+                        if (!AMX || kt + 1 == KT) tc_commit(&tfull_bar[j]);
                     }
                     __syncwarp();
                     if (++s == S) { s = 0; ph ^= 1; }
@@ -169,9 +193,9 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         const int r = 32 * q4 + lane;
         const uint32_t taddr = tm + ((uint32_t)(32 * q4) << 16) + ga * 128 + cb;
         float acc[64];
-        long long nit = 0;
-        for (long long it = ibeg; it < iend; ++it, ++nit) {
-            const int slot = (int)(it / RP), rp = (int)(it - (long long)slot * RP);
+        int nit = 0, n = 0;
+        for (int it = ibeg; it < iend; ++it, ++nit) {
+            const int slot = it / RP, rp = it - slot * RP;
             const int rt = 2 * rp + ga;
             const int4 sl = a.slots[slot];
             const int xrow0 = sl.y, cnt = sl.z;
@@ -181,13 +205,42 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                 rw0 = (cb + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + lane) : 0.f;
                 rw1 = (cb + 32 + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 + lane) : 0.f;
             }
-            if (!dead && !mbar_wait(&tfull_bar[ga], (uint32_t)(nit & 1), a.status, KID_TCP, 5)) dead = true;
-            tc_fence_after();
-            tmem_ld<32>(taddr, acc);
-            tmem_ld<32>(taddr + 32, acc + 32);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty_bar[ga]);
+            if (AMX) {
+                if (!dead && !mbar_wait(&tfull_bar[ga], (uint32_t)(nit & 1), a.status, KID_TCP, 5)) dead = true;
+                tc_fence_after();
+                tmem_ld<32>(taddr, acc);
+                tmem_ld<32>(taddr + 32, acc + 32);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty_bar[ga]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+                for (int kt = 0; kt < KT; ++kt, ++n) {
+                    if (!dead && !mbar_wait(&tfull_bar[ga], (uint32_t)(n & 1), a.status, KID_TCP, 5)) dead = true;
+                    tc_fence_after();
+                    const float* xs = s_xs + (n & (XR - 1)) * 128 + cb;
+#pragma unroll
+                    for (int c0 = 0; c0 < 64; c0 += 16) {
+                        float v[16];
+                        tmem_ld<16>(taddr + c0, v);
+                        if (c0 == 48) {
+                            // everything is in registers: hand the accumulator back before the arithmetic
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&tempty_bar[ga]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            const float4 t4 = *(const float4*)(xs + c0 + j);
+                            acc[c0 + j] = fmaf(v[j], t4.x, acc[c0 + j]);
+                            acc[c0 + j + 1] = fmaf(v[j + 1], t4.y, acc[c0 + j + 1]);
+                            acc[c0 + j + 2] = fmaf(v[j + 2], t4.z, acc[c0 + j + 2]);
+                            acc[c0 + j + 3] = fmaf(v[j + 3], t4.w, acc[c0 + j + 3]);
+                        }
+                    }
+                }
+            }
             if (EPI == EPI_W13) {
                 // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group); after the
                 // exchange the gate lane finishes column j, the up lane column j + 1.
