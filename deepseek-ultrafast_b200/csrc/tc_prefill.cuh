@@ -21,6 +21,13 @@ namespace dsuf {
 
 constexpr int KID_TCP = 4;
 
+#ifdef DSUF_TC_TIMING
+// event trace of CTA 0, steps [256, 320): [step][16] clock values behind the [grid][8] counters
+#define TCP_TRACE(n, k) do { if (a.dbg && c == 0 && (n) >= 256 && (n) < 320 && lane == 0) a.dbg[(long long)G * 8 + ((n) - 256) * 16 + (k)] = clock64(); } while (0)
+#else
+#define TCP_TRACE(n, k)
+#endif
+
 struct TcpCfg {
     static constexpr int A_BYTES = 16384;            // one weight tile, FP4 widened to 8-bit containers by TMA
     static constexpr int B_OFF = 2 * A_BYTES;        // 128 token rows of 128 bytes
@@ -103,7 +110,9 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                 int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
                 const uint8_t* sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
                 for (int kt = 0; kt < KT; ++kt, ++n) {
+                    TCP_TRACE(n, 0 + 3 * j);
                     if (n >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TCP, 1 + j)) dead = true;
+                    TCP_TRACE(n, 1 + 3 * j);
                     uint8_t* st = ring + s * Cfg::STAGE;
                     if (elect_one()) {
                         // TMA counts the bytes it reads: 8192 for a packed FP4 tile that fills 16384 of shared memory
@@ -123,6 +132,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                         }
                         cp_async_arrive_noinc(&full_bar[s]);
                     }
+                    TCP_TRACE(n, 2 + 3 * j);
                     ++tile;
                     sf_src += a.rec_bytes;
                     if (++s == S) { s = 0; ph ^= 1; }
@@ -150,6 +160,10 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             int s = 0;
             uint32_t ph = 0;
             int nit = 0, n = 0;
+#ifdef DSUF_TC_TIMING
+            unsigned long long gt0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
+            const long long ck0 = clock64();
+#endif
             for (int it = ibeg; it < iend; ++it, ++nit) {
                 if (AMX) {
                     // the accumulator is single-buffered: wait until the epilogue has drained the previous item
@@ -157,7 +171,9 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     tc_fence_after();
                 }
                 for (int kt = 0; kt < KT; ++kt, ++n) {
+                    TCP_TRACE(n, 6 + 3 * j);
                     if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TCP, 4)) dead = true;
+                    TCP_TRACE(n, 7 + 3 * j);
                     if (AMX) {
                         fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                     } else {
@@ -180,9 +196,16 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                         if (!AMX || kt + 1 == KT) tc_commit(&tfull_bar[j]);
                     }
                     __syncwarp();
+                    TCP_TRACE(n, 8 + 3 * j);
                     if (++s == S) { s = 0; ph ^= 1; }
                 }
             }
+#ifdef DSUF_TC_TIMING
+            if (a.dbg && j == 0 && lane == 0) {
+                unsigned long long gt1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
+                a.dbg[c * 8 + 3] = clock64() - ck0; a.dbg[c * 8 + 6] = (long long)(gt1 - gt0); a.dbg[c * 8 + 4] = n;
+            }
+#endif
         }
     } else if (warp >= Cfg::EPI_WARP0) {
         // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================

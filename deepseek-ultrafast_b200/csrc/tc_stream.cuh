@@ -23,7 +23,7 @@ namespace dsuf {
 
 constexpr int KID_TC = 3;
 // warp 0: weight producer, 1: MMA issuer A, 2-5: epilogue, 6: activation producer, 7: MMA issuer B,
-// 8 / 9: second weight / activation producer (token tiles up to 64 columns)
+// 8 / 9: second weight / activation producer, 10-13: second epilogue group, 14 / 15: MMA issuers C / D
 constexpr int TC_EPI_THREADS = 128;
 
 template <int N>
@@ -37,7 +37,10 @@ struct TcCfg {
     static constexpr int NE = N <= 16 ? 2 : 1;        // epilogue warp groups (per-tile mode: alternate tiles)
     static constexpr int RED_BYTES = NE == 2 ? 2 * N * 128 * 4 : 0;  // static shared memory of the group combine
     static constexpr int S_FIT = (226 * 1024 - 2048 - RED_BYTES) / STAGE;
-    static constexpr int STAGES = (S_FIT > 12 ? 12 : S_FIT) & ~1;  // even: two issuers walk the ring in steps of two
+    // A multiple of the number of issuers (4 for N <= 16, else 2), so that every stage is always handled by the
+    // same issuer: a parity wait cannot tell phase p from phase p + 2, and only the issuer that consumed phase p - 1
+    // of a stage is certain not to reach the wait before phase p has begun.
+    static constexpr int STAGES = (S_FIT > 12 ? 12 : S_FIT) & ~(N <= 16 ? 3 : 1);
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
     static constexpr int SUB = 1;                    // sub-accumulators per ring entry (4 = one per K=32 step; measured: no gain)
@@ -45,7 +48,7 @@ struct TcCfg {
     static constexpr int NB = ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
     static constexpr int XS_ENTRY = 4 * N + 16;      // per-tile fp32 scales: N activation scales + the weight scale, one entry per accumulator
     static constexpr int NP = 2;                      // producer warps per kind (weights / activations), alternate tiles
-    static constexpr int THREADS = 256 + 64 * (NP - 1) + 128;  // second producers (NP == 2), then the second epilogue group
+    static constexpr int THREADS = 256 + 64 * (NP - 1) + 128 + 64;  // second producers, the second epilogue group, issuers C and D
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
     static_assert(NB * ACC_COLS <= 256 && STAGES >= 4 && N <= 128, "tensor-memory / shared-memory budget");
 };
@@ -68,7 +71,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     using Cfg = TcCfg<N>;
     constexpr int S = Cfg::STAGES, ACC_COLS = Cfg::ACC_COLS, SUB = Cfg::SUB;
     constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
-    constexpr int NI = PER_TILE ? 2 : 1;    // MMA-issuing warps of the per-tile mode
+    // MMA-issuing warps of the per-tile mode: an issuer spends ~600 cycles per tile of its own (waits, fences, scale
+    // copies, commits around 4 MMAs), so narrow token tiles (180 cycles of MMA per tile) take four to keep up with HBM
+    constexpr int NI = PER_TILE ? (N <= 16 ? 4 : 2) : 1;
+    static_assert(S % NI == 0 && S % 2 == 0, "stage ownership must not rotate among issuers (parity waits alias)");
     // whole-K mode with token tiles up to 64 columns: two issuers as well, alternate tiles, each accumulating into its
     // own half of the ring entry; the epilogue adds the halves
     constexpr bool DUAL_WHOLE = !PER_TILE && N <= 64;
@@ -268,9 +274,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 
 #endif
         }
-    } else if (warp == 1 || warp == 7) {
+    } else if (warp == 1 || warp == 7 || (NI == 4 && warp >= EG1 + 4)) {
         // ================= MMA issuers (one thread each; issuer B only in the per-tile mode) =================
-        const int j = warp == 1 ? 0 : 1;
+        const int j = warp == 1 ? 0 : warp == 7 ? 1 : warp - (EG1 + 4) + 2;
         // The whole warp runs the loop and one elected lane issues: tcgen05 operands are uniform-register operands,
         // and a loop run by a single lane of a diverged warp pays a register-file round trip for each of them.
         if (DUAL_WHOLE) {
@@ -418,7 +424,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             }
 #endif
         }
-    } else if ((warp >= 2 && warp <= 5) || ((NE == 2 || CSPLIT) && warp >= EG1)) {
+    } else if ((warp >= 2 && warp <= 5) || ((NE == 2 || CSPLIT) && warp >= EG1 && warp < EG1 + 4)) {
         // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
         // per-tile mode with narrow token tiles: two groups of four warps take alternate tiles and add up at item end
         const int eg = warp >= EG1 ? 1 : 0;
