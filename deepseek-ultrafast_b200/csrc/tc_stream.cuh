@@ -23,7 +23,8 @@ namespace dsuf {
 
 constexpr int KID_TC = 3;
 // warp 0: weight producer, 1: MMA issuer A, 2-5: epilogue, 6: activation producer, 7: MMA issuer B,
-// 8 / 9: second weight / activation producer, 10-13: second epilogue group, 14 / 15: MMA issuers C / D
+// 8 / 9: second weight / activation producer, 10-13: second epilogue group, 14 / 15: MMA issuers C / D,
+// 16 / 17 and 18 / 19: weight and activation producers C / D (token tiles up to 16 columns)
 constexpr int TC_EPI_THREADS = 128;
 
 template <int N>
@@ -46,9 +47,10 @@ struct TcCfg {
     static constexpr int SUB = 1;                    // sub-accumulators per ring entry (4 = one per K=32 step; measured: no gain)
     static constexpr int ACC_COLS = SUB * N;
     static constexpr int NB = ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
-    static constexpr int XS_ENTRY = 4 * N + 16;      // per-tile fp32 scales: N activation scales + the weight scale, one entry per accumulator
-    static constexpr int NP = 2;                      // producer warps per kind (weights / activations), alternate tiles
-    static constexpr int THREADS = 256 + 64 * (NP - 1) + 128 + 64;  // second producers, the second epilogue group, issuers C and D
+    // producer warps per kind (weights / activations), tiles dealt round-robin: a producer spends ~1100 cycles per tile
+    // of its own (two barrier waits, the copies, the scale gathers), so narrow token tiles take four of each kind
+    static constexpr int NP = 2;  // (four of each kind were measured: no gain)
+    static constexpr int THREADS = 512 + (NP == 4 ? 128 : 0);  // 16 warps + producers C and D of each kind
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
     static_assert(NB * ACC_COLS <= 256 && STAGES >= 4 && N <= 128, "tensor-memory / shared-memory budget");
 };
@@ -74,12 +76,13 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     // MMA-issuing warps of the per-tile mode: an issuer spends ~600 cycles per tile of its own (waits, fences, scale
     // copies, commits around 4 MMAs), so narrow token tiles (180 cycles of MMA per tile) take four to keep up with HBM
     constexpr int NI = PER_TILE ? (N <= 16 ? 4 : 2) : 1;
-    static_assert(S % NI == 0 && S % 2 == 0, "stage ownership must not rotate among issuers (parity waits alias)");
-    // whole-K mode with token tiles up to 64 columns: two issuers as well, alternate tiles, each accumulating into its
-    // own half of the ring entry; the epilogue adds the halves
+    // whole-K mode with token tiles up to 64 columns: several issuers as well (four up to 16 columns, else two), tiles
+    // dealt round-robin, each accumulating into its own part of the ring entry; the epilogue adds the parts
     constexpr bool DUAL_WHOLE = !PER_TILE && N <= 64;
-    constexpr int ACCW = DUAL_WHOLE ? 2 * ACC_COLS : ACC_COLS;  // tensor-memory columns of one ring entry
-    constexpr int NB = Cfg::NB * ACCW > 256 ? Cfg::NB / 2 : Cfg::NB;  // ring entries in use
+    constexpr int NIW = !DUAL_WHOLE ? 1 : N <= 16 ? 4 : 2;
+    constexpr int ACCW = NIW * ACC_COLS;  // tensor-memory columns of one ring entry
+    static_assert(S % NI == 0 && S % NIW == 0 && S % Cfg::NP == 0, "stage ownership must not rotate among issuers or producers (parity waits alias)");
+    constexpr int NB = Cfg::NB * ACCW > 256 ? 256 / ACCW : Cfg::NB;  // ring entries in use (a power of two)
     static_assert(NB * ACCW <= 256, "accumulator ring overlaps the scale columns");
     constexpr int NP = Cfg::NP;
     // epilogue groups actually working: the second group pays off where tiles are 8.7 KB (FP4 experts), not for dense FP8
@@ -87,7 +90,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     // wide token tiles: the two epilogue groups split the token COLUMNS of every accumulator instead
     constexpr bool CSPLIT = N >= 32;
     constexpr int NC = CSPLIT ? N / 2 : N;            // columns per epilogue thread
-    constexpr int EG1 = 8 + 2 * (NP - 1);             // first warp of the second epilogue group
+    constexpr int EG1 = 10;                           // first warp of the second epilogue group
     constexpr int EPI_BAR = CSPLIT ? 256 : 128;       // threads meeting at the dense stream-K fix-up
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -95,7 +98,14 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     static_assert((NB & (NB - 1)) == 0, "accumulator ring size must be a power of two");
     __shared__ uint32_t s_tmem;
     __shared__ int s_flag;
-    __shared__ __align__(16) uint8_t s_xs[NB * Cfg::XS_ENTRY];  // DS scales travel with the accumulator, not with the stage
+    // DS scales outlive the stage (the epilogue reads them after the MMAs completed).  A ring of XR >= S + NB entries
+    // indexed by tile number needs no barrier of its own: a producer writing tile n has seen the MMAs of tile n - S
+    // complete, which were issued only after the epilogue had released the accumulator of tile n - S - NB, and the
+    // epilogue reads a tile's scales before it releases its accumulator.
+    constexpr int XSE = 4 * N + (WMX ? 0 : 16);  // entry: N activation scales (+ the tile's weight scale, DS weights)
+    constexpr int XR = S + NB <= 16 ? 16 : 32;
+    static_assert(S + NB <= XR, "scale ring shorter than stages + accumulators");
+    __shared__ __align__(16) uint8_t s_xs[XR * XSE];
     __shared__ float s_red[Cfg::NE == 2 ? 2 * N * 128 : 1];  // second epilogue group -> first, double buffered by item
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -113,7 +123,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             mbar_init(&empty_bar[s], 1);  // tcgen05.commit: the tensor core has finished reading the stage
         }
         for (int b = 0; b < NB; ++b) {
-            mbar_init(&tfull_bar[b], DUAL_WHOLE ? 2 : 1);
+            mbar_init(&tfull_bar[b], NIW);
             mbar_init(&tempty_bar[b], CSPLIT ? 8 : 4);
         }
         mbar_fence_init();
@@ -142,9 +152,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         end = ((long long)(c + 1) * q / G) * KT;
     }
 
-    if (warp == 0 || (NP == 2 && warp == 8)) {
-        // ================= weight producers (warp 8 takes the odd tiles when NP == 2): tile codes + scale atom =================
-        const int pj = warp == 0 ? 0 : 1;
+    if (warp == 0 || warp == 8 || (NP == 4 && (warp == 16 || warp == 17))) {
+        // ================= weight producers (tiles dealt round-robin): tile codes + scale atom =================
+        const int pj = warp == 0 ? 0 : warp == 8 ? 1 : warp - 14;
         // The whole warp runs the loop (so every value stays warp-uniform and the TMA descriptors live in uniform
         // registers); one elected lane issues.
         if (pj < NP && beg + pj < end) {
@@ -204,9 +214,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 
 #endif
         }
-    } else if (warp == 6 || (NP == 2 && warp == 9)) {
+    } else if (warp == 6 || warp == 9 || (NP == 4 && (warp == 18 || warp == 19))) {
         // ================= activation producers: token rows by TMA, their block scales by 4-byte async copies =================
-        const int pj = warp == 6 ? 0 : 1;
+        const int pj = warp == 6 ? 0 : warp == 9 ? 1 : warp - 16;
         if (pj < NP && beg + pj < end) {
             if (lane == 0) prefetch_tmap(&a.tm_x);
             const uint64_t pol_x = policy_evict_last();
@@ -250,10 +260,8 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 __syncwarp();
                 uint8_t* xe = nullptr;
                 if (PER_TILE) {
-                    // fp32 scales go to the entry of the accumulator this tile will use, free once the epilogue released it
-                    const int tn = (int)(i - beg), tb = tn & (NB - 1);
-                    if (tn >= NB && !dead && !mbar_wait(&tempty_bar[tb], ((tn / NB) - 1) & 1, a.status, KID_TC, 6)) dead = true;
-                    xe = s_xs + tb * Cfg::XS_ENTRY;
+                    // fp32 scales go to the tile's entry of the scale ring (free by construction, see s_xs)
+                    xe = s_xs + ((int)(i - beg) & (XR - 1)) * XSE;
                 }
 #pragma unroll
                 for (int n = lane; n < N; n += 32) {
@@ -274,16 +282,16 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 
 #endif
         }
-    } else if (warp == 1 || warp == 7 || (NI == 4 && warp >= EG1 + 4)) {
+    } else if (warp == 1 || warp == 7 || ((NI == 4 || NIW == 4) && (warp == 14 || warp == 15))) {
         // ================= MMA issuers (one thread each; issuer B only in the per-tile mode) =================
-        const int j = warp == 1 ? 0 : warp == 7 ? 1 : warp - (EG1 + 4) + 2;
+        const int j = warp == 1 ? 0 : warp == 7 ? 1 : warp - 12;
         // The whole warp runs the loop and one elected lane issues: tcgen05 operands are uniform-register operands,
         // and a loop run by a single lane of a diverged warp pays a register-file round trip for each of them.
         if (DUAL_WHOLE) {
             if (beg < end) {
-                // Both issuers walk every tile of the span (so both know the group boundaries); issuer j issues the
-                // tiles of parity j into columns [j*N, (j+1)*N) of the ring entry.  tfull needs both: a commit from an
-                // issuer that contributed MMAs, a plain arrival from one that did not.
+                // Every issuer walks every tile of the span (so all know the group boundaries); issuer j issues the tiles
+                // j, j + NIW, ... into columns [j*N, (j+1)*N) of the ring entry.  tfull needs all of them: a commit from
+                // an issuer that contributed MMAs, a plain arrival from one that did not.
                 const uint32_t tmu = uni32(tm);
                 const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
                 const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
@@ -301,7 +309,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 uint32_t ph = 0;
                 bool issued = false, entry_free = false;
                 for (long long i = beg; i < end; ++i) {
-                    const bool mine = ((int)(i - beg) & 1) == j;
+                    const bool mine = ((int)(i - beg) & (NIW - 1)) == j;
                     const bool group_end = kt + 1 == KT || i + 1 == end;
                     const int b = gidx & (NB - 1);
                     if ((mine || group_end) && !entry_free) {
@@ -477,26 +485,34 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 DSUF_TACC(te_wait, te0);
                 DSUF_T0(tl0);
                 tc_fence_after();
-                {
-                    const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + b * Cfg::XS_ENTRY + 4 * N) : 1.0f;
+                if (!DSUF_PROBE(16)) {
+                    const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * N) : 1.0f;
                     constexpr int CH = NC < 32 ? NC : 32;
-                    // two issuers in the whole-K mode: which halves of the entry hold this group's sums
-                    const bool lone = DUAL_WHOLE && i == g0;
-                    const bool has0 = !lone || (((int)(g0 - beg) & 1) == 0);
+                    // several issuers in the whole-K mode: part p of the entry holds a sum iff the group, which started at
+                    // tile g0 and has gcnt tiles, contains a tile dealt to issuer p; the parts are added in a fixed order
+                    const int gcnt = (int)(i - g0) + 1, gph = (int)(g0 - beg) & (NIW - 1);
 #pragma unroll
                     for (int c0 = 0; c0 < NC; c0 += CH) {
                         float v[CH];
-                        tmem_ld<CH>(tm + lane_base + b * ACCW + (has0 ? 0 : N) + cb + c0, v);
-                        if (DUAL_WHOLE && !lone) {
-                            float v2[CH];
-                            tmem_ld<CH>(tm + lane_base + b * ACCW + N + cb + c0, v2);
+                        if (DUAL_WHOLE) {
 #pragma unroll
-                            for (int j = 0; j < CH; ++j) v[j] += v2[j];
+                            for (int j = 0; j < CH; ++j) v[j] = 0.f;
+#pragma unroll
+                            for (int p = 0; p < NIW; ++p) {
+                                if (gcnt >= NIW || ((p - gph) & (NIW - 1)) < gcnt) {
+                                    float v2[CH];
+                                    tmem_ld<CH>(tm + lane_base + b * ACCW + p * N + cb + c0, v2);
+#pragma unroll
+                                    for (int j = 0; j < CH; ++j) v[j] += v2[j];
+                                }
+                            }
+                        } else {
+                            tmem_ld<CH>(tm + lane_base + b * ACCW + cb + c0, v);
                         }
                         if (PER_TILE) {
 #pragma unroll
                             for (int j = 0; j < CH; j += 4) {
-                                const float4 t4 = *(const float4*)(s_xs + b * Cfg::XS_ENTRY + 4 * (cb + c0 + j));
+                                const float4 t4 = *(const float4*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * (cb + c0 + j));
                                 acc[c0 + j] = fmaf(v[j], wds * t4.x, acc[c0 + j]);
                                 acc[c0 + j + 1] = fmaf(v[j + 1], wds * t4.y, acc[c0 + j + 1]);
                                 acc[c0 + j + 2] = fmaf(v[j + 2], wds * t4.z, acc[c0 + j + 2]);

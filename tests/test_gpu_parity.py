@@ -254,6 +254,15 @@ def test_moe_layer_prefill_tiles_of_128_rows(pkg, ctx, act_mode, T, E, K):
     _moe_case(pkg, ctx, act_mode, T=T, H=256, I=128, E=E, K=K, tile_rows=128, seed=T)
 
 
+@pytest.mark.parametrize("act_mode", [0, 1])
+def test_moe_layer_prefill_odd_number_of_row_tiles(pkg, ctx, act_mode):
+    """The prefill kernel pairs weight row tiles; the down projection of a 384-wide model has 3 row tiles and takes the
+    single-tile kernel instead (the gate/up projection, 2 row tiles x 3 K tiles, still takes the paired one)."""
+    if not ctx.tcgen05:
+        pytest.skip("128-row plans run on the tcgen05 path only")
+    _moe_case(pkg, ctx, act_mode, T=300, H=384, I=128, E=4, K=2, tile_rows=128, seed=11)
+
+
 def test_moe_layer_clamp_and_shared_expert_term(pkg, ctx):
     _moe_case(pkg, ctx, 1, T=16, H=256, I=128, E=8, K=2, tile_rows=8, seed=3, limit=0.05, shared=True)
 
