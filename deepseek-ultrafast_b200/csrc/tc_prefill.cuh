@@ -145,7 +145,6 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         const int j = warp >> 1;
         if (ibeg < iend) {
             const uint32_t tmu = uni32(tm);
-            const uint32_t idesc = tc_idesc_mx(128, true);
             const uint64_t ad0 = uni64(tc_smem_desc(ring + j * Cfg::A_BYTES, 16, 1024, 2)),
                            bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
             const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF + j * 512, 512, 128, 0)),
@@ -165,6 +164,10 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             const long long ck0 = clock64();
 #endif
             for (int it = ibeg; it < iend; ++it, ++nit) {
+                // the MMA's N follows the rows the slot really holds (a multiple of 16): the last tile of an expert is
+                // rarely full, and a 48-column MMA takes 60 cycles where a 128-column one takes 97
+                const int cnt = a.slots[it / RP].z;
+                const uint32_t idesc = tc_idesc_mx(cnt >= 113 ? 128 : cnt <= 16 ? 16 : (cnt + 15) & ~15, true);
                 if (AMX) {
                     // the accumulator is single-buffered: wait until the epilogue has drained the previous item
                     if (nit > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
