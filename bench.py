@@ -415,6 +415,19 @@ def run_ours(args):
                                                           "gbs": round(e_act0 * (w13_b + w2_b) / (ms_mx * 1e-3) / 1e9, 1)},
                                      "prefill_moe": prefill_moe(pkg, ctx, torch, stack, args.prefill_tokens, pkg.MODE_MX)}
             del lmx
+        # cfg4's prefill leg on one GPU: the whole 4-layer stack (dense FP8 projection + routed experts) over a
+        # prefill-size batch, sharing the decode stack's weights
+        tp = args.prefill_tokens
+        pcfg = stackmod.StackConfig(hidden=H, inter=I, n_experts=E, topk=TOPK, layers=LAYERS, tokens=tp, act_mode=amode, dense_mode=amode)
+        pstack = stackmod.LayerStack(ctx, pcfg, weights_from=stack)
+        xp = torch.randn(tp, H, generator=torch.Generator(device="cuda").manual_seed(77), device="cuda").bfloat16()
+        ms_p = time_events(torch, lambda: pstack.forward(xp), 3, 1)
+        flop_layer = 2.0 * tp * H * H + 6.0 * tp * TOPK * I * H
+        result["prefill_stack"] = {"tokens": tp, "layers": LAYERS, "ms": round(ms_p, 3), "tokens_per_s": round(tp / (ms_p * 1e-3), 1),
+                                   "tflops": round(LAYERS * flop_layer / (ms_p * 1e-3) / 1e12, 1),
+                                   "routing": "softmax of N(0,1) logits, top-8 (near-uniform expert load)",
+                                   "launches_per_layer": pstack.count_launches() // LAYERS, "device_status": int(ctx.status().code)}
+        del pstack, xp
     if world == 1 and not args.skip_cpu:
         p = cpu_prepare()
         vals, dts, t_all = [], [], time.perf_counter()

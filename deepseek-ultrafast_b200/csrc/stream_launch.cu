@@ -60,7 +60,8 @@ int stream_setup(dsuf_ctx* ctx) {
     ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2); ST(FMT_FP4, 1, 1, 128, EPI_W2);
 #undef ST
     for (const void* f : {(const void*)tc_prefill_kernel<EPI_W13, 1>, (const void*)tc_prefill_kernel<EPI_W2, 1>,
-                          (const void*)tc_prefill_kernel<EPI_W13, 0>, (const void*)tc_prefill_kernel<EPI_W2, 0>}) {
+                          (const void*)tc_prefill_kernel<EPI_W13, 0>, (const void*)tc_prefill_kernel<EPI_W2, 0>,
+                          (const void*)tc_prefill_kernel<EPI_DENSE, 1, FMT_FP8, 1>, (const void*)tc_prefill_kernel<EPI_DENSE, 0, FMT_FP8, 0>}) {
         cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, TcpCfg::SMEM);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_prefill)");
     }
@@ -88,13 +89,31 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
                         void* out, int ldo, float alpha, void* workspace, int* counters_at) {
     DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP8 && w->d.n_experts == 1, "dsuf_gemm_fp8: weight is not a dense FP8 weight");
-    const int m_max = ctx->use_tc ? 64 : 16;
-    DSUF_REQUIRE(ctx, m >= 1 && m <= m_max, "dsuf_gemm_fp8: this decode path takes 1..%d token rows per call, got %d", m_max, m);
-    DSUF_REQUIRE(ctx, w->rt <= WS_MAX_ROW_TILES, "dsuf_gemm_fp8: too many row tiles (%d)", w->rt);
     DSUF_REQUIRE(ctx, ldo >= w->d.n, "dsuf_gemm_fp8: ldo %d < n %d", ldo, w->d.n);
-    DSUF_REQUIRE(ctx, xq && xs && out && workspace, "dsuf_gemm_fp8: null pointer");
+    DSUF_REQUIRE(ctx, xq && xs && out, "dsuf_gemm_fp8: null pointer");
     StreamArgs a;
     fill_common(ctx, a, w);
+    if (ctx->use_tc && m > 64) {
+        // prefill-size M: 128-token tiles x pairs of weight row tiles (tc_prefill.cuh); needs no workspace
+        DSUF_REQUIRE(ctx, (w->rt & 1) == 0, "dsuf_gemm_fp8: more than 64 token rows need an even number of 128-row weight tiles, got %d", w->rt);
+        int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, 128);
+        if (rc) return rc;
+        a.tm_w = w->tm_tc;
+        a.xscale = xs;
+        a.out = out;
+        a.m = m;
+        a.x_rows = m;
+        a.ldo = ldo;
+        a.alpha = alpha;
+        const int grid = ctx->sm_count;
+#define GD(AMX, WMX) launch(ctx, stream, tc_prefill_kernel<EPI_DENSE, AMX, FMT_FP8, WMX>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a)
+        return w->d.mode == DSUF_MODE_MX ? GD(1, 1) : GD(0, 0);
+#undef GD
+    }
+    const int m_max = ctx->use_tc ? 64 : 16;
+    DSUF_REQUIRE(ctx, m >= 1 && m <= m_max, "dsuf_gemm_fp8: the mma.sync decode path takes 1..%d token rows per call, got %d", m_max, m);
+    DSUF_REQUIRE(ctx, w->rt <= WS_MAX_ROW_TILES, "dsuf_gemm_fp8: too many row tiles (%d)", w->rt);
+    DSUF_REQUIRE(ctx, workspace, "dsuf_gemm_fp8: null workspace");
     const int nt8 = m <= 8 ? 1 : 2;
     const int ntok = m <= 8 ? 8 : m <= 16 ? 16 : m <= 32 ? 32 : 64;
     int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, ntok);

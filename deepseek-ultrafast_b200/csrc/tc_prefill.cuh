@@ -48,9 +48,17 @@ struct TcpCfg {
 // AMX = 0: fp32 activation scales per 1x128 (DS geometry): every 128-K tile is promoted into fp32 registers with
 //          its scales.  The accumulators stay single-buffered: while the epilogue reads accumulator j, the other
 //          issuer's MMAs keep the tensor pipe busy.
-template <int EPI, int AMX>
+// FMT / WMX: FP4 expert tiles (UE8M0 weight scales in the tile record) or dense FP8 weights with UE8M0 (MX) or fp32
+// 128x128 (DS) scales.  EPI_DENSE: the "slots" are the 128-row tiles of the a.m token rows of one dense matrix.
+template <int EPI, int AMX, int FMT = FMT_FP4, int WMX = 1>
 __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __grid_constant__ StreamArgs a) {
     using Cfg = TcpCfg;
+    static_assert(WMX || !AMX, "fp32 weight scales are promoted per K tile together with fp32 activation scales");
+    // (expert, first token row, token rows, -) of a slot
+    auto slot_of = [&](int slot) -> int4 {
+        if (EPI == EPI_DENSE) return make_int4(0, slot * 128, min(128, a.m - slot * 128), 0);
+        return a.slots[slot];
+    };
     constexpr int S = Cfg::STAGES;
     constexpr int XR = 8;  // ring of fp32 activation scales (DS): outlives the stage, read after the MMAs completed
     __shared__ __align__(16) float s_xs[AMX ? 4 : XR * 128];
@@ -89,7 +97,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
     pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
 
     // items = (slot, row-tile pair); every CTA takes a contiguous range
-    const long long nitems = (long long)(*a.nslots) * RP;  // far below 2^31: slots <= permuted rows / 128 + experts
+    const long long nitems = (long long)(EPI == EPI_DENSE ? (a.m + 127) / 128 : *a.nslots) * RP;  // far below 2^31: slots <= permuted rows / 128 + experts
     const int ibeg = (int)((long long)c * nitems / G), iend = (int)((long long)(c + 1) * nitems / G);
 
     if (warp == 0 || warp == 2) {
@@ -105,7 +113,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             int n = 0;
             for (int it = ibeg; it < iend; ++it) {
                 const int slot = it / RP, rp = it - slot * RP;
-                const int4 sl = a.slots[slot];
+                const int4 sl = slot_of(slot);
                 const int xrow0 = sl.y;
                 int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
                 const uint8_t* sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
@@ -116,9 +124,9 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     uint8_t* st = ring + s * Cfg::STAGE;
                     if (elect_one()) {
                         // TMA counts the bytes it reads: 8192 for a packed FP4 tile that fills 16384 of shared memory
-                        mbar_expect_tx(&full_bar[s], 8192 + 512 + (j == 0 ? 16384 : 0));
+                        mbar_expect_tx(&full_bar[s], (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0) + (j == 0 ? 16384 : 0));
                         tma_3d_nh(st + j * Cfg::A_BYTES, &a.tm_w, 0, 0, tile, &full_bar[s]);
-                        bulk_g2s(st + Cfg::SFA_OFF + j * 512, sf_src, 512, &full_bar[s], pol);
+                        if (WMX) bulk_g2s(st + Cfg::SFA_OFF + j * 512, sf_src, 512, &full_bar[s], pol);
                         if (j == 0) tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol);
                     }
                     __syncwarp();
@@ -150,10 +158,13 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF + j * 512, 512, 128, 0)),
                            fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
             const uint32_t d = tmu + j * 128;
-            const uint32_t ones_b = tmu + Cfg::TM_SFB + 4 * (2 * S + j);
+            const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (2 * S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (2 * S + j);
             if (!AMX) {
                 const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));  // shuffles: outside the election
-                if (elect_one()) tc_cp_sf(ones_b, ones_d);
+                if (elect_one()) {
+                    tc_cp_sf(ones_b, ones_d);
+                    if (!WMX) tc_cp_sf(ones_a, ones_d);
+                }
                 __syncwarp();
             }
             int s = 0;
@@ -166,8 +177,8 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             for (int it = ibeg; it < iend; ++it, ++nit) {
                 // the MMA's N follows the rows the slot really holds (a multiple of 16): the last tile of an expert is
                 // rarely full, and a 48-column MMA takes 60 cycles where a 128-column one takes 97
-                const int cnt = a.slots[it / RP].z;
-                const uint32_t idesc = tc_idesc_mx(cnt >= 113 ? 128 : cnt <= 16 ? 16 : (cnt + 15) & ~15, true);
+                const int cnt = slot_of(it / RP).z;
+                const uint32_t idesc = tc_idesc_mx(cnt >= 113 ? 128 : cnt <= 16 ? 16 : (cnt + 15) & ~15, FMT == FMT_FP4);
                 if (AMX) {
                     // the accumulator is single-buffered: wait until the epilogue has drained the previous item
                     if (nit > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
@@ -187,9 +198,8 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
                     if (elect_one()) {
                         // each issuer keeps its own copy of the stage's scales in tensor memory
-                        const uint32_t sfa = tmu + Cfg::TM_SFA + 4 * (2 * s + j);
-                        uint32_t sfb = ones_b;
-                        tc_cp_sf(sfa, fa0 + so);
+                        uint32_t sfa = ones_a, sfb = ones_b;
+                        if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * (2 * s + j); tc_cp_sf(sfa, fa0 + so); }
                         if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * (2 * s + j); tc_cp_sf(sfb, fb0 + so); }
 #pragma unroll
                         for (int kc = 0; kc < 4; ++kc)
@@ -223,7 +233,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         for (int it = ibeg; it < iend; ++it, ++nit) {
             const int slot = it / RP, rp = it - slot * RP;
             const int rt = 2 * rp + ga;
-            const int4 sl = a.slots[slot];
+            const int4 sl = slot_of(slot);
             const int xrow0 = sl.y, cnt = sl.z;
             float rw0 = 0.f, rw1 = 0.f;
             if (EPI == EPI_W13) {
@@ -243,6 +253,8 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
 #pragma unroll
                 for (int j = 0; j < 64; ++j) acc[j] = 0.f;
                 for (int kt = 0; kt < KT; ++kt, ++n) {
+                    // DS weights: the tile's fp32 128x128 block scale, fetched before the wait
+                    const float wds = WMX ? 1.0f : __ldg(a.wscale_ds + (size_t)rt * KT + kt);
                     if (!dead && !mbar_wait(&tfull_bar[ga], (uint32_t)(n & 1), a.status, KID_TCP, 5)) dead = true;
                     tc_fence_after();
                     const float* xs = s_xs + (n & (XR - 1)) * 128 + cb;
@@ -258,7 +270,8 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                         }
 #pragma unroll
                         for (int j = 0; j < 16; j += 4) {
-                            const float4 t4 = *(const float4*)(xs + c0 + j);
+                            float4 t4 = *(const float4*)(xs + c0 + j);
+                            if (!WMX) { t4.x *= wds; t4.y *= wds; t4.z *= wds; t4.w *= wds; }
                             acc[c0 + j] = fmaf(v[j], t4.x, acc[c0 + j]);
                             acc[c0 + j + 1] = fmaf(v[j + 1], t4.y, acc[c0 + j + 1]);
                             acc[c0 + j + 2] = fmaf(v[j + 2], t4.z, acc[c0 + j + 2]);
@@ -288,6 +301,12 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                         ocol[(size_t)row * a.ldo] = __float2bfloat16(val);
                     }
                 }
+            } else if (EPI == EPI_DENSE) {
+                bf16* o = (bf16*)a.out;
+                const int col = rt * 128 + r;
+#pragma unroll
+                for (int j = 0; j < 64; ++j)
+                    if (cb + j < cnt && col < a.n_rows) o[(size_t)(xrow0 + cb + j) * a.ldo + col] = __float2bfloat16(acc[j] * a.alpha);
             } else {
                 float* o = (float*)a.out;
                 const int col = rt * 128 + r;

@@ -23,20 +23,27 @@ class StackConfig:
 class LayerStack:
     """Single-GPU stack (world size 1).  All buffers are allocated here; ``forward`` only launches kernels."""
 
-    def __init__(self, ctx, cfg):
+    def __init__(self, ctx, cfg, weights_from=None):
+        """``weights_from``: another LayerStack of the same shapes whose weights are shared (a prefill-size stack next to
+        a decode-size one); the routing logits are drawn for this stack's token count."""
         t = ctx.torch
         dev = ctx.device
         self.ctx, self.cfg = ctx, cfg
         H, I, E = cfg.hidden, cfg.inter, cfg.n_experts
         self.dense, self.moe, self.logits = [], [], []
-        tile_rows = 8
+        # decode: 8-row slots; prefill (tens of rows per expert and more): 128-row tiles (tcgen05 path only)
+        tile_rows = 128 if ctx.tcgen05 and cfg.tokens * cfg.topk >= 32 * E else 8
         for l in range(cfg.layers):
-            tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, H, cfg.std, cfg.seed + 1000 * l + 1, dev)
-            self.dense.append(Weight(ctx, 0, cfg.dense_mode, H, H, 1, False, tiles, sds))
-            w13 = synth.fp4_experts(t, E, 2 * I, H, cfg.std, cfg.seed + 1000 * l + 2, True, dev)
-            w2 = synth.fp4_experts(t, E, H, I, cfg.std, cfg.seed + 1000 * l + 3, False, dev)
-            W13 = Weight.experts_fp4_packed(ctx, w13, 2 * I, H, E, True)
-            W2 = Weight.experts_fp4_packed(ctx, w2, H, I, E, False)
+            if weights_from is not None:
+                self.dense.append(weights_from.dense[l])
+                W13, W2 = weights_from.moe[l].w13, weights_from.moe[l].w2
+            else:
+                tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, H, cfg.std, cfg.seed + 1000 * l + 1, dev)
+                self.dense.append(Weight(ctx, 0, cfg.dense_mode, H, H, 1, False, tiles, sds))
+                w13 = synth.fp4_experts(t, E, 2 * I, H, cfg.std, cfg.seed + 1000 * l + 2, True, dev)
+                w2 = synth.fp4_experts(t, E, H, I, cfg.std, cfg.seed + 1000 * l + 3, False, dev)
+                W13 = Weight.experts_fp4_packed(ctx, w13, 2 * I, H, E, True)
+                W2 = Weight.experts_fp4_packed(ctx, w2, H, I, E, False)
             self.moe.append(MoeLayer(ctx, W13, W2, cfg.tokens, cfg.topk, cfg.act_mode, tile_rows=tile_rows))
             g = t.Generator(device=dev).manual_seed(cfg.seed + 1000 * l + 4)
             self.logits.append(t.randn(cfg.tokens, E, generator=g, device=dev, dtype=t.float32))
@@ -51,6 +58,8 @@ class LayerStack:
         ctx, w = self.ctx, self.dense[l]
         act_quant(ctx, w.mode, x, self.xq, self.xs)
         T = x.shape[0]
+        if ctx.tcgen05 and (T <= 64 or (w.n // 128) % 2 == 0):
+            return gemm_fp8(ctx, w, self.xq, self.xs, T, out)   # one launch: decode kernel up to 64 rows, prefill kernel above
         slab = 64 if ctx.tcgen05 else 16
         for r0 in range(0, T, slab):
             m = min(slab, T - r0)
@@ -72,6 +81,8 @@ class LayerStack:
         cfg = self.cfg
         slab = 64 if self.ctx.tcgen05 else 16
         slabs = (cfg.tokens + slab - 1) // slab
+        if self.ctx.tcgen05 and (cfg.tokens <= 64 or (cfg.hidden // 128) % 2 == 0):
+            slabs = 1
         # act_quant + dense slabs + route + plan (1 launch up to 1024 pairs, else 3) + gather + w13 + quant + w2 + unpermute
         plan = 1 if cfg.tokens * cfg.topk <= 1024 else 3
         return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1)

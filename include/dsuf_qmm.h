@@ -116,9 +116,12 @@ int32_t dsuf_act_quant_fp8(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x
 size_t dsuf_gemm_workspace_bytes(dsuf_ctx* ctx);
 int32_t dsuf_workspace_init(dsuf_ctx* ctx, void* stream, uint64_t workspace, size_t bytes);
 
-/* ops::gemv (ops.rs:331-474) for m <= 16 token rows:
+/* ops::gemv (ops.rs:331-474), ops::tc_gemv (ops.rs:1118-1163) and Rank::gemm_tc (model.rs:1328-1370) in one call:
  * out[m][n] (bf16, row stride ldo) = alpha * W . dequant(xq, xs).  Activations come pre-quantized from
- * dsuf_act_quant_fp8 in the weight's geometry. */
+ * dsuf_act_quant_fp8 in the weight's geometry.  Token rows per call: 1..16 on the mma.sync decode path; on the
+ * tcgen05 path 1..64 take the weight-streaming kernel (one pass over W, uses the workspace) and any m > 64 takes the
+ * prefill kernel (128-token tiles x pairs of 128-row weight tiles; n/128 must be even; the workspace is not
+ * touched and may be 0). */
 int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
                       int32_t ldo, float alpha, uint64_t workspace);
 

@@ -100,6 +100,28 @@ def test_dense_gemv_up_to_64_rows_on_tcgen05(pkg, ctx, mode, n, k, m):
     _dense_case(pkg, ctx, mode, n, k, m, seed=n + m)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("n,k,m", [(1024, 2048, 200), (512, 256, 65), (256, 1024, 384)])
+def test_dense_gemm_prefill_rows_on_tcgen05(pkg, ctx, mode, n, k, m):
+    """More than 64 token rows take the prefill kernel (128-token tiles x pairs of weight row tiles): a ragged last
+    tile, one row past a tile, exactly full tiles."""
+    if not ctx.tcgen05:
+        pytest.skip("the mma.sync decode kernel takes at most 16 rows per call")
+    _dense_case(pkg, ctx, mode, n, k, m, seed=n + m)
+
+
+def test_dense_gemm_prefill_rejects_odd_row_tile_count(pkg, ctx):
+    if not ctx.tcgen05:
+        pytest.skip("tcgen05 path only")
+    g = seeded(5)
+    xt, _ = randn_bf16(g, 100, 256)
+    _, wn = randn_bf16(g, 384, 256, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(1, wn)
+    w = pkg.Weight.dense_fp8(ctx, 1, wq, ws)
+    with pytest.raises(pkg.DsufError):
+        pkg.gemv(ctx, w, xt.cuda())
+
+
 def test_dense_gemv_linearity_and_alpha(pkg, ctx):
     """Size-independent property: out(alpha) = alpha * out(1) up to bf16 rounding."""
     g = seeded(3)
