@@ -39,15 +39,14 @@ struct TcpCfg {
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
     static constexpr int EPI_WARP0 = 4;              // warps 4..19: four groups of four (accumulator x column half)
     static constexpr int THREADS = (EPI_WARP0 + 16) * 32;
-    static constexpr int TM_SFA = 256, TM_SFB = 320, TM_COLS = 512;
+    static constexpr int TM_SFA = 384, TM_SFB = 448, TM_COLS = 512;  // accumulators: columns 0..383
 };
 
 // warp 0 / 2: producers (weight row tile 0 + activation tile / weight row tile 1 + activation scales),
 // 1 / 3: MMA issuers (accumulator 0 / 1), 4..19: epilogue (640 threads: 96 registers each)
 // AMX = 1: UE8M0 activation scales per 1x32, applied by the tensor core; the whole K accumulates in tensor memory.
 // AMX = 0: fp32 activation scales per 1x128 (DS geometry): every 128-K tile is promoted into fp32 registers with
-//          its scales.  The accumulators stay single-buffered: while the epilogue reads accumulator j, the other
-//          issuer's MMAs keep the tensor pipe busy.
+//          its scales.  The two issuers rotate over three accumulators, so one is read out while two take MMAs.
 // FMT / WMX: FP4 expert tiles (UE8M0 weight scales in the tile record) or dense FP8 weights with UE8M0 (MX) or fp32
 // 128x128 (DS) scales.  EPI_DENSE: the "slots" are the 128-row tiles of the a.m token rows of one dense matrix.
 template <int EPI, int AMX, int FMT = FMT_FP4, int WMX = 1>
@@ -64,7 +63,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
     __shared__ __align__(16) float s_xs[AMX ? 4 : XR * 128];
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[2], tempty_bar[2];
+    __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[6], tempty_bar[6];  // [accumulator][issuer]
     __shared__ uint32_t s_tmem;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -81,7 +80,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             mbar_init(&full_bar[s], 2 + 32);  // one expect_tx per producer warp + 32 cp.async lanes
             mbar_init(&empty_bar[s], 2);      // one tcgen05.commit per issuer
         }
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < 6; ++j) {
             mbar_init(&tfull_bar[j], 1);
             mbar_init(&tempty_bar[j], 8);     // the eight epilogue warps of the accumulator
         }
@@ -157,7 +156,6 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                            bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
             const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF + j * 512, 512, 128, 0)),
                            fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
-            const uint32_t d = tmu + j * 128;
             const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (2 * S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (2 * S + j);
             if (!AMX) {
                 const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));  // shuffles: outside the election
@@ -170,6 +168,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             int s = 0;
             uint32_t ph = 0;
             int nit = 0, n = 0;
+            int acc_i = j;  // MX: issuer j keeps accumulator j for the whole K
 #ifdef DSUF_TC_TIMING
             unsigned long long gt0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
             const long long ck0 = clock64();
@@ -181,7 +180,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                 const uint32_t idesc = tc_idesc_mx(cnt >= 113 ? 128 : cnt <= 16 ? 16 : (cnt + 15) & ~15, FMT == FMT_FP4);
                 if (AMX) {
                     // the accumulator is single-buffered: wait until the epilogue has drained the previous item
-                    if (nit > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
+                    if (nit > 0 && !dead && !mbar_wait(&tempty_bar[3 * j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
                     tc_fence_after();
                 }
                 for (int kt = 0; kt < KT; ++kt, ++n) {
@@ -191,11 +190,19 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     if (AMX) {
                         fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                     } else {
-                        // per-tile promotion: the epilogue must have read the previous tile out of the accumulator
-                        if (n > 0 && !dead && !mbar_wait(&tempty_bar[j], (uint32_t)((n - 1) & 1), a.status, KID_TCP, 3)) dead = true;
+                        // per-tile promotion: the two issuers rotate over three accumulators (use g = 2n + j takes accumulator
+                        // g % 3), so one is being read out while the other two take MMAs; wait for its previous reader
+                        // Barriers are per (accumulator, issuer): that pair recurs every 6 uses, always with the same
+                        // committing issuer and the same reading epilogue group, so the phases of a barrier are consumed in
+                        // order by one party (a parity wait cannot tell phase p from p + 2).  The previous user of the
+                        // accumulator, use g - 3, is the other issuer's.
+                        const int g = 2 * n + j;
+                        acc_i = g % 3;
+                        if (g >= 3 && !dead && !mbar_wait(&tempty_bar[acc_i * 2 + (j ^ 1)], (uint32_t)(((g - 3) / 6) & 1), a.status, KID_TCP, 3)) dead = true;
                         tc_fence_after();
                     }
                     const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
+                    const uint32_t d = tmu + acc_i * 128;
                     if (elect_one()) {
                         // each issuer keeps its own copy of the stage's scales in tensor memory
                         uint32_t sfa = ones_a, sfb = ones_b;
@@ -206,7 +213,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                             tc_mma_mx(d, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc), sfa, sfb,
                                       ((!AMX || kt == 0) && kc == 0) ? 0u : 1u);
                         tc_commit(&empty_bar[s]);
-                        if (!AMX || kt + 1 == KT) tc_commit(&tfull_bar[j]);
+                        if (!AMX || kt + 1 == KT) tc_commit(&tfull_bar[acc_i * 2 + j]);
                     }
                     __syncwarp();
                     TCP_TRACE(n, 8 + 3 * j);
@@ -227,7 +234,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         const int cb = ((e >> 2) & 1) * 64;    // first of this thread's 64 token columns
         const int q4 = warp & 3;               // tensor-memory lane quadrant this warp may read
         const int r = 32 * q4 + lane;
-        const uint32_t taddr = tm + ((uint32_t)(32 * q4) << 16) + ga * 128 + cb;
+        const uint32_t tlane = tm + ((uint32_t)(32 * q4) << 16) + cb;  // + 128 * accumulator
         float acc[64];
         int nit = 0, n = 0;
         for (int it = ibeg; it < iend; ++it, ++nit) {
@@ -242,31 +249,32 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                 rw1 = (cb + 32 + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 + lane) : 0.f;
             }
             if (AMX) {
-                if (!dead && !mbar_wait(&tfull_bar[ga], (uint32_t)(nit & 1), a.status, KID_TCP, 5)) dead = true;
+                if (!dead && !mbar_wait(&tfull_bar[3 * ga], (uint32_t)(nit & 1), a.status, KID_TCP, 5)) dead = true;
                 tc_fence_after();
-                tmem_ld<32>(taddr, acc);
-                tmem_ld<32>(taddr + 32, acc + 32);
+                tmem_ld<32>(tlane + ga * 128, acc);
+                tmem_ld<32>(tlane + ga * 128 + 32, acc + 32);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&tempty_bar[ga]);
+                if (lane == 0) mbar_arrive(&tempty_bar[3 * ga]);
             } else {
 #pragma unroll
                 for (int j = 0; j < 64; ++j) acc[j] = 0.f;
                 for (int kt = 0; kt < KT; ++kt, ++n) {
                     // DS weights: the tile's fp32 128x128 block scale, fetched before the wait
                     const float wds = WMX ? 1.0f : __ldg(a.wscale_ds + (size_t)rt * KT + kt);
-                    if (!dead && !mbar_wait(&tfull_bar[ga], (uint32_t)(n & 1), a.status, KID_TCP, 5)) dead = true;
+                    const int g = 2 * n + ga, ai = g % 3;
+                    if (!dead && !mbar_wait(&tfull_bar[ai * 2 + ga], (uint32_t)((g / 6) & 1), a.status, KID_TCP, 5)) dead = true;
                     tc_fence_after();
                     const float* xs = s_xs + (n & (XR - 1)) * 128 + cb;
 #pragma unroll
                     for (int c0 = 0; c0 < 64; c0 += 16) {
                         float v[16];
-                        tmem_ld<16>(taddr + c0, v);
+                        tmem_ld<16>(tlane + ai * 128 + c0, v);
                         if (c0 == 48) {
                             // everything is in registers: hand the accumulator back before the arithmetic
                             tc_fence_before();
                             __syncwarp();
-                            if (lane == 0) mbar_arrive(&tempty_bar[ga]);
+                            if (lane == 0) mbar_arrive(&tempty_bar[ai * 2 + ga]);
                         }
 #pragma unroll
                         for (int j = 0; j < 16; j += 4) {
