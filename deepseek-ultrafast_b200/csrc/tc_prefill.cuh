@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[6], tempty_bar[6];  // [accumulator][issuer]
     __shared__ uint32_t s_tmem;
+    __shared__ int s_efirst[EPI == EPI_DENSE ? 1 : 512], s_elast[EPI == EPI_DENSE ? 1 : 512];  // slot range of every expert
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, c = blockIdx.x;
@@ -95,9 +96,37 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
     pdl_wait();
     pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
 
-    // items = (slot, row-tile pair); every CTA takes a contiguous range
-    const long long nitems = (long long)(EPI == EPI_DENSE ? (a.m + 127) / 128 : *a.nslots) * RP;  // far below 2^31: slots <= permuted rows / 128 + experts
-    const int ibeg = (int)((long long)c * nitems / G), iend = (int)((long long)(c + 1) * nitems / G);
+    // Items = (slot, row-tile pair), dealt to the CTAs round-robin in the order [expert][group of <= 32 slots][row-tile
+    // pair][slot of the group]: the G items in flight at any time are a block of a few row-tile pairs x the slots of one
+    // group, so a weight tile is fetched from HBM once per group (not once per slot) and a group's token tiles stay in L2
+    // while its row-tile pairs go by.  (Dealing contiguous (slot, pair) ranges instead read 13 x the unique bytes from
+    // HBM on a 2048-token profile and made the kernel HBM-bound.)
+    const int nslots = EPI == EPI_DENSE ? (a.m + 127) / 128 : *a.nslots;
+    const int nitems = nslots * RP;  // far below 2^31: slots <= permuted rows / 128 + experts
+    constexpr int SG = 32;
+    if (EPI != EPI_DENSE) {
+        // first and last slot of every expert (slots are sorted by expert)
+        for (int sidx = tid; sidx < nslots; sidx += Cfg::THREADS) {
+            const int e = a.slots[sidx].x;
+            if (sidx == 0 || a.slots[sidx - 1].x != e) s_efirst[e] = sidx;
+            if (sidx == nslots - 1 || a.slots[sidx + 1].x != e) s_elast[e] = sidx;
+        }
+        __syncthreads();
+    }
+    auto item_of = [&](int i, int& slot, int& rp) {
+        int f = 0, n = nslots;
+        if (EPI != EPI_DENSE) {
+            const int e = a.slots[i / RP].x;  // item blocks of an expert start at multiples of RP
+            f = s_efirst[e];
+            n = s_elast[e] - f + 1;
+        }
+        const int l = i - f * RP;
+        const int grp = l / (SG * RP), lg = l - grp * (SG * RP);
+        const int ng = min(SG, n - grp * SG);
+        rp = lg / ng;
+        slot = f + grp * SG + (lg - rp * ng);
+    };
+    const int ibeg = c, iend = nitems;  // it = c, c + G, ...
 
     if (warp == 0 || warp == 2) {
         // ================= producers =================
@@ -110,8 +139,9 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             int s = 0;
             uint32_t ph = 0;
             int n = 0;
-            for (int it = ibeg; it < iend; ++it) {
-                const int slot = it / RP, rp = it - slot * RP;
+            for (int it = ibeg; it < iend; it += G) {
+                int slot, rp;
+                item_of(it, slot, rp);
                 const int4 sl = slot_of(slot);
                 const int xrow0 = sl.y;
                 int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
@@ -173,10 +203,12 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             unsigned long long gt0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
             const long long ck0 = clock64();
 #endif
-            for (int it = ibeg; it < iend; ++it, ++nit) {
+            for (int it = ibeg; it < iend; it += G, ++nit) {
                 // the MMA's N follows the rows the slot really holds (a multiple of 16): the last tile of an expert is
                 // rarely full, and a 48-column MMA takes 60 cycles where a 128-column one takes 97
-                const int cnt = slot_of(it / RP).z;
+                int slot, rp;
+                item_of(it, slot, rp);
+                const int cnt = slot_of(slot).z;
                 const uint32_t idesc = tc_idesc_mx(cnt >= 113 ? 128 : cnt <= 16 ? 16 : (cnt + 15) & ~15, FMT == FMT_FP4);
                 if (AMX) {
                     // the accumulator is single-buffered: wait until the epilogue has drained the previous item
@@ -237,8 +269,9 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         const uint32_t tlane = tm + ((uint32_t)(32 * q4) << 16) + cb;  // + 128 * accumulator
         float acc[64];
         int nit = 0, n = 0;
-        for (int it = ibeg; it < iend; ++it, ++nit) {
-            const int slot = it / RP, rp = it - slot * RP;
+        for (int it = ibeg; it < iend; it += G, ++nit) {
+            int slot, rp;
+            item_of(it, slot, rp);
             const int rt = 2 * rp + ga;
             const int4 sl = slot_of(slot);
             const int xrow0 = sl.y, cnt = sl.z;
