@@ -29,8 +29,8 @@ from __graft_entry__ import load_package  # noqa: E402
 H, I, E, TOPK, LAYERS = 7168, 2048, 256, 8, 4
 DENSE_SHAPES = [(4096, 7168), (7168, 2048), (18432, 7168), (7168, 16384)]
 METRIC = "moe_layer_stack_decode_tokens_per_s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch in the ncu small case, divided by its 55 active experts
-NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT = (874.597888e6 + 3.874816e6) / 55
+# dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch in the ncu small case, divided by its 59 active experts
+NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT = (921.251584e6 + 3.779072e6) / 59
 
 
 def peaks():

@@ -47,6 +47,8 @@ def prefill(pkg, synth, argv):
 def main():
     pkg = load_package()
     synth = importlib.import_module(pkg.__name__ + ".synth")
+    torch.manual_seed(0)       # same routing (and the same number of active experts) on every run
+    torch.cuda.manual_seed(0)
     if len(sys.argv) > 1 and sys.argv[1] == "prefill":
         return prefill(pkg, synth, sys.argv[2:])
     m = int(sys.argv[1]) if len(sys.argv) > 1 else 1
