@@ -59,11 +59,17 @@ int stream_setup(dsuf_ctx* ctx) {
     ST(FMT_FP4, 1, 0, 8, EPI_W2); ST(FMT_FP4, 1, 0, 16, EPI_W2); ST(FMT_FP4, 1, 0, 128, EPI_W2);
     ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2); ST(FMT_FP4, 1, 1, 128, EPI_W2);
 #undef ST
+    // 128-token steps, except the dense DS GEMM, which walks a slot in two 64-token halves (measured: 1.51 against
+    // 1.79 ms on 7168 x 7168 x 16384 tokens; for the FP4 expert GEMMs with DS scales the halves are 12 - 19 % slower)
     for (const void* f : {(const void*)tc_prefill_kernel<EPI_W13, 1>, (const void*)tc_prefill_kernel<EPI_W2, 1>,
                           (const void*)tc_prefill_kernel<EPI_W13, 0>, (const void*)tc_prefill_kernel<EPI_W2, 0>,
-                          (const void*)tc_prefill_kernel<EPI_DENSE, 1, FMT_FP8, 1>, (const void*)tc_prefill_kernel<EPI_DENSE, 0, FMT_FP8, 0>}) {
+                          (const void*)tc_prefill_kernel<EPI_DENSE, 1, FMT_FP8, 1>}) {
         cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, TcpCfg::SMEM);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_prefill)");
+    }
+    for (const void* f : {(const void*)tc_prefill_kernel<EPI_DENSE, 0, FMT_FP8, 0, 64>}) {
+        cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, TcpCfgT<64>::SMEM);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_prefill, 64-token steps)");
     }
     return DSUF_OK;
 }
@@ -96,7 +102,8 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     if (ctx->use_tc && m > 64) {
         // prefill-size M: 128-token tiles x pairs of weight row tiles (tc_prefill.cuh); needs no workspace
         DSUF_REQUIRE(ctx, (w->rt & 1) == 0, "dsuf_gemm_fp8: more than 64 token rows need an even number of 128-row weight tiles, got %d", w->rt);
-        int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, 128);
+        const bool ds = w->d.mode != DSUF_MODE_MX;
+        int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, ds ? 64 : 128);
         if (rc) return rc;
         a.tm_w = w->tm_tc;
         a.xscale = xs;
@@ -106,9 +113,10 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
         a.ldo = ldo;
         a.alpha = alpha;
         const int grid = ctx->sm_count;
-#define GD(AMX, WMX) launch(ctx, stream, tc_prefill_kernel<EPI_DENSE, AMX, FMT_FP8, WMX>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a)
-        return w->d.mode == DSUF_MODE_MX ? GD(1, 1) : GD(0, 0);
-#undef GD
+        if (!ds)
+            return launch(ctx, stream, tc_prefill_kernel<EPI_DENSE, 1, FMT_FP8, 1>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a);
+        return launch(ctx, stream, tc_prefill_kernel<EPI_DENSE, 0, FMT_FP8, 0, 64>, dim3(grid), dim3(TcpCfgT<64>::THREADS),
+                      (size_t)TcpCfgT<64>::SMEM, a);
     }
     const int m_max = ctx->use_tc ? 64 : 16;
     DSUF_REQUIRE(ctx, m >= 1 && m <= m_max, "dsuf_gemm_fp8: the mma.sync decode path takes 1..%d token rows per call, got %d", m_max, m);
@@ -158,6 +166,7 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
     StreamArgs a;
     fill_common(ctx, a, w);
     const int nt8 = plan->tile_rows / 8;
+    const bool prefill_pairs = ctx->use_tc && plan->tile_rows == 128 && (w->rt & 1) == 0;
     int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, plan->p, plan->tile_rows);
     if (rc) return rc;
     a.xscale = xs;
@@ -174,7 +183,7 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
         a.tm_w = w->tm_tc;
 #define GT(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, a)
         const int tr = plan->tile_rows;
-        if (tr == 128 && (w->rt & 1) == 0) {
+        if (prefill_pairs) {
             // prefill-size token tiles: two row tiles per step, two issuers
 #define GP(EPI, AMX) launch(ctx, stream, tc_prefill_kernel<EPI, AMX>, dim3(grid), dim3(TcpCfg::THREADS), (size_t)TcpCfg::SMEM, a)
             if (epi == EPI_W13) return amx ? GP(EPI_W13, 1) : GP(EPI_W13, 0);

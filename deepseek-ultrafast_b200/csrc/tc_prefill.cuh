@@ -28,19 +28,24 @@ constexpr int KID_TCP = 4;
 #define TCP_TRACE(n, k)
 #endif
 
-struct TcpCfg {
+// NTOK: token rows per step.  128 is the plan's slot.  64 walks every slot as two halves: a thread of the epilogue
+// then holds 32 instead of 64 accumulators, so a whole tile's columns fit in flight in one tensor-memory load, and the
+// smaller stage leaves room for a fifth one.  Used where it measured faster: the dense GEMM with DS (fp32) scales.
+template <int NTOK>
+struct TcpCfgT {
     static constexpr int A_BYTES = 16384;            // one weight tile, FP4 widened to 8-bit containers by TMA
-    static constexpr int B_OFF = 2 * A_BYTES;        // 128 token rows of 128 bytes
-    static constexpr int SFA_OFF = B_OFF + 16384;    // two weight scale atoms (512 bytes each)
+    static constexpr int B_OFF = 2 * A_BYTES;        // NTOK token rows of 128 bytes
+    static constexpr int SFA_OFF = B_OFF + NTOK * 128;  // two weight scale atoms (512 bytes each)
     static constexpr int SFB_OFF = SFA_OFF + 1024;   // activation scale atom
-    static constexpr int STAGE = SFB_OFF + 1024;     // 51200: a multiple of 1024
-    static constexpr int STAGES = 4;
+    static constexpr int STAGE = SFB_OFF + 1024;     // 51200 / 43008: multiples of 1024
+    static constexpr int STAGES = NTOK == 128 ? 4 : 5;
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0 (DS activations)
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
     static constexpr int EPI_WARP0 = 4;              // warps 4..19: four groups of four (accumulator x column half)
     static constexpr int THREADS = (EPI_WARP0 + 16) * 32;
     static constexpr int TM_SFA = 384, TM_SFB = 448, TM_COLS = 512;  // accumulators: columns 0..383
 };
+using TcpCfg = TcpCfgT<128>;
 
 // warp 0 / 2: producers (weight row tile 0 + activation tile / weight row tile 1 + activation scales),
 // 1 / 3: MMA issuers (accumulator 0 / 1), 4..19: epilogue (640 threads: 96 registers each)
@@ -49,18 +54,23 @@ struct TcpCfg {
 //          its scales.  The two issuers rotate over three accumulators, so one is read out while two take MMAs.
 // FMT / WMX: FP4 expert tiles (UE8M0 weight scales in the tile record) or dense FP8 weights with UE8M0 (MX) or fp32
 // 128x128 (DS) scales.  EPI_DENSE: the "slots" are the 128-row tiles of the a.m token rows of one dense matrix.
-template <int EPI, int AMX, int FMT = FMT_FP4, int WMX = 1>
-__global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __grid_constant__ StreamArgs a) {
-    using Cfg = TcpCfg;
+template <int EPI, int AMX, int FMT = FMT_FP4, int WMX = 1, int NTOK = 128>
+__global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(const __grid_constant__ StreamArgs a) {
+    using Cfg = TcpCfgT<NTOK>;
     static_assert(WMX || !AMX, "fp32 weight scales are promoted per K tile together with fp32 activation scales");
-    // (expert, first token row, token rows, -) of a slot
-    auto slot_of = [&](int slot) -> int4 {
-        if (EPI == EPI_DENSE) return make_int4(0, slot * 128, min(128, a.m - slot * 128), 0);
-        return a.slots[slot];
+    static_assert(NTOK == 128 || NTOK == 64, "token rows per step");
+    constexpr int HALVES = 128 / NTOK;  // steps a 128-row slot is walked in
+    constexpr int CPT = NTOK / 2;       // token columns per epilogue thread
+    // (expert, first token row, token rows (<= 0: nothing to do), -) of sub-slot vs = slot * HALVES + half
+    auto slot_of = [&](int vs) -> int4 {
+        const int slot = vs / HALVES, r0 = (vs % HALVES) * NTOK;
+        if (EPI == EPI_DENSE) return make_int4(0, slot * 128 + r0, min(NTOK, a.m - slot * 128 - r0), 0);
+        const int4 sl = a.slots[slot];
+        return make_int4(sl.x, sl.y + r0, min(NTOK, sl.z - r0), 0);
     };
     constexpr int S = Cfg::STAGES;
     constexpr int XR = 8;  // ring of fp32 activation scales (DS): outlives the stage, read after the MMAs completed
-    __shared__ __align__(16) float s_xs[AMX ? 4 : XR * 128];
+    __shared__ __align__(16) float s_xs[AMX ? 4 : XR * NTOK];
     extern __shared__ uint8_t smem_raw[];
     uint8_t* ring = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], tfull_bar[6], tempty_bar[6];  // [accumulator][issuer]
@@ -102,7 +112,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
     // while its row-tile pairs go by.  (Dealing contiguous (slot, pair) ranges instead read 13 x the unique bytes from
     // HBM on a 2048-token profile and made the kernel HBM-bound.)
     const int nslots = EPI == EPI_DENSE ? (a.m + 127) / 128 : *a.nslots;
-    const int nitems = nslots * RP;  // far below 2^31: slots <= permuted rows / 128 + experts
+    const int nitems = nslots * HALVES * RP;  // far below 2^31: slots <= permuted rows / 128 + experts
     constexpr int SG = 32;
     if (EPI != EPI_DENSE) {
         // first and last slot of every expert (slots are sorted by expert)
@@ -114,11 +124,11 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         __syncthreads();
     }
     auto item_of = [&](int i, int& slot, int& rp) {
-        int f = 0, n = nslots;
+        int f = 0, n = nslots * HALVES;  // in sub-slots
         if (EPI != EPI_DENSE) {
-            const int e = a.slots[i / RP].x;  // item blocks of an expert start at multiples of RP
-            f = s_efirst[e];
-            n = s_elast[e] - f + 1;
+            const int e = a.slots[i / (RP * HALVES)].x;  // item blocks of an expert start at multiples of RP * HALVES
+            f = s_efirst[e] * HALVES;
+            n = (s_elast[e] + 1) * HALVES - f;
         }
         const int l = i - f * RP;
         const int grp = l / (SG * RP), lg = l - grp * (SG * RP);
@@ -143,6 +153,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                 int slot, rp;
                 item_of(it, slot, rp);
                 const int4 sl = slot_of(slot);
+                if (sl.z <= 0) continue;  // second half of a slot with at most NTOK rows: every role skips it
                 const int xrow0 = sl.y;
                 int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
                 const uint8_t* sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
@@ -153,7 +164,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     uint8_t* st = ring + s * Cfg::STAGE;
                     if (elect_one()) {
                         // TMA counts the bytes it reads: 8192 for a packed FP4 tile that fills 16384 of shared memory
-                        mbar_expect_tx(&full_bar[s], (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0) + (j == 0 ? 16384 : 0));
+                        mbar_expect_tx(&full_bar[s], (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0) + (j == 0 ? NTOK * 128 : 0));
                         tma_3d_nh(st + j * Cfg::A_BYTES, &a.tm_w, 0, 0, tile, &full_bar[s]);
                         if (WMX) bulk_g2s(st + Cfg::SFA_OFF + j * 512, sf_src, 512, &full_bar[s], pol);
                         if (j == 0) tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol);
@@ -161,11 +172,11 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     __syncwarp();
                     if (j == 1) {
 #pragma unroll
-                        for (int t = lane; t < 128; t += 32) {
+                        for (int t = lane; t < NTOK; t += 32) {
                             // MX: the token's 4 UE8M0 bytes of this K tile go to its row of the scale atom; DS: its fp32 scale
                             const uint32_t* src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + t, a.x_rows - 1) * KT + kt;
                             if (AMX) cp_async4(st + Cfg::SFB_OFF + (t & 31) * 16 + (t >> 5) * 4, src);
-                            else cp_async4(s_xs + (n & (XR - 1)) * 128 + t, src);
+                            else cp_async4(s_xs + (n & (XR - 1)) * NTOK + t, src);
                         }
                         cp_async_arrive_noinc(&full_bar[s]);
                     }
@@ -203,13 +214,14 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
             unsigned long long gt0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
             const long long ck0 = clock64();
 #endif
-            for (int it = ibeg; it < iend; it += G, ++nit) {
+            for (int it = ibeg; it < iend; it += G) {
                 // the MMA's N follows the rows the slot really holds (a multiple of 16): the last tile of an expert is
                 // rarely full, and a 48-column MMA takes 60 cycles where a 128-column one takes 97
                 int slot, rp;
                 item_of(it, slot, rp);
                 const int cnt = slot_of(slot).z;
-                const uint32_t idesc = tc_idesc_mx(cnt >= 113 ? 128 : cnt <= 16 ? 16 : (cnt + 15) & ~15, FMT == FMT_FP4);
+                if (cnt <= 0) continue;
+                const uint32_t idesc = tc_idesc_mx(cnt > NTOK - 16 ? NTOK : cnt <= 16 ? 16 : (cnt + 15) & ~15, FMT == FMT_FP4);
                 if (AMX) {
                     // the accumulator is single-buffered: wait until the epilogue has drained the previous item
                     if (nit > 0 && !dead && !mbar_wait(&tempty_bar[3 * j], (uint32_t)((nit - 1) & 1), a.status, KID_TCP, 3)) dead = true;
@@ -234,7 +246,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                         tc_fence_after();
                     }
                     const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
-                    const uint32_t d = tmu + acc_i * 128;
+                    const uint32_t d = tmu + acc_i * NTOK;
                     if (elect_one()) {
                         // each issuer keeps its own copy of the stage's scales in tensor memory
                         uint32_t sfa = ones_a, sfb = ones_b;
@@ -251,6 +263,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     TCP_TRACE(n, 8 + 3 * j);
                     if (++s == S) { s = 0; ph ^= 1; }
                 }
+                ++nit;
             }
 #ifdef DSUF_TC_TIMING
             if (a.dbg && j == 0 && lane == 0) {
@@ -263,54 +276,57 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
         // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
         const int e = warp - Cfg::EPI_WARP0;
         const int ga = e >> 3;                 // accumulator = row tile of the pair
-        const int cb = ((e >> 2) & 1) * 64;    // first of this thread's 64 token columns
+        const int cb = ((e >> 2) & 1) * CPT;   // first of this thread's CPT token columns
         const int q4 = warp & 3;               // tensor-memory lane quadrant this warp may read
         const int r = 32 * q4 + lane;
-        const uint32_t tlane = tm + ((uint32_t)(32 * q4) << 16) + cb;  // + 128 * accumulator
-        float acc[64];
+        const uint32_t tlane = tm + ((uint32_t)(32 * q4) << 16) + cb;  // + NTOK * accumulator
+        float acc[CPT];
         int nit = 0, n = 0;
-        for (int it = ibeg; it < iend; it += G, ++nit) {
+        for (int it = ibeg; it < iend; it += G) {
             int slot, rp;
             item_of(it, slot, rp);
             const int rt = 2 * rp + ga;
             const int4 sl = slot_of(slot);
             const int xrow0 = sl.y, cnt = sl.z;
+            if (cnt <= 0) continue;
             float rw0 = 0.f, rw1 = 0.f;
-            if (EPI == EPI_W13) {
+            if (EPI == EPI_W13 && AMX) {
                 // routing weights of this thread's token columns, one per lane, fetched while the item's MMAs run
                 rw0 = (cb + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + lane) : 0.f;
-                rw1 = (cb + 32 + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 + lane) : 0.f;
+                if (CPT > 32) rw1 = (cb + 32 + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 + lane) : 0.f;
             }
             if (AMX) {
                 if (!dead && !mbar_wait(&tfull_bar[3 * ga], (uint32_t)(nit & 1), a.status, KID_TCP, 5)) dead = true;
                 tc_fence_after();
-                tmem_ld<32>(tlane + ga * 128, acc);
-                tmem_ld<32>(tlane + ga * 128 + 32, acc + 32);
+#pragma unroll
+                for (int c0 = 0; c0 < CPT; c0 += 32) tmem_ld<32>(tlane + ga * NTOK + c0, acc + c0);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&tempty_bar[3 * ga]);
             } else {
 #pragma unroll
-                for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+                for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
                 for (int kt = 0; kt < KT; ++kt, ++n) {
                     // DS weights: the tile's fp32 128x128 block scale, fetched before the wait
                     const float wds = WMX ? 1.0f : __ldg(a.wscale_ds + (size_t)rt * KT + kt);
                     const int g = 2 * n + ga, ai = g % 3;
                     if (!dead && !mbar_wait(&tfull_bar[ai * 2 + ga], (uint32_t)((g / 6) & 1), a.status, KID_TCP, 5)) dead = true;
                     tc_fence_after();
-                    const float* xs = s_xs + (n & (XR - 1)) * 128 + cb;
+                    const float* xs = s_xs + (n & (XR - 1)) * NTOK + cb;
 #pragma unroll
-                    for (int c0 = 0; c0 < 64; c0 += 16) {
-                        float v[16];
-                        tmem_ld<16>(tlane + ai * 128 + c0, v);
-                        if (c0 == 48) {
+                    constexpr int CH = CPT == 32 ? 32 : 16;  // columns in flight per load: what the registers allow
+#pragma unroll
+                    for (int c0 = 0; c0 < CPT; c0 += CH) {
+                        float v[CH];
+                        tmem_ld<CH>(tlane + ai * NTOK + c0, v);
+                        if (c0 == CPT - CH) {
                             // everything is in registers: hand the accumulator back before the arithmetic
                             tc_fence_before();
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&tempty_bar[ai * 2 + ga]);
                         }
 #pragma unroll
-                        for (int j = 0; j < 16; j += 4) {
+                        for (int j = 0; j < CH; j += 4) {
                             float4 t4 = *(const float4*)(xs + c0 + j);
                             if (!WMX) { t4.x *= wds; t4.y *= wds; t4.z *= wds; t4.w *= wds; }
                             acc[c0 + j] = fmaf(v[j], t4.x, acc[c0 + j]);
@@ -321,6 +337,11 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                     }
                 }
             }
+            if (EPI == EPI_W13 && !AMX) {
+                // (per-tile promotion keeps 64 accumulators and 16 loaded columns live: no registers to spare in the K loop)
+                rw0 = (cb + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + lane) : 0.f;
+                if (CPT > 32) rw1 = (cb + 32 + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 + lane) : 0.f;
+            }
             if (EPI == EPI_W13) {
                 // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group); after the
                 // exchange the gate lane finishes column j, the up lane column j + 1.
@@ -329,7 +350,7 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                 const float L = a.swiglu_limit;
                 const bool is_gate = (r & 8) == 0;
 #pragma unroll
-                for (int j = 0; j < 64; j += 2) {
+                for (int j = 0; j < CPT; j += 2) {
                     const float o0 = __shfl_xor_sync(0xffffffffu, acc[j], 8);
                     const float o1 = __shfl_xor_sync(0xffffffffu, acc[j + 1], 8);
                     const int col = is_gate ? j : j + 1;
@@ -346,15 +367,16 @@ __global__ void __launch_bounds__(TcpCfg::THREADS, 1) tc_prefill_kernel(const __
                 bf16* o = (bf16*)a.out;
                 const int col = rt * 128 + r;
 #pragma unroll
-                for (int j = 0; j < 64; ++j)
+                for (int j = 0; j < CPT; ++j)
                     if (cb + j < cnt && col < a.n_rows) o[(size_t)(xrow0 + cb + j) * a.ldo + col] = __float2bfloat16(acc[j] * a.alpha);
             } else {
                 float* o = (float*)a.out;
                 const int col = rt * 128 + r;
 #pragma unroll
-                for (int j = 0; j < 64; ++j)
+                for (int j = 0; j < CPT; ++j)
                     if (cb + j < cnt && col < a.n_rows) o[(size_t)(xrow0 + cb + j) * a.ldo + col] = acc[j];
             }
+            ++nit;
         }
     }
     tc_fence_before();

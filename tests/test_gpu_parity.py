@@ -347,3 +347,53 @@ def test_moe_layer_full_benchmark_size_sampled_tokens(pkg, ctx):
     ids_l = np.vectorize(remap.get)(ids_n[sample]).astype(np.int32)
     ref = oracle.moe_layer(oracle.MODE_DS, xn[sample], ids_l, rw_n[sample], np.stack(c13), np.stack(s13), np.stack(c2), np.stack(s2))
     assert rel(got[sample], ref["y_f32"]) < TOL
+
+
+@pytest.mark.parametrize("act_mode", [0, 1])
+def test_moe_layer_prefill_benchmark_shapes_sampled_tokens(pkg, ctx, act_mode):
+    """The prefill kernels at the benchmark's matrix shapes (hidden 7168, inter 2048: 56 K tiles x 16 row-tile pairs for
+    gate/up, 16 x 28 for down) on 1024 tokens, 8 experts, top-2 (two or three 128-row slots per expert, the last one
+    ragged): sampled tokens against the oracle on exactly the tile bytes the kernels read, every token against the
+    size-independent check that an output row is the sum of its top-k expert rows."""
+    import importlib
+    synth = importlib.import_module(pkg.__name__ + ".synth")
+    if not ctx.tcgen05:
+        pytest.skip("128-row plans run on the tcgen05 path only")
+    T, H, I, E, K = 1024, 7168, 2048, 8, 2
+    dev = ctx.device
+    w13 = synth.fp4_experts(torch, E, 2 * I, H, 0.02, 21, True, dev)
+    w2 = synth.fp4_experts(torch, E, H, I, 0.02, 22, False, dev)
+    W13 = pkg.Weight.experts_fp4_packed(ctx, w13, 2 * I, H, E, True)
+    W2 = pkg.Weight.experts_fp4_packed(ctx, w2, H, I, E, False)
+    g = seeded(123)
+    xt, xn = randn_bf16(g, T, H)
+    logits = torch.randn(T, E, generator=g)
+    ids, rw = pkg.moe_route_tokens(ctx, pkg.SCORE_SOFTMAX, logits.cuda(), None, K)
+    layer = pkg.MoeLayer(ctx, W13, W2, T, K, act_mode, tile_rows=128)
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    layer.forward(xt.cuda(), ids, rw, y)
+    y2 = torch.empty_like(y)
+    layer.forward(xt.cuda(), ids, rw, y2)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    assert (y.view(torch.uint16) == y2.view(torch.uint16)).all(), "prefill result depends on timing"
+    ids_n, rw_n = ids.cpu().numpy(), rw.cpu().numpy()
+    pr = layer.plan.pair_row.cpu().numpy().reshape(T, K)
+    yr = layer.yrows.cpu().numpy()
+    want = torch.from_numpy(yr[pr].sum(axis=1)).bfloat16().float().numpy()
+    got = y.float().cpu().numpy()
+    assert rel(got, want) < 1e-3
+    sample = [0, 517, T - 1]
+    per13 = (2 * I // 128) * (H // 128) * synth.REC_FP4
+    per2 = (H // 128) * (I // 128) * synth.REC_FP4
+    used = sorted(set(ids_n[sample].reshape(-1).tolist()))
+    remap = {e: i for i, e in enumerate(used)}
+    c13, s13, c2, s2 = [], [], [], []
+    for e in used:
+        a, b = synth.unpack_fp4(w13[e * per13:(e + 1) * per13].cpu().numpy(), 2 * I, H, True)
+        c13.append(a); s13.append(b)
+        a, b = synth.unpack_fp4(w2[e * per2:(e + 1) * per2].cpu().numpy(), H, I, False)
+        c2.append(a); s2.append(b)
+    ids_l = np.vectorize(remap.get)(ids_n[sample]).astype(np.int32)
+    ref = oracle.moe_layer(act_mode, xn[sample], ids_l, rw_n[sample], np.stack(c13), np.stack(s13), np.stack(c2), np.stack(s2))
+    assert rel(got[sample], ref["y_f32"]) < TOL
