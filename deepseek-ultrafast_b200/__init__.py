@@ -58,6 +58,9 @@ ABI = {
     "dsuf_pack_fp4_weight": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "dsuf_weight_create": (C.c_int32, [C.c_void_p, C.POINTER(WeightDesc), C.POINTER(C.c_void_p)]),
     "dsuf_weight_destroy": (C.c_int32, [C.c_void_p]),
+    "dsuf_row_sumsq": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
+    "dsuf_act_quant_fp8_prenorm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
+                                               C.c_uint64, C.c_uint64, C.c_float, C.c_uint64, C.c_uint64]),
     "dsuf_act_quant_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_uint64, C.c_uint64]),
     "dsuf_gemm_workspace_bytes": (C.c_size_t, [C.c_void_p]),
@@ -239,6 +242,32 @@ def act_quant(ctx, mode, x, q=None, s=None):
     if s is None:
         s = t.empty((m, k // blk), dtype=t.uint8 if mode == MODE_MX else t.float32, device=x.device)
     ctx.check(lib().dsuf_act_quant_fp8(ctx.h, ctx.stream(), mode, x.data_ptr(), x.stride(0), m, k, q.data_ptr(), s.data_ptr()))
+    return q, s
+
+
+def row_sumsq(ctx, x, out=None):
+    """tc_row_sumsq (cu/tcgemm.cu:341): fp32 sum of squares of every bf16 row."""
+    t = ctx.torch
+    m, k = x.shape
+    if out is None:
+        out = t.empty(m, dtype=t.float32, device=x.device)
+    ctx.check(lib().dsuf_row_sumsq(ctx.h, ctx.stream(), x.data_ptr(), x.stride(0), m, k, out.data_ptr()))
+    return out
+
+
+def act_quant_prenorm(ctx, mode, x, norm_w, eps, sumsq=None, q=None, s=None):
+    """tc_quant_rows with RMS pre-normalisation (cu/tcgemm.cu:300): quantizes bf16(norm_w * (x * rs))."""
+    t = ctx.torch
+    m, k = x.shape
+    blk = 32 if mode == MODE_MX else 128
+    if sumsq is None:
+        sumsq = row_sumsq(ctx, x)
+    if q is None:
+        q = t.empty((m, k), dtype=t.uint8, device=x.device)
+    if s is None:
+        s = t.empty((m, k // blk), dtype=t.uint8 if mode == MODE_MX else t.float32, device=x.device)
+    ctx.check(lib().dsuf_act_quant_fp8_prenorm(ctx.h, ctx.stream(), mode, x.data_ptr(), x.stride(0), m, k, norm_w.data_ptr(),
+                                               sumsq.data_ptr(), eps, q.data_ptr(), s.data_ptr()))
     return q, s
 
 

@@ -145,6 +145,28 @@ int32_t dsuf_act_quant_fp8(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x
     return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, m, k, (void*)q_out, (void*)scale_out, nullptr, 0, 0);
 }
 
+int32_t dsuf_row_sumsq(dsuf_ctx* ctx, void* stream, uint64_t x, int32_t ldx, int32_t m, int32_t k, uint64_t sumsq_out) {
+    if (!ctx) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, m >= 0 && k > 0 && k % 8 == 0, "row_sumsq: k (%d) must be a positive multiple of 8", k);
+    DSUF_REQUIRE(ctx, ldx >= k && ldx % 8 == 0, "row_sumsq: ldx (%d) must be >= k and a multiple of 8", ldx);
+    if (m == 0) return DSUF_OK;
+    DSUF_REQUIRE(ctx, x && sumsq_out && (x & 15) == 0, "row_sumsq: null or misaligned pointer");
+    return launch_row_sumsq(ctx, (cudaStream_t)stream, (const void*)x, ldx, m, k, (float*)sumsq_out);
+}
+
+int32_t dsuf_act_quant_fp8_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t m, int32_t k,
+                                   uint64_t norm_w, uint64_t sumsq, float eps, uint64_t q_out, uint64_t scale_out) {
+    if (!ctx) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, mode == DSUF_MODE_MX || mode == DSUF_MODE_DS, "act_quant_prenorm: unknown mode %d", mode);
+    DSUF_REQUIRE(ctx, m >= 0 && k > 0 && k % 128 == 0, "act_quant_prenorm: k (%d) must be a positive multiple of 128", k);
+    DSUF_REQUIRE(ctx, ldx >= k && ldx % 8 == 0, "act_quant_prenorm: ldx (%d) must be >= k and a multiple of 8", ldx);
+    if (m == 0) return DSUF_OK;
+    DSUF_REQUIRE(ctx, x && q_out && scale_out && norm_w && sumsq, "act_quant_prenorm: null pointer");
+    DSUF_REQUIRE(ctx, (x & 15) == 0 && (norm_w & 15) == 0 && (q_out & 7) == 0, "act_quant_prenorm: x and norm_w must be 16-byte, q_out 8-byte aligned");
+    return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, m, k, (void*)q_out, (void*)scale_out, nullptr, 0, 0,
+                            (const void*)norm_w, (const float*)sumsq, eps);
+}
+
 size_t dsuf_gemm_workspace_bytes(dsuf_ctx*) { return stream_workspace_bytes(); }
 
 int32_t dsuf_workspace_init(dsuf_ctx* ctx, void* stream, uint64_t workspace, size_t bytes) {

@@ -77,7 +77,9 @@ int launch(dsuf_ctx* ctx, cudaStream_t stream, void (*kernel)(KArgs...), dim3 gr
 
 // per-file launchers
 int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
-                     void* scales, const int* pair_row, int fanout, int sf_atoms);
+                     void* scales, const int* pair_row, int fanout, int sf_atoms, const void* norm_w = nullptr,
+                     const float* sumsq = nullptr, float eps = 0.f);
+int launch_row_sumsq(dsuf_ctx* ctx, cudaStream_t stream, const void* x, int ldx, int m, int k, float* out);
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
                         void* out, int ldo, float alpha, void* workspace, int* counters_at = nullptr);
 int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, int epi, int act_mode, const dsuf_moe_plan* plan,

@@ -1,6 +1,7 @@
 // FP8 (e4m3) activation quantization, stand-alone and fused with the routed-token scatter.
 //
-// Replaces tc_quant_rows (crates/kernels/cu/tcgemm.cu:300-340), the per-CTA quant_blocks8 staging of the decode
+// Replaces tc_quant_rows (crates/kernels/cu/tcgemm.cu:300-340, with its optional RMS pre-normalisation and
+// tc_row_sumsq, :341-355), the per-CTA quant_blocks8 staging of the decode
 // GEMVs (cu/quantblocks.cuh:7-57) and moe_gather_quant (cu/tcmoe.cu:88-133).  Activations are quantized ONCE per
 // token by this kernel; every GEMM consumer reads the codes.
 //   MX geometry: 1x32 blocks, scale 2^ceil(log2(max(amax,1e-4)/448)) stored as UE8M0, exact reciprocal by
@@ -21,6 +22,9 @@ struct QuantArgs {
     const int* pair_row;  // scatter form: destination rows of token t are pair_row[t*fanout + j] (<0: skipped)
     int fanout;           // 0: plain (row r -> row r)
     int sf_atoms;         // MX only: write scales into 128-row x 128-K atoms instead of row-major
+    const bf16* norm_w;   // RMS pre-normalisation weights [k], or null
+    const float* sumsq;   // pre-normalisation: sum of squares of every input row (row_sumsq_kernel)
+    float eps;
 };
 
 template <int MODE>
@@ -36,6 +40,15 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
         const bf16* h = (const bf16*)&raw;
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(h[e]);
+        if (a.norm_w) {
+            // tc_quant_rows with pw (cu/tcgemm.cu:316-320): v = bf16(w * (x * rs)), every product rounded on its own.
+            // rs by correctly rounded sqrt and division (the reference's rsqrtf is a 2-ulp approximation).
+            const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(a.sumsq[row], (float)a.k), a.eps)));
+            const uint4 wraw = *(const uint4*)(a.norm_w + k0);
+            const bf16* hw = (const bf16*)&wraw;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = bf16_round(__fmul_rn(__bfloat162float(hw[e]), __fmul_rn(v[e], rs)));
+        }
     } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = 0.f;
@@ -82,9 +95,35 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
     }
 }
 
+// tc_row_sumsq (cu/tcgemm.cu:341-355), same summation order: one warp per row, lane l takes k = 8 l + 256 i + e.
+__global__ void __launch_bounds__(256) row_sumsq_kernel(const bf16* x, int ldx, int m, int k, float* out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= m) return;
+    float ss = 0.f;
+    for (int kk = lane * 8; kk < k; kk += 256) {
+        const uint4 raw = *(const uint4*)(x + (size_t)row * ldx + kk);
+        const bf16* h = (const bf16*)&raw;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float v = __bfloat162float(h[e]);
+            ss = __fmaf_rn(v, v, ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+    if (lane == 0) out[row] = ss;
+}
+
+int launch_row_sumsq(dsuf_ctx* ctx, cudaStream_t stream, const void* x, int ldx, int m, int k, float* out) {
+    if (m == 0) return DSUF_OK;
+    return launch(ctx, stream, row_sumsq_kernel, dim3((m + 7) / 8), dim3(256), 0, (const bf16*)x, ldx, m, k, out);
+}
+
 int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
-                     void* scales, const int* pair_row, int fanout, int sf_atoms) {
-    QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, sf_atoms};
+                     void* scales, const int* pair_row, int fanout, int sf_atoms, const void* norm_w, const float* sumsq, float eps) {
+    QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, sf_atoms, (const bf16*)norm_w, sumsq, eps};
     if (rows_in == 0) return DSUF_OK;
     dim3 grid(rows_in, (k + 2047) / 2048);
     if (mode == DSUF_MODE_MX)

@@ -110,6 +110,19 @@ int32_t dsuf_weight_destroy(dsuf_weight* w);
 int32_t dsuf_act_quant_fp8(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t m, int32_t k,
                            uint64_t q_out, uint64_t scale_out);
 
+/* tc_row_sumsq (cu/tcgemm.cu:341-355): sumsq_out[r] = sum_k x[r][k]^2 in fp32, in the reference's summation order
+ * (one warp per row, lane l takes k = 8 l + 256 i + e, xor butterfly).  k % 8 == 0. */
+int32_t dsuf_row_sumsq(dsuf_ctx* ctx, void* stream, uint64_t x, int32_t ldx, int32_t m, int32_t k, uint64_t sumsq_out);
+
+/* tc_quant_rows with RMS pre-normalisation (TqParams.pw / norm_part / eps, cu/tcgemm.cu:286-340; launched by
+ * Rank::gemm_tc, model.rs:1328-1345): quantizes v = bf16(norm_w[k] * (x[r][k] * rs[r])) with
+ * rs = 1 / sqrt(sumsq[r] / k + eps) instead of x.  norm_w bf16 [k], sumsq f32 [m] (dsuf_row_sumsq, or a producer
+ * kernel's own partial sums added up by the caller).  rs is evaluated with correctly rounded sqrt and division; the
+ * reference uses the approximate rsqrtf instruction, so its codes can differ where a product sits on a rounding
+ * boundary. */
+int32_t dsuf_act_quant_fp8_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t m, int32_t k,
+                                   uint64_t norm_w, uint64_t sumsq, float eps, uint64_t q_out, uint64_t scale_out);
+
 /* Scratch of dsuf_gemm_fp8: stream-K partial sums and arrival counters.  Must be zeroed once with
  * dsuf_workspace_init before first use; the kernels leave it zeroed.  Calls sharing one workspace must be
  * stream-ordered. */

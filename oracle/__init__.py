@@ -84,6 +84,28 @@ def act_quant(mode, x_bf16):
     return q, s
 
 
+def row_sumsq(x_bf16):
+    """tc_row_sumsq (crates/kernels/cu/tcgemm.cu:341-355), summation order restated exactly."""
+    x = _c(x_bf16, np.uint16)
+    m, k = x.shape
+    out = np.empty(m, np.float32)
+    lib().dsufo_row_sumsq(_p(x), C.c_int(k), C.c_int(m), C.c_int(k), _p(out))
+    return out
+
+
+def act_quant_prenorm(mode, x_bf16, norm_w_bf16, sumsq, eps):
+    """tc_quant_rows with RMS pre-normalisation (crates/kernels/cu/tcgemm.cu:300-340)."""
+    x = _c(x_bf16, np.uint16)
+    w = _c(norm_w_bf16, np.uint16)
+    ss = _c(sumsq, np.float32)
+    m, k = x.shape
+    blk = 32 if mode == MODE_MX else 128
+    q = np.empty((m, k), np.uint8)
+    s = np.empty((m, k // blk), np.uint8 if mode == MODE_MX else np.float32)
+    lib().dsufo_act_quant_prenorm(C.c_int(mode), _p(x), C.c_int(k), C.c_int(m), C.c_int(k), _p(w), _p(ss), C.c_float(eps), _p(q), _p(s))
+    return q, s
+
+
 def quant_fp8_weight(mode, w_bf16):
     w = _c(w_bf16, np.uint16)
     n, k = w.shape

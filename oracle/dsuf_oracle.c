@@ -145,6 +145,50 @@ void dsufo_act_quant(int mode, const uint16_t* x, int ldx, int m, int k, uint8_t
         }
 }
 
+/* ---- RMS pre-normalisation in front of the activation quantizer ----
+ * tc_row_sumsq (crates/kernels/cu/tcgemm.cu:341-355): one warp per row; lane l accumulates x[k]^2 for
+ * k = 8 l + 256 i + e (e inner, fused multiply-add), then a 16, 8, 4, 2, 1 xor butterfly (cu/common.cuh:86-90).
+ * The summation order is restated exactly, so the fp32 result is bit-identical to the CUDA path's. */
+void dsufo_row_sumsq(const uint16_t* x, int ldx, int m, int k, float* out) {
+    for (int r = 0; r < m; ++r) {
+        float lane[32], tmp[32];
+        for (int l = 0; l < 32; ++l) {
+            float ss = 0.f;
+            for (int kk = l * 8; kk < k; kk += 256)
+                for (int e = 0; e < 8; ++e) {
+                    const float v = dsufo_bf16_to_f32(x[(size_t)r * ldx + kk + e]);
+                    ss = fmaf(v, v, ss);
+                }
+            lane[l] = ss;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            for (int l = 0; l < 32; ++l) tmp[l] = lane[l] + lane[l ^ o];
+            memcpy(lane, tmp, sizeof(lane));
+        }
+        out[r] = lane[0];
+    }
+}
+
+/* tc_quant_rows with pw != null (cu/tcgemm.cu:300-340): v = bf16(w * (x * rs)), rs = 1 / sqrt(sumsq / K + eps),
+ * then the quantizer above.  The reference evaluates rs with rsqrtf, an approximate instruction (2 ulp); this
+ * restatement and the CUDA path both use the correctly rounded square root and division, so they agree bit for bit
+ * with each other and differ from the reference's rs by at most that approximation error. */
+void dsufo_act_quant_prenorm(int mode, const uint16_t* x, int ldx, int m, int k, const uint16_t* norm_w, const float* sumsq,
+                             float eps, uint8_t* q, void* scales) {
+    const int blk = mode == DSUFO_MODE_MX ? 32 : 128;
+    uint16_t* v = (uint16_t*)malloc(sizeof(uint16_t) * (size_t)k);
+    for (int r = 0; r < m; ++r) {
+        const float rs = 1.0f / sqrtf(sumsq[r] / (float)k + eps);
+        for (int c = 0; c < k; ++c) {
+            const float xr = dsufo_bf16_to_f32(x[(size_t)r * ldx + c]) * rs;
+            v[c] = dsufo_f32_to_bf16(dsufo_bf16_to_f32(norm_w[c]) * xr);
+        }
+        dsufo_act_quant(mode, v, k, 1, k, q + (size_t)r * k,
+                        (uint8_t*)scales + (size_t)r * (k / blk) * (mode == DSUFO_MODE_MX ? 1 : 4));
+    }
+    free(v);
+}
+
 /* ---- FP8 weight quantizers ----
  * MX: formats.rs:59-84 (32x32 blocks, amax floor 1e-30, inv = 1/s). scales u8 [n/32][k/32].
  * DS: 128x128 blocks, fp32 amax/448. scales f32 [n/128][k/128]. */

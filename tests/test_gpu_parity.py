@@ -36,6 +36,28 @@ def test_act_quant_bit_exact(pkg, ctx, mode, m, k, ld):
     assert (s.cpu().numpy() == so).all()
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("m,k,ld", [(4, 2048, 2048), (9, 7168, 7168), (3, 384, 512), (130, 1024, 1024)])
+def test_row_sumsq_and_prenorm_quant_bit_exact(pkg, ctx, mode, m, k, ld):
+    """tc_row_sumsq + tc_quant_rows with RMS pre-normalisation: sums, codes and scales bit-exact against the oracle."""
+    g = seeded(40 + m + k)
+    xt, _ = randn_bf16(g, m, ld)
+    xt[0, :k] = 0                                     # an all-zero row: rs = 1 / sqrt(eps)
+    wt, _ = randn_bf16(g, 1, k)
+    wt = (1.0 + 0.1 * wt.float()).bfloat16().reshape(k)
+    eps = 1e-6
+    xd = xt.cuda()[:, :k]
+    ss = pkg.row_sumsq(ctx, xd)
+    q, s = pkg.act_quant_prenorm(ctx, mode, xd, wt.cuda(), eps, sumsq=ss)
+    torch.cuda.synchronize()
+    xn = xt[:, :k].contiguous().view(torch.uint16).numpy()
+    sso = oracle.row_sumsq(xn)
+    assert (ss.cpu().numpy().view(np.uint32) == sso.view(np.uint32)).all()
+    qo, so = oracle.act_quant_prenorm(mode, xn, wt.view(torch.uint16).numpy(), sso, eps)
+    assert (q.cpu().numpy() == qo).all()
+    assert (s.cpu().numpy() == so).all()
+
+
 def test_act_quant_rejects_bad_shapes(pkg, ctx):
     x = torch.zeros(2, 100, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(pkg.DsufError):

@@ -165,3 +165,34 @@ def test_permute_plan_is_a_stable_counting_sort():
     # empty input
     off, rp, pr, tiles = oracle.permute_plan(np.zeros((0, 3), np.int32), 4, 8)
     assert off.tolist() == [0] * 5 and len(tiles) == 0
+
+
+def _bf16(a):
+    """float32 array -> (bf16 bits as uint16, the bf16 values as float32), round to nearest even."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32)
+    r = ((u + 0x7fff + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return r, (r.astype(np.uint32) << 16).view(np.float32)
+
+
+def test_row_sumsq_and_prenorm_quant():
+    """tc_row_sumsq / tc_quant_rows with pre-normalisation (crates/kernels/cu/tcgemm.cu:300-355)."""
+    rng = np.random.default_rng(5)
+    xb, xf = _bf16(rng.standard_normal((5, 1024)).astype(np.float32) * 3.0)
+    ss = oracle.row_sumsq(xb)
+    want = (xf.astype(np.float64) ** 2).sum(axis=1)
+    assert np.allclose(ss, want, rtol=2e-6)
+    # weights of one and rs == 1 exactly (sumsq = K, eps = 0): the pre-normalised quantizer is the plain one
+    ones = np.full(1024, 0x3f80, np.uint16)
+    for mode in (oracle.MODE_MX, oracle.MODE_DS):
+        q0, s0 = oracle.act_quant(mode, xb)
+        q1, s1 = oracle.act_quant_prenorm(mode, xb, ones, np.full(5, 1024.0, np.float32), 0.0)
+        assert (q0 == q1).all() and (s0 == s1).all()
+    # general case against a numpy restatement of v = bf16(w * (x * rs)) followed by the plain quantizer
+    wb, wf = _bf16(1.0 + 0.1 * rng.standard_normal(1024).astype(np.float32))
+    eps = np.float32(1e-6)
+    rs = np.float32(1.0) / np.sqrt(ss / np.float32(1024) + eps, dtype=np.float32)
+    vb, _ = _bf16(wf[None, :] * (xf * rs[:, None]))
+    for mode in (oracle.MODE_MX, oracle.MODE_DS):
+        q0, s0 = oracle.act_quant(mode, vb)
+        q1, s1 = oracle.act_quant_prenorm(mode, xb, wb, ss, float(eps))
+        assert (q0 == q1).all() and (s0 == s1).all()
