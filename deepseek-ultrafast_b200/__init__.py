@@ -61,6 +61,9 @@ ABI = {
     "dsuf_row_sumsq": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
     "dsuf_act_quant_fp8_prenorm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                                C.c_uint64, C.c_uint64, C.c_float, C.c_uint64, C.c_uint64]),
+    "dsuf_ep_flag_bytes": (C.c_size_t, [C.c_int32]),
+    "dsuf_ep_allreduce_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32,
+                                           C.c_int64, C.c_uint64, C.c_uint64]),
     "dsuf_act_quant_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_uint64, C.c_uint64]),
     "dsuf_gemm_workspace_bytes": (C.c_size_t, [C.c_void_p]),
@@ -294,6 +297,41 @@ def gemv(ctx, w, x, out=None, alpha=1.0):
     """ops::gemv (ops.rs:331-474): bf16 activations in, bf16 out; quantizes once, then streams the weight."""
     xq, xs = act_quant(ctx, w.mode, x)
     return gemm_fp8(ctx, w, xq, xs, x.shape[0], out, alpha)
+
+
+class PeerAllReduce:
+    """dsuf_ep_allreduce_bf16 over buffers that every rank of a torch.distributed group has mapped (torch symmetric memory).
+
+    ``buffer(shape)`` hands out bf16 partial buffers in symmetric memory (the kernels that produce a partial write
+    straight into them); ``__call__(partial, out)`` sums that buffer over the ranks into the local tensor ``out``."""
+
+    def __init__(self, ctx, dist, rank, world):
+        import torch.distributed._symmetric_memory as symm
+        self.ctx, self.rank, self.world, self.symm = ctx, rank, world, symm
+        self.group = dist.group.WORLD.group_name
+        t = ctx.torch
+        nflag = lib().dsuf_ep_flag_bytes(world) // 4
+        self.flags = symm.empty(nflag, dtype=t.int32, device=ctx.device)
+        self.flags.zero_()
+        h = symm.rendezvous(self.flags, self.group)
+        self.flag_ptrs = (C.c_uint64 * world)(*[int(p) for p in h.buffer_ptrs])
+        self.state = t.zeros(2, dtype=t.int32, device=ctx.device)
+        self.data_ptrs = {}
+        t.cuda.synchronize()
+        dist.barrier()   # every rank's flag block is zero before anyone announces
+
+    def buffer(self, shape):
+        t = self.ctx.torch
+        buf = self.symm.empty(*shape, dtype=t.bfloat16, device=self.ctx.device)
+        h = self.symm.rendezvous(buf, self.group)
+        self.data_ptrs[buf.data_ptr()] = (C.c_uint64 * self.world)(*[int(p) for p in h.buffer_ptrs])
+        return buf
+
+    def __call__(self, partial, out):
+        ptrs = self.data_ptrs[partial.data_ptr()]
+        self.ctx.check(lib().dsuf_ep_allreduce_bf16(self.ctx.h, self.ctx.stream(), ptrs, self.flag_ptrs, self.rank, self.world,
+                                                    partial.numel(), self.state.data_ptr(), out.data_ptr()))
+        return out
 
 
 class MoePlan:

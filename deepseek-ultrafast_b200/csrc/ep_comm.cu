@@ -1,0 +1,134 @@
+// One-shot all-reduce of bf16 activation rows over NVLink peer memory, for the two per-layer exchanges of the
+// expert-parallel stack (the sum of the K-sharded dense partials and the sum of the per-rank expert outputs).
+//
+// Replaces comm_push / comm_push2_body / nv_contrib (crates/kernels/cu/comm.cu:134-279, 355-375, 559-584): the
+// reference pushes partial rows into every peer and sums what arrived.  Here every rank leaves its partial where the
+// producing kernel wrote it (a buffer all ranks mapped at set-up), announces it to its peers with a release store of
+// the call's epoch, waits for the peers' announcements, then READS the peers' partials with plain peer loads and
+// adds them up in rank order in fp32 (so every rank rounds the same sum to the same bf16).  At 0.9 MB per rank
+// (64 tokens x 7168) that is 7 peer reads of 0.9 MB per rank: latency-, not bandwidth-bound, which is why it is one
+// kernel with one hand-shake instead of a ring or a tree.
+//
+// Every wait is bounded (common.cuh WAIT_BUDGET_TICKS): a rank that never announces makes the others record
+// DEVERR_WAIT_TIMEOUT in the context's status word and finish with an incomplete sum instead of hanging.
+// Nothing here uses multimem or TMA multicast: plain ld/st on peer pointers only.
+#include "internal.h"
+
+namespace dsuf {
+
+constexpr int KID_EPCOMM = 5;
+constexpr int EPC_MAX_WORLD = 8;
+constexpr int EPC_CTAS = 128;     // flag slots per rank: [EPC_CTAS][world]; enough threads that a 0.9 MB sum is 1-2 loads per rank and thread
+constexpr int EPC_THREADS = 256;
+
+struct EpcArgs {
+    const uint4* data[EPC_MAX_WORLD];  // every rank's partial buffer (index = rank), n_elems bf16 each
+    uint32_t* flags[EPC_MAX_WORLD];    // every rank's flag block: [EPC_CTAS][world] epochs
+    bf16* out;                         // local result
+    DevStatus* status;
+    long long n_vec;                   // n_elems / 8
+    int rank, world;
+    uint32_t* state;                   // local: [0] calls completed (the epoch lives on the device so that a captured
+                                       // graph advances it on every replay), [1] CTAs finished in this call
+};
+
+DSUF_DEV void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+DSUF_DEV uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// system-scope relaxed load: never served from this SM's L1, which is not coherent with a peer's writes
+DSUF_DEV uint4 ld_relaxed_sys_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(EPC_THREADS) ep_allreduce_kernel(const EpcArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, b = blockIdx.x;
+    const uint32_t epoch = *(volatile uint32_t*)a.state + 1;  // every rank makes the same sequence of calls
+    // ---- announce: this rank's partial (written by earlier kernels of this stream) is complete ----
+    // (the partial was written by kernels that completed before this grid started, so it is already in this GPU's
+    // L2 / HBM, which is where peer loads are served from; the release store orders it before the flag)
+    if (tid < a.world) st_release_sys(a.flags[tid] + b * a.world + a.rank, epoch);
+    // ---- wait for every peer's announcement of this epoch (a peer can be at most one epoch ahead) ----
+    if (tid < a.world) {
+        const uint32_t* f = a.flags[a.rank] + b * a.world + tid;
+        const long long t0 = clock64();
+        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
+            if (clock64() - t0 > WAIT_BUDGET_TICKS) {
+                report(a.status, DEVERR_WAIT_TIMEOUT, KID_EPCOMM, tid);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    // ---- sum in rank order; all of an element's loads are issued before the first add (peer latency, not bandwidth,
+    //      bounds this kernel) ----
+    for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
+        uint4 v[EPC_MAX_WORLD];
+#pragma unroll
+        for (int r = 0; r < EPC_MAX_WORLD; ++r)
+            if (r < a.world) v[r] = ld_relaxed_sys_v4(a.data[r] + i);
+        float s[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] = 0.f;
+#pragma unroll
+        for (int r = 0; r < EPC_MAX_WORLD; ++r)
+            if (r < a.world) {
+                const bf16* h = (const bf16*)&v[r];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[e] += __bfloat162float(h[e]);
+            }
+        uint4 o;
+        bf16* ho = (bf16*)&o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16(s[e]);
+        *(uint4*)(a.out + i * 8) = o;
+    }
+    // ---- the last CTA to finish closes the call: the next call (stream-ordered behind this grid) sees epoch + 1 ----
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(a.state + 1, 1u) == gridDim.x - 1) {
+            a.state[1] = 0;
+            __threadfence();
+            *(volatile uint32_t*)a.state = epoch;
+        }
+    }
+}
+
+}  // namespace dsuf
+
+using namespace dsuf;
+
+extern "C" size_t dsuf_ep_flag_bytes(int32_t world) { return (size_t)EPC_CTAS * (world > 0 ? world : 0) * sizeof(uint32_t); }
+
+extern "C" int32_t dsuf_ep_allreduce_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
+                                          int32_t world, int64_t n_elems, uint64_t state, uint64_t out) {
+    if (!ctx) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, world >= 1 && world <= EPC_MAX_WORLD && rank >= 0 && rank < world, "ep_allreduce: rank %d of world %d", rank, world);
+    DSUF_REQUIRE(ctx, n_elems >= 0 && n_elems % 8 == 0, "ep_allreduce: n_elems must be a multiple of 8");
+    DSUF_REQUIRE(ctx, peer_data && peer_flags && out && (out & 15) == 0, "ep_allreduce: null or misaligned pointer");
+    DSUF_REQUIRE(ctx, state && (state & 3) == 0, "ep_allreduce: null or misaligned state");
+    EpcArgs a;
+    memset(&a, 0, sizeof(a));
+    for (int r = 0; r < world; ++r) {
+        DSUF_REQUIRE(ctx, peer_data[r] && peer_flags[r] && (peer_data[r] & 15) == 0, "ep_allreduce: null or misaligned peer pointer %d", r);
+        DSUF_REQUIRE(ctx, r == rank || peer_data[r] != out, "ep_allreduce: out must not be a buffer a peer reads");
+        a.data[r] = (const uint4*)peer_data[r];
+        a.flags[r] = (uint32_t*)peer_flags[r];
+    }
+    DSUF_REQUIRE(ctx, peer_data[rank] != out, "ep_allreduce: out must differ from this rank's partial (peers still read it)");
+    a.out = (bf16*)out;
+    a.status = ctx->dev_status;
+    a.n_vec = n_elems / 8;
+    a.rank = rank;
+    a.world = world;
+    a.state = (uint32_t*)state;
+    if (n_elems == 0) return DSUF_OK;
+    return launch(ctx, (cudaStream_t)stream, ep_allreduce_kernel, dim3(EPC_CTAS), dim3(EPC_THREADS), 0, a);
+}

@@ -17,7 +17,9 @@ so sending every row everywhere costs < 40 % extra on a sub-megabyte message and
 collective launches per layer.  Routing is evaluated redundantly on every rank from the gathered rows (64 x 256 scores).
 Token ownership only matters at the ends of the stack: one all-gather going in, a slice coming out.
 The reference has no expert parallelism (tensor parallel + its own push all-reduce,
-crates/kernels/cu/comm.cu:134-279); this exchange is this library's design.
+crates/kernels/cu/comm.cu:134-279); this exchange is this library's design.  On GPUs the two all-reduces run as this
+library's own one-shot kernel over NVLink peer memory (csrc/ep_comm.cu) when torch's symmetric memory can map the
+buffers, else as NCCL all-reduces.
 
 The compute steps are injected (``compute``) so the same exchange code runs on the CUDA kernels (stack.EpLayerStack)
 and, in the CPU tests, on the oracle.
@@ -27,8 +29,12 @@ and, in the CPU tests, on the oracle.
 class Exchange:
     """Thin wrapper over a torch.distributed process group with the two collectives the layer needs."""
 
-    def __init__(self, dist, rank, world, group=None):
+    def __init__(self, dist, rank, world, group=None, peer=None):
+        """``peer``: optional callable (partial, out) -> out that sums a partial buffer over the ranks without the
+        process-group library (the peer-memory all-reduce kernel); ``peer_out`` maps a partial buffer to its result
+        tensor."""
         self.dist, self.rank, self.world, self.group = dist, rank, world, group
+        self.peer, self.peer_out = peer, {}
 
     def all_gather_rows(self, out, local):
         """out [W*n][...] <- concatenation of every rank's local [n][...]."""
@@ -39,8 +45,11 @@ class Exchange:
         return out
 
     def all_reduce(self, t):
-        """In-place element-wise sum over ranks."""
+        """Element-wise sum over ranks; returns the tensor that holds it (``t`` itself on the process-group path)."""
         if self.world > 1:
+            out = self.peer_out.get(t.data_ptr()) if self.peer is not None else None
+            if out is not None:
+                return self.peer(t, out)
             self.dist.all_reduce(t, group=self.group)
         return t
 

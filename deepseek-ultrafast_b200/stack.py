@@ -9,6 +9,9 @@ the per-rank expert outputs (combine), which also is the next layer's gathered i
 The reference is tensor-parallel only and combines with its own push all-reduce (cu/comm.cu:134-279); the
 expert-parallel exchange here is this library's design.
 """
+import os
+import sys
+
 from . import (MODE_DS, MODE_MX, SCORE_SOFTMAX, MoeLayer, Weight, act_quant, gemm_fp8, moe_route_tokens)
 from . import synth
 
@@ -146,8 +149,26 @@ class EpLayerStack:
         blk = 32 if cfg.dense_mode == MODE_MX else 128
         self.xq = t.empty((T, kloc), dtype=t.uint8, device=dev)
         self.xs = t.empty((T, kloc // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
-        self.partial = t.empty((T, H), dtype=t.bfloat16, device=dev)
-        self.y_part = [t.empty((T, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
+        # The two per-layer sums run as the library's peer-memory all-reduce when the partial buffers can be mapped
+        # by every rank (torch symmetric memory); DSUF_EP_PEER=0 or a failed mapping falls back to NCCL.
+        self.peer = None
+        if world > 1 and os.environ.get("DSUF_EP_PEER", "1") != "0":
+            try:
+                from . import PeerAllReduce
+                self.peer = PeerAllReduce(ctx, dist, rank, world)
+            except Exception as e:  # noqa: BLE001 - any failure to map means: use the process group
+                if rank == 0:
+                    print(f"peer-memory all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+                self.peer = None
+        if self.peer is not None:
+            self.partial = self.peer.buffer((T, H))
+            self.y_part = [self.peer.buffer((T, H)) for _ in range(2)]
+            self.xch.peer = self.peer
+            for buf in [self.partial] + self.y_part:
+                self.xch.peer_out[buf.data_ptr()] = t.empty((T, H), dtype=t.bfloat16, device=dev)
+        else:
+            self.partial = t.empty((T, H), dtype=t.bfloat16, device=dev)
+            self.y_part = [t.empty((T, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
         self.x_all = t.empty((T, H), dtype=t.bfloat16, device=dev)
         self.ids = t.empty((T, cfg.topk), dtype=t.int32, device=dev)
         self.w = t.empty((T, cfg.topk), dtype=t.float32, device=dev)

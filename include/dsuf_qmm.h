@@ -201,6 +201,23 @@ int32_t dsuf_moe_w2(dsuf_ctx* ctx, void* stream, const dsuf_weight* w2, int32_t 
 int32_t dsuf_moe_unpermute(dsuf_ctx* ctx, void* stream, const dsuf_moe_plan* plan, uint64_t yrows, uint64_t shared, int32_t t,
                            int32_t topk, int32_t h, uint64_t out, int32_t ldo);
 
+/* ---- expert-parallel exchange over NVLink peer memory ----
+ * One-shot all-reduce of bf16 rows: out[i] = bf16(sum over ranks r = 0..world-1, in that order, of peer_data[r][i]).
+ * Replaces comm_push / comm_push2_body / nv_contrib (crates/kernels/cu/comm.cu:134-279, 355-375, 559-584).
+ *   peer_data[r]   device address, valid on THIS GPU, of rank r's partial buffer (n_elems bf16); entry `rank` is this
+ *                  rank's own buffer, which the producing kernels of this stream have already written
+ *   peer_flags[r]  device address of rank r's flag block (dsuf_ep_flag_bytes(world) bytes, zeroed once at set-up)
+ *   state          this rank's own 8 zero-initialised bytes of device memory (call counter), one per flag block
+ *   out            local result buffer, distinct from every partial buffer
+ * The caller maps the buffers (CUDA IPC / VMM; the Python mirror uses torch's symmetric memory).  Every rank must
+ * make the same sequence of calls with the same flag blocks.  A partial buffer may be rewritten only after a LATER
+ * call on this rank has returned on the stream (alternate two buffers, as the layer stack does).  Waits are
+ * bounded: a missing peer ends in DSUF_DEVERR_WAIT_TIMEOUT in the status word, not in a hang.
+ * world <= 8; n_elems % 8 == 0.  Safe to capture in a CUDA graph (the epoch lives in `state`). */
+size_t dsuf_ep_flag_bytes(int32_t world);
+int32_t dsuf_ep_allreduce_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
+                               int32_t world, int64_t n_elems, uint64_t state, uint64_t out);
+
 #ifdef __cplusplus
 }
 #endif
