@@ -191,4 +191,5 @@ class EpLayerStack:
         slab = 64 if self.ctx.tcgen05 else 16
         slabs = (cfg.tokens + slab - 1) // slab
         plan = 1 if cfg.tokens * cfg.topk <= 1024 else 3
-        return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1)
+        ar = 2 if self.peer is not None else 0   # this library's all-reduce kernel (NCCL's kernels are not counted)
+        return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1 + ar)
