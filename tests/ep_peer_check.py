@@ -1,0 +1,50 @@
+"""Child program of test_ep_peer.py: every rank sums seeded partials with the peer-memory all-reduce kernel and checks
+them against an fp32 NCCL all-reduce; also through a replayed CUDA graph.  Launched with torch.distributed.run."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+from __graft_entry__ import load_package  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = load_package()
+    ctx = pkg.Ctx(local)
+    ar = pkg.PeerAllReduce(ctx, dist, rank, world)
+    rows, width = 64, 7168
+    bufs = [ar.buffer((rows, width)) for _ in range(2)]
+    out = torch.empty(rows, width, dtype=torch.bfloat16, device="cuda")
+    ok = True
+    for it in range(6):
+        b = bufs[it & 1]                      # a partial buffer is rewritten only after a later call completed
+        g = torch.Generator(device="cuda").manual_seed(100 * it + rank)
+        b.copy_(torch.randn(rows, width, generator=g, device="cuda").bfloat16())
+        ref = b.float().clone()
+        dist.all_reduce(ref)
+        ar(b, out)
+        torch.cuda.synchronize()
+        # the kernel adds the bf16 partials in fp32 and rounds once: within one bf16 ulp of the fp32 sum
+        ok = ok and bool(((out.float() - ref).abs() <= ref.abs() * 2.0 ** -8 + 1e-6).all()) and ctx.status().code == 0
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ar(bufs[0], out)
+        ar(bufs[1], out)
+    for _ in range(4):
+        graph.replay()                        # the epoch advances on the device
+    torch.cuda.synchronize()
+    ref = bufs[1].float().clone()
+    dist.all_reduce(ref)
+    ok = ok and bool(((out.float() - ref).abs() <= ref.abs() * 2.0 ** -8 + 1e-6).all()) and ctx.status().code == 0
+    dist.barrier()
+    torch.cuda.synchronize()
+    print(f"rank {rank}: {'ok' if ok else 'MISMATCH'}", flush=True)
+    os._exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,55 @@
+"""The peer-memory all-reduce kernel of the expert-parallel exchange (csrc/ep_comm.cu, dsuf_ep_allreduce_bf16)."""
+import ctypes as C
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _call(pkg, ctx, data, flags, state, out, n):
+    lib = pkg.lib()
+    ptrs = (C.c_uint64 * 1)(data.data_ptr())
+    fl = (C.c_uint64 * 1)(flags.data_ptr())
+    return lib.dsuf_ep_allreduce_bf16(ctx.h, ctx.stream(), ptrs, fl, 0, 1, n, state.data_ptr(), out.data_ptr())
+
+
+def test_single_rank_sum_is_a_copy_and_the_epoch_advances(pkg, ctx):
+    """world = 1: the hand-shake is with itself; three calls in a row and a replayed graph keep the flags consistent."""
+    n = 64 * 7168
+    x = torch.randn(n, device="cuda").bfloat16()
+    out = torch.zeros_like(x)
+    flags = torch.zeros(pkg.lib().dsuf_ep_flag_bytes(1) // 4, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        assert _call(pkg, ctx, x, flags, state, out, n) == 0
+    torch.cuda.synchronize()
+    assert (out.view(torch.uint16) == x.view(torch.uint16)).all()
+    assert state.cpu().tolist() == [3, 0] and int(flags.max()) == 3
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        assert _call(pkg, ctx, x, flags, state, out, n) == 0
+    for _ in range(4):
+        g.replay()
+    torch.cuda.synchronize()
+    assert state.cpu().tolist()[0] == 7 and ctx.status().code == 0
+
+
+def test_rejects_aliasing_and_bad_sizes(pkg, ctx):
+    x = torch.zeros(64, device="cuda").bfloat16()
+    flags = torch.zeros(pkg.lib().dsuf_ep_flag_bytes(1) // 4, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    assert _call(pkg, ctx, x, flags, state, x, 64) != 0          # out must not be the partial the peers read
+    assert _call(pkg, ctx, x, flags, state, torch.empty_like(x), 60) != 0   # n_elems % 8
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_against_nccl():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                        "--master-port", "29577", os.path.join(HERE, "ep_peer_check.py")], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
