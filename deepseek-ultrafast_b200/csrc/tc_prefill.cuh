@@ -1,5 +1,6 @@
-// tcgen05 grouped GEMM for prefill-size token tiles: 128 tokens x TWO 128-row weight tiles per CTA step, MX
-// (power-of-two) scales on both operands applied by the tensor core.
+// tcgen05 GEMM for prefill-size token tiles: 128 tokens x TWO 128-row weight tiles per CTA step.  Grouped MXFP4
+// expert GEMMs (gate/up + SwiGLU, down) and the dense FP8 projection; MX (power-of-two, applied by the tensor core)
+// or DS (fp32 per 1x128, promoted per K tile) activation scales.
 //
 // Measured on B200 with the decode kernel (tc_stream.cuh) at 128-token tiles: a tcgen05.mma occupies its issuing
 // thread for about as long as it occupies the tensor pipe (97 cycles at N = 128), and everything else that thread
@@ -7,13 +8,15 @@
 // issuer keeps the pipe barely half busy; the ring of six 33 KB stages also covers too little latency.  Here
 //   * a stage holds one activation tile (128 tokens x 128 K) and the tiles of two adjacent weight row tiles, so
 //     every activation byte brought into shared memory feeds 256 weight rows (a third less ingest per flop);
-//   * two issuer warps each own one of the two row tiles and one accumulator (128 lanes x 128 columns of tensor
-//     memory): the bookkeeping of one overlaps the MMAs of the other, and the summation order of every output is
-//     fixed (results do not depend on timing);
-//   * sixteen epilogue warps drain both accumulators into registers in one go (64 columns per thread), release
-//     the tensor memory, and run the SwiGLU / store epilogue while the next item's MMAs proceed.
-// Replaces tc_moe_w13 / tc_moe_w2 (crates/kernels/cu/tcmoe.cu:184-588) for MX activations; the weights come
-// straight from the tile records (no in-kernel re-layout warps, cu/tcmoe.cu:412-456).
+//   * two issuer warps each own one of the two row tiles: the bookkeeping of one overlaps the MMAs of the other, and
+//     the summation order of every output is fixed (results do not depend on timing);
+//   * sixteen epilogue warps drain an accumulator into registers (64 columns per thread), release the tensor
+//     memory, and run the SwiGLU / store epilogue while the next item's MMAs proceed;
+//   * work items are dealt so that the items in flight share weight tiles and token tiles through L2 (see the item
+//     order in the kernel): every input byte comes from HBM once.
+// Replaces tc_moe_w13 / tc_moe_w2 (crates/kernels/cu/tcmoe.cu:184-588) and tc_gemm_fp8 / tc_gemm_fp8p
+// (cu/tcgemm.cu:20-288); the weights come straight from the tile records (no in-kernel re-layout warps,
+// cu/tcmoe.cu:412-456).
 #pragma once
 #include "tc_stream.cuh"
 
