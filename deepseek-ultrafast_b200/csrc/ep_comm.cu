@@ -11,7 +11,7 @@
 //
 // Every wait is bounded (common.cuh WAIT_BUDGET_TICKS): a rank that never announces makes the others record
 // DEVERR_WAIT_TIMEOUT in the context's status word and finish with an incomplete sum instead of hanging.
-// Nothing here uses multimem or TMA multicast: plain ld/st on peer pointers only.
+// The only peer accesses are plain ld / st on peer pointers.
 #include "internal.h"
 
 namespace dsuf {
