@@ -64,6 +64,8 @@ ABI = {
     "dsuf_ep_flag_bytes": (C.c_size_t, [C.c_int32]),
     "dsuf_ep_allreduce_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32,
                                            C.c_int64, C.c_uint64, C.c_uint64]),
+    "dsuf_ep_combine_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
+                                         C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
     "dsuf_act_quant_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_uint64, C.c_uint64]),
     "dsuf_gemm_workspace_bytes": (C.c_size_t, [C.c_void_p]),
@@ -333,6 +335,15 @@ class PeerAllReduce:
                                                     partial.numel(), self.state.data_ptr(), out.data_ptr()))
         return out
 
+    def combine(self, plan, yrows, shared, partial, out):
+        """dsuf_ep_combine_bf16: the local sum of every token's expert rows and its exchange in one kernel."""
+        tok, h = out.shape
+        ptrs = self.data_ptrs[partial.data_ptr()]
+        self.ctx.check(lib().dsuf_ep_combine_bf16(self.ctx.h, self.ctx.stream(), plan.pair_row.data_ptr(), yrows.data_ptr(),
+                                                  shared.data_ptr() if shared is not None else 0, tok, plan.topk, h, ptrs,
+                                                  self.flag_ptrs, self.rank, self.world, self.state.data_ptr(), out.data_ptr()))
+        return out
+
 
 class MoePlan:
     """Caller-owned buffers of the permute plan (MpParams, ops.rs:1478-1491)."""
@@ -420,8 +431,10 @@ class MoeLayer:
         self.act_s = t.zeros((p, self.inter // blk), dtype=sdt, device=dev)
         self.yrows = t.zeros((p, self.h), dtype=t.float32, device=dev)
 
-    def forward(self, x, ids, w, out, shared=None, events=None):
-        """``events``: optional list; (start, end) CUDA events around the gate/up kernel are appended (bench timing)."""
+    def forward(self, x, ids, w, out, shared=None, events=None, combine=None):
+        """``events``: optional list; (start, end) CUDA events around the gate/up kernel are appended (bench timing).
+        ``combine``: optional callable (plan, yrows, shared) -> tensor that replaces the local unpermute (the
+        expert-parallel stack passes the kernel that sums locally and across ranks in one launch)."""
         ctx, plan = self.ctx, self.plan
         if events is None:
             events = getattr(self, "events", None)
@@ -436,5 +449,7 @@ class MoeLayer:
             events.append((e0, e1))
         act_quant(ctx, self.act_mode, self.act, self.act_q, self.act_s)
         moe_w2(ctx, self.w2, self.act_mode, plan, self.act_q, self.act_s, self.yrows)
+        if combine is not None:
+            return combine(plan, self.yrows, shared)
         moe_unpermute(ctx, plan, self.yrows, out, shared)
         return out

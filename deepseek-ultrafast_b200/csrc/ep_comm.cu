@@ -101,34 +101,153 @@ __global__ void __launch_bounds__(EPC_THREADS) ep_allreduce_kernel(const EpcArgs
     }
 }
 
+// Combine fused with its exchange: every thread first forms this rank's partial of its own elements
+// (out[tok][c] = sum of the token's top-k expert rows that live on this rank, unpermute_kernel's sum), publishes it in the
+// mapped partial buffer, and after the hand-shake adds the peers' partials of the SAME elements.  A rank's CTA b
+// produces exactly the elements the peers' CTA b consume, so the per-CTA hand-shake is all the ordering needed: no
+// grid-wide barrier and no separate unpermute launch.
+struct EpCombineArgs {
+    EpcArgs c;
+    const int* pair_row;   // [t][topk] permuted row of every (token, choice), < 0: not on this rank
+    const float* yrows;    // fp32 [rows][h] output of the down projection
+    const bf16* shared;    // optional bf16 [t][h] added by THIS rank (pass it on one rank only)
+    bf16* partial;         // = c.data[c.rank], writable
+    int topk, h;
+};
+
+__global__ void __launch_bounds__(EPC_THREADS) ep_combine_kernel(const EpCombineArgs p) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const EpcArgs& a = p.c;
+    const int tid = threadIdx.x, b = blockIdx.x;
+    const uint32_t epoch = *(volatile uint32_t*)a.state + 1;
+    // ---- this rank's partial of this thread's elements ----
+    for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
+        const long long el = i * 8;
+        const int tok = (int)(el / p.h), col = (int)(el - (long long)tok * p.h);
+        float s[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] = 0.f;
+        for (int j = 0; j < p.topk; ++j) {
+            const int r = __ldg(p.pair_row + (size_t)tok * p.topk + j);
+            if (r < 0) continue;
+            const float4 v0 = __ldcs((const float4*)(p.yrows + (size_t)r * p.h + col));
+            const float4 v1 = __ldcs((const float4*)(p.yrows + (size_t)r * p.h + col + 4));
+            s[0] += v0.x; s[1] += v0.y; s[2] += v0.z; s[3] += v0.w;
+            s[4] += v1.x; s[5] += v1.y; s[6] += v1.z; s[7] += v1.w;
+        }
+        if (p.shared) {
+            const uint4 raw = *(const uint4*)(p.shared + el);
+            const bf16* sh = (const bf16*)&raw;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[e] += __bfloat162float(sh[e]);
+        }
+        uint4 o;
+        bf16* ho = (bf16*)&o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16(s[e]);
+        *(uint4*)(p.partial + el) = o;
+    }
+    __threadfence_system();
+    __syncthreads();
+    // ---- announce, wait (bounded), sum in rank order: as ep_allreduce_kernel ----
+    if (tid < a.world) st_release_sys(a.flags[tid] + b * a.world + a.rank, epoch);
+    if (tid < a.world) {
+        const uint32_t* f = a.flags[a.rank] + b * a.world + tid;
+        const long long t0 = clock64();
+        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
+            if (clock64() - t0 > WAIT_BUDGET_TICKS) {
+                report(a.status, DEVERR_WAIT_TIMEOUT, KID_EPCOMM, 16 + tid);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
+        uint4 v[EPC_MAX_WORLD];
+#pragma unroll
+        for (int r = 0; r < EPC_MAX_WORLD; ++r)
+            if (r < a.world) v[r] = ld_relaxed_sys_v4(a.data[r] + i);
+        float s[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] = 0.f;
+#pragma unroll
+        for (int r = 0; r < EPC_MAX_WORLD; ++r)
+            if (r < a.world) {
+                const bf16* h = (const bf16*)&v[r];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[e] += __bfloat162float(h[e]);
+            }
+        uint4 o;
+        bf16* ho = (bf16*)&o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16(s[e]);
+        *(uint4*)(a.out + i * 8) = o;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(a.state + 1, 1u) == gridDim.x - 1) {
+            a.state[1] = 0;
+            __threadfence();
+            *(volatile uint32_t*)a.state = epoch;
+        }
+    }
+}
+
 }  // namespace dsuf
 
 using namespace dsuf;
 
-extern "C" size_t dsuf_ep_flag_bytes(int32_t world) { return (size_t)EPC_CTAS * (world > 0 ? world : 0) * sizeof(uint32_t); }
-
-extern "C" int32_t dsuf_ep_allreduce_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
-                                          int32_t world, int64_t n_elems, uint64_t state, uint64_t out) {
-    if (!ctx) return DSUF_E_BADARG;
-    DSUF_REQUIRE(ctx, world >= 1 && world <= EPC_MAX_WORLD && rank >= 0 && rank < world, "ep_allreduce: rank %d of world %d", rank, world);
-    DSUF_REQUIRE(ctx, n_elems >= 0 && n_elems % 8 == 0, "ep_allreduce: n_elems must be a multiple of 8");
-    DSUF_REQUIRE(ctx, peer_data && peer_flags && out && (out & 15) == 0, "ep_allreduce: null or misaligned pointer");
-    DSUF_REQUIRE(ctx, state && (state & 3) == 0, "ep_allreduce: null or misaligned state");
-    EpcArgs a;
+static int fill_epc(dsuf_ctx* ctx, EpcArgs& a, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank, int32_t world,
+                    int64_t n_elems, uint64_t state, uint64_t out) {
+    DSUF_REQUIRE(ctx, world >= 1 && world <= EPC_MAX_WORLD && rank >= 0 && rank < world, "ep exchange: rank %d of world %d", rank, world);
+    DSUF_REQUIRE(ctx, n_elems >= 0 && n_elems % 8 == 0, "ep exchange: n_elems must be a multiple of 8");
+    DSUF_REQUIRE(ctx, peer_data && peer_flags && out && (out & 15) == 0, "ep exchange: null or misaligned pointer");
+    DSUF_REQUIRE(ctx, state && (state & 3) == 0, "ep exchange: null or misaligned state");
     memset(&a, 0, sizeof(a));
     for (int r = 0; r < world; ++r) {
-        DSUF_REQUIRE(ctx, peer_data[r] && peer_flags[r] && (peer_data[r] & 15) == 0, "ep_allreduce: null or misaligned peer pointer %d", r);
-        DSUF_REQUIRE(ctx, r == rank || peer_data[r] != out, "ep_allreduce: out must not be a buffer a peer reads");
+        DSUF_REQUIRE(ctx, peer_data[r] && peer_flags[r] && (peer_data[r] & 15) == 0, "ep exchange: null or misaligned peer pointer %d", r);
+        DSUF_REQUIRE(ctx, peer_data[r] != out, "ep exchange: out must not be a partial buffer (peers still read it)");
         a.data[r] = (const uint4*)peer_data[r];
         a.flags[r] = (uint32_t*)peer_flags[r];
     }
-    DSUF_REQUIRE(ctx, peer_data[rank] != out, "ep_allreduce: out must differ from this rank's partial (peers still read it)");
     a.out = (bf16*)out;
     a.status = ctx->dev_status;
     a.n_vec = n_elems / 8;
     a.rank = rank;
     a.world = world;
     a.state = (uint32_t*)state;
+    return DSUF_OK;
+}
+
+extern "C" size_t dsuf_ep_flag_bytes(int32_t world) { return (size_t)EPC_CTAS * (world > 0 ? world : 0) * sizeof(uint32_t); }
+
+extern "C" int32_t dsuf_ep_allreduce_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
+                                          int32_t world, int64_t n_elems, uint64_t state, uint64_t out) {
+    if (!ctx) return DSUF_E_BADARG;
+    EpcArgs a;
+    int rc = fill_epc(ctx, a, peer_data, peer_flags, rank, world, n_elems, state, out);
+    if (rc) return rc;
     if (n_elems == 0) return DSUF_OK;
     return launch(ctx, (cudaStream_t)stream, ep_allreduce_kernel, dim3(EPC_CTAS), dim3(EPC_THREADS), 0, a);
+}
+
+extern "C" int32_t dsuf_ep_combine_bf16(dsuf_ctx* ctx, void* stream, uint64_t pair_row, uint64_t yrows, uint64_t shared, int32_t t,
+                                        int32_t topk, int32_t h, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
+                                        int32_t world, uint64_t state, uint64_t out) {
+    if (!ctx) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, t >= 0 && topk >= 1 && topk <= 16 && h > 0 && h % 8 == 0, "ep_combine: t >= 0, topk in 1..16, h a multiple of 8");
+    DSUF_REQUIRE(ctx, pair_row && yrows && (yrows & 15) == 0 && (shared & 15) == 0, "ep_combine: null or misaligned pointer");
+    EpCombineArgs p;
+    int rc = fill_epc(ctx, p.c, peer_data, peer_flags, rank, world, (int64_t)t * h, state, out);
+    if (rc) return rc;
+    p.pair_row = (const int*)pair_row;
+    p.yrows = (const float*)yrows;
+    p.shared = (const bf16*)shared;
+    p.partial = (bf16*)peer_data[rank];
+    p.topk = topk;
+    p.h = h;
+    if (t == 0) return DSUF_OK;
+    return launch(ctx, (cudaStream_t)stream, ep_combine_kernel, dim3(EPC_CTAS), dim3(EPC_THREADS), 0, p);
 }

@@ -35,6 +35,7 @@ class Exchange:
         tensor."""
         self.dist, self.rank, self.world, self.group = dist, rank, world, group
         self.peer, self.peer_out = peer, {}
+        self.reduced = set()   # data pointers of tensors a fused compute + exchange kernel has already summed over the ranks
 
     def all_gather_rows(self, out, local):
         """out [W*n][...] <- concatenation of every rank's local [n][...]."""
@@ -47,6 +48,8 @@ class Exchange:
     def all_reduce(self, t):
         """Element-wise sum over ranks; returns the tensor that holds it (``t`` itself on the process-group path)."""
         if self.world > 1:
+            if t.data_ptr() in self.reduced:
+                return t
             out = self.peer_out.get(t.data_ptr()) if self.peer is not None else None
             if out is not None:
                 return self.peer(t, out)

@@ -115,7 +115,13 @@ class _KernelCompute:
 
     def experts_partial(self, h_all, ids_all, w_all):
         s = self.s
-        return s.moe[self.l].forward(h_all, ids_all, w_all, s.y_part[self.l & 1])
+        part = s.y_part[self.l & 1]
+        if s.peer is not None and s.fuse_combine:
+            # one kernel: local sum of the top-k rows into the mapped partial buffer, hand-shake, sum over the ranks
+            out = s.xch.peer_out[part.data_ptr()]
+            return s.moe[self.l].forward(h_all, ids_all, w_all, part,
+                                         combine=lambda plan, yrows, shared: s.peer.combine(plan, yrows, shared, part, out))
+        return s.moe[self.l].forward(h_all, ids_all, w_all, part)
 
 
 class EpLayerStack:
@@ -151,7 +157,7 @@ class EpLayerStack:
         self.xs = t.empty((T, kloc // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
         # The two per-layer sums run as the library's peer-memory all-reduce when the partial buffers can be mapped
         # by every rank (torch symmetric memory); DSUF_EP_PEER=0 or a failed mapping falls back to NCCL.
-        self.peer = None
+        self.peer, self.fuse_combine = None, False
         if world > 1 and os.environ.get("DSUF_EP_PEER", "1") != "0":
             try:
                 from . import PeerAllReduce
@@ -166,6 +172,10 @@ class EpLayerStack:
             self.xch.peer = self.peer
             for buf in [self.partial] + self.y_part:
                 self.xch.peer_out[buf.data_ptr()] = t.empty((T, H), dtype=t.bfloat16, device=dev)
+            self.fuse_combine = os.environ.get("DSUF_EP_FUSE_COMBINE", "1") != "0"
+            if self.fuse_combine:
+                for buf in self.y_part:
+                    self.xch.reduced.add(self.xch.peer_out[buf.data_ptr()].data_ptr())
         else:
             self.partial = t.empty((T, H), dtype=t.bfloat16, device=dev)
             self.y_part = [t.empty((T, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
@@ -191,5 +201,7 @@ class EpLayerStack:
         slab = 64 if self.ctx.tcgen05 else 16
         slabs = (cfg.tokens + slab - 1) // slab
         plan = 1 if cfg.tokens * cfg.topk <= 1024 else 3
-        ar = 2 if self.peer is not None else 0   # this library's all-reduce kernel (NCCL's kernels are not counted)
+        # this library's exchange kernels (NCCL's kernels are not counted): the dense all-reduce, and the combine that
+        # either follows the unpermute as a second all-reduce or replaces it
+        ar = 0 if self.peer is None else 1 if self.fuse_combine else 2
         return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1 + ar)

@@ -218,6 +218,15 @@ size_t dsuf_ep_flag_bytes(int32_t world);
 int32_t dsuf_ep_allreduce_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
                                int32_t world, int64_t n_elems, uint64_t state, uint64_t out);
 
+/* Combine fused with its exchange, one kernel: dsuf_moe_unpermute's sum of every token's top-k expert rows on this
+ * rank (pair_row from the plan, yrows fp32 [rows][h] from dsuf_moe_w2, optional bf16 `shared` rows added by this rank:
+ * pass them on ONE rank), written into this rank's partial buffer peer_data[rank], then dsuf_ep_allreduce_bf16's
+ * hand-shake and rank-ordered sum into out [t][h] bf16 (dense rows).  Replaces the nsum / src2 sum plus push of
+ * comm_push (cu/comm.cu:167-180) across ranks.  Same buffer, flag, state and sequencing rules as above; h % 8 == 0. */
+int32_t dsuf_ep_combine_bf16(dsuf_ctx* ctx, void* stream, uint64_t pair_row, uint64_t yrows, uint64_t shared, int32_t t,
+                             int32_t topk, int32_t h, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
+                             int32_t world, uint64_t state, uint64_t out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,24 @@ def main():
     ref = bufs[1].float().clone()
     dist.all_reduce(ref)
     ok = ok and bool(((out.float() - ref).abs() <= ref.abs() * 2.0 ** -8 + 1e-6).all()) and ctx.status().code == 0
+    # combine fused with the exchange: every (token, choice) pair lives on exactly one rank
+    tokens, topk = rows, 8
+    plan = pkg.MoePlan(ctx, tokens, topk, 8, 8)
+    g = torch.Generator(device="cuda").manual_seed(7)          # same on every rank
+    owner = torch.randint(0, world, (tokens, topk), generator=g, device="cuda")
+    rows_of = torch.arange(tokens * topk, device="cuda", dtype=torch.int32).view(tokens, topk)
+    plan.pair_row.copy_(torch.where(owner == rank, rows_of, torch.full_like(rows_of, -1)).view(-1))
+    gy = torch.Generator(device="cuda").manual_seed(1000 + rank)
+    yrows = torch.randn(tokens * topk, width, generator=gy, device="cuda")
+    local = torch.where((owner == rank).view(tokens, topk, 1), yrows.view(tokens, topk, width), torch.zeros((), device="cuda")).sum(1)
+    ref = local.bfloat16().float()
+    dist.all_reduce(ref)
+    mag = local.abs()
+    dist.all_reduce(mag)     # the partials are rounded to bf16 before they are exchanged: the error scales with their sizes
+    for it in range(3):
+        ar.combine(plan, yrows, None, bufs[it & 1], out)
+        torch.cuda.synchronize()
+        ok = ok and bool(((out.float() - ref).abs() <= mag * 2.0 ** -7 + 1e-5).all()) and ctx.status().code == 0
     dist.barrier()
     torch.cuda.synchronize()
     print(f"rank {rank}: {'ok' if ok else 'MISMATCH'}", flush=True)

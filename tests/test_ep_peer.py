@@ -39,6 +39,32 @@ def test_single_rank_sum_is_a_copy_and_the_epoch_advances(pkg, ctx):
     assert state.cpu().tolist()[0] == 7 and ctx.status().code == 0
 
 
+def test_single_rank_combine_equals_unpermute(pkg, ctx):
+    """world = 1: the fused combine is the plain unpermute (sum of the top-k rows, one bf16 round), rows missing on
+    this rank (< 0) skipped, optional shared rows added."""
+    tokens, topk, h = 24, 4, 512
+    plan = pkg.MoePlan(ctx, tokens, topk, 8, 8)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    pr = torch.randperm(tokens * topk, generator=g, device="cuda").to(torch.int32)
+    pr[::5] = -1
+    plan.pair_row.copy_(pr)
+    yrows = torch.randn(tokens * topk, h, generator=g, device="cuda")
+    shared = torch.randn(tokens, h, generator=g, device="cuda").bfloat16()
+    want = torch.empty(tokens, h, dtype=torch.bfloat16, device="cuda")
+    pkg.moe_unpermute(ctx, plan, yrows, want, shared)
+    partial = torch.zeros(tokens, h, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros_like(partial)
+    flags = torch.zeros(pkg.lib().dsuf_ep_flag_bytes(1) // 4, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    ptrs, fl = (C.c_uint64 * 1)(partial.data_ptr()), (C.c_uint64 * 1)(flags.data_ptr())
+    rc = pkg.lib().dsuf_ep_combine_bf16(ctx.h, ctx.stream(), plan.pair_row.data_ptr(), yrows.data_ptr(), shared.data_ptr(), tokens, topk, h,
+                                        ptrs, fl, 0, 1, state.data_ptr(), out.data_ptr())
+    torch.cuda.synchronize()
+    assert rc == 0 and ctx.status().code == 0
+    assert (out.view(torch.uint16) == want.view(torch.uint16)).all()
+    assert (partial.view(torch.uint16) == want.view(torch.uint16)).all()
+
+
 def test_rejects_aliasing_and_bad_sizes(pkg, ctx):
     x = torch.zeros(64, device="cuda").bfloat16()
     flags = torch.zeros(pkg.lib().dsuf_ep_flag_bytes(1) // 4, dtype=torch.int32, device="cuda")
