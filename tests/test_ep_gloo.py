@@ -112,3 +112,43 @@ def test_shard_bounds_reject_uneven_splits():
     assert ep.shard_bounds(256, 8, 3) == (96, 128)
     with pytest.raises(ValueError):
         ep.shard_bounds(10, 4, 0)
+
+
+def test_exchange_routes_registered_buffers_through_the_peer_kernel():
+    """Host logic of the GPU exchange, with stand-ins for the process group and the peer-memory kernel: a registered
+    partial buffer is summed by the peer callable into its result tensor, a tensor that a fused compute + exchange
+    kernel has already summed passes through untouched, anything else goes to the process group."""
+    sys.path.insert(0, ROOT)
+    import importlib
+    from __graft_entry__ import load_package
+    ep = importlib.import_module(load_package().__name__ + ".ep")
+
+    class FakeDist:
+        def __init__(self):
+            self.calls = 0
+
+        def all_reduce(self, t, group=None):
+            self.calls += 1
+            t.mul_(2)   # "sum over two ranks holding the same values"
+
+    peer_calls = []
+
+    def peer(partial, out):
+        peer_calls.append((partial.data_ptr(), out.data_ptr()))
+        out.copy_(partial * 2)
+        return out
+
+    dist = FakeDist()
+    xch = ep.Exchange(dist, 0, 2, peer=peer)
+    partial, result, fused, other = (torch.ones(4) * v for v in (1.0, 0.0, 5.0, 3.0))
+    xch.peer_out[partial.data_ptr()] = result
+    xch.reduced.add(fused.data_ptr())
+    r = xch.all_reduce(partial)
+    assert r is result and torch.equal(result, torch.full((4,), 2.0)) and torch.equal(partial, torch.ones(4))
+    assert xch.all_reduce(fused) is fused and torch.equal(fused, torch.full((4,), 5.0))
+    assert xch.all_reduce(other) is other and torch.equal(other, torch.full((4,), 6.0))
+    assert dist.calls == 1 and len(peer_calls) == 1
+    # without a peer kernel every tensor goes to the process group; a single rank does nothing at all
+    xch2 = ep.Exchange(dist, 0, 2)
+    assert xch2.all_reduce(partial) is partial and dist.calls == 2
+    assert ep.Exchange(dist, 0, 1, peer=peer).all_reduce(other) is other and dist.calls == 2
