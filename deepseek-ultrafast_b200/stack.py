@@ -166,6 +166,12 @@ class EpLayerStack:
                 if rank == 0:
                     print(f"peer-memory all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
                 self.peer = None
+        if world > 1 and hasattr(dist, "ReduceOp"):
+            # every rank must take the same path: one rank that could not map its buffers sends all of them to NCCL
+            agreed = t.tensor([1 if self.peer is not None else 0], dtype=t.int32, device=dev)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 0:
+                self.peer = None
         if self.peer is not None:
             self.partial = self.peer.buffer((T, H))
             self.y_part = [self.peer.buffer((T, H)) for _ in range(2)]
