@@ -78,6 +78,8 @@ ABI = {
                                    C.c_int32, C.c_float, C.c_uint64, C.c_uint64]),
     "dsuf_moe_plan_scratch_ints": (C.c_size_t, [C.c_int32, C.c_int32]),
     "dsuf_moe_permute_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.POINTER(PlanStruct)]),
+    "dsuf_moe_gather_quant_prenorm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
+                                                  C.c_int32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64, C.c_uint64]),
     "dsuf_moe_gather_quant": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                           C.c_int32, C.POINTER(PlanStruct), C.c_uint64, C.c_uint64]),
     "dsuf_moe_w13_swiglu": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.POINTER(PlanStruct), C.c_uint64,
@@ -388,6 +390,15 @@ def moe_gather_quant(ctx, mode, plan, x, xq, xs):
     tok, h = x.shape
     ctx.check(lib().dsuf_moe_gather_quant(ctx.h, ctx.stream(), mode, x.data_ptr(), x.stride(0), tok, h, plan.topk,
                                           C.byref(plan.c), xq.data_ptr(), xs.data_ptr()))
+
+
+def moe_gather_quant_prenorm(ctx, mode, plan, x, norm_w, eps, xq, xs, sumsq=None):
+    """moe_gather_quant with RMS pre-normalisation (cu/tcmoe.cu:88): bf16(norm_w * (x * rs)) quantised once per token."""
+    tok, h = x.shape
+    if sumsq is None:
+        sumsq = row_sumsq(ctx, x)
+    ctx.check(lib().dsuf_moe_gather_quant_prenorm(ctx.h, ctx.stream(), mode, x.data_ptr(), x.stride(0), tok, h, plan.topk,
+                                                  C.byref(plan.c), norm_w.data_ptr(), sumsq.data_ptr(), eps, xq.data_ptr(), xs.data_ptr()))
 
 
 def moe_w13_swiglu(ctx, w13, act_mode, plan, xq, xs, act_out, swiglu_limit=0.0):

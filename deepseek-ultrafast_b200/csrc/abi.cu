@@ -231,6 +231,21 @@ int32_t dsuf_moe_gather_quant(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_
                             (const int*)plan->pair_row, topk, 0);
 }
 
+int32_t dsuf_moe_gather_quant_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t t, int32_t h,
+                                      int32_t topk, const dsuf_moe_plan* plan, uint64_t norm_w, uint64_t sumsq, float eps,
+                                      uint64_t xq_out, uint64_t xs_out) {
+    if (!ctx) return DSUF_E_BADARG;
+    int rc = check_plan(ctx, plan);
+    if (rc) return rc;
+    DSUF_REQUIRE(ctx, mode == DSUF_MODE_MX || mode == DSUF_MODE_DS, "gather_quant_prenorm: unknown mode %d", mode);
+    DSUF_REQUIRE(ctx, h > 0 && h % 128 == 0 && ldx >= h && ldx % 8 == 0, "gather_quant_prenorm: h (%d) must be a multiple of 128, ldx a multiple of 8", h);
+    DSUF_REQUIRE(ctx, topk >= 1 && (long long)t * topk == plan->p, "gather_quant_prenorm: t*topk != plan.p");
+    DSUF_REQUIRE(ctx, x && xq_out && xs_out && norm_w && sumsq && (x & 15) == 0 && (xq_out & 15) == 0 && (norm_w & 15) == 0,
+                 "gather_quant_prenorm: null or misaligned pointer");
+    return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, t, h, (void*)xq_out, (void*)xs_out,
+                            (const int*)plan->pair_row, topk, 0, (const void*)norm_w, (const float*)sumsq, eps);
+}
+
 int32_t dsuf_moe_w13_swiglu(dsuf_ctx* ctx, void* stream, const dsuf_weight* w13, int32_t act_mode, const dsuf_moe_plan* plan,
                             uint64_t xq, uint64_t xs, float swiglu_limit, uint64_t act_out) {
     if (!ctx || !w13) return DSUF_E_BADARG;

@@ -186,6 +186,13 @@ int32_t dsuf_moe_permute_plan(dsuf_ctx* ctx, void* stream, uint64_t ids, uint64_
 int32_t dsuf_moe_gather_quant(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t t, int32_t h,
                               int32_t topk, const dsuf_moe_plan* plan, uint64_t xq_out, uint64_t xs_out);
 
+/* The same with the RMS pre-normalisation of dsuf_act_quant_fp8_prenorm in front (moe_gather_quant with MqParams.pw,
+ * cu/tcmoe.cu:88-133: every token row is normalised and quantised once, then written to its topk permuted rows).
+ * norm_w bf16 [h], sumsq f32 [t] (dsuf_row_sumsq of x). */
+int32_t dsuf_moe_gather_quant_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t t, int32_t h,
+                                      int32_t topk, const dsuf_moe_plan* plan, uint64_t norm_w, uint64_t sumsq, float eps,
+                                      uint64_t xq_out, uint64_t xs_out);
+
 /* Grouped gate/up GEMM + SwiGLU: moe_fp4_swiglu (cu/gemv.cu:1016-1692 via ops::moe_gemv, ops.rs:482-634) for
  * decode plans, tc_moe_w13 (cu/tcmoe.cu:184-588, TmParams ops.rs:1513-1534) for 128-row plans.
  * act_out bf16 [p][inter] indexed by permuted row:

@@ -241,6 +241,28 @@ def test_gather_quant_rows_equal_plain_quant(pkg, ctx, mode):
     assert (xs.cpu().numpy() == so[row_pair // k]).all()
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+def test_gather_quant_prenorm_rows_equal_plain_prenorm_quant(pkg, ctx, mode):
+    t, k, e, h = 24, 4, 16, 512
+    g = seeded(19)
+    xt, xn = randn_bf16(g, t, h)
+    wt, _ = randn_bf16(g, 1, h)
+    wt = (1.0 + 0.1 * wt.float()).bfloat16().reshape(h)
+    rng = np.random.default_rng(2)
+    ids = np.stack([rng.choice(e, k, replace=False) for _ in range(t)]).astype(np.int32)
+    plan = pkg.MoePlan(ctx, t, k, e, 8)
+    pkg.moe_perm(ctx, plan, torch.from_numpy(ids).cuda(), torch.ones(t, k).cuda())
+    blk = 32 if mode == 0 else 128
+    xq = torch.zeros(t * k, h, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(t * k, h // blk, dtype=torch.uint8 if mode == 0 else torch.float32, device="cuda")
+    pkg.moe_gather_quant_prenorm(ctx, mode, plan, xt.cuda(), wt.cuda(), 1e-6, xq, xs)
+    torch.cuda.synchronize()
+    qo, so = oracle.act_quant_prenorm(mode, xn, wt.view(torch.uint16).numpy(), oracle.row_sumsq(xn), 1e-6)
+    row_pair = plan.row_pair.cpu().numpy()
+    assert (xq.cpu().numpy() == qo[row_pair // k]).all()
+    assert (xs.cpu().numpy() == so[row_pair // k]).all()
+
+
 # ------------------------------------------------------------------ routed-expert layer
 def _moe_case(pkg, ctx, act_mode, T, H, I, E, K, tile_rows, seed, e_lo=0, n_loc=None, limit=0.0, shared=False):
     n_loc = E if n_loc is None else n_loc
