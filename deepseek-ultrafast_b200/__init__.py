@@ -51,6 +51,7 @@ ABI = {
     "dsuf_ctx_set_decode_path": (C.c_int32, [C.c_void_p, C.c_int32]),
     "dsuf_status_poll": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(DevStatus)]),
     "dsuf_sm_count": (C.c_int32, [C.c_void_p]),
+    "dsuf_ctx_set_wait_budget_us": (C.c_int32, [C.c_void_p, C.c_int64]),
     "dsuf_quant_fp8_weight_host": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_quant_fp4_weight_host": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_packed_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
@@ -74,6 +75,7 @@ ABI = {
                                   C.c_int32, C.c_float, C.c_uint64]),
     "dsuf_gemm_fp8_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
                                          C.c_int32, C.c_float]),
+    "dsuf_probe_tensor_rate": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_double)]),
     "dsuf_moe_route": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32,
                                    C.c_int32, C.c_float, C.c_uint64, C.c_uint64]),
     "dsuf_moe_plan_scratch_ints": (C.c_size_t, [C.c_int32, C.c_int32]),
@@ -180,6 +182,10 @@ class Ctx:
         """True: tcgen05 streaming kernels for decode shapes; False: the mma.sync streaming kernels."""
         self.check(lib().dsuf_ctx_set_decode_path(self.h, 1 if tcgen05 else 0))
         self.tcgen05 = bool(tcgen05)
+
+    def set_wait_budget_us(self, microseconds):
+        """Upper bound of the peer-exchange kernels' wait for a peer (they report a time-out in the status word after it)."""
+        self.check(lib().dsuf_ctx_set_wait_budget_us(self.h, int(microseconds)))
 
     def stream(self):
         return C.c_void_p(self.torch.cuda.current_stream(self.device).cuda_stream)
@@ -347,6 +353,22 @@ class PeerAllReduce:
         return out
 
 
+def probe_tensor_rate(ctx, n_cols=128, a_is_e2m1=False, iters=20000, reps=5):
+    """TFLOP/s the tensor cores deliver to the library's MMA instruction with no memory traffic (dsuf_probe_tensor_rate),
+    best of ``reps`` launches timed with CUDA events."""
+    t = ctx.torch
+    flop = C.c_double()
+    best = 0.0
+    for _ in range(reps + 1):
+        e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.check(lib().dsuf_probe_tensor_rate(ctx.h, ctx.stream(), n_cols, int(bool(a_is_e2m1)), iters, C.byref(flop)))
+        e1.record()
+        t.cuda.synchronize()
+        best = max(best, flop.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
 class MoePlan:
     """Caller-owned buffers of the permute plan (MpParams, ops.rs:1478-1491)."""
 
@@ -452,7 +474,10 @@ class MoeLayer:
         moe_perm(ctx, plan, ids, w, self.e_lo)
         moe_gather_quant(ctx, self.act_mode, plan, x, self.xq, self.xs)
         if events is not None:
-            e0, e1 = ctx.torch.cuda.Event(enable_timing=True), ctx.torch.cuda.Event(enable_timing=True)
+            # inside a stream capture the events must be recorded as graph nodes of their own (external events), so that
+            # every replay of the graph stamps them
+            ext = {"external": True} if ctx.torch.cuda.is_current_stream_capturing() else {}
+            e0, e1 = ctx.torch.cuda.Event(enable_timing=True, **ext), ctx.torch.cuda.Event(enable_timing=True, **ext)
             e0.record()
         moe_w13_swiglu(ctx, self.w13, self.act_mode, plan, self.xq, self.xs, self.act, self.swiglu_limit)
         if events is not None:

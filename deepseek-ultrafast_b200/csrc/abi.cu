@@ -29,6 +29,8 @@ int32_t dsuf_ctx_create(int32_t device, dsuf_ctx** out) {
     }
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    ctx->clock_khz = prop.clockRate > 0 ? prop.clockRate : 1965000;
+    ctx->xchg_wait_ticks = WAIT_BUDGET_TICKS;
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -66,6 +68,13 @@ int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled) {
 int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05) {
     if (!ctx) return DSUF_E_BADARG;
     ctx->use_tc = tcgen05 ? 1 : 0;
+    return DSUF_OK;
+}
+
+int32_t dsuf_ctx_set_wait_budget_us(dsuf_ctx* ctx, int64_t microseconds) {
+    if (!ctx) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, microseconds >= 1 && microseconds <= 10000000, "wait budget must be 1 us .. 10 s, got %lld", (long long)microseconds);
+    ctx->xchg_wait_ticks = (long long)microseconds * ctx->clock_khz / 1000;
     return DSUF_OK;
 }
 
@@ -214,7 +223,7 @@ int32_t dsuf_moe_permute_plan(dsuf_ctx* ctx, void* stream, uint64_t ids, uint64_
     if (!ctx) return DSUF_E_BADARG;
     int rc = check_plan(ctx, plan);
     if (rc) return rc;
-    DSUF_REQUIRE(ctx, ids && w, "permute_plan: null pointer");
+    DSUF_REQUIRE(ctx, plan->p == 0 || (ids && w), "permute_plan: null pointer");
     return launch_plan(ctx, (cudaStream_t)stream, (const int*)ids, (const float*)w, e_lo, plan);
 }
 
@@ -226,6 +235,7 @@ int32_t dsuf_moe_gather_quant(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_
     DSUF_REQUIRE(ctx, mode == DSUF_MODE_MX || mode == DSUF_MODE_DS, "gather_quant: unknown mode %d", mode);
     DSUF_REQUIRE(ctx, h > 0 && h % 128 == 0 && ldx >= h && ldx % 8 == 0, "gather_quant: h (%d) must be a multiple of 128, ldx a multiple of 8", h);
     DSUF_REQUIRE(ctx, topk >= 1 && (long long)t * topk == plan->p, "gather_quant: t*topk != plan.p");
+    if (t == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, x && xq_out && xs_out && (x & 15) == 0 && (xq_out & 15) == 0, "gather_quant: null or misaligned pointer");
     return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, t, h, (void*)xq_out, (void*)xs_out,
                             (const int*)plan->pair_row, topk, 0);
@@ -240,6 +250,7 @@ int32_t dsuf_moe_gather_quant_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode,
     DSUF_REQUIRE(ctx, mode == DSUF_MODE_MX || mode == DSUF_MODE_DS, "gather_quant_prenorm: unknown mode %d", mode);
     DSUF_REQUIRE(ctx, h > 0 && h % 128 == 0 && ldx >= h && ldx % 8 == 0, "gather_quant_prenorm: h (%d) must be a multiple of 128, ldx a multiple of 8", h);
     DSUF_REQUIRE(ctx, topk >= 1 && (long long)t * topk == plan->p, "gather_quant_prenorm: t*topk != plan.p");
+    if (t == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, x && xq_out && xs_out && norm_w && sumsq && (x & 15) == 0 && (xq_out & 15) == 0 && (norm_w & 15) == 0,
                  "gather_quant_prenorm: null or misaligned pointer");
     return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, t, h, (void*)xq_out, (void*)xs_out,
@@ -251,6 +262,7 @@ int32_t dsuf_moe_w13_swiglu(dsuf_ctx* ctx, void* stream, const dsuf_weight* w13,
     if (!ctx || !w13) return DSUF_E_BADARG;
     int rc = check_plan(ctx, plan);
     if (rc) return rc;
+    if (plan->p == 0) return DSUF_OK;   /* an empty batch launches nothing, like route / quant / unpermute */
     DSUF_REQUIRE(ctx, (xq & 15) == 0, "moe_w13: xq must be 16-byte aligned");
     return launch_stream_moe(ctx, (cudaStream_t)stream, w13, EPI_W13, act_mode, plan, (const void*)xq, (const void*)xs, swiglu_limit,
                              (void*)act_out, w13->d.n / 2);
@@ -261,6 +273,7 @@ int32_t dsuf_moe_w2(dsuf_ctx* ctx, void* stream, const dsuf_weight* w2, int32_t 
     if (!ctx || !w2) return DSUF_E_BADARG;
     int rc = check_plan(ctx, plan);
     if (rc) return rc;
+    if (plan->p == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, (act_q & 15) == 0, "moe_w2: act_q must be 16-byte aligned");
     return launch_stream_moe(ctx, (cudaStream_t)stream, w2, EPI_W2, act_mode, plan, (const void*)act_q, (const void*)act_s, 0.f,
                              (void*)yrows_out, w2->d.n);
@@ -273,6 +286,7 @@ int32_t dsuf_moe_unpermute(dsuf_ctx* ctx, void* stream, const dsuf_moe_plan* pla
     if (rc) return rc;
     DSUF_REQUIRE(ctx, topk >= 1 && topk <= 16 && (long long)t * topk == plan->p, "unpermute: t*topk != plan.p");
     DSUF_REQUIRE(ctx, h > 0 && h % 4 == 0 && ldo >= h && ldo % 4 == 0, "unpermute: h and ldo must be multiples of 4");
+    if (t == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, yrows && out && (yrows & 15) == 0 && (out & 7) == 0, "unpermute: null or misaligned pointer");
     return launch_unpermute(ctx, (cudaStream_t)stream, plan, (const float*)yrows, (const void*)shared, t, topk, h, (void*)out, ldo);
 }

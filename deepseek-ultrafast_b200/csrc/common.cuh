@@ -18,7 +18,7 @@ struct DevStatus {
     int cta;      // blockIdx.x of the reporter
     int where;    // site id inside the kernel
 };
-enum { DEVERR_NONE = 0, DEVERR_WAIT_TIMEOUT = 1, DEVERR_BAD_PLAN = 2 };
+enum { DEVERR_NONE = 0, DEVERR_WAIT_TIMEOUT = 1, DEVERR_BAD_PLAN = 2, DEVERR_EPOCH_DRIFT = 3 };
 
 // Every spin in this library gives up after this many clock64 ticks (~2 s at 2 GHz) and reports instead of hanging.
 constexpr long long WAIT_BUDGET_TICKS = 4000000000ll;
@@ -133,15 +133,33 @@ DSUF_DEV void prefetch_tmap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
-DSUF_DEV bool elect_one() {
-    uint32_t pred;
-    asm volatile("{ .reg .pred e; elect.sync _|e, 0xffffffff; selp.u32 %0, 1, 0, e; }" : "=r"(pred));
-    return pred != 0;
+// ---- warp-level helpers ----
+// True in exactly one lane of a converged warp (the hardware picks it); the others skip the guarded statement.
+DSUF_DEV bool warp_elect() {
+    uint32_t chosen = 0;
+    asm volatile(
+        "{\n"
+        "  .reg .pred is_leader;\n"
+        "  elect.sync _|is_leader, %1;\n"
+        "  @is_leader mov.u32 %0, 1;\n"
+        "}\n"
+        : "+r"(chosen)
+        : "r"(0xffffffffu));
+    return chosen != 0;
 }
-// Warp-uniform broadcasts: tcgen05 / TMA instructions take their descriptors from uniform registers; values the
-// compiler cannot prove uniform cost a register-file round trip per operand on every issue.
-DSUF_DEV uint32_t uni32(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
-DSUF_DEV uint64_t uni64(uint64_t v) { return ((uint64_t)uni32((uint32_t)(v >> 32)) << 32) | uni32((uint32_t)v); }
+// Lane 0's value in every lane.  tcgen05 / TMA instructions read descriptors and addresses from uniform registers;
+// handing the compiler a value it can prove warp-uniform saves a register-file round trip per operand per issue.
+template <typename T>
+DSUF_DEV T warp_uniform(T v) {
+    static_assert(sizeof(T) == 4 || sizeof(T) == 8, "32- or 64-bit values");
+    if constexpr (sizeof(T) == 4) {
+        return (T)__shfl_sync(0xffffffffu, (uint32_t)v, 0);
+    } else {
+        const uint32_t lo = __shfl_sync(0xffffffffu, (uint32_t)((uint64_t)v & 0xffffffffu), 0);
+        const uint32_t hi = __shfl_sync(0xffffffffu, (uint32_t)((uint64_t)v >> 32), 0);
+        return (T)(((uint64_t)hi << 32) | lo);
+    }
+}
 DSUF_DEV void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
 
 // ---- codecs ----
@@ -186,92 +204,115 @@ DSUF_DEV float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)
 DSUF_DEV int rowmap8(int g) { return ((g & 3) << 1) | (g >> 2); }
 
 
-// ---- tcgen05 (5th-generation tensor cores: operands in shared memory, accumulators in tensor memory) ----
-DSUF_DEV void tmem_alloc(uint32_t* slot_in_smem, uint32_t ncols) {   // whole warp; ncols a power of two >= 32
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)), "r"(ncols) : "memory");
+// ---- tcgen05: operands in shared memory, accumulators and block scales in tensor memory ----
+// Every wrapper is the single-CTA form (cta_group::1).  Tensor-memory addresses are (lane << 16) | column.
+
+// Allocation: a whole warp asks for `ncols` columns (a power of two, at least 32); the base address is written to
+// `result_in_smem`.  The same warp must give the columns back before the CTA exits.
+DSUF_DEV void tmem_alloc(uint32_t* result_in_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" : : "r"(smem_u32(result_in_smem)), "r"(ncols) : "memory");
 }
-DSUF_DEV void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
-DSUF_DEV void tmem_dealloc(uint32_t taddr, uint32_t ncols) {          // whole warp
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+DSUF_DEV void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" : : : "memory"); }
+DSUF_DEV void tmem_dealloc(uint32_t base, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" : : "r"(base), "r"(ncols) : "memory");
 }
-DSUF_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-DSUF_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-DSUF_DEV void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// The mbarrier receives one arrival when every tcgen05 operation issued so far by this thread has completed.
+
+// Ordering of tensor-core work against barriers / thread synchronisation, and of generic-proxy shared-memory writes
+// against the asynchronous proxy (TMA, tcgen05 operand reads).
+DSUF_DEV void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" : : : "memory"); }
+DSUF_DEV void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" : : : "memory"); }
+DSUF_DEV void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" : : : "memory"); }
+
+// One arrival on `bar` once all tcgen05 operations this thread has issued so far are complete.
 DSUF_DEV void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" : : "r"(smem_u32(bar)) : "memory");
 }
-// 512-byte scale-factor atom (32 rows x 16 bytes) from shared memory to 4 tensor-memory columns, all 4 lane quarters.
-DSUF_DEV void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+
+// Shared-memory operand descriptor.  Fields, low to high: start address, leading-dimension byte offset, stride byte
+// offset (each in 16-byte units, 14 bits), the constant 0b001 at bit 46 that sm_100 descriptors carry, and the swizzle
+// mode in the top three bits.
+enum : uint32_t { TC_SWIZZLE_NONE = 0, TC_SWIZZLE_128B = 2 };
+DSUF_DEV uint64_t tc_smem_desc(const void* smem_ptr, uint32_t leading_bytes, uint32_t stride_bytes, uint32_t swizzle) {
+    auto units16 = [](uint32_t bytes) -> uint64_t { return (uint64_t)((bytes >> 4) & 0x3fffu); };
+    return units16(smem_u32(smem_ptr)) | (units16(leading_bytes) << 16) | (units16(stride_bytes) << 32) | (1ull << 46) |
+           ((uint64_t)(swizzle & 7u) << 61);
 }
-// D[tmem] (+)= A[smem] * B[smem] with UE8M0 block scales from tensor memory; one K=32 step of 8-bit containers.
-DSUF_DEV void tc_mma_mx(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
-    asm volatile(
-        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p; }" ::"r"(d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-        : "memory");
-}
-// Shared-memory matrix descriptor: start address, leading / stride byte offsets (16-byte units), descriptor
-// version 1 (bit 46), layout type (2 = 128-byte swizzle, 0 = none).
-DSUF_DEV uint64_t tc_smem_desc(const void* p, uint32_t lbo, uint32_t sbo, uint32_t layout) {
-    uint64_t d = (uint64_t)((smem_u32(p) & 0x3FFFF) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)(layout & 7) << 61;
+
+// Instruction descriptor of kind::mxf8f6f4 with block scaling, M = 128 rows of A, `n` columns of B (a multiple of 8).
+// Bit positions: A element type at 7 (0 = e4m3, 5 = e2m1), B element type at 10 (e4m3 = 0), N / 8 at 17, the scale type
+// at 23 (1 = UE8M0), M / 16 at 24.  The byte of each 4-byte scale word that a K = 32 step uses is chosen per step by
+// tc_idesc_sf (B's selector at bit 4, A's at bit 29).
+struct TcIdesc {
+    static constexpr uint32_t A_TYPE_SHIFT = 7, N_SHIFT = 17, SCALE_UE8M0 = 1u << 23, M_SHIFT = 24, SFB_SEL_SHIFT = 4, SFA_SEL_SHIFT = 29;
+    static constexpr uint32_t TYPE_E2M1 = 5;
+};
+DSUF_DEV uint32_t tc_idesc_mx(int n, bool a_is_e2m1) {
+    uint32_t d = TcIdesc::SCALE_UE8M0 | ((uint32_t)(128 / 16) << TcIdesc::M_SHIFT) | ((uint32_t)(n / 8) << TcIdesc::N_SHIFT);
+    if (a_is_e2m1) d |= TcIdesc::TYPE_E2M1 << TcIdesc::A_TYPE_SHIFT;
     return d;
 }
-// Instruction descriptor of kind::mxf8f6f4 with M = 128: N>>3 at bit 17, UE8M0 scale type (bit 23), M>>4 at bit 24,
-// A format at bits 7-9 (0 = e4m3, 5 = e2m1), B format e4m3; scale-factor byte selectors (bits 4-5 for B, 29-30 for A)
-// are OR-ed in per K step.
-DSUF_DEV uint32_t tc_idesc_mx(int n, bool a_is_e2m1) {
-    return ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24) | (a_is_e2m1 ? (5u << 7) : 0u);
+DSUF_DEV uint32_t tc_idesc_sf(uint32_t idesc, uint32_t k_step) {
+    return idesc | (k_step << TcIdesc::SFA_SEL_SHIFT) | (k_step << TcIdesc::SFB_SEL_SHIFT);
 }
-DSUF_DEV uint32_t tc_idesc_sf(uint32_t idesc, uint32_t kc) { return idesc | (kc << 29) | (kc << 4); }
 
-// Accumulator read-back: this warp's 32 lanes x NCOL consecutive fp32 columns.
+// Copies one 512-byte scale atom (32 rows x 16 bytes in shared memory) into 4 tensor-memory columns, replicated to the
+// four 32-lane quarters.
+DSUF_DEV void tc_cp_sf(uint32_t tmem_cols, uint64_t atom_desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" : : "r"(tmem_cols), "l"(atom_desc) : "memory");
+}
+
+// One K = 32 step on 8-bit containers: D[tmem] = (accumulate ? D : 0) + (A * scale_a) (B * scale_b), scales read from
+// tensor memory.  Issued by a single thread.
+DSUF_DEV void tc_mma_mx(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                        uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        "  .reg .pred keep_d;\n"
+        "  setp.ne.u32 keep_d, %6, 0;\n"
+        "  tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], keep_d;\n"
+        "}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+
+// Accumulator read-back.  A warp reads its own 32 lanes (lane quarter = warp index % 4) x NCOL consecutive fp32
+// columns; thread i of the warp receives lane i's values.  The destination registers are written as floats directly
+// (the instruction moves untyped 32-bit words).
+#define DSUF_TM_F4(v, i) "=f"(v[i]), "=f"(v[(i) + 1]), "=f"(v[(i) + 2]), "=f"(v[(i) + 3])
+#define DSUF_TM_F8(v, i) DSUF_TM_F4(v, i), DSUF_TM_F4(v, (i) + 4)
+#define DSUF_TM_F16(v, i) DSUF_TM_F8(v, i), DSUF_TM_F8(v, (i) + 8)
+DSUF_DEV void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" : : : "memory"); }
 template <int NCOL>
-DSUF_DEV void tmem_ld(uint32_t taddr, float* v);
-template <>
-DSUF_DEV void tmem_ld<8>(uint32_t taddr, float* v) {
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+DSUF_DEV void tmem_ld_issue(uint32_t taddr, float* v) {
+    static_assert(NCOL == 8 || NCOL == 16 || NCOL == 32, "columns per load");
+    if constexpr (NCOL == 8) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : DSUF_TM_F8(v, 0)
+                     : "r"(taddr)
+                     : "memory");
+    } else if constexpr (NCOL == 16) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : DSUF_TM_F16(v, 0)
+            : "r"(taddr)
+            : "memory");
+    } else {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : DSUF_TM_F16(v, 0), DSUF_TM_F16(v, 16)
+            : "r"(taddr)
+            : "memory");
+    }
 }
-template <>
-DSUF_DEV void tmem_ld<16>(uint32_t taddr, float* v) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-template <>
-DSUF_DEV void tmem_ld<32>(uint32_t taddr, float* v) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+// Load and wait for the data to be in registers.
+template <int NCOL>
+DSUF_DEV void tmem_ld(uint32_t taddr, float* v) {
+    tmem_ld_issue<NCOL>(taddr, v);
+    tmem_wait_ld();
 }
 
 }  // namespace dsuf

@@ -9,7 +9,7 @@
 // (64 tokens x 7168) that is 7 peer reads of 0.9 MB per rank: latency-, not bandwidth-bound, which is why it is one
 // kernel with one hand-shake instead of a ring or a tree.
 //
-// Every wait is bounded (common.cuh WAIT_BUDGET_TICKS): a rank that never announces makes the others record
+// Every wait is bounded (dsuf_ctx_set_wait_budget_us, default common.cuh WAIT_BUDGET_TICKS): a rank that never announces makes the others record
 // DEVERR_WAIT_TIMEOUT in the context's status word and finish with an incomplete sum instead of hanging.
 // The only peer accesses are plain ld / st on peer pointers.
 #include "internal.h"
@@ -28,6 +28,7 @@ struct EpcArgs {
     DevStatus* status;
     long long n_vec;                   // n_elems / 8
     int rank, world;
+    long long wait_ticks;              // clock64 budget of the wait for the peers' announcements
     uint32_t* state;                   // local: [0] calls completed (the epoch lives on the device so that a captured
                                        // graph advances it on every replay), [1] CTAs finished in this call
 };
@@ -45,6 +46,24 @@ DSUF_DEV uint4 ld_relaxed_sys_v4(const uint4* p) {
     return v;
 }
 
+// Waits until the peer's flag has reached this call's epoch, for at most a.wait_ticks.  A peer runs at most one call
+// ahead of this rank (it needs this rank's announcement of call n + 1 to finish that call), so a flag further ahead
+// means the two ranks no longer count the same calls (a launch that failed or timed out on one side): reported as
+// DEVERR_EPOCH_DRIFT instead of summing partials of different calls in silence.
+DSUF_DEV void exchange_wait(const EpcArgs& a, const uint32_t* f, uint32_t epoch, long long t0, int site) {
+    for (;;) {
+        const int32_t ahead = (int32_t)(ld_acquire_sys(f) - epoch);
+        if (ahead >= 0) {
+            if (ahead > 1) report(a.status, DEVERR_EPOCH_DRIFT, KID_EPCOMM, site);
+            return;
+        }
+        if (clock64() - t0 > a.wait_ticks) {
+            report(a.status, DEVERR_WAIT_TIMEOUT, KID_EPCOMM, site);
+            return;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(EPC_THREADS) ep_allreduce_kernel(const EpcArgs a) {
     pdl_wait();
     pdl_launch_dependents();
@@ -58,12 +77,7 @@ __global__ void __launch_bounds__(EPC_THREADS) ep_allreduce_kernel(const EpcArgs
     if (tid < a.world) {
         const uint32_t* f = a.flags[a.rank] + b * a.world + tid;
         const long long t0 = clock64();
-        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
-            if (clock64() - t0 > WAIT_BUDGET_TICKS) {
-                report(a.status, DEVERR_WAIT_TIMEOUT, KID_EPCOMM, tid);
-                break;
-            }
-        }
+        exchange_wait(a, f, epoch, t0, tid);
     }
     __syncthreads();
     // ---- sum in rank order; all of an element's loads are issued before the first add (peer latency, not bandwidth,
@@ -155,12 +169,7 @@ __global__ void __launch_bounds__(EPC_THREADS) ep_combine_kernel(const EpCombine
     if (tid < a.world) {
         const uint32_t* f = a.flags[a.rank] + b * a.world + tid;
         const long long t0 = clock64();
-        while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
-            if (clock64() - t0 > WAIT_BUDGET_TICKS) {
-                report(a.status, DEVERR_WAIT_TIMEOUT, KID_EPCOMM, 16 + tid);
-                break;
-            }
-        }
+        exchange_wait(a, f, epoch, t0, 16 + tid);
     }
     __syncthreads();
     for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
@@ -214,6 +223,7 @@ static int fill_epc(dsuf_ctx* ctx, EpcArgs& a, const uint64_t* peer_data, const 
     }
     a.out = (bf16*)out;
     a.status = ctx->dev_status;
+    a.wait_ticks = ctx->xchg_wait_ticks;
     a.n_vec = n_elems / 8;
     a.rank = rank;
     a.world = world;

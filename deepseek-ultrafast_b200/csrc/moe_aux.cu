@@ -21,7 +21,7 @@ __global__ void __launch_bounds__(256) route_kernel(int score_fn, const float* s
     pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
     const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (tok >= t) return;
-    float sc[ROUTE_MAX_PER_LANE], key[ROUTE_MAX_PER_LANE];
+    float sc[ROUTE_MAX_PER_LANE];
     const float* s = scores + (size_t)tok * n_exp;
     float mx = -INFINITY;
 #pragma unroll
@@ -48,33 +48,42 @@ __global__ void __launch_bounds__(256) route_kernel(int score_fn, const float* s
         for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
             if (lane + 32 * i < n_exp) sc[i] = sqrtf(sc[i] > 20.f ? sc[i] : log1pf(expf(sc[i])));
     }
+    // Selection works on one 64-bit word per candidate: the biased score mapped to an unsigned integer that orders like
+    // the float (high half) and the complement of the expert id (low half).  The largest word is the best score and,
+    // among equal scores, the lowest id -- the reference's tie rule (cu/route.cuh:3-56) -- and it names its own expert,
+    // so one butterfly maximum per pick is the whole selection.  A picked candidate is retired by zeroing its word.
+    unsigned long long cand[ROUTE_MAX_PER_LANE];
 #pragma unroll
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        key[i] = e < n_exp ? sc[i] + (bias ? bias[e] : 0.f) : -INFINITY;
+        cand[i] = 0ull;
+        if (e < n_exp) {
+            const float biased = sc[i] + (bias ? bias[e] : 0.f) + 0.0f;  // + 0.0f: -0 and +0 compare equal, as floats do
+            const unsigned bits = __float_as_uint(biased);
+            const unsigned ordered = (bits >> 31) ? ~bits : (bits | 0x80000000u);
+            cand[i] = ((unsigned long long)ordered << 32) | (unsigned)(0xffffffffu - (unsigned)e);
+        }
     }
     float wsum = 0.f, myw = 0.f;
     int myid = 0;
     for (int j = 0; j < topk; ++j) {
-        // lane-local best (first maximum = lowest expert id among this lane's ties)
-        float bv = key[0];
-        int bi = 0;
+        unsigned long long best = cand[0];
 #pragma unroll
-        for (int i = 1; i < ROUTE_MAX_PER_LANE; ++i)
-            if (key[i] > bv) { bv = key[i]; bi = i; }
-        // order-preserving integer key so the warp reduction is exact
-        const unsigned u = __float_as_uint(bv);
-        const unsigned k32 = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-        const unsigned kmax = __reduce_max_sync(0xffffffffu, k32);
-        const int cand = lane + 32 * bi;
-        const int win = (int)__reduce_min_sync(0xffffffffu, k32 == kmax ? (unsigned)cand : 0x7fffffffu);
+        for (int i = 1; i < ROUTE_MAX_PER_LANE; ++i) best = cand[i] > best ? cand[i] : best;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        const int picked = (int)(0xffffffffu - (unsigned)(best & 0xffffffffull));  // every lane holds the same word
+        // the owner lane retires the candidate and publishes its unbiased score
         float wv = 0.f;
 #pragma unroll
         for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
-            if (lane + 32 * i == win) { wv = sc[i]; key[i] = -INFINITY; }
-        wv = __shfl_sync(0xffffffffu, wv, win & 31);
+            if (cand[i] == best) { wv = sc[i]; cand[i] = 0ull; }
+        wv = __shfl_sync(0xffffffffu, wv, picked & 31);
         wsum += wv;
-        if (lane == j) { myw = wv; myid = win; }
+        if (lane == j) { myw = wv; myid = picked; }
     }
     if (lane < topk) {
         const float v = topk > 1 ? __fdiv_rn(myw, wsum + 1e-20f) : myw;

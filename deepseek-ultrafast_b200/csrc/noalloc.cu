@@ -14,7 +14,9 @@
 //     stream-ordered.  The arrival counters must start at zero: they are cleared on the stream before every launch,
 //     whatever the previous call left behind.  The partial sums are fully rewritten before they are read.
 //   * the first call on a device looks the array's address up (cudaGetSymbolAddress) and remembers it; make that
-//     first call before any stream capture begins.
+//     first call before any stream capture begins.  With lazy module loading (the CUDA default) that look-up is also
+//     the moment the driver places this file's device image, array included, in device memory: a caller that is about
+//     to hand all remaining device memory to its own arena makes one small call first.
 #include <mutex>
 
 #include "internal.h"
@@ -36,12 +38,13 @@ void* g_scratch_addr[MAX_DEVICES];  // device address of g_static_scratch on eac
 int scratch_for_current_device(dsuf_ctx* ctx, void** out) {
     const int dev = ctx->device;
     if (dev < 0 || dev >= MAX_DEVICES) return dsuf::fail(ctx, DSUF_E_BADARG, "gemm_fp8_static: device index %d out of range", dev);
+    // every call: the launch below goes to the current device, and the address only means something there
+    int cur = -1;
+    cudaError_t e = cudaGetDevice(&cur);
+    if (e != cudaSuccess) return dsuf::cuda_fail(ctx, e, "cudaGetDevice");
+    if (cur != dev) return dsuf::fail(ctx, DSUF_E_BADARG, "gemm_fp8_static: device %d must be current (current is %d)", dev, cur);
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_scratch_addr[dev]) {
-        int cur = -1;
-        cudaError_t e = cudaGetDevice(&cur);
-        if (e != cudaSuccess) return dsuf::cuda_fail(ctx, e, "cudaGetDevice");
-        if (cur != dev) return dsuf::fail(ctx, DSUF_E_BADARG, "gemm_fp8_static: device %d must be current (current is %d)", dev, cur);
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);
         if (e != cudaSuccess || !p) return dsuf::cuda_fail(ctx, e, "cudaGetSymbolAddress(static scratch)");

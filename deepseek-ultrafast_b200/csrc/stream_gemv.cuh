@@ -49,8 +49,6 @@ struct StreamArgs {
     float alpha;
     float swiglu_limit;
     int whole_items;  // dense: give every CTA whole row tiles (no stream-K partials) when that costs no extra wave
-    long long* dbg;   // optional [grid][8] cycle counters (debug builds of the bench only)
-    int probe;        // debug builds only: bit mask of pipeline parts to leave out (results are then wrong)
 };
 
 template <int FMT>

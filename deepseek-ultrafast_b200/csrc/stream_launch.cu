@@ -86,10 +86,6 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
     a.codes_bytes = w->codes_bytes;
     a.n_rows = w->d.n;
     a.alpha = 1.0f;
-#ifdef DSUF_TC_TIMING
-    a.dbg = getenv("DSUF_DBG_PTR") ? (long long*)strtoull(getenv("DSUF_DBG_PTR"), nullptr, 0) : nullptr;
-    a.probe = getenv("DSUF_PROBE") ? atoi(getenv("DSUF_PROBE")) : 0;
-#endif
 }
 
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
@@ -163,6 +159,7 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
                  "grouped GEMM: plan tile_rows must be 8 or 16 (any decode path) or 128 (tcgen05 path)");
     DSUF_REQUIRE(ctx, xq && xs && out, "grouped streaming GEMM: null pointer");
     DSUF_REQUIRE(ctx, epi != EPI_W13 || w->d.gate_up, "dsuf_moe_w13_swiglu: weight was not packed with gate_up=1");
+    if (plan->p == 0) return DSUF_OK;  // an empty batch: nothing to launch (route, quant and unpermute return OK as well)
     StreamArgs a;
     fill_common(ctx, a, w);
     const int nt8 = plan->tile_rows / 8;

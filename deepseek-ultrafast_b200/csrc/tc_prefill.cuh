@@ -24,12 +24,6 @@ namespace dsuf {
 
 constexpr int KID_TCP = 4;
 
-#ifdef DSUF_TC_TIMING
-// event trace of CTA 0, steps [256, 320): [step][16] clock values behind the [grid][8] counters
-#define TCP_TRACE(n, k) do { if (a.dbg && c == 0 && (n) >= 256 && (n) < 320 && lane == 0) a.dbg[(long long)G * 8 + ((n) - 256) * 16 + (k)] = clock64(); } while (0)
-#else
-#define TCP_TRACE(n, k)
-#endif
 
 // NTOK: token rows per step.  128 is the plan's slot.  64 walks every slot as two halves: a thread of the epilogue
 // then holds 32 instead of 64 accumulators, so a whole tile's columns fit in flight in one tensor-memory load, and the
@@ -161,11 +155,9 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                 int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
                 const uint8_t* sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
                 for (int kt = 0; kt < KT; ++kt, ++n) {
-                    TCP_TRACE(n, 0 + 3 * j);
                     if (n >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TCP, 1 + j)) dead = true;
-                    TCP_TRACE(n, 1 + 3 * j);
                     uint8_t* st = ring + s * Cfg::STAGE;
-                    if (elect_one()) {
+                    if (warp_elect()) {
                         // TMA counts the bytes it reads: 8192 for a packed FP4 tile that fills 16384 of shared memory
                         mbar_expect_tx(&full_bar[s], (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0) + (j == 0 ? NTOK * 128 : 0));
                         tma_3d_nh(st + j * Cfg::A_BYTES, &a.tm_w, 0, 0, tile, &full_bar[s]);
@@ -183,7 +175,6 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                         }
                         cp_async_arrive_noinc(&full_bar[s]);
                     }
-                    TCP_TRACE(n, 2 + 3 * j);
                     ++tile;
                     sf_src += a.rec_bytes;
                     if (++s == S) { s = 0; ph ^= 1; }
@@ -195,15 +186,15 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
         // The whole warp runs the loop and one elected lane issues (tcgen05 operands are uniform-register operands).
         const int j = warp >> 1;
         if (ibeg < iend) {
-            const uint32_t tmu = uni32(tm);
-            const uint64_t ad0 = uni64(tc_smem_desc(ring + j * Cfg::A_BYTES, 16, 1024, 2)),
-                           bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
-            const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF + j * 512, 512, 128, 0)),
-                           fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
+            const uint32_t tmu = warp_uniform(tm);
+            const uint64_t ad0 = warp_uniform(tc_smem_desc(ring + j * Cfg::A_BYTES, 16, 1024, 2)),
+                           bd0 = warp_uniform(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
+            const uint64_t fa0 = warp_uniform(tc_smem_desc(ring + Cfg::SFA_OFF + j * 512, 512, 128, 0)),
+                           fb0 = warp_uniform(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
             const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (2 * S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (2 * S + j);
             if (!AMX) {
-                const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));  // shuffles: outside the election
-                if (elect_one()) {
+                const uint64_t ones_d = warp_uniform(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));  // shuffles: outside the election
+                if (warp_elect()) {
                     tc_cp_sf(ones_b, ones_d);
                     if (!WMX) tc_cp_sf(ones_a, ones_d);
                 }
@@ -213,10 +204,6 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
             uint32_t ph = 0;
             int nit = 0, n = 0;
             int acc_i = j;  // MX: issuer j keeps accumulator j for the whole K
-#ifdef DSUF_TC_TIMING
-            unsigned long long gt0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
-            const long long ck0 = clock64();
-#endif
             for (int it = ibeg; it < iend; it += G) {
                 // the MMA's N follows the rows the slot really holds (a multiple of 16): the last tile of an expert is
                 // rarely full, and a 48-column MMA takes 60 cycles where a 128-column one takes 97
@@ -231,9 +218,7 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                     tc_fence_after();
                 }
                 for (int kt = 0; kt < KT; ++kt, ++n) {
-                    TCP_TRACE(n, 6 + 3 * j);
                     if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TCP, 4)) dead = true;
-                    TCP_TRACE(n, 7 + 3 * j);
                     if (AMX) {
                         fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                     } else {
@@ -250,7 +235,7 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                     }
                     const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
                     const uint32_t d = tmu + acc_i * NTOK;
-                    if (elect_one()) {
+                    if (warp_elect()) {
                         // each issuer keeps its own copy of the stage's scales in tensor memory
                         uint32_t sfa = ones_a, sfb = ones_b;
                         if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * (2 * s + j); tc_cp_sf(sfa, fa0 + so); }
@@ -263,17 +248,10 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                         if (!AMX || kt + 1 == KT) tc_commit(&tfull_bar[acc_i * 2 + j]);
                     }
                     __syncwarp();
-                    TCP_TRACE(n, 8 + 3 * j);
                     if (++s == S) { s = 0; ph ^= 1; }
                 }
                 ++nit;
             }
-#ifdef DSUF_TC_TIMING
-            if (a.dbg && j == 0 && lane == 0) {
-                unsigned long long gt1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
-                a.dbg[c * 8 + 3] = clock64() - ck0; a.dbg[c * 8 + 6] = (long long)(gt1 - gt0); a.dbg[c * 8 + 4] = n;
-            }
-#endif
         }
     } else if (warp >= Cfg::EPI_WARP0) {
         // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================

@@ -7,8 +7,6 @@
 //   * accumulators live in tensor memory; four epilogue warps read them back.  With MX (power-of-two) activation
 //     scales the whole K accumulates in tensor memory; with DS (fp32 per 128-K) activation / weight scales each
 //     128-K tile is promoted into fp32 registers with its scale pair, on a 4-deep ring of accumulators.
-//   * The four K=32 steps of a tile go to four separate sub-accumulators that the epilogue adds up, so no two
-//     MMAs of a tile depend on each other.
 //   * Measured on B200: the thread that issues the tcgen05 instructions is the serial resource of this kernel
 //     (~75 cycles per MMA of issue back-pressure plus the scale copy and the commit).  In the per-tile (DS) mode
 //     two warps therefore issue alternate tiles, each into its own accumulator-ring entries.
@@ -23,8 +21,8 @@ namespace dsuf {
 
 constexpr int KID_TC = 3;
 // warp 0: weight producer, 1: MMA issuer A, 2-5: epilogue, 6: activation producer, 7: MMA issuer B,
-// 8 / 9: second weight / activation producer, 10-13: second epilogue group, 14 / 15: MMA issuers C / D,
-// 16 / 17 and 18 / 19: weight and activation producers C / D (token tiles up to 16 columns)
+// 8 / 9: second weight / activation producer, 10-13: second epilogue group, 14 / 15: MMA issuers C / D
+// (token tiles up to 16 columns)
 constexpr int TC_EPI_THREADS = 128;
 
 template <int N>
@@ -44,34 +42,21 @@ struct TcCfg {
     static constexpr int STAGES = (S_FIT > 12 ? 12 : S_FIT) & ~(N <= 16 ? 3 : 1);
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
-    static constexpr int SUB = 1;                    // sub-accumulators per ring entry (4 = one per K=32 step; measured: no gain)
-    static constexpr int ACC_COLS = SUB * N;
+    static constexpr int ACC_COLS = N;               // tensor-memory columns of one accumulator
     static constexpr int NB = ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
     // producer warps per kind (weights / activations), tiles dealt round-robin: a producer spends ~1100 cycles per tile
-    // of its own (two barrier waits, the copies, the scale gathers), so narrow token tiles take four of each kind
-    static constexpr int NP = 2;  // (four of each kind were measured: no gain)
-    static constexpr int THREADS = 512 + (NP == 4 ? 128 : 0);  // 16 warps + producers C and D of each kind
+    // of its own (two barrier waits, the copies, the scale gathers); four of each kind measured no faster than two
+    static constexpr int NP = 2;
+    static constexpr int THREADS = 512;  // 16 warps
     static constexpr int TM_SFA = 256, TM_SFB = 384, TM_COLS = 512;
     static_assert(NB * ACC_COLS <= 256 && STAGES >= 4 && N <= 128, "tensor-memory / shared-memory budget");
 };
 
-#ifdef DSUF_TC_TIMING
-#define DSUF_T0(v) const long long v = clock64()
-#define DSUF_TACC(acc, v) acc += clock64() - v
-#define DSUF_PROBE(bit) (a.probe & (bit))
-// event trace of CTA 0, tiles [256, 320): [tile][16] clock values behind the [grid][8] counters
-#define DSUF_TRACE(i, k) do { const long long tn_ = (i) - beg; if (a.dbg && c == 0 && tn_ >= 256 && tn_ < 320 && lane == 0) a.dbg[(long long)G * 8 + (tn_ - 256) * 16 + (k)] = clock64(); } while (0)
-#else
-#define DSUF_TRACE(i, k)
-#define DSUF_T0(v)
-#define DSUF_TACC(acc, v)
-#define DSUF_PROBE(bit) false
-#endif
 
 template <int FMT, int WMX, int AMX, int N, int EPI>
 __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
     using Cfg = TcCfg<N>;
-    constexpr int S = Cfg::STAGES, ACC_COLS = Cfg::ACC_COLS, SUB = Cfg::SUB;
+    constexpr int S = Cfg::STAGES, ACC_COLS = Cfg::ACC_COLS;
     constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
     // MMA-issuing warps of the per-tile mode: an issuer spends ~600 cycles per tile of its own (waits, fences, scale
     // copies, commits around 4 MMAs), so narrow token tiles (180 cycles of MMA per tile) take four to keep up with HBM
@@ -152,9 +137,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         end = ((long long)(c + 1) * q / G) * KT;
     }
 
-    if (warp == 0 || warp == 8 || (NP == 4 && (warp == 16 || warp == 17))) {
+    if (warp == 0 || warp == 8) {
         // ================= weight producers (tiles dealt round-robin): tile codes + scale atom =================
-        const int pj = warp == 0 ? 0 : warp == 8 ? 1 : warp - 14;
+        const int pj = warp == 0 ? 0 : 1;
         // The whole warp runs the loop (so every value stays warp-uniform and the TMA descriptors live in uniform
         // registers); one elected lane issues.
         if (pj < NP && beg + pj < end) {
@@ -170,8 +155,6 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             uint8_t* st = ring + pj * Cfg::STAGE;
             // TMA counts the bytes it READS: a packed FP4 tile is 8192 bytes although it fills 16384 of shared memory
             constexpr uint32_t W_TX = (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0);
-            long long tw_wait = 0;
-            DSUF_T0(tw_start);
             for (long long i = beg + pj; i < end; i += NP) {
                 if (fresh) {
                     long long wbase;
@@ -186,22 +169,13 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
                     fresh = false;
                 }
-                DSUF_T0(tw0);
-                DSUF_TRACE(i, 0);
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 1)) dead = true;
-                DSUF_TRACE(i, 1);
-                DSUF_TACC(tw_wait, tw0);
-                if (elect_one()) {
-                    if (DSUF_PROBE(2)) {
-                        mbar_expect_tx(&full_bar[s], WMX ? 512 : 0);
-                    } else {
-                        mbar_expect_tx(&full_bar[s], W_TX);
-                        tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
-                    }
+                if (warp_elect()) {
+                    mbar_expect_tx(&full_bar[s], W_TX);
+                    tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
                     if (WMX) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
                 }
                 __syncwarp();
-                DSUF_TRACE(i, 2);
                 tile += NP;
                 sf_src += (size_t)NP * a.rec_bytes;
                 s += NP;
@@ -210,13 +184,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 kt += NP;
                 while (kt >= KT) { kt -= KT; ++q; fresh = true; }
             }
-#ifdef DSUF_TC_TIMING
-
-#endif
         }
-    } else if (warp == 6 || warp == 9 || (NP == 4 && (warp == 18 || warp == 19))) {
+    } else if (warp == 6 || warp == 9) {
         // ================= activation producers: token rows by TMA, their block scales by 4-byte async copies =================
-        const int pj = warp == 6 ? 0 : warp == 9 ? 1 : warp - 16;
+        const int pj = warp == 6 ? 0 : 1;
         if (pj < NP && beg + pj < end) {
             if (lane == 0) prefetch_tmap(&a.tm_x);
             const uint64_t pol_x = policy_evict_last();
@@ -228,8 +199,6 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             int s = pj;
             uint32_t ph = 0;
             uint8_t* st = ring + pj * Cfg::STAGE;
-            long long tx_wait = 0;
-            DSUF_T0(tx_start);
             for (long long i = beg + pj; i < end; i += NP) {
                 if (fresh) {
                     int rt;
@@ -244,18 +213,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     ws_src = (!WMX && lane == 31) ? a.wscale_ds + (size_t)rt * KT : nullptr;
                     fresh = false;
                 }
-                DSUF_T0(tx0);
-                DSUF_TRACE(i, 3);
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
-                DSUF_TRACE(i, 4);
-                DSUF_TACC(tx_wait, tx0);
-                if (elect_one()) {
-                    if (DSUF_PROBE(1)) {
-                        mbar_arrive(&full_bar[s]);
-                    } else {
-                        mbar_expect_tx(&full_bar[s], N * 128);
-                        tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
-                    }
+                if (warp_elect()) {
+                    mbar_expect_tx(&full_bar[s], N * 128);
+                    tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
                 }
                 __syncwarp();
                 uint8_t* xe = nullptr;
@@ -271,16 +232,12 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 }
                 if (!WMX && lane == 31) cp_async4(xe + 4 * N, ws_src + kt);
                 cp_async_arrive_noinc(&full_bar[s]);
-                DSUF_TRACE(i, 5);
                 s += NP;
                 st += NP * Cfg::STAGE;
                 if (s >= S) { s -= S; st -= S * Cfg::STAGE; ph ^= 1; }
                 kt += NP;
                 while (kt >= KT) { kt -= KT; ++q; fresh = true; }
             }
-#ifdef DSUF_TC_TIMING
-
-#endif
         }
     } else if (warp == 1 || warp == 7 || ((NI == 4 || NIW == 4) && (warp == 14 || warp == 15))) {
         // ================= MMA issuers (one thread each; issuer B only in the per-tile mode) =================
@@ -292,18 +249,18 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 // Every issuer walks every tile of the span (so all know the group boundaries); issuer j issues the tiles
                 // j, j + NIW, ... into columns [j*N, (j+1)*N) of the ring entry.  tfull needs all of them: a commit from
                 // an issuer that contributed MMAs, a plain arrival from one that did not.
-                const uint32_t tmu = uni32(tm);
+                const uint32_t tmu = warp_uniform(tm);
                 const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
                 const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
-                const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
-                if (elect_one()) {
+                const uint64_t ones_d = warp_uniform(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+                if (warp_elect()) {
                     if (!WMX) tc_cp_sf(ones_a, ones_d);
                     if (!AMX) tc_cp_sf(ones_b, ones_d);
                 }
                 __syncwarp();
-                const uint64_t ad0 = uni64(tc_smem_desc(ring, 16, 1024, 2)), bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
-                const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0)),
-                               fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
+                const uint64_t ad0 = warp_uniform(tc_smem_desc(ring, 16, 1024, 2)), bd0 = warp_uniform(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
+                const uint64_t fa0 = warp_uniform(tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0)),
+                               fb0 = warp_uniform(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
                 int kt = (int)(beg % KT);
                 int s = 0, gidx = 0;
                 uint32_t ph = 0;
@@ -322,7 +279,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         tc_fence_after();
                         if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                         const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
-                        if (elect_one()) {
+                        if (warp_elect()) {
                             uint32_t sfa = ones_a, sfb = ones_b;
                             if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
                             if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
@@ -336,7 +293,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         }
                         issued = true;
                     } else if (group_end) {
-                        if (elect_one()) {
+                        if (warp_elect()) {
                             if (issued) tc_commit(&tfull_bar[b]);
                             else mbar_arrive(&tfull_bar[b]);
                         }
@@ -348,40 +305,30 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 }
             }
         } else if (j < NI && beg + j < end) {
-            const uint32_t tmu = uni32(tm);
+            const uint32_t tmu = warp_uniform(tm);
             const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
             const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
-            const uint64_t ones_d = uni64(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
-            if (elect_one()) {
+            const uint64_t ones_d = warp_uniform(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
+            if (warp_elect()) {
                 if (!WMX) tc_cp_sf(ones_a, ones_d);
                 if (!AMX) tc_cp_sf(ones_b, ones_d);
             }
             __syncwarp();
             // descriptors of stage 0; a stage is selected by adding its byte offset / 16 to the address field
-            const uint64_t ad0 = uni64(tc_smem_desc(ring, 16, 1024, 2)), bd0 = uni64(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
-            const uint64_t fa0 = uni64(tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0)),
-                           fb0 = uni64(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
+            const uint64_t ad0 = warp_uniform(tc_smem_desc(ring, 16, 1024, 2)), bd0 = warp_uniform(tc_smem_desc(ring + Cfg::B_OFF, 16, 1024, 2));
+            const uint64_t fa0 = warp_uniform(tc_smem_desc(ring + Cfg::SFA_OFF, 512, 128, 0)),
+                           fb0 = warp_uniform(tc_smem_desc(ring + Cfg::SFB_OFF, 512, 128, 0));
             long long q = beg / KT;
             int kt = (int)(beg - q * KT);
             int s = j, gidx = 0;
             uint32_t ph = 0;
             bool group_open = false;
-            DSUF_T0(t_start);
-#ifdef DSUF_TC_TIMING
-            unsigned long long gt0; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt0));
-#endif
-            long long t_full = 0, t_tempty = 0, t_issue = 0;
             for (long long i = beg + j; i < end; i += NI) {
-                DSUF_T0(t0);
-                DSUF_TRACE(i, 6);
                 if (!dead && !mbar_wait(&full_bar[s], ph, a.status, KID_TC, 2)) dead = true;
-                DSUF_TRACE(i, 7);
-                DSUF_TACC(t_full, t0);
                 tc_fence_after();
-                if (AMX && !DSUF_PROBE(4)) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
+                if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                 int b;
                 bool first_of_group;
-                DSUF_T0(t1);
                 if (PER_TILE) {
                     const int n = (int)(i - beg);
                     b = n & (NB - 1);
@@ -397,20 +344,17 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         group_open = true;
                     }
                 }
-                DSUF_TACC(t_tempty, t1);
-                DSUF_T0(t2);
                 const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
                 const bool group_end = PER_TILE || kt + 1 == KT || i + 1 == end;
-                if (elect_one()) {
+                if (warp_elect()) {
                     uint32_t sfa = ones_a, sfb = ones_b;
                     if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
                     if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
                     const uint32_t d = tmu + b * ACC_COLS;
 #pragma unroll
                     for (int kc = 0; kc < 4; ++kc)
-                        if (!DSUF_PROBE(8) || kc == 0)
-                        tc_mma_mx(d + (SUB == 4 ? kc * N : 0), ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
-                                  tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && (SUB == 4 || kc == 0)) ? 0u : 1u);
+                        tc_mma_mx(d, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
+                                  tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && kc == 0) ? 0u : 1u);
                     tc_commit(&empty_bar[s]);
                     if (group_end) tc_commit(&tfull_bar[b]);
                 }
@@ -419,18 +363,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     if (group_end) { ++gidx; group_open = false; }
                     if (++kt == KT) { kt = 0; ++q; }
                 }
-                DSUF_TACC(t_issue, t2);
-                DSUF_TRACE(i, 8);
                 s += NI;
                 if (s >= S) { s -= S; ph ^= 1; }
             }
-#ifdef DSUF_TC_TIMING
-            if (a.dbg && j == 0 && lane == 0) {
-                a.dbg[c * 8 + 0] = t_full; a.dbg[c * 8 + 2] = t_issue;
-                a.dbg[c * 8 + 3] = clock64() - t_start; a.dbg[c * 8 + 4] = (end - beg + NI - 1) / NI;
-                unsigned long long gt1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1)); a.dbg[c * 8 + 6] = (long long)(gt1 - gt0);
-            }
-#endif
         }
     } else if ((warp >= 2 && warp <= 5) || ((NE == 2 || CSPLIT) && warp >= EG1 && warp < EG1 + 4)) {
         // ================= epilogue warps (thread = weight row of the tile = tensor-memory lane) =================
@@ -450,10 +385,8 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         bool fresh = true;
         int gidx = 0, es = 0, items_done = 0;
         const uint8_t* est = ring;
-        long long te_wait = 0, te_ld = 0, te_arr = 0, te_flush = 0;
         long long g0 = beg;  // first tile of the current accumulation group
         float rwreg[(NC + 31) / 32] = {};
-        DSUF_T0(te_start);
         for (long long i = beg; i < end; ++i) {
             if (fresh) {
                 if (EPI == EPI_DENSE) {
@@ -480,12 +413,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             if (!mine) ++gidx;
             if ((PER_TILE || item_end) && mine) {
                 const int b = gidx % NB;
-                DSUF_T0(te0);
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
-                DSUF_TACC(te_wait, te0);
-                DSUF_T0(tl0);
                 tc_fence_after();
-                if (!DSUF_PROBE(16)) {
+                {
                     const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * N) : 1.0f;
                     constexpr int CH = NC < 32 ? NC : 32;
                     // several issuers in the whole-K mode: part p of the entry holds a sum iff the group, which started at
@@ -524,17 +454,13 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         }
                     }
                 }
-                DSUF_TACC(te_ld, tl0);
-                DSUF_T0(ta0);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&tempty_bar[b]);
                 }
                 ++gidx;
-                DSUF_TACC(te_arr, ta0);
             }
-            DSUF_T0(tf0);
             if (item_end && NE == 2) {
                 float* red = s_red + (items_done & 1) * (N * 128);
                 if (eg == 1) {
@@ -628,14 +554,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 for (int j = 0; j < NC; ++j) acc[j] = 0.f;
                 g0 = i + 1;
             }
-            DSUF_TACC(te_flush, tf0);
             est += Cfg::STAGE;
             if (++es == S) { es = 0; est = ring; }
             if (++kt == KT) { kt = 0; ++q; fresh = true; }
         }
-#ifdef DSUF_TC_TIMING
-        if (a.dbg && tid == 64) { a.dbg[c * 8 + 7] = clock64() - te_start - te_wait; a.dbg[c * 8 + 5] = te_ld; a.dbg[c * 8 + 1] = te_flush; }
-#endif
     }
     tc_fence_before();
     __syncthreads();

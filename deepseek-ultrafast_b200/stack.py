@@ -69,10 +69,10 @@ class LayerStack:
             gemm_fp8(ctx, w, self.xq[r0:r0 + m], self.xs[r0:r0 + m], m, out[r0:r0 + m])
         return out
 
-    def forward(self, x, events=None):
+    def forward(self, x, events=None, layers=None):
         cfg = self.cfg
         cur = x
-        for l in range(cfg.layers):
+        for l in range(cfg.layers if layers is None else layers):
             self.dense_forward(l, cur, self.h)
             ids, w = moe_route_tokens(self.ctx, SCORE_SOFTMAX, self.logits[l], None, cfg.topk)
             out = self.y[l & 1]
@@ -142,11 +142,13 @@ class EpLayerStack:
         n_loc, kloc = e_hi - self.e_lo, self.kslice[1] - self.kslice[0]
         self.dense, self.moe, self.logits = [], [], []
         for l in range(cfg.layers):
-            base = cfg.seed + 1000 * l + 100000 * rank   # random-init weights: every shard draws its own
-            tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, kloc, cfg.std, base + 1, dev)
+            # the shards of ONE set of random-init weights (the seeds of LayerStack): the dense weight's K-slice and the
+            # experts at their global ids, so the W-rank result is comparable with the single-GPU one
+            base = cfg.seed + 1000 * l
+            tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, H, cfg.std, base + 1, dev, k_slice=self.kslice)
             self.dense.append(Weight(ctx, 0, cfg.dense_mode, H, kloc, 1, False, tiles, sds))
-            w13 = synth.fp4_experts(t, n_loc, 2 * I, H, cfg.std, base + 2, True, dev)
-            w2 = synth.fp4_experts(t, n_loc, H, I, cfg.std, base + 3, False, dev)
+            w13 = synth.fp4_experts(t, n_loc, 2 * I, H, cfg.std, base + 2, True, dev, first_expert=self.e_lo)
+            w2 = synth.fp4_experts(t, n_loc, H, I, cfg.std, base + 3, False, dev, first_expert=self.e_lo)
             W13 = Weight.experts_fp4_packed(ctx, w13, 2 * I, H, n_loc, True)
             W2 = Weight.experts_fp4_packed(ctx, w2, H, I, n_loc, False)
             self.moe.append(MoeLayer(ctx, W13, W2, T, cfg.topk, cfg.act_mode, e_lo=self.e_lo, tile_rows=8))
@@ -157,14 +159,14 @@ class EpLayerStack:
         self.xs = t.empty((T, kloc // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
         # The two per-layer sums run as the library's peer-memory all-reduce when the partial buffers can be mapped
         # by every rank (torch symmetric memory); DSUF_EP_PEER=0 or a failed mapping falls back to NCCL.
-        self.peer, self.fuse_combine = None, False
+        self.peer, self.fuse_combine, self.peer_error = None, False, None
         if world > 1 and os.environ.get("DSUF_EP_PEER", "1") != "0":
             try:
                 from . import PeerAllReduce
                 self.peer = PeerAllReduce(ctx, dist, rank, world)
             except Exception as e:  # noqa: BLE001 - any failure to map means: use the process group
-                if rank == 0:
-                    print(f"peer-memory all-reduce unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+                self.peer_error = f"{type(e).__name__}: {e}"
+                print(f"rank {rank}: peer-memory all-reduce unavailable ({self.peer_error}); using NCCL", file=sys.stderr)
                 self.peer = None
         if world > 1 and hasattr(dist, "ReduceOp"):
             # every rank must take the same path: one rank that could not map its buffers sends all of them to NCCL
@@ -193,11 +195,19 @@ class EpLayerStack:
     def logits_full(self, l):
         return self.logits[l]
 
-    def forward(self, x_local, events=None):
-        """x_local bf16 [T/W][H] (this rank's tokens) -> this rank's rows of the stack output."""
+    def exchange_path(self):
+        """Which code sums the per-rank partials: "peer_fused" (this library's kernels over peer memory, the combine fused
+        with the unpermute), "peer" (this library's all-reduce kernel, unpermute separate) or "nccl"."""
+        if self.peer is None:
+            return "nccl"
+        return "peer_fused" if self.fuse_combine else "peer"
+
+    def forward(self, x_local, events=None, layers=None):
+        """x_local bf16 [T/W][H] (this rank's tokens) -> this rank's rows of the stack output (after ``layers`` layers,
+        default all)."""
         from . import ep
         cur = self.xch.all_gather_rows(self.x_all, x_local)
-        for l in range(self.cfg.layers):
+        for l in range(self.cfg.layers if layers is None else layers):
             self.moe[l].events = events
             cur = ep.ep_layer_forward(self.xch, self.compute[l], cur)
         return cur[self.t0:self.t1]

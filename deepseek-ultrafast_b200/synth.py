@@ -47,19 +47,29 @@ def fp4_expert_tiles(torch, n, k, std, gen, gate_up, device):
     return torch.cat([ct, _atoms(torch, sc.contiguous())], dim=2).reshape(-1)
 
 
-def fp4_experts(torch, n_experts, n, k, std, seed, gate_up, device):
-    gen = torch.Generator(device=device).manual_seed(seed)
+def fp4_experts(torch, n_experts, n, k, std, seed, gate_up, device, first_expert=0):
+    """Experts first_expert .. first_expert + n_experts - 1 of the stream named by `seed`: every expert is drawn from its
+    own generator state (seed, global expert id), so an expert-parallel shard holds exactly the experts the unsharded
+    weight holds at those ids."""
+    gen = torch.Generator(device=device)
     per = (n // 128) * (k // 128) * REC_FP4
     out = torch.empty(n_experts * per, dtype=torch.uint8, device=device)
     for e in range(n_experts):
+        gen.manual_seed(seed * 1000003 + first_expert + e)
         out[e * per:(e + 1) * per] = fp4_expert_tiles(torch, n, k, std, gen, gate_up, device)
     return out
 
 
-def fp8_dense(torch, mode_mx, n, k, std, seed, device):
-    """Dense weight [n][k] ~ N(0,std) -> (tile records u8, ds scales f32 [n/128][k/128] or None)."""
+def fp8_dense(torch, mode_mx, n, k, std, seed, device, k_slice=None):
+    """Dense weight [n][k] ~ N(0,std) -> (tile records u8, ds scales f32 [n/128][k/128] or None).
+    ``k_slice`` = (k0, k1), multiples of 128: only columns k0..k1 of the same [n][k] weight are quantized and packed (the
+    K-shard of a tensor-parallel rank; block scales do not straddle a multiple of 128, so the shard's codes and scales
+    are those of the whole weight)."""
     gen = torch.Generator(device=device).manual_seed(seed)
     w = (torch.randn(n, k, generator=gen, device=device, dtype=torch.float32) * std).bfloat16().float()
+    if k_slice is not None:
+        w = w[:, k_slice[0]:k_slice[1]].contiguous()
+        k = k_slice[1] - k_slice[0]
     rt, kt = n // 128, k // 128
     if mode_mx:
         wb = w.view(n // 32, 32, k // 32, 32)

@@ -41,7 +41,8 @@ typedef struct dsuf_ctx dsuf_ctx;
 typedef struct dsuf_weight dsuf_weight;
 
 typedef struct {
-    int32_t code;   /* 0 = no device-side error; 1 = a bounded wait expired; 2 = inconsistent plan */
+    int32_t code;   /* 0 = no device-side error; 1 = a bounded wait expired; 2 = inconsistent plan; 3 = the ranks of a peer
+                       exchange no longer count the same calls (a peer's flag is more than one call ahead) */
     int32_t kernel; /* kernel id */
     int32_t cta;
     int32_t where;
@@ -65,6 +66,11 @@ int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05);
  * spins with no error reporting (cu/comm.cu:217-224); here every wait is bounded and reports through this. */
 int32_t dsuf_status_poll(dsuf_ctx* ctx, void* stream, dsuf_dev_status* out);
 int32_t dsuf_sm_count(dsuf_ctx* ctx);
+/* How long the peer-exchange kernels (dsuf_ep_allreduce_bf16, dsuf_ep_combine_bf16) wait for a peer's announcement
+ * before they give up, record code 1 in the status word and return with an incomplete sum: 1 us .. 10 s, default
+ * about 2 s.  Set it to what the deployment's worst rank-to-rank skew allows.  The reference's waits never give up
+ * (cu/comm.cu:217-224). */
+int32_t dsuf_ctx_set_wait_budget_us(dsuf_ctx* ctx, int64_t microseconds);
 
 /* ---- host-side weight formats (load-time, no GPU).  Replace crates/model/src/formats.rs + packing.rs. ---- */
 
@@ -147,11 +153,22 @@ int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_
  *     DSUF_E_BADARG with a message that says so;
  *   - all calls share the one array: calls that overlap on the GPU race, so keep them stream-ordered; its arrival
  *     counters are cleared on the stream before each launch, nothing else carries over between calls;
- *   - the first call on a device resolves the array's device address (that device must be current); make that call
- *     before any stream capture starts.
+ *   - the first call on a device resolves the array's device address; make that call before any stream capture
+ *     starts, and -- since the CUDA runtime may place the library's device image (the array included) in device memory
+ *     only at that moment -- before the caller gives the rest of the device memory away.  The context's device must be
+ *     current on every call.
  * Calls no cudaMalloc / cudaFree and no allocating library routine. */
 int32_t dsuf_gemm_fp8_static(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m,
                              uint64_t out, int32_t ldo, float alpha);
+
+/* No counterpart in the reference: a measurement aid for the roofline of the GEMM kernels.  Launches one CTA per SM that
+ * issues `iters` tcgen05.mma (kind::mxf8f6f4.block_scale, M = 128, N = n_cols, K = 32; A e4m3 or e2m1) back to back on
+ * operands that already sit in shared memory, and returns in *flop_per_launch the floating-point operations of the
+ * launch; the caller times the launch with CUDA events.  FLOP / time is what the tensor cores of this GPU deliver to
+ * that instruction at the clocks they hold: the measured ceiling the prefill kernels are compared with.
+ * n_cols a multiple of 16 in 16..256. */
+int32_t dsuf_probe_tensor_rate(dsuf_ctx* ctx, void* stream, int32_t n_cols, int32_t a_is_e2m1, int32_t iters,
+                               double* flop_per_launch);
 
 /* moe_route_tokens + route_token (cu/ops.cu:615-623, cu/route.cuh:3-56; RouteArgs ops.rs:124-135):
  * top-k of score+bias, ties to the lower id, weights = score / sum(selected scores) * route_scale.

@@ -42,6 +42,8 @@ def lib():
         L.dsufo_f32_to_bf16.argtypes = [C.c_float]
         L.dsufo_permute_plan.restype = C.c_int
         L.dsufo_num_threads.restype = C.c_int
+        L.dsufo_set_num_threads.restype = C.c_int
+        L.dsufo_set_num_threads.argtypes = [C.c_int]
         _LIB = L
     return _LIB
 
@@ -229,3 +231,11 @@ def dequant_fp4(codes, s):
 
 def num_threads():
     return lib().dsufo_num_threads()
+
+
+def use_all_host_cores():
+    """Sets the OpenMP thread count to the cores this process may run on (a launcher may have exported
+    OMP_NUM_THREADS=1); returns the count in force."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return lib().dsufo_set_num_threads(n)

@@ -474,6 +474,18 @@ int dsufo_num_threads(void) {
 #endif
 }
 
+/* The timed CPU baseline wants every host core even when the launcher exported OMP_NUM_THREADS=1 (torch.distributed.run
+ * does): n <= 0 leaves the setting alone.  Returns the thread count in force. */
+int dsufo_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+    return dsufo_num_threads();
+}
+
 /* ---- known-answer sweeps restated from the reference's own unit tests ---- */
 
 /* formats.rs:235-248: the bit-trick encoder equals the nearest-value search on every bf16 value, on two

@@ -65,6 +65,48 @@ def test_single_rank_combine_equals_unpermute(pkg, ctx):
     assert (partial.view(torch.uint16) == want.view(torch.uint16)).all()
 
 
+def test_wait_for_a_missing_peer_runs_out_and_reports(pkg, ctx):
+    """A peer that never announces: the kernel's wait is given 1 ms, runs out, records a time-out (kernel id 5) in the
+    status word and returns; the context stays usable and the next call, whose peer flag is present, sums both
+    partials.  Both "ranks" live on this GPU (world = 2 with local buffers), nothing faults and nothing waits for long."""
+    lib = pkg.lib()
+    n = 16 * 1024
+    g = torch.Generator(device="cuda").manual_seed(9)
+    mine = torch.randn(n, generator=g, device="cuda").bfloat16()
+    peer = torch.randn(n, generator=g, device="cuda").bfloat16()
+    out = torch.zeros_like(mine)
+    nflag = lib.dsuf_ep_flag_bytes(2) // 4
+    my_flags = torch.zeros(nflag, dtype=torch.int32, device="cuda")
+    peer_flags = torch.zeros(nflag, dtype=torch.int32, device="cuda")   # where this rank announces itself; nobody reads it
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    data = (C.c_uint64 * 2)(mine.data_ptr(), peer.data_ptr())
+    flags = (C.c_uint64 * 2)(my_flags.data_ptr(), peer_flags.data_ptr())
+    ctx.set_wait_budget_us(1000)
+    try:
+        rc = lib.dsuf_ep_allreduce_bf16(ctx.h, ctx.stream(), data, flags, 0, 2, n, state.data_ptr(), out.data_ptr())
+        assert rc == 0
+        st = pkg.DevStatus()
+        rc = lib.dsuf_status_poll(ctx.h, ctx.stream(), C.byref(st))
+        assert rc == -3 and st.code == 1 and st.kernel == 5      # DSUF_E_TIMEOUT, a bounded wait expired, the exchange kernel
+        assert state.cpu().tolist() == [1, 0]                    # the call is over and counted
+        # the peer "arrives" for the second call: its announcements of epoch 2 appear in this rank's flag block
+        my_flags.view(-1, 2)[:, 1] = 2
+        torch.cuda.synchronize()
+        rc = lib.dsuf_ep_allreduce_bf16(ctx.h, ctx.stream(), data, flags, 0, 2, n, state.data_ptr(), out.data_ptr())
+        assert rc == 0 and ctx.status().code == 0
+        want = (mine.float() + peer.float()).bfloat16()
+        assert (out.view(torch.uint16) == want.view(torch.uint16)).all()
+        # a peer that is more than one call ahead is reported, not summed in silence
+        my_flags.view(-1, 2)[:, 1] = 7
+        torch.cuda.synchronize()
+        rc = lib.dsuf_ep_allreduce_bf16(ctx.h, ctx.stream(), data, flags, 0, 2, n, state.data_ptr(), out.data_ptr())
+        assert rc == 0
+        rc = lib.dsuf_status_poll(ctx.h, ctx.stream(), C.byref(st))
+        assert rc == -3 and st.code == 3 and st.kernel == 5
+    finally:
+        ctx.set_wait_budget_us(2000000)
+
+
 def test_rejects_aliasing_and_bad_sizes(pkg, ctx):
     x = torch.zeros(64, device="cuda").bfloat16()
     flags = torch.zeros(pkg.lib().dsuf_ep_flag_bytes(1) // 4, dtype=torch.int32, device="cuda")

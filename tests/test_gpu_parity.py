@@ -264,7 +264,7 @@ def test_gather_quant_prenorm_rows_equal_plain_prenorm_quant(pkg, ctx, mode):
 
 
 # ------------------------------------------------------------------ routed-expert layer
-def _moe_case(pkg, ctx, act_mode, T, H, I, E, K, tile_rows, seed, e_lo=0, n_loc=None, limit=0.0, shared=False):
+def _moe_case(pkg, ctx, act_mode, T, H, I, E, K, tile_rows, seed, e_lo=0, n_loc=None, limit=0.0, shared=False, ids_rw=None):
     n_loc = E if n_loc is None else n_loc
     g = seeded(seed)
     xt, xn = randn_bf16(g, T, H)
@@ -275,7 +275,7 @@ def _moe_case(pkg, ctx, act_mode, T, H, I, E, K, tile_rows, seed, e_lo=0, n_loc=
     q2 = [oracle.quant_fp4_weight(w2[e]) for e in range(E)]
     c13, s13 = np.stack([a for a, _ in q13]), np.stack([b for _, b in q13])
     c2, s2 = np.stack([a for a, _ in q2]), np.stack([b for _, b in q2])
-    ids, rw = oracle.route(1, logits.numpy(), None, K)
+    ids, rw = oracle.route(1, logits.numpy(), None, K) if ids_rw is None else ids_rw
     sh_t, sh_n = randn_bf16(g, T, H, std=0.1) if shared else (None, None)
     ref = oracle.moe_layer(act_mode, xn, ids, rw, c13, s13, c2, s2, swiglu_limit=limit, shared=sh_n, e_lo=e_lo,
                            e_hi=e_lo + n_loc, want_act=True)
@@ -329,6 +329,59 @@ def test_moe_layer_prefill_odd_number_of_row_tiles(pkg, ctx, act_mode):
     _moe_case(pkg, ctx, act_mode, T=300, H=384, I=128, E=4, K=2, tile_rows=128, seed=11)
 
 
+@pytest.mark.parametrize("act_mode", [0, 1])
+def test_moe_layer_prefill_experts_spanning_several_slot_groups(pkg, ctx, act_mode):
+    """The prefill kernel deals (slot, row-tile pair) items per expert in groups of 32 slots.  Skewed top-1 routing gives
+    one expert 66 slots (groups of 32 + 32 + 2, the last slot ragged), one exactly 33 full slots (32 + 1), one 129 rows
+    (a full slot and a single row), one a single row and one nothing: the shape of the 16384-token Zipf benchmark (one
+    expert with 112 slots) at a size the CPU oracle evaluates in full.  Two row-tile pairs per expert in both GEMMs."""
+    if not ctx.tcgen05:
+        pytest.skip("128-row plans run on the tcgen05 path only")
+    counts = [65 * 128 + 17, 0, 1, 129, 33 * 128]
+    T = sum(counts)
+    rng = np.random.default_rng(77)
+    ids = np.repeat(np.arange(len(counts), dtype=np.int32), counts)
+    rng.shuffle(ids)
+    rw = rng.uniform(0.5, 1.5, size=T).astype(np.float32)
+    layer = _moe_case(pkg, ctx, act_mode, T=T, H=512, I=256, E=len(counts), K=1, tile_rows=128, seed=31,
+                      ids_rw=(ids.reshape(T, 1), rw.reshape(T, 1)))
+    tiles = layer.plan.tiles.cpu().numpy()[:int(layer.plan.ntiles.cpu()[0])]
+    per_expert = np.bincount(tiles[:, 0], minlength=len(counts))
+    assert per_expert.tolist() == [66, 0, 1, 2, 33]
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_dense_gemm_prefill_benchmark_size_sampled(pkg, ctx, mode):
+    """The dense projection of the layer stack at its prefill size (7168 x 7168 weights, 16384 token rows = 128 token
+    tiles x 28 row-tile pairs): sampled token rows x sampled weight row blocks against the oracle, and two runs bitwise
+    equal."""
+    if not ctx.tcgen05:
+        pytest.skip("more than 16 token rows run on the tcgen05 path only")
+    n = k = 7168
+    m = 16384
+    g = seeded(4242)
+    xt, xn = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, n, k, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(mode, wn)
+    w = pkg.Weight.dense_fp8(ctx, mode, wq, ws)
+    xd = xt.cuda()
+    out = pkg.gemv(ctx, w, xd)
+    out2 = pkg.gemv(ctx, w, xd)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    assert (out.view(torch.uint16) == out2.view(torch.uint16)).all(), "prefill GEMM result depends on timing"
+    rng = np.random.default_rng(5)
+    tok = np.sort(np.concatenate([np.arange(0, 8), np.arange(m - 8, m), rng.choice(m, 112, replace=False)]))
+    blk = 32 if mode == 0 else 128
+    sel = np.sort(np.concatenate([[0, n // blk - 1], rng.choice(n // blk, 4, replace=False)]))
+    sel = np.unique(sel)
+    ridx = (sel[:, None] * blk + np.arange(blk)[None]).reshape(-1)
+    xq, xs = oracle.act_quant(mode, np.ascontiguousarray(xn[tok]))
+    _, ref = oracle.gemm_fp8(mode, np.ascontiguousarray(wq[ridx]), np.ascontiguousarray(ws[sel]), xq, xs)
+    got = out[torch.from_numpy(tok).cuda()].float().cpu().numpy()[:, ridx]
+    assert rel(got, ref) < TOL
+
+
 def test_moe_layer_clamp_and_shared_expert_term(pkg, ctx):
     _moe_case(pkg, ctx, 1, T=16, H=256, I=128, E=8, K=2, tile_rows=8, seed=3, limit=0.05, shared=True)
 
@@ -337,6 +390,29 @@ def test_moe_layer_expert_parallel_shards_sum_to_whole(pkg, ctx):
     """Two expert shards (experts 0-3 and 4-7) evaluated separately add up to the full layer (fp32, before rounding)."""
     _moe_case(pkg, ctx, 1, T=16, H=256, I=128, E=8, K=2, tile_rows=8, seed=4, e_lo=0, n_loc=4)
     _moe_case(pkg, ctx, 1, T=16, H=256, I=128, E=8, K=2, tile_rows=8, seed=4, e_lo=4, n_loc=4)
+
+
+def test_moe_layer_empty_batch_launches_nothing_and_succeeds(pkg, ctx):
+    """No tokens: every entry of the layer returns OK (the reference's callers never launch with m = 0; here it is a
+    defined no-op instead of an error from one of the five entries)."""
+    H, I, E, K = 256, 128, 4, 2
+    g = seeded(8)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    q13 = [oracle.quant_fp4_weight(w13[e]) for e in range(E)]
+    q2 = [oracle.quant_fp4_weight(w2[e]) for e in range(E)]
+    W13 = pkg.Weight.experts_fp4(ctx, np.stack([a for a, _ in q13]), np.stack([b for _, b in q13]), True)
+    W2 = pkg.Weight.experts_fp4(ctx, np.stack([a for a, _ in q2]), np.stack([b for _, b in q2]), False)
+    for tile_rows in ([8, 128] if ctx.tcgen05 else [8]):
+        layer = pkg.MoeLayer(ctx, W13, W2, 0, K, pkg.MODE_DS, tile_rows=tile_rows)
+        x = torch.zeros(0, H, dtype=torch.bfloat16, device="cuda")
+        ids = torch.zeros(0, K, dtype=torch.int32, device="cuda")
+        w = torch.zeros(0, K, dtype=torch.float32, device="cuda")
+        y = torch.zeros(0, H, dtype=torch.bfloat16, device="cuda")
+        layer.forward(x, ids, w, y)
+        torch.cuda.synchronize()
+        assert ctx.status().code == 0
+        assert layer.plan.ntiles.cpu().tolist() == [0, 0]
 
 
 def test_moe_single_token_single_expert(pkg, ctx):
