@@ -71,6 +71,12 @@ int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05) {
     return DSUF_OK;
 }
 
+int32_t dsuf_ctx_set_prenorm_rsqrt(dsuf_ctx* ctx, int32_t approximate) {
+    if (!ctx) return DSUF_E_BADARG;
+    ctx->prenorm_approx = approximate ? 1 : 0;
+    return DSUF_OK;
+}
+
 int32_t dsuf_ctx_set_wait_budget_us(dsuf_ctx* ctx, int64_t microseconds) {
     if (!ctx) return DSUF_E_BADARG;
     DSUF_REQUIRE(ctx, microseconds >= 1 && microseconds <= 10000000, "wait budget must be 1 us .. 10 s, got %lld", (long long)microseconds);

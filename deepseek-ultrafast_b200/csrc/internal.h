@@ -22,6 +22,7 @@ struct dsuf_ctx {
     int smem_optin;
     int use_pdl;                   // launch with programmatic stream serialization
     int use_tc;                    // decode shapes on the tcgen05 streaming kernel (1) or the mma.sync one (0)
+    int prenorm_approx;            // RMS pre-normalisation with the approximate rsqrt instruction, as the reference's kernels
     int clock_khz;                 // SM clock rate the wait budgets are converted with
     long long xchg_wait_ticks;     // clock64 budget of the peer-exchange kernels' waits (dsuf_ctx_set_wait_budget_us)
     dsuf::DevStatus* dev_status;   // device word written by a kernel whose bounded wait expired

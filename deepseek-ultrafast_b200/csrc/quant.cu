@@ -25,6 +25,7 @@ struct QuantArgs {
     const bf16* norm_w;   // RMS pre-normalisation weights [k], or null
     const float* sumsq;   // pre-normalisation: sum of squares of every input row (row_sumsq_kernel)
     float eps;
+    int approx_rsqrt;     // pre-normalisation: 1 = the reference's rsqrtf (approximate instruction), 0 = correctly rounded 1/sqrt
 };
 
 template <int MODE>
@@ -42,8 +43,10 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
         for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(h[e]);
         if (a.norm_w) {
             // tc_quant_rows with pw (cu/tcgemm.cu:316-320): v = bf16(w * (x * rs)), every product rounded on its own.
-            // rs by correctly rounded sqrt and division (the reference's rsqrtf is a 2-ulp approximation).
-            const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(a.sumsq[row], (float)a.k), a.eps)));
+            // rs by correctly rounded sqrt and division by default (the reference's rsqrtf is a 2-ulp approximation).
+            // With approx_rsqrt the same instruction is used and the codes are the reference kernel's on the same GPU.
+            const float ms = __fadd_rn(__fdiv_rn(a.sumsq[row], (float)a.k), a.eps);
+            const float rs = a.approx_rsqrt ? rsqrtf(ms) : __fdiv_rn(1.0f, __fsqrt_rn(ms));
             const uint4 wraw = *(const uint4*)(a.norm_w + k0);
             const bf16* hw = (const bf16*)&wraw;
 #pragma unroll
@@ -123,7 +126,7 @@ int launch_row_sumsq(dsuf_ctx* ctx, cudaStream_t stream, const void* x, int ldx,
 
 int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
                      void* scales, const int* pair_row, int fanout, int sf_atoms, const void* norm_w, const float* sumsq, float eps) {
-    QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, sf_atoms, (const bf16*)norm_w, sumsq, eps};
+    QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, sf_atoms, (const bf16*)norm_w, sumsq, eps, ctx->prenorm_approx};
     if (rows_in == 0) return DSUF_OK;
     dim3 grid(rows_in, (k + 2047) / 2048);
     if (mode == DSUF_MODE_MX)

@@ -123,11 +123,16 @@ int32_t dsuf_row_sumsq(dsuf_ctx* ctx, void* stream, uint64_t x, int32_t ldx, int
 /* tc_quant_rows with RMS pre-normalisation (TqParams.pw / norm_part / eps, cu/tcgemm.cu:286-340; launched by
  * Rank::gemm_tc, model.rs:1328-1345): quantizes v = bf16(norm_w[k] * (x[r][k] * rs[r])) with
  * rs = 1 / sqrt(sumsq[r] / k + eps) instead of x.  norm_w bf16 [k], sumsq f32 [m] (dsuf_row_sumsq, or a producer
- * kernel's own partial sums added up by the caller).  rs is evaluated with correctly rounded sqrt and division; the
- * reference uses the approximate rsqrtf instruction, so its codes can differ where a product sits on a rounding
- * boundary. */
+ * kernel's own partial sums added up by the caller).  By default rs is evaluated with correctly rounded sqrt and
+ * division; the reference uses the approximate rsqrtf instruction, so its codes can differ where a product sits on a
+ * rounding boundary (dsuf_ctx_set_prenorm_rsqrt selects the reference's instruction). */
 int32_t dsuf_act_quant_fp8_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t m, int32_t k,
                                    uint64_t norm_w, uint64_t sumsq, float eps, uint64_t q_out, uint64_t scale_out);
+/* How the pre-normalising quantizers (dsuf_act_quant_fp8_prenorm, dsuf_moe_gather_quant_prenorm) evaluate 1/sqrt:
+ * 0 (default) correctly rounded, which a CPU can reproduce bit for bit; 1 the GPU's approximate rsqrt instruction, which
+ * is what the reference's kernels execute (cu/tcgemm.cu:305, cu/tcmoe.cu:97) -- with it the codes and scales equal the
+ * reference kernels' on the same GPU (about 1 code in 10^4 differs otherwise). */
+int32_t dsuf_ctx_set_prenorm_rsqrt(dsuf_ctx* ctx, int32_t approximate);
 
 /* Scratch of dsuf_gemm_fp8: stream-K partial sums and arrival counters.  Must be zeroed once with
  * dsuf_workspace_init before first use; the kernels leave it zeroed.  Calls sharing one workspace must be
