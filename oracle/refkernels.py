@@ -328,3 +328,159 @@ def moe_gather_quant(x, pw, eps, plan, part=None):
     launch(function("tcmoe", "moe_gather_quant"), ((m * (k // 32) + 255) // 256,), 256, 0, [mq])
     _KEEP.append((x, pw, part, plan))
     return xq, sf
+
+
+# ------------------------------------------------------------------------------------------------ decode GEMVs
+def tile_fp8(codes):
+    """tile_fp8 (crates/model/src/formats.rs:96-118): e4m3 codes u8 [n][k] -> the mma.sync m16n8k16 A-fragment order the
+    decode GEMV streams: per 64-row quad and 32-K step 2048 bytes = 4 row groups x 32 lanes x 16 bytes; lane (g = lane/4,
+    t = lane%4) holds rows {g, g+8} x columns {2t, 2t+1, 8+2t, 9+2t, 16+2t, 17+2t, 24+2t, 25+2t}."""
+    w = np.ascontiguousarray(codes, np.uint8)
+    n, k = w.shape
+    require(n % 64 == 0 and k % 32 == 0, "tile_fp8 needs n % 64 == 0 and k % 32 == 0")
+    t = np.arange(4)[:, None]
+    kk = np.concatenate([np.stack([2 * t[:, 0] + 8 * j, 2 * t[:, 0] + 8 * j + 1], axis=1) for j in range(4)], axis=1)   # [t][8]
+    w6 = w.reshape(n // 64, 4, 2, 8, k // 32, 32)            # [q][rg][h][g][ks][c], row = rg*16 + h*8 + g
+    a = w6[..., kk]                                          # [q][rg][h][g][ks][t][j]
+    return np.ascontiguousarray(a.transpose(0, 4, 1, 3, 5, 2, 6)).reshape(-1)   # [q][ks][rg][g][t][h][j]
+
+
+class RouteArgs(C.Structure):      # crates/engine/src/ops.rs:124-135
+    _fields_ = [("scores", C.c_uint64), ("bias", C.c_uint64), ("ids", C.c_uint64), ("w", C.c_uint64), ("n_exp", C.c_int32), ("topk", C.c_int32),
+                ("scale", C.c_float), ("nsum", C.c_int32)]
+
+
+class RopeParams(C.Structure):     # crates/engine/src/ops.rs:42-61
+    _fields_ = [("x", C.c_uint64), ("ldx", C.c_int32), ("n", C.c_int32), ("rows_per_token", C.c_int32), ("rope_off", C.c_int32),
+                ("cos", C.c_uint64), ("sin", C.c_uint64), ("inverse", C.c_int32), ("quant", C.c_int32), ("ratio", C.c_int32), ("dst", C.c_uint64),
+                ("pos_offset", C.c_int32), ("norm_w", C.c_uint64), ("norm_eps", C.c_float), ("dst_by_row", C.c_int32), ("q4", C.c_uint64),
+                ("sf4", C.c_uint64)]
+
+
+class GemvParams(C.Structure):     # crates/engine/src/ops.rs:63-115, mirror of cu/gemv.cu:19-71
+    _fields_ = [("w", C.c_uint64), ("ws", C.c_uint64), ("x", C.c_uint64), ("out", C.c_uint64), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+                ("ldx", C.c_int32), ("ldo", C.c_int32), ("out_f32", C.c_int32), ("x_group_rows", C.c_int32), ("alpha", C.c_float),
+                ("stage_steps", C.c_int32), ("plan", C.c_uint64), ("w_stride", C.c_uint64), ("mode", C.c_int32), ("swiglu_limit", C.c_float),
+                ("prenorm_w", C.c_uint64), ("prenorm_eps", C.c_float), ("norm_part", C.c_uint64), ("norm_nslices", C.c_int32),
+                ("ksplit_slots", C.c_int32), ("xq", C.c_uint64), ("xsq", C.c_uint64), ("oq", C.c_uint64), ("osq", C.c_uint64), ("sched", C.c_uint64),
+                ("out2", C.c_uint64), ("ldo2", C.c_int32), ("n_split", C.c_int32), ("rope_cos", C.c_uint64), ("rope_sin", C.c_uint64),
+                ("rope_pos", C.c_uint64), ("rope_head", C.c_int32), ("rope_off", C.c_int32), ("w_sh", C.c_uint64), ("route", RouteArgs),
+                ("kvr", RopeParams), ("kvr_on", C.c_int32), ("_pad_kvr", C.c_int32), ("out_pos", C.c_uint64), ("iq_head", C.c_int32),
+                ("iq_off", C.c_int32), ("sp", C.c_uint64), ("spart", C.c_uint64), ("sp_vloc", C.c_int32), ("sp_off", C.c_int32),
+                ("xshift", C.c_int32), ("_padx", C.c_int32)]
+
+
+class TvParams(C.Structure):       # crates/engine/src/ops.rs:1072-1103, mirror of cu/tcgemv.cu:10-31
+    _fields_ = [("tmap", C.c_uint64), ("sfa", C.c_uint64), ("x", C.c_uint64), ("prenorm_w", C.c_uint64), ("norm_part", C.c_uint64), ("out", C.c_uint64),
+                ("out2", C.c_uint64), ("rope_cos", C.c_uint64), ("rope_sin", C.c_uint64), ("meta", C.c_uint64), ("alpha", C.c_float), ("eps", C.c_float),
+                ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("kpt", C.c_int32), ("ldx", C.c_int32), ("ldo", C.c_int32), ("ldo2", C.c_int32),
+                ("n_split", C.c_int32), ("out_f32", C.c_int32), ("nslices", C.c_int32), ("rope_head", C.c_int32), ("rope_off", C.c_int32),
+                ("partial", C.c_int32), ("group_rows", C.c_int32), ("kvr", RopeParams), ("kvr_on", C.c_int32), ("_pad2", C.c_int32)]
+
+
+# the reference asserts these sizes (crates/engine/src/ops.rs:1165-1166)
+assert C.sizeof(RopeParams) == 104 and C.sizeof(RouteArgs) == 48 and C.sizeof(GemvParams) == 432 and C.sizeof(TvParams) == 256
+
+GEMV_STAGES = 4
+SMEM_OPTIN = 227 * 1024            # ops::hw() for cc 10.0 (crates/engine/src/ops.rs:215)
+
+
+def pick_ph(steps):                # crates/engine/src/ops.rs:290-292
+    return 4 if steps >= 48 else 2 if steps >= 12 else 1
+
+
+def gemv_smem(k, m, cs, tile_k=32, step_bytes=2048, prenorm=False):   # crates/engine/src/ops.rs:310-317
+    mt = 8 if m <= 8 else 16
+    ks = k // cs
+    nsteps = ks // tile_k
+    ss = min((nsteps + GEMV_STAGES - 1) // GEMV_STAGES, 12)
+    return (GEMV_STAGES * ss * step_bytes + 2 * GEMV_STAGES * 8 + mt * (ks + 32) * 2 + mt * (ks // 32) * 4 + pick_ph(nsteps) * mt * 64 * 4
+            + (ks * 2 if prenorm else 0) + ((mt * 64 + 4 * cs) * 4 if cs > 1 else 0))
+
+
+def gemv_geometry(n, k, m, sms=148):
+    """ops::gemv's choices for a dense FP8 weight (crates/engine/src/ops.rs:298-328, 331-474): K-split cluster size, pipeline
+    depth, stage steps, grid, block and shared memory."""
+    require(1 <= m <= 16, "gemv supports 1..=16 rows (ops.rs:342)")
+    require(n % 64 == 0, "gemv needs n % 64 == 0 (ops.rs:343)")
+    quads, unit = n // 64, 32
+    cs = 1
+    for c in (1, 2, 4, 8):                                    # pick_cluster (ops.rs:298-308)
+        if k % (c * unit) == 0 and quads * c <= 2 * sms:
+            cs = c
+    while gemv_smem(k, m, cs) > SMEM_OPTIN and cs < 16 and k % (2 * cs * unit) == 0:   # gemv_cluster (ops.rs:319-328)
+        cs *= 2
+    ks = k // cs
+    require(k % cs == 0 and ks % 32 == 0, f"bad split {cs} for k {k} (ops.rs:349)")
+    require(ks // 32 <= 256, "the kernel stages at most 256 weight-scale bytes per scale row (cu/gemv.cu:194)")
+    nsteps = ks // 32
+    ss = min((nsteps + GEMV_STAGES - 1) // GEMV_STAGES, 12)
+    smem = gemv_smem(k, m, cs)
+    require(smem <= SMEM_OPTIN, f"gemv smem {smem} too large (ops.rs:354)")
+    ph = pick_ph(nsteps)
+    return {"nt": 1 if m <= 8 else 2, "ph": ph, "cs": cs, "ss": ss, "smem": smem, "grid": (quads, cs, 1), "block": (4 * ph + 1) * 32,
+            "kernel": f"gemv_fp8_n{1 if m <= 8 else 2}_p{ph}"}
+
+
+class GemvWeight:
+    """Loader::fp8 (crates/engine/src/weights.rs:254-264): fragment-tiled codes + the raw 32x32 scale rows."""
+
+    def __init__(self, codes, scales32):
+        import torch
+        codes = np.ascontiguousarray(codes, np.uint8)
+        self.n, self.k = codes.shape
+        self.w = torch.from_numpy(tile_fp8(codes)).cuda()
+        self.s = torch.from_numpy(np.ascontiguousarray(scales32, np.uint8).reshape(self.n // 32, self.k // 32)).cuda()
+
+
+def gemv_fp8(gw, x, out=None, alpha=1.0, pdl=False):
+    """ops::gemv (crates/engine/src/ops.rs:331-474) for a dense FP8 weight with the Store epilogue: x bf16 [m][k] in (the
+    kernel quantizes it 1x32 in shared memory, cu/quantblocks.cuh:7-57), bf16 [m][n] out."""
+    import torch
+    m, k = x.shape
+    require(k == gw.k and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0, "x bf16 [m][k]")
+    geo = gemv_geometry(gw.n, gw.k, m, sm_count())
+    if out is None:
+        out = torch.empty(m, gw.n, dtype=torch.bfloat16, device=x.device)
+    p = GemvParams()
+    p.w, p.ws, p.x, p.out = gw.w.data_ptr(), gw.s.data_ptr(), x.data_ptr(), out.data_ptr()
+    p.m, p.n, p.k, p.ldx, p.ldo = m, gw.n, gw.k, x.stride(0), out.stride(0)
+    p.alpha, p.stage_steps = float(alpha), geo["ss"]
+    f = function("gemv", geo["kernel"], geo["smem"], big_cluster=geo["cs"] > 8)
+    launch(f, geo["grid"], geo["block"], geo["smem"], [p], cluster=(1, geo["cs"], 1), pdl=pdl)
+    _KEEP.append((gw, x, out))
+    return out
+
+
+def tc_gemv_cluster(n, k, sms=148):   # crates/engine/src/ops.rs:1105-1107
+    for c in (8, 5, 4, 2, 1):
+        if k % (128 * c) == 0 and k // c <= 1024 and (n // 128) * c <= sms:
+            return c if (n // 128) * c >= 96 else None
+    return None
+
+
+def tc_gemv_fp8(tw, x, out=None, alpha=1.0, pdl=False):
+    """ops::tc_gemv (crates/engine/src/ops.rs:1118-1163): the tcgen05 decode GEMV, m <= 8; the whole K slice of a 128-row
+    tile resident in shared memory, K split over a cluster with a push reduce."""
+    import torch
+    m, k = x.shape
+    require(m <= 8 and tw.n % 128 == 0, "m <= 8 && n % 128 == 0 (ops.rs:1119)")
+    require(k == tw.k and x.dtype == torch.bfloat16 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0, "x bf16 [m][k]")
+    cs = tc_gemv_cluster(tw.n, tw.k, sm_count())
+    require(cs is not None, f"tc_gemv: no split for n {tw.n} k {tw.k} (ops.rs:1120)")
+    ks = k // cs
+    kt = ks // 128
+    smem = kt * (16384 + 1024 + 512 + 512) + 8 * ks * 2 + ks * 2 + 8 * 128 * 4 + 1040 * 4 + 1024
+    require(smem <= SMEM_OPTIN, "tc_gemv shared memory")
+    # the push reduce: every CTA expects (cs-1) * per * 4 bytes and sends per * 4 to each peer (cu/tcgemv.cu:62-74,196-208)
+    per = ((m * 128 + cs - 1) // cs + 3) & ~3
+    require(cs * per <= 1040, "receive buffer of the cluster reduce holds 1040 floats (ops.rs:1123)")
+    if out is None:
+        out = torch.empty(m, tw.n, dtype=torch.bfloat16, device=x.device)
+    p = TvParams()
+    p.tmap, p.sfa, p.x, p.out = tw.tmap128.data_ptr(), tw.sf.data_ptr(), x.data_ptr(), out.data_ptr()
+    p.alpha, p.m, p.n, p.k, p.kpt, p.ldx, p.ldo = float(alpha), m, tw.n, tw.k, tw.k // 128, x.stride(0), out.stride(0)
+    f = function("tcgemv", "tc_gemv_fp8", smem)
+    launch(f, (tw.n // 128, cs, 1), 128, smem, [p], cluster=(1, cs, 1), pdl=pdl)
+    _KEEP.append((tw, x, out))
+    return out

@@ -198,3 +198,39 @@ def test_tc_gemm_fp8_outputs_pin_the_oracle_and_match_the_library(pkg, tc_only, 
     assert rel(got_l, got_r) < TOL, "library differs from the reference kernel"
     # both sum exact products of the same codes in fp32 and round once to bf16: differences are single bf16 ulps
     assert np.abs(got_l - got_r).max() <= np.abs(got_r).max() * 2 ** -7
+
+
+@pytest.mark.parametrize("n,k,m", [(512, 1024, 1), (7168, 2048, 5), (4096, 7168, 16), (1024, 2048, 8)])
+def test_gemv_fp8_decode_kernel_pins_the_oracle_and_matches_the_library(pkg, tc_only, n, k, m):
+    """gemv_fp8_n{1,2}_p{1,2,4} (cu/gemv.cu:133-540): the reference's mma.sync decode GEMV (bf16 activations in, quantized
+    1x32 in the kernel, K split over a cluster) against the oracle and this library's gemv in the reference's geometry."""
+    ctx = tc_only
+    g = seeded(3 * n + k + m)
+    xt, xn = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, n, k, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(oracle.MODE_MX, wn)
+    out_r = rk.gemv_fp8(rk.GemvWeight(wq, ws), xt.cuda())
+    out_l = pkg.gemv(ctx, pkg.Weight.dense_fp8(ctx, pkg.MODE_MX, wq, ws), xt.cuda())
+    rk.synchronize()
+    xq, xs = oracle.act_quant(oracle.MODE_MX, xn)
+    _, ref = oracle.gemm_fp8(oracle.MODE_MX, wq, ws, xq, xs)
+    got_r, got_l = out_r.float().cpu().numpy(), out_l.float().cpu().numpy()
+    assert rel(ref, got_r) < TOL and rel(got_l, got_r) < TOL
+
+
+@pytest.mark.parametrize("n,k,m", [(7168, 2048, 1), (7168, 2048, 8), (12288, 1024, 3)])
+def test_tc_gemv_fp8_pins_the_oracle_and_matches_the_library(pkg, tc_only, n, k, m):
+    """tc_gemv_fp8 (cu/tcgemv.cu:33-241): the reference's tcgen05 decode GEMV at the shape that qualifies for it
+    (7168 x 2048, K split over clusters of two) against the oracle and this library's tcgen05 streaming GEMV."""
+    ctx = tc_only
+    g = seeded(n + 5 * k + m)
+    xt, xn = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, n, k, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(oracle.MODE_MX, wn)
+    out_r = rk.tc_gemv_fp8(rk.TcWeight(wq, ws), xt.cuda())
+    out_l = pkg.gemv(ctx, pkg.Weight.dense_fp8(ctx, pkg.MODE_MX, wq, ws), xt.cuda())
+    rk.synchronize()
+    xq, xs = oracle.act_quant(oracle.MODE_MX, xn)
+    _, ref = oracle.gemm_fp8(oracle.MODE_MX, wq, ws, xq, xs)
+    got_r, got_l = out_r.float().cpu().numpy(), out_l.float().cpu().numpy()
+    assert rel(ref, got_r) < TOL and rel(got_l, got_r) < TOL
