@@ -234,6 +234,93 @@ def dense_sweep(pkg, ctx, torch, hbm_peak, quick):
     return out
 
 
+def _graph_us(torch, launches, reps=10):
+    """Microseconds per launch of a list of callables captured into one CUDA graph and replayed (GPU time, not launch rate)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in launches:
+            f()
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for f in launches:
+                f()
+    torch.cuda.current_stream().wait_stream(side)
+    ms = time_events(torch, graph.replay, reps, 2) / len(launches)
+    del graph
+    return ms * 1e3
+
+
+def reference_kernels(pkg, ctx, torch, hbm_peak, quick):
+    """The reference's own sm_100a kernels (compiled from its sources into oracle/_ref, launched with its own geometry by
+    oracle/refkernels.py) timed on this GPU beside this library's kernels on the same codes, in the reference's (MX) scale
+    geometry, which is the only one the reference implements.  Decode GEMVs rotate over enough weight copies to defeat L2."""
+    import oracle.refkernels as rk
+    if not rk.available():
+        return {"unavailable": "oracle/_ref cubins or oracle/librefk.so not built (the reference's sources were absent at build time)"}
+    rng = np.random.default_rng(0)
+
+    def rand_weight(n, k):
+        codes = rng.integers(0, 0x7e, (n, k), dtype=np.uint8) | (rng.integers(0, 2, (n, k), dtype=np.uint8) << 7)   # finite e4m3
+        scales = rng.integers(118, 122, (n // 32, k // 32), dtype=np.uint8)
+        return codes, scales
+
+    out = {"geometry": "MX (1x32 activations, 32x32 weights, UE8M0 scales): the reference's", "decode_gemv": [], "notes": []}
+    for (n, k) in DENSE_SHAPES:
+        wbytes = n * k + (n // 32) * (k // 32)
+        copies = max(2, int(np.ceil(260e6 / wbytes)))
+        codes, scales = rand_weight(n, k)
+        ref_w = [rk.GemvWeight(np.roll(codes, c, axis=0), scales) for c in range(copies)]
+        ours_w = [pkg.Weight.dense_fp8(ctx, pkg.MODE_MX, np.roll(codes, c, axis=0), scales) for c in range(copies)]
+        tc_w = [rk.TcWeight(np.roll(codes, c, axis=0), scales) for c in range(copies)] if rk.tc_gemv_cluster(n, k, ctx.sm_count) else None
+        for m in ([1] if quick else [1, 16]):
+            x = torch.randn(m, k, device=ctx.device).bfloat16()
+            o = torch.empty(m, n, dtype=torch.bfloat16, device=ctx.device)
+            xq, xs = pkg.act_quant(ctx, pkg.MODE_MX, x)
+            geo = rk.gemv_geometry(n, k, m, ctx.sm_count)
+            us_ref = _graph_us(torch, [lambda w=w: rk.gemv_fp8(w, x, o) for w in ref_w])
+            us_ours = _graph_us(torch, [lambda w=w: (pkg.act_quant(ctx, pkg.MODE_MX, x, xq, xs), pkg.gemm_fp8(ctx, w, xq, xs, m, o)) for w in ours_w])
+            algo = wbytes + 2 * m * k + 2 * m * n
+            row = {"n": n, "k": k, "m": m, "reference_kernel": geo["kernel"], "reference_cluster": geo["cs"], "reference_us": round(us_ref, 2),
+                   "reference_gbs": round(algo / us_ref / 1e3, 1), "ours_us_with_act_quant": round(us_ours, 2),
+                   "ours_gbs": round(algo / us_ours / 1e3, 1), "speedup": round(us_ref / us_ours, 2)}
+            if tc_w is not None and m <= 8:
+                us_tc = _graph_us(torch, [lambda w=w: rk.tc_gemv_fp8(w, x, o) for w in tc_w])
+                row["reference_tc_gemv_fp8_us"] = round(us_tc, 2)
+                row["speedup_vs_tc_gemv_fp8"] = round(us_tc / us_ours, 2)
+            out["decode_gemv"].append(row)
+            rk.synchronize()
+        del ref_w, ours_w, tc_w
+        torch.cuda.empty_cache()
+    out["notes"].append("tc_gemv_fp8 (the reference's tcgen05 decode GEMV) accepts only the 7168 x 2048 shape of the four "
+                        "(K/cluster <= 1024 and 96..SMs CTAs, crates/engine/src/ops.rs:1105-1107)")
+    # prefill dense: tc_quant_rows + tc_gemm_fp8p at the reference's chunk limit of 8192 tokens (PMAX, model.rs:13)
+    tokens = 8192
+    codes, scales = rand_weight(H, H)
+    tw = rk.TcWeight(codes, scales)
+    w = pkg.Weight.dense_fp8(ctx, pkg.MODE_MX, codes, scales)
+    x = torch.randn(tokens, H, device=ctx.device).bfloat16()
+    o = torch.empty(tokens, H, dtype=torch.bfloat16, device=ctx.device)
+    aq, sfa = rk.tc_quant_rows(x)
+    xq, xs = pkg.act_quant(ctx, pkg.MODE_MX, x)
+    flops = 2.0 * tokens * H * H
+    ms_ref_q = time_events(torch, lambda: rk.tc_quant_rows(x, aq=aq, sfa=sfa), 5, 2)
+    ms_ref = time_events(torch, lambda: rk.tc_gemm(tw, aq, sfa, tokens, out=o), 5, 2)
+    rk.synchronize()
+    ms_ours_q = time_events(torch, lambda: pkg.act_quant(ctx, pkg.MODE_MX, x, xq, xs), 5, 2)
+    ms_ours = time_events(torch, lambda: pkg.gemm_fp8(ctx, w, xq, xs, tokens, o), 5, 2)
+    out["prefill_dense"] = {"n": H, "k": H, "tokens": tokens, "reference_kernel": "tc_gemm_fp8p", "reference_ms": round(ms_ref, 4),
+                            "reference_tflops": round(flops / ms_ref / 1e9, 1), "reference_tc_quant_rows_ms": round(ms_ref_q, 4),
+                            "ours_ms": round(ms_ours, 4), "ours_tflops": round(flops / ms_ours / 1e9, 1), "ours_act_quant_ms": round(ms_ours_q, 4),
+                            "speedup_gemm": round(ms_ref / ms_ours, 2), "speedup_quant": round(ms_ref_q / ms_ours_q, 2)}
+    out["notes"].append("tc_moe_w13 / tc_moe_w2 (the reference's prefill expert GEMMs) keep the scale atoms of all K tiles of a token tile in 40 "
+                        "shared-memory slots (cu/tcmoe.cu:171, SFB_MAX): K <= 5120, so the gate/up GEMM cannot run at hidden 7168; the fused decode "
+                        "MoE entries and comm.cu spin on global memory without a bound and are not launched on a shared GPU")
+    out["device_status"] = int(ctx.status().code)
+    return out
+
+
 def zipf_routing(torch, tokens, n_exp, topk, seed, device):
     """cfg3 routing: expert popularity Zipf(s=1.1) over a seeded permutation; each token draws `topk` distinct experts
     without replacement in proportion to popularity (Gumbel top-k); weights = softmax of `topk` fresh N(0,1) logits."""
@@ -528,6 +615,11 @@ def run_ours(args):
                                    "routing": "softmax of N(0,1) logits, top-8 (near-uniform expert load)",
                                    "launches_per_layer": pstack.count_launches() // LAYERS, "device_status": int(ctx.status().code)}
         del pstack, xp
+    if world == 1 and not args.skip_sub and not args.skip_ref_kernels:
+        try:
+            result["reference_kernels"] = reference_kernels(pkg, ctx, torch, hbm_peak, args.quick)
+        except Exception as ex:  # noqa: BLE001 - the comparison must not take the benchmark line down with it
+            result["reference_kernels"] = {"unavailable": f"{type(ex).__name__}: {ex}"}
     if world == 1 and not args.skip_cpu:
         p = cpu_prepare()
         vals, dts, t_all = [], [], time.perf_counter()
@@ -597,6 +689,7 @@ def main():
     ap.add_argument("--quick", action="store_true", help="shorter GEMV sweep")
     ap.add_argument("--skip-sub", action="store_true", help="main line only")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-ref-kernels", action="store_true", help="leave out the reference's own kernels (oracle/_ref) timed beside ours")
     ap.add_argument("--skip-parity", action="store_true", help="N > 1: leave out the one-layer comparison with the single-GPU stack")
     ap.add_argument("--no-sustain", dest="sustain", action="store_false", help="leave out the second timed region of >= 1 s")
     ap.add_argument("--small-case", default=None, choices=["decode", "prefill"],

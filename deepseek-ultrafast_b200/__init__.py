@@ -53,6 +53,7 @@ ABI = {
     "dsuf_sm_count": (C.c_int32, [C.c_void_p]),
     "dsuf_ctx_set_wait_budget_us": (C.c_int32, [C.c_void_p, C.c_int64]),
     "dsuf_ctx_set_prenorm_rsqrt": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "dsuf_ctx_set_dense_ksplit": (C.c_int32, [C.c_void_p, C.c_int32]),
     "dsuf_quant_fp8_weight_host": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_quant_fp4_weight_host": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_packed_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
@@ -183,6 +184,10 @@ class Ctx:
         """True: tcgen05 streaming kernels for decode shapes; False: the mma.sync streaming kernels."""
         self.check(lib().dsuf_ctx_set_decode_path(self.h, 1 if tcgen05 else 0))
         self.tcgen05 = bool(tcgen05)
+
+    def set_dense_ksplit(self, enabled):
+        """Cluster K-split for dense decode GEMVs with few row tiles (default on)."""
+        self.check(lib().dsuf_ctx_set_dense_ksplit(self.h, 1 if enabled else 0))
 
     def set_prenorm_rsqrt_approx(self, approximate):
         """True: the pre-normalising quantizers use the GPU's approximate rsqrt, as the reference's kernels do."""

@@ -31,6 +31,7 @@ int32_t dsuf_ctx_create(int32_t device, dsuf_ctx** out) {
     ctx->smem_optin = (int)prop.sharedMemPerBlockOptin;
     ctx->clock_khz = prop.clockRate > 0 ? prop.clockRate : 1965000;
     ctx->xchg_wait_ticks = WAIT_BUDGET_TICKS;
+    ctx->use_kslices = 1;
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -68,6 +69,12 @@ int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled) {
 int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05) {
     if (!ctx) return DSUF_E_BADARG;
     ctx->use_tc = tcgen05 ? 1 : 0;
+    return DSUF_OK;
+}
+
+int32_t dsuf_ctx_set_dense_ksplit(dsuf_ctx* ctx, int32_t enabled) {
+    if (!ctx) return DSUF_E_BADARG;
+    ctx->use_kslices = enabled ? 1 : 0;
     return DSUF_OK;
 }
 

@@ -22,6 +22,7 @@ struct dsuf_ctx {
     int smem_optin;
     int use_pdl;                   // launch with programmatic stream serialization
     int use_tc;                    // decode shapes on the tcgen05 streaming kernel (1) or the mma.sync one (0)
+    int use_kslices;               // dense decode GEMV: cluster K-split where it pays (default on)
     int prenorm_approx;            // RMS pre-normalisation with the approximate rsqrt instruction, as the reference's kernels
     int clock_khz;                 // SM clock rate the wait budgets are converted with
     long long xchg_wait_ticks;     // clock64 budget of the peer-exchange kernels' waits (dsuf_ctx_set_wait_budget_us)
@@ -60,22 +61,41 @@ inline int cuda_fail(dsuf_ctx* ctx, cudaError_t e, const char* what) {
 
 // One launch path for every kernel: asynchronous on the caller's stream, optional PDL attribute, no
 // allocation and no synchronisation (safe inside stream capture).
+// `cluster_x` > 1 launches thread-block clusters of that many CTAs along x (the grid must be a multiple of it).
 template <typename... KArgs, typename... Args>
-int launch(dsuf_ctx* ctx, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+int launch_cluster(dsuf_ctx* ctx, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x,
+                   Args&&... args) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    memset(attr, 0, sizeof(attr));
+    unsigned n = 0;
+    if (ctx->use_pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = (unsigned)cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = ctx->use_pdl ? 1 : 0;
+    cfg.numAttrs = n;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "kernel launch");
     return DSUF_OK;
+}
+
+template <typename... KArgs, typename... Args>
+int launch(dsuf_ctx* ctx, cudaStream_t stream, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    return launch_cluster(ctx, stream, kernel, grid, block, smem, 1, std::forward<Args>(args)...);
 }
 
 // per-file launchers

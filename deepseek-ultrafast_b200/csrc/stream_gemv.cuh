@@ -49,6 +49,8 @@ struct StreamArgs {
     float alpha;
     float swiglu_limit;
     int whole_items;  // dense: give every CTA whole row tiles (no stream-K partials) when that costs no extra wave
+    int kslices;      // dense, tcgen05 kernel: > 0 = one row tile per cluster of `kslices` CTAs, each taking a slice of K;
+                      // the slices are summed through distributed shared memory (no global partials)
 };
 
 template <int FMT>

@@ -138,9 +138,23 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     const long long steps_streamk = (tot + grid - 1) / grid + 6, steps_whole = (long long)((w->rt + grid - 1) / grid) * w->kt;
     a.whole_items = steps_whole <= steps_streamk ? 1 : 0;
     const bool mx = w->d.mode == DSUF_MODE_MX;
+    int cluster = 1;
+    if (ctx->use_tc && ctx->use_kslices) {
+        // Weights with few row tiles: one row tile per cluster, K cut into 1, 2 or 4 slices that are summed through
+        // distributed shared memory (~1.5 us) instead of through global partials (~4 us on a kernel of 10).  Cost in tile
+        // steps of a CTA's stream; taken when no worse than the other two decompositions.
+        const long long steps_other = a.whole_items ? steps_whole : steps_streamk;
+        long long best = steps_other;
+        for (int cs : {1, 2, 4}) {
+            if ((long long)w->rt * cs > grid || w->kt < cs) continue;
+            const long long steps = (w->kt + cs - 1) / cs + (cs > 1 ? 3 : 0);
+            if (steps < best) { best = steps; cluster = cs; a.kslices = cs; }
+        }
+        if (a.kslices) grid = w->rt * a.kslices;
+    }
     if (ctx->use_tc) {
         a.tm_w = w->tm_tc;
-#define GT(WMX, AMX, NN) launch(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, a)
+#define GT(WMX, AMX, NN) launch_cluster(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, cluster, a)
         if (mx) return ntok == 8 ? GT(1, 1, 8) : ntok == 16 ? GT(1, 1, 16) : ntok == 32 ? GT(1, 1, 32) : GT(1, 1, 64);
         return ntok == 8 ? GT(0, 0, 8) : ntok == 16 ? GT(0, 0, 16) : ntok == 32 ? GT(0, 0, 32) : GT(0, 0, 64);
 #undef GT

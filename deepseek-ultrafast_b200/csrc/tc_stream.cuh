@@ -124,7 +124,16 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 
     // ---- this CTA's span of the global tile sequence (see stream_gemv.cuh) ----
     long long beg, end;
-    if (EPI == EPI_DENSE && a.whole_items) {
+    // cluster K-split (dense weights with few row tiles): cluster r owns row tile r, its CTA j the K tiles
+    // [j KT / cs, (j + 1) KT / cs); the partial sums meet in CTA 0 of the cluster through distributed shared memory
+    const int ksl = EPI == EPI_DENSE ? a.kslices : 0;
+    const int krank = ksl > 1 ? (int)cluster_cta_rank() : 0;
+    bool cluster_done = false;  // this warp has been through the two cluster barriers of the reduce
+    if (EPI == EPI_DENSE && ksl > 0) {
+        const int rt_c = c / ksl;
+        beg = (long long)rt_c * KT + (long long)krank * KT / ksl;
+        end = (long long)rt_c * KT + (long long)(krank + 1) * KT / ksl;
+    } else if (EPI == EPI_DENSE && a.whole_items) {
         beg = ((long long)c * RT / G) * KT;
         end = ((long long)(c + 1) * RT / G) * KT;
     } else if (EPI == EPI_DENSE) {
@@ -480,7 +489,24 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                     const long long it0 = q * KT;
                     const bool whole = beg <= it0 && end >= it0 + KT;
                     bool do_store = whole;
-                    if (!whole) {
+                    if (ksl > 1) {
+                        // This CTA's only item.  Every CTA parks its partial in its own ring (all of its MMAs have completed
+                        // and nothing is in flight into the ring any more), the cluster meets, CTA 0 adds the others' in
+                        // rank order and stores, and the cluster meets again before anyone's shared memory goes away.
+                        float* park = (float*)ring + (size_t)cb * 128 + etid;
+#pragma unroll
+                        for (int j = 0; j < NC; ++j) park[(size_t)j * 128] = acc[j];
+                        cluster_barrier();
+                        if (krank == 0) {
+                            for (int pr = 1; pr < ksl; ++pr) {
+#pragma unroll
+                                for (int j = 0; j < NC; ++j) acc[j] += ld_cluster_f32(park + (size_t)j * 128, (uint32_t)pr);
+                            }
+                        }
+                        cluster_barrier();
+                        cluster_done = true;
+                        do_store = krank == 0;
+                    } else if (!whole) {
                         const int slot = (q == beg / KT) ? 0 : 1;
                         float* pw = a.partial + ((size_t)(c * 2 + slot) * 64 + cb) * 128 + etid;
 #pragma unroll
@@ -558,6 +584,11 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             if (++es == S) { es = 0; est = ring; }
             if (++kt == KT) { kt = 0; ++q; fresh = true; }
         }
+    }
+    if (ksl > 1 && !cluster_done) {
+        // warps that hold no partial sum still take part in the reduce's two cluster-wide barriers
+        cluster_barrier();
+        cluster_barrier();
     }
     tc_fence_before();
     __syncthreads();

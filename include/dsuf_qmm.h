@@ -62,6 +62,11 @@ int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled);
  * 0 = mma.sync streaming kernel (the counterpart of the reference's cu/gemv.cu family).  Both compute the same
  * function; the choice mirrors the reference's runtime switch between gemv and tc_gemv (model.rs:1523-1530). */
 int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05);
+/* Decode-shape dense GEMV on the tcgen05 path: 1 (default) lets weights with few row tiles run as one row tile per
+ * thread-block cluster with K cut into slices summed through distributed shared memory -- the counterpart of the cluster
+ * K-split of ops::gemv / ops::tc_gemv (ops.rs:298-328, 1105-1107) -- where that beats stream-K with global partial sums;
+ * 0 keeps stream-K / whole row tiles only.  The results of the two are both deterministic but differ in summation order. */
+int32_t dsuf_ctx_set_dense_ksplit(dsuf_ctx* ctx, int32_t enabled);
 /* (synchronises `stream`) Reads and clears the device status word.  The reference's device waits are unbounded
  * spins with no error reporting (cu/comm.cu:217-224); here every wait is bounded and reports through this. */
 int32_t dsuf_status_poll(dsuf_ctx* ctx, void* stream, dsuf_dev_status* out);

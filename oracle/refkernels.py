@@ -25,6 +25,7 @@ LIB_PATH = os.path.join(HERE, "librefk.so")
 _LIB = None
 _MODULES = {}
 _FUNCS = {}
+_TMAPS = {}  # uploaded tensor maps by (base, dims, box)
 _KEEP = []   # host-side parameter blocks of launches in flight are kept alive until the next synchronize()
 
 
@@ -111,10 +112,14 @@ def upload_tmap_u8_sw128(base_tensor, cols, rows, stride, box_rows):
     """tensor_map_u8_sw128 (crates/cuda/src/lib.rs:742-763) uploaded to device memory (cu::upload_synced)."""
     import torch
     require(base_tensor.data_ptr() % 16 == 0 and stride % 16 == 0 and box_rows <= 256, "tensor map alignment / box")
+    key = (base_tensor.data_ptr(), cols, rows, stride, box_rows)
+    if key in _TMAPS:                  # the reference caches its activation maps the same way (model.rs:1343-1358)
+        return _TMAPS[key]
     host = np.zeros(128, np.uint8)
     _check(lib().refk_tmap_u8_sw128(host.ctypes.data_as(C.c_void_p), base_tensor.data_ptr(), cols, rows, stride, box_rows))
     dev = torch.from_numpy(host).cuda()
     require(dev.data_ptr() % 64 == 0, "tensor map must be 64-byte aligned in device memory")
+    _TMAPS[key] = dev
     return dev
 
 
@@ -213,7 +218,7 @@ def tc_row_sumsq(x):
     return part
 
 
-def tc_quant_rows(x, pw=None, eps=0.0, part=None, rows_alloc=None):
+def tc_quant_rows(x, pw=None, eps=0.0, part=None, rows_alloc=None, aq=None, sfa=None):
     """tc_quant_rows (cu/tcgemm.cu:300-340) as Rank::gemm_tc launches it (model.rs:1328-1345): one CTA per row,
     min(ceil(k/32 / 32) * 32, 256) threads.  Returns (aq u8 [rows_alloc][k], sfa atoms u8 [rows_alloc/128 * k/128 * 512])."""
     import torch
@@ -222,8 +227,10 @@ def tc_quant_rows(x, pw=None, eps=0.0, part=None, rows_alloc=None):
     require(x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0, "16-byte aligned rows")
     rows_alloc = rows_alloc or (m + 127) // 128 * 128
     require(rows_alloc >= m and rows_alloc % 128 == 0, "scratch rows")
-    aq = torch.zeros(rows_alloc, k, dtype=torch.uint8, device=x.device)
-    sfa = torch.full((rows_alloc // 128 * (k // 128) * 512,), 127, dtype=torch.uint8, device=x.device)
+    if aq is None:
+        aq = torch.zeros(rows_alloc, k, dtype=torch.uint8, device=x.device)
+        sfa = torch.full((rows_alloc // 128 * (k // 128) * 512,), 127, dtype=torch.uint8, device=x.device)
+    require(aq.shape == (rows_alloc, k) and sfa.numel() == rows_alloc // 128 * (k // 128) * 512, "scratch sizes")
     if pw is not None:
         require(pw.dtype == torch.bfloat16 and pw.numel() == k and pw.data_ptr() % 16 == 0, "norm weight bf16 [k]")
         if part is None:

@@ -132,6 +132,32 @@ def test_dense_gemm_prefill_rows_on_tcgen05(pkg, ctx, mode, n, k, m):
     _dense_case(pkg, ctx, mode, n, k, m, seed=n + m)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("n,k,m", [(7168, 2048, 1), (7168, 2048, 33), (4096, 7168, 64), (7168, 896, 8), (2048, 512, 16)])
+def test_dense_gemv_cluster_k_split(pkg, ctx, mode, n, k, m):
+    """Weights with few row tiles run as one row tile per thread-block cluster, K cut into 2 or 4 slices summed through
+    distributed shared memory (clusters of 2: 7168 x 2048 and the 8-GPU K shard 7168 x 896; of 4: 4096 x 7168; token
+    tiles of 8, 16 and, with the column-split epilogue, 64 columns).  Against the oracle on sampled rows, repeatable bit for
+    bit, and equal within rounding to the stream-K decomposition of the same product."""
+    if not ctx.tcgen05:
+        pytest.skip("cluster K-split is a decomposition of the tcgen05 streaming kernel")
+    _dense_case(pkg, ctx, mode, n, k, m, seed=n + k + m, rows=3)
+    g = seeded(n + k + m)
+    xt, xn = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, n, k, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(mode, wn)
+    w = pkg.Weight.dense_fp8(ctx, mode, wq, ws)
+    a = pkg.gemv(ctx, w, xt.cuda())
+    ctx.set_dense_ksplit(False)
+    try:
+        b = pkg.gemv(ctx, w, xt.cuda())
+    finally:
+        ctx.set_dense_ksplit(True)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    assert rel(a.float().cpu().numpy(), b.float().cpu().numpy()) < 2e-3
+
+
 def test_dense_gemm_prefill_rejects_odd_row_tile_count(pkg, ctx):
     if not ctx.tcgen05:
         pytest.skip("tcgen05 path only")
