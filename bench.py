@@ -398,7 +398,9 @@ def run_ours(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a rank that is two minutes late at a barrier has failed: end the run instead of waiting out the default ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
     pkg = load_package()
     stackmod = importlib.import_module(pkg.__name__ + ".stack")
     ctx = pkg.Ctx(local, pdl=args.pdl)
@@ -458,6 +460,15 @@ def run_ours(args):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        # every rank must agree on the figure (and on the number of steps derived from it below: the ranks replay a
+        # graph that contains their exchange, so they have to replay it the same number of times)
+        tms = torch.tensor([ms], device="cuda")
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    st_mid = ctx.status()
+    if st_mid.code:
+        raise RuntimeError(f"device status {st_mid.code} (kernel {st_mid.kernel}, site {st_mid.where}) after the timed steps: the result is void")
     # ---- the same step over a region of at least a second (the K timed steps above are the contract's number) ----
     n_long = max(args.steps, int(np.ceil(1100.0 / max(ms, 1e-3)))) if args.sustain else 0
     ms_long = None
@@ -521,9 +532,9 @@ def run_ours(args):
             torch.cuda.empty_cache()
         barrier()
     if world > 1:
-        tms = torch.tensor([ms, ms_e2e, ms_long if ms_long is not None else 0.0], device="cuda")
+        tms = torch.tensor([ms_e2e, ms_long if ms_long is not None else 0.0], device="cuda")
         dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        ms, ms_e2e, ml = tms.tolist()
+        ms_e2e, ml = tms.tolist()
         ms_long = ml if ms_long is not None else None
     if rank != 0:
         finish(torch, dist, world, graph)

@@ -67,6 +67,8 @@ ABI = {
     "dsuf_ep_flag_bytes": (C.c_size_t, [C.c_int32]),
     "dsuf_ep_allreduce_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32,
                                            C.c_int64, C.c_uint64, C.c_uint64]),
+    "dsuf_ep_allgather_cols_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32,
+                                                C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
     "dsuf_ep_combine_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                          C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
     "dsuf_act_quant_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
@@ -351,6 +353,15 @@ class PeerAllReduce:
         ptrs = self.data_ptrs[partial.data_ptr()]
         self.ctx.check(lib().dsuf_ep_allreduce_bf16(self.ctx.h, self.ctx.stream(), ptrs, self.flag_ptrs, self.rank, self.world,
                                                     partial.numel(), self.state.data_ptr(), out.data_ptr()))
+        return out
+
+    def gather_cols(self, buf, out):
+        """dsuf_ep_allgather_cols_bf16: every rank wrote its column slice of ``buf`` (a buffer from ``buffer``); ``out``
+        receives all slices."""
+        rows, cols = buf.shape
+        ptrs = self.data_ptrs[buf.data_ptr()]
+        self.ctx.check(lib().dsuf_ep_allgather_cols_bf16(self.ctx.h, self.ctx.stream(), ptrs, self.flag_ptrs, self.rank, self.world,
+                                                         rows, cols, self.state.data_ptr(), out.data_ptr()))
         return out
 
     def combine(self, plan, yrows, shared, partial, out):

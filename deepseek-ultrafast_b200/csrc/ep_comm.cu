@@ -28,6 +28,7 @@ struct EpcArgs {
     DevStatus* status;
     long long n_vec;                   // n_elems / 8
     int rank, world;
+    int gather_vec, row_vec;           // all-gather of column slices: 16-byte vectors per slice / per row (0: all-reduce)
     long long wait_ticks;              // clock64 budget of the wait for the peers' announcements
     uint32_t* state;                   // local: [0] calls completed (the epoch lives on the device so that a captured
                                        // graph advances it on every replay), [1] CTAs finished in this call
@@ -82,6 +83,13 @@ __global__ void __launch_bounds__(EPC_THREADS) ep_allreduce_kernel(const EpcArgs
     __syncthreads();
     // ---- sum in rank order; all of an element's loads are issued before the first add (peer latency, not bandwidth,
     //      bounds this kernel) ----
+    if (a.gather_vec) {
+        // all-gather of column slices: every element has one owner (the rank that computed that column range)
+        for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
+            const int owner = (int)((i % a.row_vec) / a.gather_vec);
+            *(uint4*)(a.out + i * 8) = ld_relaxed_sys_v4(a.data[owner] + i);
+        }
+    } else
     for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
         uint4 v[EPC_MAX_WORLD];
 #pragma unroll
@@ -240,6 +248,19 @@ extern "C" int32_t dsuf_ep_allreduce_bf16(dsuf_ctx* ctx, void* stream, const uin
     int rc = fill_epc(ctx, a, peer_data, peer_flags, rank, world, n_elems, state, out);
     if (rc) return rc;
     if (n_elems == 0) return DSUF_OK;
+    return launch(ctx, (cudaStream_t)stream, ep_allreduce_kernel, dim3(EPC_CTAS), dim3(EPC_THREADS), 0, a);
+}
+
+extern "C" int32_t dsuf_ep_allgather_cols_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags,
+                                               int32_t rank, int32_t world, int32_t rows, int32_t cols, uint64_t state, uint64_t out) {
+    if (!ctx) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, rows >= 0 && cols > 0 && world >= 1 && cols % (8 * world) == 0, "ep_allgather_cols: cols (%d) must be a multiple of 8 * world", cols);
+    EpcArgs a;
+    int rc = fill_epc(ctx, a, peer_data, peer_flags, rank, world, (int64_t)rows * cols, state, out);
+    if (rc) return rc;
+    a.row_vec = cols / 8;
+    a.gather_vec = cols / world / 8;
+    if (rows == 0) return DSUF_OK;
     return launch(ctx, (cudaStream_t)stream, ep_allreduce_kernel, dim3(EPC_CTAS), dim3(EPC_THREADS), 0, a);
 }
 

@@ -3,9 +3,9 @@ FFN (route -> plan -> gather+quant -> gate/up+SwiGLU -> quant -> down -> unpermu
 
 Single GPU: every expert is local.  Several GPUs (one process each, torch.distributed over NCCL): experts are
 sharded world-ways (rank r owns experts [r*E/W, (r+1)*E/W)), tokens are data parallel (rank r owns T/W of them);
-per layer the exchanges are two all-reduces of the [tokens][hidden] bf16 activations (ep.py): the tensor-parallel sum
-of the K-sharded dense projection, which also delivers every token row to every expert owner (dispatch), and the sum of
-the per-rank expert outputs (combine), which also is the next layer's gathered input.
+per layer the exchanges are an all-gather of the column slices of the output-sharded dense projection, which delivers
+every token row to every expert owner (dispatch), and the sum of the per-rank expert outputs (combine), which also is the
+next layer's input (ep.py).
 The reference is tensor-parallel only and combines with its own push all-reduce (cu/comm.cu:134-279); the
 expert-parallel exchange here is this library's design.
 """
@@ -97,16 +97,16 @@ class _KernelCompute:
     def __init__(self, stack, l):
         self.s, self.l = stack, l
 
-    def dense_partial(self, x_all):
+    def dense_slice(self, x_all):
         s, w = self.s, self.s.dense[self.l]
         ctx = s.ctx
-        k0, k1 = s.kslice
-        act_quant(ctx, w.mode, x_all[:, k0:k1], s.xq, s.xs)
+        n0, n1 = s.nslice
+        act_quant(ctx, w.mode, x_all, s.xq, s.xs)
         T = x_all.shape[0]
         slab = 64 if ctx.tcgen05 else 16
         for r0 in range(0, T, slab):
             m = min(slab, T - r0)
-            gemm_fp8(ctx, w, s.xq[r0:r0 + m], s.xs[r0:r0 + m], m, s.partial[r0:r0 + m])
+            gemm_fp8(ctx, w, s.xq[r0:r0 + m], s.xs[r0:r0 + m], m, s.partial[r0:r0 + m, n0:n1])
         return s.partial
 
     def route(self, h_all):
@@ -134,19 +134,19 @@ class EpLayerStack:
         self.ctx, self.cfg, self.rank, self.world = ctx, cfg, rank, world
         self.xch = ep.Exchange(dist, rank, world)
         H, I, E, T = cfg.hidden, cfg.inter, cfg.n_experts, cfg.tokens
-        self.kslice = ep.shard_bounds(H, world, rank)
-        if (self.kslice[1] - self.kslice[0]) % 128:
+        self.nslice = ep.shard_bounds(H, world, rank)   # this rank's output columns of the dense projection
+        if (self.nslice[1] - self.nslice[0]) % 128:
             raise ValueError("hidden / world must be a multiple of 128")
         self.e_lo, e_hi = ep.shard_bounds(E, world, rank)
         self.t0, self.t1 = ep.shard_bounds(T, world, rank)
-        n_loc, kloc = e_hi - self.e_lo, self.kslice[1] - self.kslice[0]
+        n_loc, nloc_d = e_hi - self.e_lo, self.nslice[1] - self.nslice[0]
         self.dense, self.moe, self.logits = [], [], []
         for l in range(cfg.layers):
-            # the shards of ONE set of random-init weights (the seeds of LayerStack): the dense weight's K-slice and the
-            # experts at their global ids, so the W-rank result is comparable with the single-GPU one
+            # the shards of ONE set of random-init weights (the seeds of LayerStack): the dense weight's rows of this rank's
+            # output columns and the experts at their global ids, so the W-rank result is comparable with the single-GPU one
             base = cfg.seed + 1000 * l
-            tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, H, cfg.std, base + 1, dev, k_slice=self.kslice)
-            self.dense.append(Weight(ctx, 0, cfg.dense_mode, H, kloc, 1, False, tiles, sds))
+            tiles, sds = synth.fp8_dense(t, cfg.dense_mode == MODE_MX, H, H, cfg.std, base + 1, dev, n_slice=self.nslice)
+            self.dense.append(Weight(ctx, 0, cfg.dense_mode, nloc_d, H, 1, False, tiles, sds))
             w13 = synth.fp4_experts(t, n_loc, 2 * I, H, cfg.std, base + 2, True, dev, first_expert=self.e_lo)
             w2 = synth.fp4_experts(t, n_loc, H, I, cfg.std, base + 3, False, dev, first_expert=self.e_lo)
             W13 = Weight.experts_fp4_packed(ctx, w13, 2 * I, H, n_loc, True)
@@ -155,8 +155,8 @@ class EpLayerStack:
             g = t.Generator(device=dev).manual_seed(cfg.seed + 1000 * l + 4)   # same logits on every rank
             self.logits.append(t.randn(T, E, generator=g, device=dev, dtype=t.float32))
         blk = 32 if cfg.dense_mode == MODE_MX else 128
-        self.xq = t.empty((T, kloc), dtype=t.uint8, device=dev)
-        self.xs = t.empty((T, kloc // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
+        self.xq = t.empty((T, H), dtype=t.uint8, device=dev)
+        self.xs = t.empty((T, H // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
         # The two per-layer sums run as the library's peer-memory all-reduce when the partial buffers can be mapped
         # by every rank (torch symmetric memory); DSUF_EP_PEER=0 or a failed mapping falls back to NCCL.
         self.peer, self.fuse_combine, self.peer_error = None, False, None
@@ -175,6 +175,9 @@ class EpLayerStack:
             if int(agreed.item()) == 0:
                 self.peer = None
         if self.peer is not None:
+            # the ranks of this stack run in lock step (one captured graph each, replayed together): a peer that is half a
+            # second late is a failed peer, and the kernels report it instead of waiting for the library's default 2 s
+            ctx.set_wait_budget_us(500000)
             self.partial = self.peer.buffer((T, H))
             self.y_part = [self.peer.buffer((T, H)) for _ in range(2)]
             self.xch.peer = self.peer

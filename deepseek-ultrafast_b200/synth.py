@@ -60,16 +60,19 @@ def fp4_experts(torch, n_experts, n, k, std, seed, gate_up, device, first_expert
     return out
 
 
-def fp8_dense(torch, mode_mx, n, k, std, seed, device, k_slice=None):
+def fp8_dense(torch, mode_mx, n, k, std, seed, device, k_slice=None, n_slice=None):
     """Dense weight [n][k] ~ N(0,std) -> (tile records u8, ds scales f32 [n/128][k/128] or None).
     ``k_slice`` = (k0, k1), multiples of 128: only columns k0..k1 of the same [n][k] weight are quantized and packed (the
     K-shard of a tensor-parallel rank; block scales do not straddle a multiple of 128, so the shard's codes and scales
-    are those of the whole weight)."""
+    are those of the whole weight); ``n_slice`` = (n0, n1) likewise selects rows."""
     gen = torch.Generator(device=device).manual_seed(seed)
     w = (torch.randn(n, k, generator=gen, device=device, dtype=torch.float32) * std).bfloat16().float()
     if k_slice is not None:
         w = w[:, k_slice[0]:k_slice[1]].contiguous()
         k = k_slice[1] - k_slice[0]
+    if n_slice is not None:      # rows n0..n1 (multiples of 128): the shard of a rank that owns those OUTPUT columns
+        w = w[n_slice[0]:n_slice[1]].contiguous()
+        n = n_slice[1] - n_slice[0]
     rt, kt = n // 128, k // 128
     if mode_mx:
         wb = w.view(n // 32, 32, k // 32, 32)

@@ -252,6 +252,15 @@ size_t dsuf_ep_flag_bytes(int32_t world);
 int32_t dsuf_ep_allreduce_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
                                int32_t world, int64_t n_elems, uint64_t state, uint64_t out);
 
+/* All-gather of column slices over the same buffers, flags and hand-shake: rank r has written columns
+ * [r * cols / world, (r + 1) * cols / world) of every row of ITS buffer peer_data[r] (bf16 [rows][cols]); out [rows][cols]
+ * receives every slice from its owner.  This is the exchange after a tensor-parallel projection whose OUTPUT is sharded
+ * (each rank computes complete dot products for its columns, so nothing is summed across ranks and the result equals the
+ * unsharded projection bit for bit); each rank pulls (world - 1) / world of the rows' bytes instead of world - 1 times
+ * all of them.  cols % (8 * world) == 0.  The reference, tensor-parallel over K, has no counterpart (cu/comm.cu sums). */
+int32_t dsuf_ep_allgather_cols_bf16(dsuf_ctx* ctx, void* stream, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
+                                    int32_t world, int32_t rows, int32_t cols, uint64_t state, uint64_t out);
+
 /* Combine fused with its exchange, one kernel: dsuf_moe_unpermute's sum of every token's top-k expert rows on this
  * rank (pair_row from the plan, yrows fp32 [rows][h] from dsuf_moe_w2, optional bf16 `shared` rows added by this rank:
  * pass them on ONE rank), written into this rank's partial buffer peer_data[rank], then dsuf_ep_allreduce_bf16's

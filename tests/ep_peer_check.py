@@ -58,6 +58,18 @@ def main():
         ar.combine(plan, yrows, None, bufs[it & 1], out)
         torch.cuda.synchronize()
         ok = ok and bool(((out.float() - ref).abs() <= mag * 2.0 ** -7 + 1e-5).all()) and ctx.status().code == 0
+    # all-gather of column slices: rank r fills its own columns, everybody ends up with the same full rows, bit for bit
+    gg = torch.Generator(device="cuda").manual_seed(4242)      # same on every rank
+    full = torch.randn(rows, width, generator=gg, device="cuda").bfloat16()
+    wsl = width // world
+    for it in range(3):
+        b = bufs[it & 1]
+        b.zero_()
+        b[:, rank * wsl:(rank + 1) * wsl] = full[:, rank * wsl:(rank + 1) * wsl]
+        out.zero_()
+        ar.gather_cols(b, out)
+        torch.cuda.synchronize()
+        ok = ok and bool((out.view(torch.uint16) == full.view(torch.uint16)).all()) and ctx.status().code == 0
     dist.barrier()
     torch.cuda.synchronize()
     print(f"rank {rank}: {'ok' if ok else 'MISMATCH'}", flush=True)
