@@ -38,6 +38,10 @@ class PlanStruct(C.Structure):
                 ("n_exp", C.c_int32), ("tile_rows", C.c_int32), ("max_tiles", C.c_int32)]
 
 
+class TensorInfo(C.Structure):
+    _fields_ = [("dtype", C.c_char * 16), ("rank", C.c_int32), ("shape", C.c_int64 * 8), ("data", C.c_void_p), ("nbytes", C.c_size_t)]
+
+
 class DevStatus(C.Structure):
     _fields_ = [("code", C.c_int32), ("kernel", C.c_int32), ("cta", C.c_int32), ("where", C.c_int32)]
 
@@ -54,11 +58,19 @@ ABI = {
     "dsuf_ctx_set_wait_budget_us": (C.c_int32, [C.c_void_p, C.c_int64]),
     "dsuf_ctx_set_prenorm_rsqrt": (C.c_int32, [C.c_void_p, C.c_int32]),
     "dsuf_ctx_set_dense_ksplit": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "dsuf_ctx_set_stage_pairs": (C.c_int32, [C.c_void_p, C.c_int32]),
     "dsuf_quant_fp8_weight_host": (C.c_int32, [C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_quant_fp4_weight_host": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_packed_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "dsuf_pack_fp8_weight": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "dsuf_pack_fp4_weight": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "dsuf_ckpt_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "dsuf_ckpt_close": (C.c_int32, [C.c_void_p]),
+    "dsuf_ckpt_last_error": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_size_t]),
+    "dsuf_ckpt_count": (C.c_int64, [C.c_void_p]),
+    "dsuf_ckpt_tensor": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(TensorInfo)]),
+    "dsuf_ckpt_load_fp8_dense": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "dsuf_ckpt_load_fp4_experts": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_weight_create": (C.c_int32, [C.c_void_p, C.POINTER(WeightDesc), C.POINTER(C.c_void_p)]),
     "dsuf_weight_destroy": (C.c_int32, [C.c_void_p]),
     "dsuf_row_sumsq": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
@@ -84,6 +96,9 @@ ABI = {
                                    C.c_int32, C.c_float, C.c_uint64, C.c_uint64]),
     "dsuf_moe_plan_scratch_ints": (C.c_size_t, [C.c_int32, C.c_int32]),
     "dsuf_moe_permute_plan": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.POINTER(PlanStruct)]),
+    "dsuf_moe_route_plan_gather": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
+                                               C.c_float, C.c_uint64, C.c_uint64, C.c_int32, C.POINTER(PlanStruct), C.c_int32, C.c_uint64,
+                                               C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
     "dsuf_moe_gather_quant_prenorm": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                                   C.c_int32, C.c_void_p, C.c_uint64, C.c_uint64, C.c_float, C.c_uint64, C.c_uint64]),
     "dsuf_moe_gather_quant": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
@@ -161,6 +176,74 @@ def pack_fp4_weight(codes, scales, gate_up):
     return out
 
 
+class Checkpoint:
+    """Checkpoint (crates/model/src/st.rs:17-106) + the weight loaders (crates/engine/src/weights.rs:254-276, 421-446):
+    a directory of .safetensors files (or one file), read-only mapped; tensors by name, FP8 dense weights and FP4 experts
+    as this library's tile records."""
+
+    def __init__(self, path):
+        h = C.c_void_p()
+        rc = lib().dsuf_ckpt_open(os.fsencode(path), C.byref(h))
+        self.h = h
+        if rc:
+            msg = self._err()
+            self.close()
+            raise DsufError(rc, msg)
+
+    def _err(self):
+        buf = C.create_string_buffer(512)
+        lib().dsuf_ckpt_last_error(self.h, buf, 512)
+        return buf.value.decode()
+
+    def _check(self, rc):
+        if rc:
+            raise DsufError(rc, self._err())
+
+    def close(self):
+        if self.h:
+            lib().dsuf_ckpt_close(self.h)
+            self.h = None
+
+    def __len__(self):
+        return int(lib().dsuf_ckpt_count(self.h))
+
+    def tensor(self, name):
+        """(dtype string, shape tuple, uint8 numpy view of the bytes inside the mapping)."""
+        ti = TensorInfo()
+        self._check(lib().dsuf_ckpt_tensor(self.h, name.encode(), C.byref(ti)))
+        raw = np.ctypeslib.as_array(C.cast(ti.data, C.POINTER(C.c_uint8)), shape=(ti.nbytes,)) if ti.nbytes else np.empty(0, np.uint8)
+        return ti.dtype.decode(), tuple(ti.shape[i] for i in range(ti.rank)), raw
+
+    def fp8_dense_tiles(self, name, rows=None):
+        """Loader::fp8: MX tile records (host numpy) of `{name}.weight` / `{name}.scale`, optionally rows [r0, r1)."""
+        _, shape, _ = self.tensor(name + ".weight")
+        n, k = shape
+        r0, r1 = rows if rows is not None else (0, n)
+        out = np.empty(lib().dsuf_packed_bytes(FMT_FP8, MODE_MX, r1 - r0, k), np.uint8)
+        self._check(lib().dsuf_ckpt_load_fp8_dense(self.h, name.encode(), n, k, r0, r1, _np_ptr(out)))
+        return out, r1 - r0, k
+
+    def fp4_expert_tiles(self, prefix, e0, e1, dim, inter):
+        """Experts e0 .. e1-1 of `{prefix}.ffn.experts.{e}`: (w13 records, w2 records) as host numpy arrays."""
+        per13 = lib().dsuf_packed_bytes(FMT_FP4, MODE_MX, 2 * inter, dim)
+        per2 = lib().dsuf_packed_bytes(FMT_FP4, MODE_MX, dim, inter)
+        o13, o2 = np.empty((e1 - e0) * per13, np.uint8), np.empty((e1 - e0) * per2, np.uint8)
+        self._check(lib().dsuf_ckpt_load_fp4_experts(self.h, prefix.encode(), e0, e1, dim, inter, _np_ptr(o13), _np_ptr(o2)))
+        return o13, o2
+
+    def load_fp8_dense(self, ctx, name, rows=None):
+        """`{name}` as a device Weight (MX geometry, the checkpoint's own)."""
+        tiles, n, k = self.fp8_dense_tiles(name, rows)
+        return Weight(ctx, FMT_FP8, MODE_MX, n, k, 1, False, ctx.torch.from_numpy(tiles).to(ctx.device))
+
+    def load_experts(self, ctx, prefix, e0, e1, dim, inter):
+        """(W13, W2) device Weights of the experts e0 .. e1-1 (an expert-parallel rank passes its own range)."""
+        o13, o2 = self.fp4_expert_tiles(prefix, e0, e1, dim, inter)
+        t = ctx.torch
+        return (Weight.experts_fp4_packed(ctx, t.from_numpy(o13).to(ctx.device), 2 * inter, dim, e1 - e0, True),
+                Weight.experts_fp4_packed(ctx, t.from_numpy(o2).to(ctx.device), dim, inter, e1 - e0, False))
+
+
 # ------------------------------------------------------------------ device side
 class Ctx:
     """dsuf_ctx wrapper: one per device (Device::new + ops::hw(), crates/cuda/src/lib.rs:52, ops.rs:205)."""
@@ -186,6 +269,10 @@ class Ctx:
         """True: tcgen05 streaming kernels for decode shapes; False: the mma.sync streaming kernels."""
         self.check(lib().dsuf_ctx_set_decode_path(self.h, 1 if tcgen05 else 0))
         self.tcgen05 = bool(tcgen05)
+
+    def set_stage_pairs(self, enabled):
+        """Two tile records per ring stage in the decode expert GEMMs (default on)."""
+        self.check(lib().dsuf_ctx_set_stage_pairs(self.h, 1 if enabled else 0))
 
     def set_dense_ksplit(self, enabled):
         """Cluster K-split for dense decode GEMVs with few row tiles (default on)."""
@@ -435,6 +522,14 @@ def moe_gather_quant(ctx, mode, plan, x, xq, xs):
                                           C.byref(plan.c), xq.data_ptr(), xs.data_ptr()))
 
 
+def moe_route_plan_gather(ctx, score_fn, scores, bias, topk, route_scale, ids, w, e_lo, plan, mode, x, xq, xs):
+    """dsuf_moe_route_plan_gather: router + permute plan + gather/quant of a decode-size batch in one launch."""
+    tok, h = x.shape
+    ctx.check(lib().dsuf_moe_route_plan_gather(ctx.h, ctx.stream(), score_fn, scores.data_ptr(), bias.data_ptr() if bias is not None else 0,
+                                               tok, scores.shape[1], topk, route_scale, ids.data_ptr(), w.data_ptr(), e_lo, C.byref(plan.c),
+                                               mode, x.data_ptr(), x.stride(0), h, xq.data_ptr(), xs.data_ptr()))
+
+
 def moe_gather_quant_prenorm(ctx, mode, plan, x, norm_w, eps, xq, xs, sumsq=None):
     """moe_gather_quant with RMS pre-normalisation (cu/tcmoe.cu:88): bf16(norm_w * (x * rs)) quantised once per token."""
     tok, h = x.shape
@@ -471,6 +566,7 @@ class MoeLayer:
         dev = ctx.device
         self.ctx, self.w13, self.w2, self.tokens, self.topk, self.act_mode = ctx, w13, w2, tokens, topk, act_mode
         self.e_lo, self.swiglu_limit = e_lo, swiglu_limit
+        self.fuse_front = True   # decode-size batches: router + plan + gather/quant in one launch (when forward gets `route`)
         self.h, self.inter = w13.k, w13.n // 2
         if tile_rows is None:
             tile_rows = 8
@@ -485,15 +581,24 @@ class MoeLayer:
         self.act_s = t.zeros((p, self.inter // blk), dtype=sdt, device=dev)
         self.yrows = t.zeros((p, self.h), dtype=t.float32, device=dev)
 
-    def forward(self, x, ids, w, out, shared=None, events=None, combine=None):
+    def forward(self, x, ids, w, out, shared=None, events=None, combine=None, route=None):
         """``events``: optional list; (start, end) CUDA events around the gate/up kernel are appended (bench timing).
         ``combine``: optional callable (plan, yrows, shared) -> tensor that replaces the local unpermute (the
-        expert-parallel stack passes the kernel that sums locally and across ranks in one launch)."""
+        expert-parallel stack passes the kernel that sums locally and across ranks in one launch).
+        ``route``: optional (score_fn, scores [t][experts], bias, route_scale): the router runs here and writes ``ids`` / ``w``;
+        decode-size batches (at most 1024 pairs) take one launch for router + plan + gather/quant."""
         ctx, plan = self.ctx, self.plan
         if events is None:
             events = getattr(self, "events", None)
-        moe_perm(ctx, plan, ids, w, self.e_lo)
-        moe_gather_quant(ctx, self.act_mode, plan, x, self.xq, self.xs)
+        if route is not None and plan.p <= 1024 and plan.p > 0 and self.fuse_front:
+            score_fn, scores, bias, scale = route
+            moe_route_plan_gather(ctx, score_fn, scores, bias, self.topk, scale, ids, w, self.e_lo, plan, self.act_mode, x, self.xq, self.xs)
+        else:
+            if route is not None:
+                score_fn, scores, bias, scale = route
+                moe_route_tokens(ctx, score_fn, scores, bias, self.topk, scale, ids=ids, w=w)
+            moe_perm(ctx, plan, ids, w, self.e_lo)
+            moe_gather_quant(ctx, self.act_mode, plan, x, self.xq, self.xs)
         if events is not None:
             # inside a stream capture the events must be recorded as graph nodes of their own (external events), so that
             # every replay of the graph stamps them

@@ -32,6 +32,7 @@ int32_t dsuf_ctx_create(int32_t device, dsuf_ctx** out) {
     ctx->clock_khz = prop.clockRate > 0 ? prop.clockRate : 1965000;
     ctx->xchg_wait_ticks = WAIT_BUDGET_TICKS;
     ctx->use_kslices = 1;
+    ctx->use_pairs = 1;
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -69,6 +70,12 @@ int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled) {
 int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05) {
     if (!ctx) return DSUF_E_BADARG;
     ctx->use_tc = tcgen05 ? 1 : 0;
+    return DSUF_OK;
+}
+
+int32_t dsuf_ctx_set_stage_pairs(dsuf_ctx* ctx, int32_t enabled) {
+    if (!ctx) return DSUF_E_BADARG;
+    ctx->use_pairs = enabled ? 1 : 0;
     return DSUF_OK;
 }
 
@@ -252,6 +259,27 @@ int32_t dsuf_moe_gather_quant(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_
     DSUF_REQUIRE(ctx, x && xq_out && xs_out && (x & 15) == 0 && (xq_out & 15) == 0, "gather_quant: null or misaligned pointer");
     return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, t, h, (void*)xq_out, (void*)xs_out,
                             (const int*)plan->pair_row, topk, 0);
+}
+
+int32_t dsuf_moe_route_plan_gather(dsuf_ctx* ctx, void* stream, int32_t score_fn, uint64_t scores, uint64_t bias, int32_t t,
+                                   int32_t n_exp_all, int32_t topk, float route_scale, uint64_t ids_out, uint64_t w_out, int32_t e_lo,
+                                   const dsuf_moe_plan* plan, int32_t mode, uint64_t x, int32_t ldx, int32_t h, uint64_t xq_out,
+                                   uint64_t xs_out) {
+    if (!ctx) return DSUF_E_BADARG;
+    int rc = check_plan(ctx, plan);
+    if (rc) return rc;
+    DSUF_REQUIRE(ctx, n_exp_all >= 1 && n_exp_all <= 512, "route_plan_gather: n_exp_all (%d) must be in 1..512", n_exp_all);
+    DSUF_REQUIRE(ctx, topk >= 1 && topk <= 16 && topk <= n_exp_all, "route_plan_gather: topk (%d) must be in 1..min(16, n_exp_all)", topk);
+    DSUF_REQUIRE(ctx, score_fn >= 0 && score_fn <= 2, "route_plan_gather: unknown score_fn %d", score_fn);
+    DSUF_REQUIRE(ctx, t >= 0 && (long long)t * topk == plan->p, "route_plan_gather: t*topk != plan.p");
+    DSUF_REQUIRE(ctx, plan->p <= 1024, "route_plan_gather: at most 1024 (token, expert) pairs per call, got %d: use the separate entries", plan->p);
+    DSUF_REQUIRE(ctx, mode == DSUF_MODE_MX || mode == DSUF_MODE_DS, "route_plan_gather: unknown mode %d", mode);
+    DSUF_REQUIRE(ctx, h > 0 && h % 128 == 0 && ldx >= h && ldx % 8 == 0, "route_plan_gather: h (%d) must be a multiple of 128, ldx a multiple of 8", h);
+    if (t == 0) return launch_plan(ctx, (cudaStream_t)stream, nullptr, nullptr, e_lo, plan);
+    DSUF_REQUIRE(ctx, scores && ids_out && w_out && x && xq_out && xs_out && (x & 15) == 0 && (xq_out & 15) == 0,
+                 "route_plan_gather: null or misaligned pointer");
+    return launch_front(ctx, (cudaStream_t)stream, score_fn, (const float*)scores, (const float*)bias, t, n_exp_all, topk, route_scale,
+                        (int*)ids_out, (float*)w_out, e_lo, plan, mode, (const void*)x, ldx, h, (void*)xq_out, (void*)xs_out);
 }
 
 int32_t dsuf_moe_gather_quant_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t t, int32_t h,

@@ -22,6 +22,7 @@ struct dsuf_ctx {
     int smem_optin;
     int use_pdl;                   // launch with programmatic stream serialization
     int use_tc;                    // decode shapes on the tcgen05 streaming kernel (1) or the mma.sync one (0)
+    int use_pairs;                 // decode expert GEMMs: two tile records per ring stage where K allows (default on)
     int use_kslices;               // dense decode GEMV: cluster K-split where it pays (default on)
     int prenorm_approx;            // RMS pre-normalisation with the approximate rsqrt instruction, as the reference's kernels
     int clock_khz;                 // SM clock rate the wait budgets are converted with
@@ -109,6 +110,9 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
                       const void* xq, const void* xs, float swiglu_limit, void* out, int ldo);
 int launch_route(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp,
                  int topk, float route_scale, int* ids, float* w);
+int launch_front(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp_all,
+                 int topk, float route_scale, int* ids, float* w, int e_lo, const dsuf_moe_plan* plan, int mode, const void* x, int ldx,
+                 int h, void* xq, void* xs);
 int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float* w, int e_lo, const dsuf_moe_plan* plan);
 int launch_unpermute(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
                      int t, int topk, int h, void* out, int ldo);

@@ -9,20 +9,18 @@
 // by a stable counting sort (one fused launch for decode-sized plans, three phases that scale over CTAs above
 // that), and every consumer (decode or prefill) reads it.
 #include "internal.h"
+#include "quant_core.cuh"
 
 namespace dsuf {
 
 // ---------------------------------------------------------------- router
 constexpr int ROUTE_MAX_PER_LANE = 16;  // n_exp <= 512
 
-__global__ void __launch_bounds__(256) route_kernel(int score_fn, const float* scores, const float* bias, int t, int n_exp,
-                                                    int topk, float route_scale, int* ids, float* w) {
-    pdl_wait();
-    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
-    const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (tok >= t) return;
+// One token by one warp: top-k of score + bias (ties to the lower id), weights = score / sum of the picked scores * scale.
+// ids_out / w_out point at the token's topk entries (global or shared memory).
+DSUF_DEV void route_one_token(int score_fn, const float* s, const float* bias, int n_exp, int topk, float route_scale, int lane,
+                              int* ids_out, float* w_out) {
     float sc[ROUTE_MAX_PER_LANE];
-    const float* s = scores + (size_t)tok * n_exp;
     float mx = -INFINITY;
 #pragma unroll
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
@@ -87,9 +85,19 @@ __global__ void __launch_bounds__(256) route_kernel(int score_fn, const float* s
     }
     if (lane < topk) {
         const float v = topk > 1 ? __fdiv_rn(myw, wsum + 1e-20f) : myw;
-        ids[(size_t)tok * topk + lane] = myid;
-        w[(size_t)tok * topk + lane] = v * route_scale;
+        ids_out[lane] = myid;
+        w_out[lane] = v * route_scale;
     }
+}
+
+__global__ void __launch_bounds__(256) route_kernel(int score_fn, const float* scores, const float* bias, int t, int n_exp,
+                                                    int topk, float route_scale, int* ids, float* w) {
+    pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+    const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (tok >= t) return;
+    route_one_token(score_fn, scores + (size_t)tok * n_exp, bias, n_exp, topk, route_scale, lane, ids + (size_t)tok * topk,
+                    w + (size_t)tok * topk);
 }
 
 int launch_route(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp,
@@ -228,15 +236,16 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_place_kernel(const PlanArgs a
 }
 
 
-// Decode-sized plans (all pairs fit one block): histogram, scans, tile list and placement in ONE launch.
-// Same result as the three-phase path, bit for bit (the order inside an expert is the pair order either way).
-__global__ void __launch_bounds__(PLAN_BLOCK) plan_small_kernel(const PlanArgs a) {
-    pdl_wait();
-    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
-    __shared__ unsigned short warp_hist[32][PLAN_MAX_EXP];
-    __shared__ int s_off[PLAN_MAX_EXP + 1], s_wa[32], s_wb[32];
+// Decode-sized plans (all pairs fit one block of PLAN_BLOCK threads): histogram, scans, tile list and placement in one
+// pass.  Same result as the three-phase path, bit for bit (the order inside an expert is the pair order either way).
+// `write` = this CTA stores the plan to global memory; `s_pair_row` (optional, shared) receives pair_row as well.
+struct PlanSmem {
+    unsigned short warp_hist[32][PLAN_MAX_EXP];
+    int off[PLAN_MAX_EXP + 1], wa[32], wb[32];
+};
+DSUF_DEV void plan_small_body(const PlanArgs& a, PlanSmem& sm, bool write, int* s_pair_row) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    for (int i = tid; i < 32 * PLAN_MAX_EXP; i += PLAN_BLOCK) (&warp_hist[0][0])[i] = 0;
+    for (int i = tid; i < 32 * PLAN_MAX_EXP; i += PLAN_BLOCK) (&sm.warp_hist[0][0])[i] = 0;
     __syncthreads();
     int e = -1;
     if (tid < a.p) {
@@ -245,27 +254,29 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_small_kernel(const PlanArgs a
     }
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
-    if (e >= 0 && rank_in_warp == 0) warp_hist[warp][e] = (unsigned short)__popc(peers);
+    if (e >= 0 && rank_in_warp == 0) sm.warp_hist[warp][e] = (unsigned short)__popc(peers);
     __syncthreads();
     int cnt = 0;
     if (tid < a.n_exp) {
         for (int wv = 0; wv < 32; ++wv) {
-            const int c = warp_hist[wv][tid];
-            warp_hist[wv][tid] = (unsigned short)cnt;
+            const int c = sm.warp_hist[wv][tid];
+            sm.warp_hist[wv][tid] = (unsigned short)cnt;
             cnt += c;
         }
     }
     const int ntile = (cnt + a.tile_rows - 1) / a.tile_rows;
     int off, toff, rows, tiles_total;
-    block_exscan2(cnt, ntile, off, toff, rows, tiles_total, s_wa, s_wb);
+    block_exscan2(cnt, ntile, off, toff, rows, tiles_total, sm.wa, sm.wb);
     if (tid < a.n_exp) {
-        s_off[tid] = off;
-        a.expert_off[tid] = off;
-        int ti = toff;
-        for (int r0 = 0; r0 < cnt; r0 += a.tile_rows, ++ti)
-            if (ti < a.max_tiles) a.tiles[ti] = make_int4(tid, off + r0, min(a.tile_rows, cnt - r0), 0);
+        sm.off[tid] = off;
+        if (write) {
+            a.expert_off[tid] = off;
+            int ti = toff;
+            for (int r0 = 0; r0 < cnt; r0 += a.tile_rows, ++ti)
+                if (ti < a.max_tiles) a.tiles[ti] = make_int4(tid, off + r0, min(a.tile_rows, cnt - r0), 0);
+        }
     }
-    if (tid == 0) {
+    if (tid == 0 && write) {
         a.expert_off[a.n_exp] = rows;
         a.ntiles[0] = tiles_total <= a.max_tiles ? tiles_total : a.max_tiles;
         a.ntiles[1] = rows;
@@ -273,13 +284,94 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_small_kernel(const PlanArgs a
     }
     __syncthreads();
     if (tid < a.p) {
-        if (e < 0) {
-            a.pair_row[tid] = -1;
-        } else {
-            const int row = s_off[e] + warp_hist[warp][e] + rank_in_warp;
-            a.row_pair[row] = tid;
+        const int row = e < 0 ? -1 : sm.off[e] + sm.warp_hist[warp][e] + rank_in_warp;
+        if (s_pair_row) s_pair_row[tid] = row;
+        if (write) {
             a.pair_row[tid] = row;
-            a.row_w[row] = a.w[tid];
+            if (row >= 0) {
+                a.row_pair[row] = tid;
+                a.row_w[row] = a.w[tid];
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(PLAN_BLOCK) plan_small_kernel(const PlanArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+    __shared__ PlanSmem sm;
+    plan_small_body(a, sm, true, nullptr);
+}
+
+// Decode front end in ONE launch: router, permute plan and gather + quant for batches of at most 1024 (token, expert)
+// pairs -- the counterpart of the routing the reference runs inside its decode MoE launch (route_plan,
+// cu/gemv.cu:715-776).  Every CTA routes all tokens and builds the whole plan in shared memory (64 x 256 scores and
+// 512 pairs at the decode size: microseconds, and no second and third launch); CTA 0 stores ids, weights and the plan;
+// CTA b quantizes token rows b, b + gridDim.x, ... and writes each to its top-k permuted rows.
+struct FrontArgs {
+    PlanArgs plan;          // ids / w point at the routing outputs in global memory (written by CTA 0)
+    const float* scores;    // [t][n_exp_all]
+    const float* bias;      // [n_exp_all] or null
+    int score_fn, t, n_exp_all, topk;
+    float route_scale;
+    int* ids_out;           // [t][topk]
+    float* w_out;
+    const bf16* x;          // [t][ldx]
+    int ldx, h;
+    uint8_t* xq;            // [p][h]
+    void* xs;               // MX u8 [p][h/32], DS f32 [p][h/128]
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(PLAN_BLOCK) moe_front_kernel(const FrontArgs f) {
+    pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+    __shared__ PlanSmem sm;
+    __shared__ int s_ids[PLAN_BLOCK], s_pair_row[PLAN_BLOCK];
+    __shared__ float s_w[PLAN_BLOCK];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool first = blockIdx.x == 0;
+    for (int tok = warp; tok < f.t; tok += PLAN_BLOCK / 32)
+        route_one_token(f.score_fn, f.scores + (size_t)tok * f.n_exp_all, f.bias, f.n_exp_all, f.topk, f.route_scale, lane,
+                        s_ids + tok * f.topk, s_w + tok * f.topk);
+    __syncthreads();
+    if (first && tid < f.plan.p) {
+        f.ids_out[tid] = s_ids[tid];
+        f.w_out[tid] = s_w[tid];
+    }
+    PlanArgs pa = f.plan;
+    pa.ids = s_ids;
+    pa.w = s_w;
+    plan_small_body(pa, sm, first, s_pair_row);
+    __syncthreads();
+    constexpr int LANES = MODE == DSUF_MODE_MX ? 4 : 16;
+    for (int tok = blockIdx.x; tok < f.t; tok += gridDim.x) {
+        for (int base = 0; base < f.h; base += PLAN_BLOCK * 8) {   // every thread makes every pass (the quantizer shuffles)
+            const int k0 = base + tid * 8;
+            const bool live = k0 < f.h;   // h % 128 == 0: a scale block is live or dead as a whole
+            float v[8];
+            if (live) {
+                const uint4 raw = *(const uint4*)(f.x + (size_t)tok * f.ldx + k0);
+                const bf16* hh = (const bf16*)&raw;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(hh[e]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = 0.f;
+            }
+            uint2 codes;
+            float sc;
+            quant8<MODE>(v, codes, sc);
+            if (!live) continue;
+            for (int j = 0; j < f.topk; ++j) {
+                const int dst = s_pair_row[tok * f.topk + j];
+                if (dst < 0) continue;
+                *(uint2*)(f.xq + (size_t)dst * f.h + k0) = codes;
+                if ((tid & (LANES - 1)) == 0) {
+                    if (MODE == DSUF_MODE_MX) ((uint8_t*)f.xs)[(size_t)dst * (f.h >> 5) + (k0 >> 5)] = (uint8_t)(__float_as_uint(sc) >> 23);
+                    else ((float*)f.xs)[(size_t)dst * (f.h >> 7) + (k0 >> 7)] = sc;
+                }
+            }
         }
     }
 }
@@ -301,6 +393,24 @@ int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float*
     if (rc) return rc;
     if (a.nblk == 0) return DSUF_OK;
     return launch(ctx, stream, plan_place_kernel, dim3(a.nblk), dim3(PLAN_BLOCK), 0, a);
+}
+
+int launch_front(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp_all,
+                 int topk, float route_scale, int* ids, float* w, int e_lo, const dsuf_moe_plan* plan, int mode, const void* x, int ldx,
+                 int h, void* xq, void* xs) {
+    FrontArgs f;
+    PlanArgs& a = f.plan;
+    a.ids = ids; a.w = w; a.e_lo = e_lo; a.n_exp = plan->n_exp; a.p = plan->p; a.tile_rows = plan->tile_rows;
+    a.max_tiles = plan->max_tiles; a.nblk = 1;
+    a.expert_off = (int*)plan->expert_off; a.row_pair = (int*)plan->row_pair; a.pair_row = (int*)plan->pair_row;
+    a.row_w = (float*)plan->row_w; a.tiles = (int4*)plan->tiles; a.ntiles = (int*)plan->ntiles;
+    a.block_cnt = nullptr; a.local_rank = nullptr;
+    a.status = ctx->dev_status;
+    f.scores = scores; f.bias = bias; f.score_fn = score_fn; f.t = t; f.n_exp_all = n_exp_all; f.topk = topk; f.route_scale = route_scale;
+    f.ids_out = ids; f.w_out = w; f.x = (const bf16*)x; f.ldx = ldx; f.h = h; f.xq = (uint8_t*)xq; f.xs = xs;
+    const int grid = t < ctx->sm_count ? t : ctx->sm_count;
+    if (mode == DSUF_MODE_MX) return launch(ctx, stream, moe_front_kernel<DSUF_MODE_MX>, dim3(grid), dim3(PLAN_BLOCK), 0, f);
+    return launch(ctx, stream, moe_front_kernel<DSUF_MODE_DS>, dim3(grid), dim3(PLAN_BLOCK), 0, f);
 }
 
 // ---------------------------------------------------------------- unpermute / combine

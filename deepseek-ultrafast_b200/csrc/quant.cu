@@ -11,6 +11,7 @@
 // HBM-bound: reads 2 B and writes ~1.03 B (x fan-out for the scatter form) per element; 16-byte loads,
 // 8-byte stores, amax by warp shuffles.
 #include "internal.h"
+#include "quant_core.cuh"
 
 namespace dsuf {
 
@@ -56,24 +57,10 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) v[e] = 0.f;
     }
-    float amax = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
     constexpr int LANES = MODE == DSUF_MODE_MX ? 4 : 16;  // lanes sharing one scale block
-#pragma unroll
-    for (int o = 1; o < LANES; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     float sc;
     uint2 out;
-    if (MODE == DSUF_MODE_MX) {
-        sc = round_scale_pow2(fmaxf(amax, 1e-4f), 1.0f / 448.0f);
-        const float inv = __uint_as_float(0x7f000000u - __float_as_uint(sc));
-        out.x = f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-        out.y = f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-    } else {
-        sc = amax == 0.f ? 1.0f : __fdiv_rn(amax, 448.0f);
-        out.x = f32x4_to_e4m3x4(__fdiv_rn(v[0], sc), __fdiv_rn(v[1], sc), __fdiv_rn(v[2], sc), __fdiv_rn(v[3], sc));
-        out.y = f32x4_to_e4m3x4(__fdiv_rn(v[4], sc), __fdiv_rn(v[5], sc), __fdiv_rn(v[6], sc), __fdiv_rn(v[7], sc));
-    }
+    quant8<MODE>(v, out, sc);
     if (!live) return;
     const bool writes_scale = (threadIdx.x & (LANES - 1)) == 0;
     const int nfan = a.fanout > 0 ? a.fanout : 1;

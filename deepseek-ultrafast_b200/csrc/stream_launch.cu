@@ -26,9 +26,10 @@ int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, 
     return DSUF_OK;
 }
 
-template <int FMT, int WMX, int AMX, int N, int EPI>
+template <int FMT, int WMX, int AMX, int N, int EPI, int PAIR = 1>
 static int set_attr_tc(dsuf_ctx* ctx) {
-    cudaError_t e = cudaFuncSetAttribute(tc_stream_kernel<FMT, WMX, AMX, N, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<N>::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(tc_stream_kernel<FMT, WMX, AMX, N, EPI, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TcCfg<N, PAIR>::SMEM);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(tc_stream)");
     return DSUF_OK;
 }
@@ -58,6 +59,9 @@ int stream_setup(dsuf_ctx* ctx) {
     ST(FMT_FP4, 1, 1, 8, EPI_W13); ST(FMT_FP4, 1, 1, 16, EPI_W13); ST(FMT_FP4, 1, 1, 128, EPI_W13);
     ST(FMT_FP4, 1, 0, 8, EPI_W2); ST(FMT_FP4, 1, 0, 16, EPI_W2); ST(FMT_FP4, 1, 0, 128, EPI_W2);
     ST(FMT_FP4, 1, 1, 8, EPI_W2); ST(FMT_FP4, 1, 1, 16, EPI_W2); ST(FMT_FP4, 1, 1, 128, EPI_W2);
+    // two tile records per ring stage (weights with an even number of K tiles)
+    ST(FMT_FP4, 1, 0, 8, EPI_W13, 2); ST(FMT_FP4, 1, 0, 16, EPI_W13, 2); ST(FMT_FP4, 1, 1, 8, EPI_W13, 2); ST(FMT_FP4, 1, 1, 16, EPI_W13, 2);
+    ST(FMT_FP4, 1, 0, 8, EPI_W2, 2); ST(FMT_FP4, 1, 0, 16, EPI_W2, 2); ST(FMT_FP4, 1, 1, 8, EPI_W2, 2); ST(FMT_FP4, 1, 1, 16, EPI_W2, 2);
 #undef ST
     // 128-token steps, except the dense DS GEMM, which walks a slot in two 64-token halves (measured: 1.51 against
     // 1.79 ms on 7168 x 7168 x 16384 tokens; for the FP4 expert GEMMs with DS scales the halves are 12 - 19 % slower)
@@ -200,6 +204,17 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
             if (epi == EPI_W13) return amx ? GP(EPI_W13, 1) : GP(EPI_W13, 0);
             return amx ? GP(EPI_W2, 1) : GP(EPI_W2, 0);
 #undef GP
+        }
+        if (tr <= 16 && (w->kt & 1) == 0 && ctx->use_pairs) {
+            // decode slots: two tile records per ring stage, half the pipeline hand-offs per byte streamed
+#define GT2(AMX, NN, EPI) launch(ctx, stream, tc_stream_kernel<FMT_FP4, 1, AMX, NN, EPI, 2>, dim3(grid), dim3(TcCfg<NN, 2>::THREADS), (size_t)TcCfg<NN, 2>::SMEM, a)
+            if (epi == EPI_W13) {
+                if (amx) return tr == 8 ? GT2(1, 8, EPI_W13) : GT2(1, 16, EPI_W13);
+                return tr == 8 ? GT2(0, 8, EPI_W13) : GT2(0, 16, EPI_W13);
+            }
+            if (amx) return tr == 8 ? GT2(1, 8, EPI_W2) : GT2(1, 16, EPI_W2);
+            return tr == 8 ? GT2(0, 8, EPI_W2) : GT2(0, 16, EPI_W2);
+#undef GT2
         }
         if (epi == EPI_W13) {
             if (amx) return tr == 8 ? GT(1, 8, EPI_W13) : tr == 16 ? GT(1, 16, EPI_W13) : GT(1, 128, EPI_W13);

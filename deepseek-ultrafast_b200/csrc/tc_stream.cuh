@@ -25,25 +25,33 @@ constexpr int KID_TC = 3;
 // (token tiles up to 16 columns)
 constexpr int TC_EPI_THREADS = 128;
 
-template <int N>
+// PAIR: tile records (128-K tiles) per ring stage.  With two, every hand-off of the pipeline (stage full / stage free /
+// accumulator full / accumulator free) moves 256 K of a weight row tile instead of 128: half the barrier round trips
+// per byte, which is what bounds the 8.7 KB FP4 tiles (the tensor pipe and TMA are far from busy).
+template <int N, int PAIR = 1>
 struct TcCfg {
-    static constexpr int A_BYTES = 16384;
-    static constexpr int B_BYTES = N * 128 < 1024 ? 1024 : N * 128;  // N token rows of 128 bytes
+    static constexpr int A1 = 16384;                                 // one weight tile in 8-bit containers
+    static constexpr int B1 = N * 128 < 1024 ? 1024 : N * 128;       // N token rows of 128 bytes of one K tile
+    static constexpr int A_BYTES = A1 * PAIR;
+    static constexpr int B_BYTES = B1 * PAIR;
     static constexpr int B_OFF = A_BYTES;
-    static constexpr int SFA_OFF = B_OFF + B_BYTES;  // weight scale atom (512)
-    static constexpr int SFB_OFF = SFA_OFF + 512;    // MX activations: activation scale atom (512)
-    static constexpr int STAGE = A_BYTES + B_BYTES + 1024;
+    static constexpr int SFA_OFF = B_OFF + B_BYTES;          // weight scale atoms (512 each)
+    static constexpr int SFB_OFF = SFA_OFF + 512 * PAIR;     // MX activations: activation scale atoms (512 each)
+    static constexpr int STAGE = A_BYTES + B_BYTES + 1024 * PAIR;
     static constexpr int NE = N <= 16 ? 2 : 1;        // epilogue warp groups (per-tile mode: alternate tiles)
     static constexpr int RED_BYTES = NE == 2 ? 2 * N * 128 * 4 : 0;  // static shared memory of the group combine
     static constexpr int S_FIT = (226 * 1024 - 2048 - RED_BYTES) / STAGE;
     // A multiple of the number of issuers (4 for N <= 16, else 2), so that every stage is always handled by the
     // same issuer: a parity wait cannot tell phase p from phase p + 2, and only the issuer that consumed phase p - 1
     // of a stage is certain not to reach the wait before phase p has begun.
-    static constexpr int STAGES = (S_FIT > 12 ? 12 : S_FIT) & ~(N <= 16 ? 3 : 1);
+    static constexpr int NISSUE = (N <= 16 && PAIR == 1) ? 4 : 2;   // issuer warps dealing stages round-robin
+    static constexpr int STAGES = (S_FIT > 12 ? 12 : S_FIT) & ~(NISSUE - 1);
     static constexpr int ONES_OFF = STAGE * STAGES;  // 512-byte atom of UE8M0 1.0
     static constexpr int SMEM = STAGE * STAGES + 512 + 1024;
-    static constexpr int ACC_COLS = N;               // tensor-memory columns of one accumulator
-    static constexpr int NB = ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;  // accumulator ring (power of two)
+    static constexpr int ACC_COLS = N * PAIR;        // tensor-memory columns of one accumulator-ring entry (per-tile mode)
+    // accumulator ring (a power of two); with two tiles per entry eight entries are as deep as sixteen single ones, and the
+    // shorter scale ring that goes with them keeps the static shared memory inside the budget
+    static constexpr int NB = PAIR == 2 ? 8 : ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;
     // producer warps per kind (weights / activations), tiles dealt round-robin: a producer spends ~1100 cycles per tile
     // of its own (two barrier waits, the copies, the scale gathers); four of each kind measured no faster than two
     static constexpr int NP = 2;
@@ -53,18 +61,19 @@ struct TcCfg {
 };
 
 
-template <int FMT, int WMX, int AMX, int N, int EPI>
-__global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
-    using Cfg = TcCfg<N>;
-    constexpr int S = Cfg::STAGES, ACC_COLS = Cfg::ACC_COLS;
+template <int FMT, int WMX, int AMX, int N, int EPI, int PAIR = 1>
+__global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(const __grid_constant__ StreamArgs a) {
+    using Cfg = TcCfg<N, PAIR>;
     constexpr bool PER_TILE = (AMX == 0);   // promote every 128-K tile with fp32 scales
+    constexpr int S = Cfg::STAGES, ACC_COLS = PER_TILE ? Cfg::ACC_COLS : N;
+    constexpr int A1 = Cfg::A1, B1 = Cfg::B1;
     // MMA-issuing warps of the per-tile mode: an issuer spends ~600 cycles per tile of its own (waits, fences, scale
     // copies, commits around 4 MMAs), so narrow token tiles (180 cycles of MMA per tile) take four to keep up with HBM
-    constexpr int NI = PER_TILE ? (N <= 16 ? 4 : 2) : 1;
+    constexpr int NI = PER_TILE ? Cfg::NISSUE : 1;
     // whole-K mode with token tiles up to 64 columns: several issuers as well (four up to 16 columns, else two), tiles
     // dealt round-robin, each accumulating into its own part of the ring entry; the epilogue adds the parts
     constexpr bool DUAL_WHOLE = !PER_TILE && N <= 64;
-    constexpr int NIW = !DUAL_WHOLE ? 1 : N <= 16 ? 4 : 2;
+    constexpr int NIW = !DUAL_WHOLE ? 1 : Cfg::NISSUE;
     constexpr int ACCW = NIW * ACC_COLS;  // tensor-memory columns of one ring entry
     static_assert(S % NI == 0 && S % NIW == 0 && S % Cfg::NP == 0, "stage ownership must not rotate among issuers or producers (parity waits alias)");
     constexpr int NB = Cfg::NB * ACCW > 256 ? 256 / ACCW : Cfg::NB;  // ring entries in use (a power of two)
@@ -87,7 +96,8 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
     // indexed by tile number needs no barrier of its own: a producer writing tile n has seen the MMAs of tile n - S
     // complete, which were issued only after the epilogue had released the accumulator of tile n - S - NB, and the
     // epilogue reads a tile's scales before it releases its accumulator.
-    constexpr int XSE = 4 * N + (WMX ? 0 : 16);  // entry: N activation scales (+ the tile's weight scale, DS weights)
+    constexpr int XSE = 4 * N * PAIR + (WMX ? 0 : 16);  // entry: N activation scales per K tile (+ the tile's weight scale, DS weights)
+    static_assert(PAIR == 1 || WMX, "two tiles per stage: weights with UE8M0 scales only (one fp32 weight scale slot per entry)");
     constexpr int XR = S + NB <= 16 ? 16 : 32;
     static_assert(S + NB <= XR, "scale ring shorter than stages + accumulators");
     __shared__ __align__(16) uint8_t s_xs[XR * XSE];
@@ -95,7 +105,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, c = blockIdx.x;
-    const int RT = a.RT, KT = a.KT;
+    const int RT = a.RT;
+    const int KT = a.KT / PAIR;   // ring steps per item: PAIR K tiles each (the launcher checks that the K tile count divides)
+    const int KTT = a.KT;         // K tiles per item (row stride of the scale arrays and of the tile sequence)
     bool dead = false;  // set by the first expired wait: nothing is waited for again, the loops stay finite
 
     if (warp == 1) {
@@ -163,30 +175,33 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
             uint32_t ph = 0;
             uint8_t* st = ring + pj * Cfg::STAGE;
             // TMA counts the bytes it READS: a packed FP4 tile is 8192 bytes although it fills 16384 of shared memory
-            constexpr uint32_t W_TX = (FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0);
+            constexpr uint32_t W_TX = PAIR * ((FMT == FMT_FP4 ? 8192 : 16384) + (WMX ? 512 : 0));
             for (long long i = beg + pj; i < end; i += NP) {
                 if (fresh) {
                     long long wbase;
                     if (EPI == EPI_DENSE) {
-                        wbase = q * KT;
+                        wbase = q * KTT;
                     } else {
                         const int slot = (int)(q / RT);
                         const int rt = (int)(q - (long long)slot * RT);
-                        wbase = ((long long)a.slots[slot].x * RT + rt) * KT;
+                        wbase = ((long long)a.slots[slot].x * RT + rt) * KTT;
                     }
-                    tile = (int)(wbase + kt);
+                    tile = (int)(wbase + kt * PAIR);
                     sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
                     fresh = false;
                 }
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 1)) dead = true;
                 if (warp_elect()) {
                     mbar_expect_tx(&full_bar[s], W_TX);
-                    tma_3d(st, &a.tm_w, 0, 0, tile, &full_bar[s], pol_w);
-                    if (WMX) bulk_g2s(st + Cfg::SFA_OFF, sf_src, 512, &full_bar[s], pol_w);
+#pragma unroll
+                    for (int pp = 0; pp < PAIR; ++pp) {
+                        tma_3d(st + pp * A1, &a.tm_w, 0, 0, tile + pp, &full_bar[s], pol_w);
+                        if (WMX) bulk_g2s(st + Cfg::SFA_OFF + pp * 512, sf_src + (size_t)pp * a.rec_bytes, 512, &full_bar[s], pol_w);
+                    }
                 }
                 __syncwarp();
-                tile += NP;
-                sf_src += (size_t)NP * a.rec_bytes;
+                tile += NP * PAIR;
+                sf_src += (size_t)(NP * PAIR) * a.rec_bytes;
                 s += NP;
                 st += NP * Cfg::STAGE;
                 if (s >= S) { s -= S; st -= S * Cfg::STAGE; ph ^= 1; }
@@ -219,13 +234,15 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         rt = (int)(q - (long long)slot * RT);
                         xrow0 = a.slots[slot].y;
                     }
-                    ws_src = (!WMX && lane == 31) ? a.wscale_ds + (size_t)rt * KT : nullptr;
+                    ws_src = (!WMX && lane == 31) ? a.wscale_ds + (size_t)rt * KTT : nullptr;
                     fresh = false;
                 }
                 if (i - beg >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TC, 5)) dead = true;
                 if (warp_elect()) {
-                    mbar_expect_tx(&full_bar[s], N * 128);
-                    tma_2d(st + Cfg::B_OFF, &a.tm_x, kt * 128, xrow0, &full_bar[s], pol_x);
+                    mbar_expect_tx(&full_bar[s], PAIR * N * 128);
+#pragma unroll
+                    for (int pp = 0; pp < PAIR; ++pp)
+                        tma_2d(st + Cfg::B_OFF + pp * B1, &a.tm_x, (kt * PAIR + pp) * 128, xrow0, &full_bar[s], pol_x);
                 }
                 __syncwarp();
                 uint8_t* xe = nullptr;
@@ -236,10 +253,12 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
 #pragma unroll
                 for (int n = lane; n < N; n += 32) {
                     // MX: the token's 4 UE8M0 bytes go to its row of the scale atom; DS: its fp32 scale
-                    const uint32_t* src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + n, a.x_rows - 1) * KT + kt;
-                    cp_async4(AMX ? st + Cfg::SFB_OFF + (n & 31) * 16 + (n >> 5) * 4 : xe + 4 * n, src);
+                    const uint32_t* src = (const uint32_t*)a.xscale + (size_t)min(xrow0 + n, a.x_rows - 1) * KTT + kt * PAIR;
+#pragma unroll
+                    for (int pp = 0; pp < PAIR; ++pp)
+                        cp_async4(AMX ? st + Cfg::SFB_OFF + pp * 512 + (n & 31) * 16 + (n >> 5) * 4 : xe + 4 * (pp * N + n), src + pp);
                 }
-                if (!WMX && lane == 31) cp_async4(xe + 4 * N, ws_src + kt);
+                if (!WMX && lane == 31) cp_async4(xe + 4 * N * PAIR, ws_src + kt);
                 cp_async_arrive_noinc(&full_bar[s]);
                 s += NP;
                 st += NP * Cfg::STAGE;
@@ -260,7 +279,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 // an issuer that contributed MMAs, a plain arrival from one that did not.
                 const uint32_t tmu = warp_uniform(tm);
                 const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
-                const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
+                const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S * PAIR + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S * PAIR + j);
                 const uint64_t ones_d = warp_uniform(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
                 if (warp_elect()) {
                     if (!WMX) tc_cp_sf(ones_a, ones_d);
@@ -289,14 +308,17 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                         if (AMX) fence_proxy_async();  // the activation scale atom was written by cp.async (generic proxy)
                         const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
                         if (warp_elect()) {
-                            uint32_t sfa = ones_a, sfb = ones_b;
-                            if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
-                            if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
                             const uint32_t d = tmu + b * ACCW + j * N;
 #pragma unroll
-                            for (int kc = 0; kc < 4; ++kc)
-                                tc_mma_mx(d, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2), tc_idesc_sf(idesc, kc),
-                                          sfa, sfb, (!issued && kc == 0) ? 0u : 1u);
+                            for (int pp = 0; pp < PAIR; ++pp) {
+                                uint32_t sfa = ones_a, sfb = ones_b;
+                                if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * (s * PAIR + pp); tc_cp_sf(sfa, fa0 + so + (uint64_t)(pp * 32)); }
+                                if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * (s * PAIR + pp); tc_cp_sf(sfb, fb0 + so + (uint64_t)(pp * 32)); }
+#pragma unroll
+                                for (int kc = 0; kc < 4; ++kc)
+                                    tc_mma_mx(d, ad0 + so + (uint64_t)(pp * (A1 >> 4) + kc * 2), bd0 + so + (uint64_t)(pp * (B1 >> 4) + kc * 2),
+                                              tc_idesc_sf(idesc, kc), sfa, sfb, (!issued && pp == 0 && kc == 0) ? 0u : 1u);
+                            }
                             tc_commit(&empty_bar[s]);
                             if (group_end) tc_commit(&tfull_bar[b]);
                         }
@@ -316,7 +338,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
         } else if (j < NI && beg + j < end) {
             const uint32_t tmu = warp_uniform(tm);
             const uint32_t idesc = tc_idesc_mx(N, FMT == FMT_FP4);
-            const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S + j);
+            const uint32_t ones_a = tmu + Cfg::TM_SFA + 4 * (S * PAIR + j), ones_b = tmu + Cfg::TM_SFB + 4 * (S * PAIR + j);
             const uint64_t ones_d = warp_uniform(tc_smem_desc(ring + Cfg::ONES_OFF, 512, 128, 0));
             if (warp_elect()) {
                 if (!WMX) tc_cp_sf(ones_a, ones_d);
@@ -356,14 +378,18 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 const uint64_t so = (uint64_t)((s * Cfg::STAGE) >> 4);
                 const bool group_end = PER_TILE || kt + 1 == KT || i + 1 == end;
                 if (warp_elect()) {
-                    uint32_t sfa = ones_a, sfb = ones_b;
-                    if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * s; tc_cp_sf(sfa, fa0 + so); }
-                    if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * s; tc_cp_sf(sfb, fb0 + so); }
-                    const uint32_t d = tmu + b * ACC_COLS;
 #pragma unroll
-                    for (int kc = 0; kc < 4; ++kc)
-                        tc_mma_mx(d, ad0 + so + (uint64_t)(kc * 2), bd0 + so + (uint64_t)(kc * 2),
-                                  tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && kc == 0) ? 0u : 1u);
+                    for (int pp = 0; pp < PAIR; ++pp) {
+                        uint32_t sfa = ones_a, sfb = ones_b;
+                        if (WMX) { sfa = tmu + Cfg::TM_SFA + 4 * (s * PAIR + pp); tc_cp_sf(sfa, fa0 + so + (uint64_t)(pp * 32)); }
+                        if (AMX) { sfb = tmu + Cfg::TM_SFB + 4 * (s * PAIR + pp); tc_cp_sf(sfb, fb0 + so + (uint64_t)(pp * 32)); }
+                        // per-tile mode: every K tile of the stage has its own accumulator columns (promoted with its own scales)
+                        const uint32_t d = tmu + b * ACC_COLS + (PER_TILE ? pp * N : 0);
+#pragma unroll
+                        for (int kc = 0; kc < 4; ++kc)
+                            tc_mma_mx(d, ad0 + so + (uint64_t)(pp * (A1 >> 4) + kc * 2), bd0 + so + (uint64_t)(pp * (B1 >> 4) + kc * 2),
+                                      tc_idesc_sf(idesc, kc), sfa, sfb, (first_of_group && (PER_TILE || pp == 0) && kc == 0) ? 0u : 1u);
+                    }
                     tc_commit(&empty_bar[s]);
                     if (group_end) tc_commit(&tfull_bar[b]);
                 }
@@ -425,7 +451,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
                 tc_fence_after();
                 {
-                    const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * N) : 1.0f;
+                    const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * N * PAIR) : 1.0f;
                     constexpr int CH = NC < 32 ? NC : 32;
                     // several issuers in the whole-K mode: part p of the entry holds a sum iff the group, which started at
                     // tile g0 and has gcnt tiles, contains a tile dealt to issuer p; the parts are added in a fixed order
@@ -445,17 +471,29 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, 1) tc_stream_kernel(const _
                                     for (int j = 0; j < CH; ++j) v[j] += v2[j];
                                 }
                             }
-                        } else {
+                        } else if (PAIR == 1) {
                             tmem_ld<CH>(tm + lane_base + b * ACCW + cb + c0, v);
                         }
                         if (PER_TILE) {
+                            // the stage's K tiles, each with its own accumulator columns and its own activation scales;
+                            // both loads are in flight before the first is waited for
+                            float v1[PAIR == 2 ? CH : 1];
+                            if (PAIR == 2) {
+                                tmem_ld_issue<CH>(tm + lane_base + b * ACCW + cb + c0, v);
+                                tmem_ld_issue<CH>(tm + lane_base + b * ACCW + N + cb + c0, v1);
+                                tmem_wait_ld();
+                            }
 #pragma unroll
-                            for (int j = 0; j < CH; j += 4) {
-                                const float4 t4 = *(const float4*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * (cb + c0 + j));
-                                acc[c0 + j] = fmaf(v[j], wds * t4.x, acc[c0 + j]);
-                                acc[c0 + j + 1] = fmaf(v[j + 1], wds * t4.y, acc[c0 + j + 1]);
-                                acc[c0 + j + 2] = fmaf(v[j + 2], wds * t4.z, acc[c0 + j + 2]);
-                                acc[c0 + j + 3] = fmaf(v[j + 3], wds * t4.w, acc[c0 + j + 3]);
+                            for (int pp = 0; pp < PAIR; ++pp) {
+#pragma unroll
+                                for (int j = 0; j < CH; j += 4) {
+                                    const float4 t4 = *(const float4*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * (pp * N + cb + c0 + j));
+                                    const float* vv = (PAIR == 2 && pp == 1) ? v1 : v;
+                                    acc[c0 + j] = fmaf(vv[j], wds * t4.x, acc[c0 + j]);
+                                    acc[c0 + j + 1] = fmaf(vv[j + 1], wds * t4.y, acc[c0 + j + 1]);
+                                    acc[c0 + j + 2] = fmaf(vv[j + 2], wds * t4.z, acc[c0 + j + 2]);
+                                    acc[c0 + j + 3] = fmaf(vv[j + 3], wds * t4.w, acc[c0 + j + 3]);
+                                }
                             }
                         } else {
 #pragma unroll

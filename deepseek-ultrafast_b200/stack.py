@@ -55,6 +55,8 @@ class LayerStack:
         self.xs = t.empty((cfg.tokens, H // blk), dtype=t.uint8 if cfg.dense_mode == MODE_MX else t.float32, device=dev)
         self.h = t.empty((cfg.tokens, H), dtype=t.bfloat16, device=dev)
         self.y = [t.empty((cfg.tokens, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
+        self.ids = t.empty((cfg.tokens, cfg.topk), dtype=t.int32, device=dev)
+        self.w = t.empty((cfg.tokens, cfg.topk), dtype=t.float32, device=dev)
 
     def dense_forward(self, l, x, out):
         """x bf16 [T][H] -> out bf16 [T][H]; processed in slabs of the decode kernel's row limit (64 tcgen05, 16 mma.sync)."""
@@ -74,9 +76,9 @@ class LayerStack:
         cur = x
         for l in range(cfg.layers if layers is None else layers):
             self.dense_forward(l, cur, self.h)
-            ids, w = moe_route_tokens(self.ctx, SCORE_SOFTMAX, self.logits[l], None, cfg.topk)
             out = self.y[l & 1]
-            self.moe[l].forward(self.h, ids, w, out, events=events)
+            # router inside the layer: decode-size batches take one launch for router + plan + gather/quant
+            self.moe[l].forward(self.h, self.ids, self.w, out, events=events, route=(SCORE_SOFTMAX, self.logits[l], None, 1.0))
             cur = out
         return cur
 
@@ -86,9 +88,10 @@ class LayerStack:
         slabs = (cfg.tokens + slab - 1) // slab
         if self.ctx.tcgen05 and (cfg.tokens <= 64 or (cfg.hidden // 128) % 2 == 0):
             slabs = 1
-        # act_quant + dense slabs + route + plan (1 launch up to 1024 pairs, else 3) + gather + w13 + quant + w2 + unpermute
-        plan = 1 if cfg.tokens * cfg.topk <= 1024 else 3
-        return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1)
+        # act_quant + dense slabs + front end (router + plan + gather/quant: 1 launch up to 1024 pairs, else 1 + 3 + 1)
+        # + w13 + quant + w2 + unpermute
+        front = 1 if cfg.tokens * cfg.topk <= 1024 else 5
+        return cfg.layers * (1 + slabs + front + 1 + 1 + 1 + 1)
 
 
 class _KernelCompute:
@@ -110,18 +113,21 @@ class _KernelCompute:
         return s.partial
 
     def route(self, h_all):
+        """The router runs inside the expert step (one launch with the plan and the gather/quant); this hands out the
+        buffers it fills."""
         s = self.s
-        return moe_route_tokens(s.ctx, SCORE_SOFTMAX, s.logits[self.l], None, s.cfg.topk, ids=s.ids, w=s.w)
+        return s.ids, s.w
 
     def experts_partial(self, h_all, ids_all, w_all):
         s = self.s
         part = s.y_part[self.l & 1]
+        route = (SCORE_SOFTMAX, s.logits[self.l], None, 1.0)
         if s.peer is not None and s.fuse_combine:
             # one kernel: local sum of the top-k rows into the mapped partial buffer, hand-shake, sum over the ranks
             out = s.xch.peer_out[part.data_ptr()]
-            return s.moe[self.l].forward(h_all, ids_all, w_all, part,
+            return s.moe[self.l].forward(h_all, ids_all, w_all, part, route=route,
                                          combine=lambda plan, yrows, shared: s.peer.combine(plan, yrows, shared, part, out))
-        return s.moe[self.l].forward(h_all, ids_all, w_all, part)
+        return s.moe[self.l].forward(h_all, ids_all, w_all, part, route=route)
 
 
 class EpLayerStack:
@@ -219,8 +225,8 @@ class EpLayerStack:
         cfg = self.cfg
         slab = 64 if self.ctx.tcgen05 else 16
         slabs = (cfg.tokens + slab - 1) // slab
-        plan = 1 if cfg.tokens * cfg.topk <= 1024 else 3
-        # this library's exchange kernels (NCCL's kernels are not counted): the dense all-reduce, and the combine that
-        # either follows the unpermute as a second all-reduce or replaces it
+        front = 1 if cfg.tokens * cfg.topk <= 1024 else 5
+        # this library's exchange kernels (NCCL's kernels are not counted): the gather of the dense slices, and the combine
+        # that either follows the unpermute as an all-reduce or replaces it
         ar = 0 if self.peer is None else 1 if self.fuse_combine else 2
-        return cfg.layers * (1 + slabs + 1 + plan + 1 + 1 + 1 + 1 + 1 + ar)
+        return cfg.layers * (1 + slabs + front + 1 + 1 + 1 + 1 + ar)

@@ -62,6 +62,10 @@ int32_t dsuf_ctx_set_pdl(dsuf_ctx* ctx, int32_t enabled);
  * 0 = mma.sync streaming kernel (the counterpart of the reference's cu/gemv.cu family).  Both compute the same
  * function; the choice mirrors the reference's runtime switch between gemv and tc_gemv (model.rs:1523-1530). */
 int32_t dsuf_ctx_set_decode_path(dsuf_ctx* ctx, int32_t tcgen05);
+/* Decode-shape expert GEMMs on the tcgen05 path: 1 (default) streams two 128-K tile records per ring stage where the
+ * weight has an even number of K tiles (half the barrier hand-offs per byte), 0 one per stage.  Both are deterministic;
+ * they add the per-tile fp32 partial sums in a different order. */
+int32_t dsuf_ctx_set_stage_pairs(dsuf_ctx* ctx, int32_t enabled);
 /* Decode-shape dense GEMV on the tcgen05 path: 1 (default) lets weights with few row tiles run as one row tile per
  * thread-block cluster with K cut into slices summed through distributed shared memory -- the counterpart of the cluster
  * K-split of ops::gemv / ops::tc_gemv (ops.rs:298-328, 1105-1107) -- where that beats stream-K with global partial sums;
@@ -98,6 +102,35 @@ int32_t dsuf_pack_fp8_weight(int32_t mode, const uint8_t* codes, const void* sca
  * interleaved per 16-row group as 8 gate + the 8 matching up rows (the reference interleaves 32+32 per
  * 64-row quad, packing.rs:237-241) so the SwiGLU epilogue finds both halves in one thread. */
 int32_t dsuf_pack_fp4_weight(const uint8_t* codes, const uint8_t* scales, int32_t n, int32_t k, int32_t gate_up, uint8_t* out);
+
+/* ---- checkpoint-facing loaders (load-time, host only).  Replace Checkpoint (crates/model/src/st.rs:17-106), Loader::fp8
+ * (crates/engine/src/weights.rs:254-276) and the expert part of Loader::layer (weights.rs:421-446). ---- */
+typedef struct dsuf_ckpt dsuf_ckpt;
+typedef struct {
+    char dtype[16];        /* the safetensors dtype string: "F8_E4M3", "BF16", "F32", ... */
+    int32_t rank;
+    int64_t shape[8];
+    const void* data;      /* inside the read-only mapping of the file; valid until dsuf_ckpt_close */
+    size_t nbytes;
+} dsuf_tensor_info;
+/* Maps one .safetensors file, or every *.safetensors file of a directory in name order (Checkpoint::open, st.rs:24-31),
+ * and indexes the tensors.  *out is set even when the call fails, so that dsuf_ckpt_last_error can be read; close it. */
+int32_t dsuf_ckpt_open(const char* path, dsuf_ckpt** out);
+int32_t dsuf_ckpt_close(dsuf_ckpt* c);
+int32_t dsuf_ckpt_last_error(dsuf_ckpt* c, char* buf, size_t len);
+int64_t dsuf_ckpt_count(dsuf_ckpt* c);
+int32_t dsuf_ckpt_tensor(dsuf_ckpt* c, const char* name, dsuf_tensor_info* out);
+/* Loader::fp8: `{name}.weight` F8_E4M3 [n][k] + `{name}.scale` UE8M0 [n/32][k/32] -> MX tile records of rows [r0, r1)
+ * (multiples of 32; the records pad rows up to a multiple of 128), dsuf_packed_bytes(FP8, MX, r1 - r0, k) bytes at
+ * tiles_out.  One image serves both the decode and the prefill kernels (the reference keeps a fragment-tiled and a
+ * row-major copy, weights.rs:181-214). */
+int32_t dsuf_ckpt_load_fp8_dense(dsuf_ckpt* c, const char* name, int32_t n, int32_t k, int32_t r0, int32_t r1, uint8_t* tiles_out);
+/* Experts e0 .. e1-1 of `{prefix}.ffn.experts.{e}.{w1,w3,w2}.{weight,scale}` (FP4 codes two per byte + UE8M0 per 1x32;
+ * w1 = gate [inter][dim], w3 = up [inter][dim], w2 = down [dim][inter]) -> tile records: w13_out receives
+ * (e1 - e0) x dsuf_packed_bytes(FP4, MX, 2 inter, dim) bytes with gate / up rows interleaved for the SwiGLU epilogue,
+ * w2_out (e1 - e0) x dsuf_packed_bytes(FP4, MX, dim, inter).  dim and inter multiples of 128. */
+int32_t dsuf_ckpt_load_fp4_experts(dsuf_ckpt* c, const char* prefix, int32_t e0, int32_t e1, int32_t dim, int32_t inter, uint8_t* w13_out,
+                                   uint8_t* w2_out);
 
 /* Weight descriptor = Weight{fmt,w,s,n,k} / Experts (ops.rs:6-39, weights.rs:82-92). */
 typedef struct {
@@ -212,6 +245,16 @@ int32_t dsuf_moe_permute_plan(dsuf_ctx* ctx, void* stream, uint64_t ids, uint64_
  * to all of its permuted rows.  x bf16 [t][ldx] -> xq [p][h], xs MX u8 [p][h/32] / DS f32 [p][h/128]. */
 int32_t dsuf_moe_gather_quant(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x, int32_t ldx, int32_t t, int32_t h,
                               int32_t topk, const dsuf_moe_plan* plan, uint64_t xq_out, uint64_t xs_out);
+
+/* Decode front end in one launch: dsuf_moe_route + dsuf_moe_permute_plan + dsuf_moe_gather_quant for at most 1024
+ * (token, expert) pairs, with the same outputs bit for bit.  The reference routes inside its decode MoE launch as well
+ * (route_plan, cu/gemv.cu:715-776, RouteArgs in GemvParams); here the routing, the plan and the quantized permuted rows
+ * are produced together and every later kernel only reads them.  scores f32 [t][n_exp_all] over ALL experts; the plan
+ * keeps the pairs whose expert lies in [e_lo, e_lo + plan->n_exp). */
+int32_t dsuf_moe_route_plan_gather(dsuf_ctx* ctx, void* stream, int32_t score_fn, uint64_t scores, uint64_t bias, int32_t t,
+                                   int32_t n_exp_all, int32_t topk, float route_scale, uint64_t ids_out, uint64_t w_out, int32_t e_lo,
+                                   const dsuf_moe_plan* plan, int32_t mode, uint64_t x, int32_t ldx, int32_t h, uint64_t xq_out,
+                                   uint64_t xs_out);
 
 /* The same with the RMS pre-normalisation of dsuf_act_quant_fp8_prenorm in front (moe_gather_quant with MqParams.pw,
  * cu/tcmoe.cu:88-133: every token row is normalised and quantised once, then written to its topk permuted rows).

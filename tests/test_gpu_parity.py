@@ -289,6 +289,47 @@ def test_gather_quant_prenorm_rows_equal_plain_prenorm_quant(pkg, ctx, mode):
     assert (xs.cpu().numpy() == so[row_pair // k]).all()
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("t,e,k,h,e_lo,n_loc,tile", [(64, 256, 8, 7168, 0, 256, 8), (64, 256, 8, 1024, 32, 32, 8), (1, 8, 2, 128, 0, 8, 8),
+                                                     (100, 16, 3, 512, 0, 16, 16), (128, 256, 8, 256, 0, 256, 8), (40, 384, 6, 8320, 128, 128, 8)])
+def test_fused_decode_front_end_equals_the_separate_kernels(pkg, ctx, mode, t, e, k, h, e_lo, n_loc, tile):
+    """Router + permute plan + gather/quant in one launch (at most 1024 pairs) against the three separate entries: routing,
+    every plan array and the quantized permuted rows bit for bit; expert-parallel shards (pairs of other ranks' experts
+    dropped) and a hidden size above one 8192-element pass included."""
+    g = seeded(t + e + h)
+    xt, _ = randn_bf16(g, t, h)
+    logits = torch.randn(t, e, generator=g).cuda()
+    bias = (0.01 * torch.randn(e, generator=g)).cuda()
+    xd = xt.cuda()
+    sdt = torch.uint8 if mode == 0 else torch.float32
+    blk = 32 if mode == 0 else 128
+    res = []
+    for fused in (False, True):
+        plan = pkg.MoePlan(ctx, t, k, n_loc, tile)
+        ids = torch.full((t, k), -7, dtype=torch.int32, device="cuda")
+        w = torch.zeros(t, k, dtype=torch.float32, device="cuda")
+        xq = torch.zeros(t * k, h, dtype=torch.uint8, device="cuda")
+        xs = torch.zeros(t * k, h // blk, dtype=sdt, device="cuda")
+        if fused:
+            pkg.moe_route_plan_gather(ctx, pkg.SCORE_SOFTMAX, logits, bias, k, 2.5, ids, w, e_lo, plan, mode, xd, xq, xs)
+        else:
+            pkg.moe_route_tokens(ctx, pkg.SCORE_SOFTMAX, logits, bias, k, 2.5, ids=ids, w=w)
+            pkg.moe_perm(ctx, plan, ids, w, e_lo)
+            pkg.moe_gather_quant(ctx, mode, plan, xd, xq, xs)
+        torch.cuda.synchronize()
+        assert ctx.status().code == 0
+        nt, rows = plan.ntiles.cpu().tolist()
+        res.append(dict(ids=ids.cpu(), w=w.cpu().view(torch.int32), off=plan.expert_off.cpu(), row_pair=plan.row_pair.cpu()[:rows],
+                        pair_row=plan.pair_row.cpu(), row_w=plan.row_w.cpu()[:rows].view(torch.int32), tiles=plan.tiles.cpu()[:nt],
+                        nt=nt, rows=rows, xq=xq.cpu()[:rows], xs=xs.cpu()[:rows]))
+    a, b = res
+    assert a["nt"] == b["nt"] and a["rows"] == b["rows"]
+    for key in ("ids", "w", "off", "row_pair", "pair_row", "row_w", "tiles", "xq", "xs"):
+        assert torch.equal(a[key], b[key]), key
+    if e_lo == 0 and n_loc == e:
+        assert a["rows"] == t * k
+
+
 # ------------------------------------------------------------------ routed-expert layer
 def _moe_case(pkg, ctx, act_mode, T, H, I, E, K, tile_rows, seed, e_lo=0, n_loc=None, limit=0.0, shared=False, ids_rw=None):
     n_loc = E if n_loc is None else n_loc
@@ -406,6 +447,22 @@ def test_dense_gemm_prefill_benchmark_size_sampled(pkg, ctx, mode):
     _, ref = oracle.gemm_fp8(mode, np.ascontiguousarray(wq[ridx]), np.ascontiguousarray(ws[sel]), xq, xs)
     got = out[torch.from_numpy(tok).cuda()].float().cpu().numpy()[:, ridx]
     assert rel(got, ref) < TOL
+
+
+@pytest.mark.parametrize("act_mode", [0, 1])
+@pytest.mark.parametrize("tile_rows", [8, 16])
+def test_moe_decode_two_tiles_per_stage_equals_one(pkg, ctx, act_mode, tile_rows):
+    """The decode expert GEMMs stream two 128-K tile records per ring stage when the weight has an even number of K tiles
+    (hidden 1024: 8 K tiles for gate/up; inter 512: 4 for down).  Both that kernel and the one-tile-per-stage kernel
+    against the oracle."""
+    if not ctx.tcgen05:
+        pytest.skip("a variant of the tcgen05 streaming kernel")
+    _moe_case(pkg, ctx, act_mode, T=64, H=1024, I=512, E=32, K=8, tile_rows=tile_rows, seed=2)
+    ctx.set_stage_pairs(False)
+    try:
+        _moe_case(pkg, ctx, act_mode, T=64, H=1024, I=512, E=32, K=8, tile_rows=tile_rows, seed=2)
+    finally:
+        ctx.set_stage_pairs(True)
 
 
 def test_moe_layer_clamp_and_shared_expert_term(pkg, ctx):
