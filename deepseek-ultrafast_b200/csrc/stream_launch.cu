@@ -62,6 +62,8 @@ int stream_setup(dsuf_ctx* ctx) {
     // two tile records per ring stage (weights with an even number of K tiles)
     ST(FMT_FP4, 1, 0, 8, EPI_W13, 2); ST(FMT_FP4, 1, 0, 16, EPI_W13, 2); ST(FMT_FP4, 1, 1, 8, EPI_W13, 2); ST(FMT_FP4, 1, 1, 16, EPI_W13, 2);
     ST(FMT_FP4, 1, 0, 8, EPI_W2, 2); ST(FMT_FP4, 1, 0, 16, EPI_W2, 2); ST(FMT_FP4, 1, 1, 8, EPI_W2, 2); ST(FMT_FP4, 1, 1, 16, EPI_W2, 2);
+    ST(FMT_FP8, 0, 0, 8, EPI_DENSE, 2); ST(FMT_FP8, 0, 0, 16, EPI_DENSE, 2); ST(FMT_FP8, 0, 0, 32, EPI_DENSE, 2); ST(FMT_FP8, 0, 0, 64, EPI_DENSE, 2);
+    ST(FMT_FP8, 1, 1, 8, EPI_DENSE, 2); ST(FMT_FP8, 1, 1, 16, EPI_DENSE, 2); ST(FMT_FP8, 1, 1, 32, EPI_DENSE, 2); ST(FMT_FP8, 1, 1, 64, EPI_DENSE, 2);
 #undef ST
     // 128-token steps, except the dense DS GEMM, which walks a slot in two 64-token halves (measured: 1.51 against
     // 1.79 ms on 7168 x 7168 x 16384 tokens; for the FP4 expert GEMMs with DS scales the halves are 12 - 19 % slower)
@@ -134,12 +136,16 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     a.x_rows = m;
     a.ldo = ldo;
     a.alpha = alpha;
-    const long long tot = (long long)w->rt * w->kt;
+    // the tcgen05 kernel streams two K tiles per ring step where the tile count is even: everything below counts steps
+    const int pair = (ctx->use_tc && ctx->use_pairs && (w->kt & 1) == 0) ? 2 : 1;
+    const int kt = w->kt / pair;
+    const long long tot = (long long)w->rt * kt;
     int grid = ctx->sm_count < WS_MAX_CTAS ? ctx->sm_count : WS_MAX_CTAS;
     if (tot < grid) grid = (int)tot;
     // Stream-K balances to one tile but pays a partial-sum exchange per split row tile (a few microseconds on a kernel
     // of tens); whole row tiles per CTA are preferred when they need no more tile-steps than that.
-    const long long steps_streamk = (tot + grid - 1) / grid + 6, steps_whole = (long long)((w->rt + grid - 1) / grid) * w->kt;
+    const long long fix = 6 / pair;   // the stream-K exchange of partial sums costs about six 16 KB tile steps
+    const long long steps_streamk = (tot + grid - 1) / grid + fix, steps_whole = (long long)((w->rt + grid - 1) / grid) * kt;
     a.whole_items = steps_whole <= steps_streamk ? 1 : 0;
     const bool mx = w->d.mode == DSUF_MODE_MX;
     int cluster = 1;
@@ -150,15 +156,16 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
         const long long steps_other = a.whole_items ? steps_whole : steps_streamk;
         long long best = steps_other;
         for (int cs : {1, 2, 4}) {
-            if ((long long)w->rt * cs > grid || w->kt < cs) continue;
-            const long long steps = (w->kt + cs - 1) / cs + (cs > 1 ? 3 : 0);
+            if ((long long)w->rt * cs > grid || kt < cs) continue;
+            const long long steps = (kt + cs - 1) / cs + (cs > 1 ? (pair == 2 ? 2 : 3) : 0);
             if (steps < best) { best = steps; cluster = cs; a.kslices = cs; }
         }
         if (a.kslices) grid = w->rt * a.kslices;
     }
     if (ctx->use_tc) {
         a.tm_w = w->tm_tc;
-#define GT(WMX, AMX, NN) launch_cluster(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, cluster, a)
+#define GT(WMX, AMX, NN) (pair == 2 ? launch_cluster(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE, 2>, dim3(grid), dim3(TcCfg<NN, 2>::THREADS), (size_t)TcCfg<NN, 2>::SMEM, cluster, a) \
+                                 : launch_cluster(ctx, stream, tc_stream_kernel<FMT_FP8, WMX, AMX, NN, EPI_DENSE>, dim3(grid), dim3(TcCfg<NN>::THREADS), (size_t)TcCfg<NN>::SMEM, cluster, a))
         if (mx) return ntok == 8 ? GT(1, 1, 8) : ntok == 16 ? GT(1, 1, 16) : ntok == 32 ? GT(1, 1, 32) : GT(1, 1, 64);
         return ntok == 8 ? GT(0, 0, 8) : ntok == 16 ? GT(0, 0, 16) : ntok == 32 ? GT(0, 0, 32) : GT(0, 0, 64);
 #undef GT

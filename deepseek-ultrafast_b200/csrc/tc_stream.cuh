@@ -51,7 +51,7 @@ struct TcCfg {
     static constexpr int ACC_COLS = N * PAIR;        // tensor-memory columns of one accumulator-ring entry (per-tile mode)
     // accumulator ring (a power of two); with two tiles per entry eight entries are as deep as sixteen single ones, and the
     // shorter scale ring that goes with them keeps the static shared memory inside the budget
-    static constexpr int NB = PAIR == 2 ? 8 : ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;
+    static constexpr int NB = PAIR == 2 ? (ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2) : ACC_COLS <= 16 ? 16 : ACC_COLS <= 32 ? 8 : ACC_COLS <= 64 ? 4 : 2;
     // producer warps per kind (weights / activations), tiles dealt round-robin: a producer spends ~1100 cycles per tile
     // of its own (two barrier waits, the copies, the scale gathers); four of each kind measured no faster than two
     static constexpr int NP = 2;
@@ -96,8 +96,7 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
     // indexed by tile number needs no barrier of its own: a producer writing tile n has seen the MMAs of tile n - S
     // complete, which were issued only after the epilogue had released the accumulator of tile n - S - NB, and the
     // epilogue reads a tile's scales before it releases its accumulator.
-    constexpr int XSE = 4 * N * PAIR + (WMX ? 0 : 16);  // entry: N activation scales per K tile (+ the tile's weight scale, DS weights)
-    static_assert(PAIR == 1 || WMX, "two tiles per stage: weights with UE8M0 scales only (one fp32 weight scale slot per entry)");
+    constexpr int XSE = 4 * N * PAIR + (WMX ? 0 : 16);  // entry: N activation scales per K tile (+ the tiles' weight scales, DS weights)
     constexpr int XR = S + NB <= 16 ? 16 : 32;
     static_assert(S + NB <= XR, "scale ring shorter than stages + accumulators");
     __shared__ __align__(16) uint8_t s_xs[XR * XSE];
@@ -258,7 +257,10 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                     for (int pp = 0; pp < PAIR; ++pp)
                         cp_async4(AMX ? st + Cfg::SFB_OFF + pp * 512 + (n & 31) * 16 + (n >> 5) * 4 : xe + 4 * (pp * N + n), src + pp);
                 }
-                if (!WMX && lane == 31) cp_async4(xe + 4 * N * PAIR, ws_src + kt);
+                if (!WMX && lane == 31) {
+#pragma unroll
+                    for (int pp = 0; pp < PAIR; ++pp) cp_async4(xe + 4 * N * PAIR + 4 * pp, ws_src + kt * PAIR + pp);
+                }
                 cp_async_arrive_noinc(&full_bar[s]);
                 s += NP;
                 st += NP * Cfg::STAGE;
@@ -451,7 +453,10 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                 if (!dead && !mbar_wait(&tfull_bar[b], (gidx / NB) & 1, a.status, KID_TC, 4)) dead = true;
                 tc_fence_after();
                 {
-                    const float wds = (PER_TILE && !WMX) ? *(const float*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * N * PAIR) : 1.0f;
+                    float wdsp[PAIR];
+#pragma unroll
+                    for (int pp = 0; pp < PAIR; ++pp)
+                        wdsp[pp] = (PER_TILE && !WMX) ? *(const float*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * N * PAIR + 4 * pp) : 1.0f;
                     constexpr int CH = NC < 32 ? NC : 32;
                     // several issuers in the whole-K mode: part p of the entry holds a sum iff the group, which started at
                     // tile g0 and has gcnt tiles, contains a tile dealt to issuer p; the parts are added in a fixed order
@@ -489,6 +494,7 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                                 for (int j = 0; j < CH; j += 4) {
                                     const float4 t4 = *(const float4*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * (pp * N + cb + c0 + j));
                                     const float* vv = (PAIR == 2 && pp == 1) ? v1 : v;
+                                    const float wds = wdsp[pp];
                                     acc[c0 + j] = fmaf(vv[j], wds * t4.x, acc[c0 + j]);
                                     acc[c0 + j + 1] = fmaf(vv[j + 1], wds * t4.y, acc[c0 + j + 1]);
                                     acc[c0 + j + 2] = fmaf(vv[j + 2], wds * t4.z, acc[c0 + j + 2]);
