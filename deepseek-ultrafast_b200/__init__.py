@@ -38,6 +38,10 @@ class PlanStruct(C.Structure):
                 ("n_exp", C.c_int32), ("tile_rows", C.c_int32), ("max_tiles", C.c_int32)]
 
 
+class GemmOpts(C.Structure):
+    _fields_ = [("alpha", C.c_float), ("out_f32", C.c_int32), ("n_split", C.c_int32), ("ldo2", C.c_int32), ("out2", C.c_uint64)]
+
+
 class TensorInfo(C.Structure):
     _fields_ = [("dtype", C.c_char * 16), ("rank", C.c_int32), ("shape", C.c_int64 * 8), ("data", C.c_void_p), ("nbytes", C.c_size_t)]
 
@@ -89,6 +93,8 @@ ABI = {
     "dsuf_workspace_init": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_size_t]),
     "dsuf_gemm_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
                                   C.c_int32, C.c_float, C.c_uint64]),
+    "dsuf_gemm_fp8_ex": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
+                                     C.c_int32, C.POINTER(GemmOpts), C.c_uint64]),
     "dsuf_gemm_fp8_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
                                          C.c_int32, C.c_float]),
     "dsuf_probe_tensor_rate": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_double)]),
@@ -390,6 +396,22 @@ def gemm_fp8(ctx, w, xq, xs, m, out=None, alpha=1.0):
     ctx.check(lib().dsuf_gemm_fp8(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0),
                                   alpha, ctx.workspace.data_ptr()))
     return out
+
+
+def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None):
+    """dsuf_gemm_fp8_ex = ops::gemv with GemvOpts {alpha, out_f32, split} (ops.rs:165-193): fp32 or bf16 output, and with
+    ``n_split`` > 0 the weight rows from n_split on go to a second tensor.  Returns out, or (out, out2)."""
+    t = ctx.torch
+    dt = t.float32 if out_f32 else t.bfloat16
+    n1 = n_split if n_split > 0 else w.n
+    if out is None:
+        out = t.empty((m, n1), dtype=dt, device=xq.device)
+    if n_split > 0 and out2 is None:
+        out2 = t.empty((m, w.n - n_split), dtype=dt, device=xq.device)
+    o = GemmOpts(alpha, int(bool(out_f32)), n_split, out2.stride(0) if out2 is not None else 0, out2.data_ptr() if out2 is not None else 0)
+    ctx.check(lib().dsuf_gemm_fp8_ex(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0), C.byref(o),
+                                     ctx.workspace.data_ptr()))
+    return (out, out2) if n_split > 0 else out
 
 
 def gemm_fp8_static(ctx, w, xq, xs, m, out=None, alpha=1.0):

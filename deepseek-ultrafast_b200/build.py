@@ -52,10 +52,12 @@ def build(verbose=False):
         with ThreadPoolExecutor(max_workers=8) as ex:
             list(ex.map(lambda j: _compile(*j), jobs))
     if jobs or not os.path.exists(OUT):
-        cmd = [NVCC, "-shared", "-o", OUT, *objs, "-ccbin", "/usr/bin/g++", "-lcudart", "-lpthread"]
+        # link beside the target and rename: a reader never sees a half-written library
+        cmd = [NVCC, "-shared", "-o", OUT + ".tmp", *objs, "-ccbin", "/usr/bin/g++", "-lcudart", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
+        os.replace(OUT + ".tmp", OUT)
     if verbose:
         for s, _, log in jobs:
             print(open(log).read())

@@ -213,6 +213,14 @@ int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_
     return launch_stream_dense(ctx, (cudaStream_t)stream, w, (const void*)xq, (const void*)xs, m, (void*)out, ldo, alpha, (void*)workspace);
 }
 
+int32_t dsuf_gemm_fp8_ex(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
+                         int32_t ldo, const dsuf_gemm_opts* opts, uint64_t workspace) {
+    if (!ctx || !w || !opts) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, (xq & 15) == 0, "dsuf_gemm_fp8_ex: xq must be 16-byte aligned");
+    return launch_stream_dense(ctx, (cudaStream_t)stream, w, (const void*)xq, (const void*)xs, m, (void*)out, ldo, opts->alpha,
+                               (void*)workspace, nullptr, opts);
+}
+
 int32_t dsuf_moe_route(dsuf_ctx* ctx, void* stream, int32_t score_fn, uint64_t scores, uint64_t bias, int32_t t,
                        int32_t n_exp, int32_t topk, float route_scale, uint64_t ids_out, uint64_t w_out) {
     if (!ctx) return DSUF_E_BADARG;

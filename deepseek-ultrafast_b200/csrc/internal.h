@@ -105,7 +105,7 @@ int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x
                      const float* sumsq = nullptr, float eps = 0.f);
 int launch_row_sumsq(dsuf_ctx* ctx, cudaStream_t stream, const void* x, int ldx, int m, int k, float* out);
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
-                        void* out, int ldo, float alpha, void* workspace, int* counters_at = nullptr);
+                        void* out, int ldo, float alpha, void* workspace, int* counters_at = nullptr, const dsuf_gemm_opts* opts = nullptr);
 int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, int epi, int act_mode, const dsuf_moe_plan* plan,
                       const void* xq, const void* xs, float swiglu_limit, void* out, int ldo);
 int launch_route(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* scores, const float* bias, int t, int n_exp,

@@ -49,9 +49,23 @@ struct StreamArgs {
     float alpha;
     float swiglu_limit;
     int whole_items;  // dense: give every CTA whole row tiles (no stream-K partials) when that costs no extra wave
+    int out_f32;      // dense: 1 = fp32 output instead of bf16 (GemvOpts.out_f32, crates/engine/src/ops.rs:165-193)
+    int n_split;      // dense: > 0 = weight rows >= n_split go to out2 (row stride ldo2) at column row - n_split (GemvOpts.split)
+    void* out2;
+    int ldo2;
     int kslices;      // dense, tcgen05 kernel: > 0 = one row tile per cluster of `kslices` CTAs, each taking a slice of K;
                       // the slices are summed through distributed shared memory (no global partials)
 };
+
+// The dense epilogue's store: output element (token row `tok`, weight row `row`) with the caller's options -- the Store
+// epilogue of the reference's GEMV with out_f32 and n_split (crates/kernels/cu/gemv.cu:510-517, cu/tcgemm.cu:117-134).
+DSUF_DEV void dense_store(const StreamArgs& a, int tok, int row, float v) {
+    void* ob = a.out;
+    int ld = a.ldo, col = row;
+    if (a.n_split > 0 && row >= a.n_split) { ob = a.out2; ld = a.ldo2; col = row - a.n_split; }
+    if (a.out_f32) ((float*)ob)[(size_t)tok * ld + col] = v;
+    else ((__nv_bfloat16*)ob)[(size_t)tok * ld + col] = __float2bfloat16(v);
+}
 
 template <int FMT>
 struct StreamCfg {
@@ -321,14 +335,13 @@ __global__ void __launch_bounds__(STREAM_THREADS, 1) stream_gemv_kernel(const __
                         }
                     }
                     if (do_store) {
-                        bf16* o = (bf16*)a.out;
 #pragma unroll
                         for (int u = 0; u < NT8; ++u)
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const int tok = 8 * u + ((e & 1) ? cb : ca);
                                 const int row = rt * 128 + ((e & 2) ? rb : ra);
-                                if (tok < cnt && row < a.n_rows) o[(size_t)tok * a.ldo + row] = __float2bfloat16(acc[u][e] * a.alpha * unscale);
+                                if (tok < cnt && row < a.n_rows) dense_store(a, tok, row, acc[u][e] * a.alpha * unscale);
                             }
                     }
                 } else if (EPI == EPI_W13) {

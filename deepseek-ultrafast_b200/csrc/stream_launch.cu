@@ -95,12 +95,23 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
 }
 
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
-                        void* out, int ldo, float alpha, void* workspace, int* counters_at) {
+                        void* out, int ldo, float alpha, void* workspace, int* counters_at, const dsuf_gemm_opts* opts) {
     DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP8 && w->d.n_experts == 1, "dsuf_gemm_fp8: weight is not a dense FP8 weight");
-    DSUF_REQUIRE(ctx, ldo >= w->d.n, "dsuf_gemm_fp8: ldo %d < n %d", ldo, w->d.n);
+    const int n_first = (opts && opts->n_split > 0) ? opts->n_split : w->d.n;   // columns that go to `out`
+    DSUF_REQUIRE(ctx, ldo >= n_first, "dsuf_gemm_fp8: ldo %d < %d output columns", ldo, n_first);
     DSUF_REQUIRE(ctx, xq && xs && out, "dsuf_gemm_fp8: null pointer");
     StreamArgs a;
     fill_common(ctx, a, w);
+    if (opts) {
+        DSUF_REQUIRE(ctx, opts->n_split >= 0 && opts->n_split < w->d.n, "dsuf_gemm_fp8_ex: n_split (%d) must be in 0..n-1", opts->n_split);
+        DSUF_REQUIRE(ctx, opts->n_split == 0 || (opts->out2 && opts->ldo2 >= w->d.n - opts->n_split),
+                     "dsuf_gemm_fp8_ex: n_split needs out2 with ldo2 >= n - n_split");
+        a.out_f32 = opts->out_f32 ? 1 : 0;
+        a.n_split = opts->n_split;
+        a.out2 = (void*)opts->out2;
+        a.ldo2 = opts->ldo2;
+        alpha = opts->alpha;
+    }
     if (ctx->use_tc && m > 64) {
         // prefill-size M: 128-token tiles x pairs of weight row tiles (tc_prefill.cuh); needs no workspace
         DSUF_REQUIRE(ctx, (w->rt & 1) == 0, "dsuf_gemm_fp8: more than 64 token rows need an even number of 128-row weight tiles, got %d", w->rt);

@@ -345,11 +345,10 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                     }
                 }
             } else if (EPI == EPI_DENSE) {
-                bf16* o = (bf16*)a.out;
                 const int col = rt * 128 + r;
 #pragma unroll
                 for (int j = 0; j < CPT; ++j)
-                    if (cb + j < cnt && col < a.n_rows) o[(size_t)(xrow0 + cb + j) * a.ldo + col] = __float2bfloat16(acc[j] * a.alpha);
+                    if (cb + j < cnt && col < a.n_rows) dense_store(a, xrow0 + cb + j, col, acc[j] * a.alpha);
             } else {
                 float* o = (float*)a.out;
                 const int col = rt * 128 + r;

@@ -582,11 +582,10 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                         }
                     }
                     if (do_store) {
-                        bf16* o = (bf16*)a.out;
                         const int row = rt * 128 + r;
 #pragma unroll
                         for (int j = 0; j < NC; ++j)
-                            if (cb + j < cnt && row < a.n_rows) o[(size_t)(cb + j) * a.ldo + row] = __float2bfloat16(acc[j] * a.alpha);
+                            if (cb + j < cnt && row < a.n_rows) dense_store(a, cb + j, row, acc[j] * a.alpha);
                     }
                 } else if (EPI == EPI_W13) {
                     // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group);

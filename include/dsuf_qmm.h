@@ -187,6 +187,24 @@ int32_t dsuf_workspace_init(dsuf_ctx* ctx, void* stream, uint64_t workspace, siz
 int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
                       int32_t ldo, float alpha, uint64_t workspace);
 
+/* GemvOpts (crates/engine/src/ops.rs:165-193), the part that concerns the Store epilogue of a dense projection:
+ *   alpha    the output scale
+ *   out_f32  1 = fp32 output (out / out2 are float buffers) instead of bf16 (GemvOpts.out_f32; cu/gemv.cu:510-517)
+ *   n_split  > 0 = weight rows [n_split, n) are written to out2 (row stride ldo2) at column row - n_split, rows
+ *            [0, n_split) to out (GemvOpts.split: one launch for two projections merged along n, e.g. Loader::fp8_merged)
+ * The SwiGLU / AtomicAdd / sqrt-softplus / Partial epilogue kinds of the reference's dense GEMV and its fused RoPE are
+ * not offered (the expert GEMMs have their own SwiGLU epilogue). */
+typedef struct {
+    float alpha;
+    int32_t out_f32;
+    int32_t n_split;
+    int32_t ldo2;
+    uint64_t out2;
+} dsuf_gemm_opts;
+/* dsuf_gemm_fp8 with options; same kernels, any number of token rows. */
+int32_t dsuf_gemm_fp8_ex(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
+                         int32_t ldo, const dsuf_gemm_opts* opts, uint64_t workspace);
+
 /* No counterpart in the reference.  Same function as dsuf_gemm_fp8 for callers that cannot allocate device memory
  * (an engine that spent its device budget on one start-up arena, a plugin without its own allocator, a caller for which
  * an allocation would synchronise the device): the stream-K scratch is a fixed array inside the library's device image

@@ -170,6 +170,35 @@ def test_dense_gemm_prefill_rejects_odd_row_tile_count(pkg, ctx):
         pkg.gemv(ctx, w, xt.cuda())
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("n,k,m,split", [(1024, 2048, 4, 384), (7168, 2048, 3, 4096), (512, 1024, 16, 0), (512, 1024, 200, 128), (2048, 512, 40, 1000)])
+def test_dense_gemv_options_fp32_output_and_column_split(pkg, ctx, mode, n, k, m, split):
+    """GemvOpts' out_f32 and split on every dense kernel (decode stream-K / cluster K-split, prefill tiles): the fp32
+    output rounds to the bf16 output bit for bit, and the two halves of a split output are the columns of the unsplit one."""
+    if not ctx.tcgen05 and m > 16:
+        pytest.skip("the mma.sync decode kernel takes at most 16 rows per call")
+    g = seeded(n + k + m + split)
+    xt, xn = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, n, k, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(mode, wn)
+    w = pkg.Weight.dense_fp8(ctx, mode, wq, ws)
+    xq, xs = pkg.act_quant(ctx, mode, xt.cuda())
+    base = pkg.gemm_fp8(ctx, w, xq, xs, m, alpha=0.5)
+    f32 = pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, out_f32=True)
+    torch.cuda.synchronize()
+    assert f32.dtype == torch.float32 and torch.equal(f32.bfloat16().view(torch.uint16), base.view(torch.uint16))
+    if split:
+        a, b = pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, n_split=split)
+        af, bf = pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, n_split=split, out_f32=True)
+        torch.cuda.synchronize()
+        assert torch.equal(a.view(torch.uint16), base[:, :split].contiguous().view(torch.uint16))
+        assert torch.equal(b.view(torch.uint16), base[:, split:].contiguous().view(torch.uint16))
+        assert torch.equal(af, f32[:, :split]) and torch.equal(bf, f32[:, split:])
+        with pytest.raises(pkg.DsufError):
+            pkg.gemm_fp8_ex(ctx, w, xq, xs, m, n_split=n)          # nothing left for the second output
+    assert ctx.status().code == 0
+
+
 def test_dense_gemv_linearity_and_alpha(pkg, ctx):
     """Size-independent property: out(alpha) = alpha * out(1) up to bf16 rounding."""
     g = seeded(3)
