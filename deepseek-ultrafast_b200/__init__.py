@@ -39,7 +39,8 @@ class PlanStruct(C.Structure):
 
 
 class GemmOpts(C.Structure):
-    _fields_ = [("alpha", C.c_float), ("out_f32", C.c_int32), ("n_split", C.c_int32), ("ldo2", C.c_int32), ("out2", C.c_uint64)]
+    _fields_ = [("alpha", C.c_float), ("out_f32", C.c_int32), ("n_split", C.c_int32), ("ldo2", C.c_int32), ("out2", C.c_uint64),
+                ("epilogue", C.c_int32), ("swiglu_limit", C.c_float)]
 
 
 class TensorInfo(C.Structure):
@@ -67,6 +68,7 @@ ABI = {
     "dsuf_quant_fp4_weight_host": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "dsuf_packed_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "dsuf_pack_fp8_weight": (C.c_int32, [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "dsuf_pack_fp8_weight_gate_up": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "dsuf_pack_fp4_weight": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "dsuf_ckpt_open": (C.c_int32, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "dsuf_ckpt_close": (C.c_int32, [C.c_void_p]),
@@ -335,6 +337,20 @@ class Weight:
         return Weight(ctx, FMT_FP8, mode, n, k, 1, False, tiles, sds)
 
     @staticmethod
+    def dense_fp8_gate_up(ctx, codes, scales):
+        """The FP8 shared expert's gate/up weight: MX codes u8 [2*inter][k] (gate rows, then up rows) + u8 [2*inter/32][k/32]
+        scales, rows interleaved for the SwiGLU epilogue (gemm_fp8_swiglu)."""
+        t = ctx.torch
+        codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        scales = np.ascontiguousarray(scales, dtype=np.uint8)
+        n, k = codes.shape
+        out = np.empty(lib().dsuf_packed_bytes(FMT_FP8, MODE_MX, n, k), np.uint8)
+        rc = lib().dsuf_pack_fp8_weight_gate_up(_np_ptr(codes), _np_ptr(scales), n, k, _np_ptr(out))
+        if rc:
+            raise DsufError(rc, "dsuf_pack_fp8_weight_gate_up")
+        return Weight(ctx, FMT_FP8, MODE_MX, n, k, 1, True, t.from_numpy(out).to(ctx.device))
+
+    @staticmethod
     def experts_fp4(ctx, codes, scales, gate_up):
         """codes u8 [E][n][k/2], scales u8 [E][n][k/32] (host arrays); gate_up: rows are [gate; up]."""
         t = ctx.torch
@@ -398,6 +414,18 @@ def gemm_fp8(ctx, w, xq, xs, m, out=None, alpha=1.0):
     return out
 
 
+def gemm_fp8_swiglu(ctx, w, xq, xs, m, out=None, swiglu_limit=0.0):
+    """The FP8 shared expert's gate/up projection (gemm_tc with Epilogue::SwiGlu, model.rs:3081-3084): w packed by
+    Weight.dense_fp8_gate_up; returns bf16 [m][n/2] = silu(gate) * up."""
+    t = ctx.torch
+    if out is None:
+        out = t.empty((m, w.n // 2), dtype=t.bfloat16, device=xq.device)
+    o = GemmOpts(1.0, 0, 0, 0, 0, 1, swiglu_limit)
+    ctx.check(lib().dsuf_gemm_fp8_ex(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0), C.byref(o),
+                                     ctx.workspace.data_ptr()))
+    return out
+
+
 def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None):
     """dsuf_gemm_fp8_ex = ops::gemv with GemvOpts {alpha, out_f32, split} (ops.rs:165-193): fp32 or bf16 output, and with
     ``n_split`` > 0 the weight rows from n_split on go to a second tensor.  Returns out, or (out, out2)."""
@@ -408,7 +436,7 @@ def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None
         out = t.empty((m, n1), dtype=dt, device=xq.device)
     if n_split > 0 and out2 is None:
         out2 = t.empty((m, w.n - n_split), dtype=dt, device=xq.device)
-    o = GemmOpts(alpha, int(bool(out_f32)), n_split, out2.stride(0) if out2 is not None else 0, out2.data_ptr() if out2 is not None else 0)
+    o = GemmOpts(alpha, int(bool(out_f32)), n_split, out2.stride(0) if out2 is not None else 0, out2.data_ptr() if out2 is not None else 0, 0, 0.0)
     ctx.check(lib().dsuf_gemm_fp8_ex(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0), C.byref(o),
                                      ctx.workspace.data_ptr()))
     return (out, out2) if n_split > 0 else out

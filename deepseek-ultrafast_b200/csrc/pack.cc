@@ -162,6 +162,32 @@ int32_t dsuf_pack_fp8_weight(int32_t mode, const uint8_t* codes, const void* sca
     return DSUF_OK;
 }
 
+int32_t dsuf_pack_fp8_weight_gate_up(const uint8_t* codes, const uint8_t* scales, int32_t n, int32_t k, uint8_t* out) {
+    // FP8 MX weight [n = 2 inter][k], gate rows first, then up rows: the same 8 + 8 row interleave per 16-row group as the
+    // FP4 expert packer, every row keeping the scales of the 32 x 32 block it came from
+    if (!codes || !scales || !out || n <= 0 || k <= 0 || k % 128 || n % 64) return DSUF_E_BADARG;
+    const int rt = (n + 127) / 128, kt = k / 128, inter = n / 2;
+    const size_t rec = 16384 + 512;
+    parallel_for(rt, [=](int t) {
+        for (int c = 0; c < kt; ++c) {
+            uint8_t* rec_p = out + ((size_t)t * kt + c) * rec;
+            uint8_t* sf = rec_p + 16384;
+            for (int r = 0; r < 128; ++r) {
+                const int pr = t * 128 + r;
+                if (pr < n) {
+                    const int src = ((pr % 16) / 8 ? inter : 0) + (pr / 16) * 8 + pr % 8;
+                    memcpy(rec_p + r * 128, codes + (size_t)src * k + c * 128, 128);
+                    for (int b = 0; b < 4; ++b) sf[(r % 32) * 16 + (r / 32) * 4 + b] = scales[(size_t)(src / 32) * (k / 32) + c * 4 + b];
+                } else {
+                    memset(rec_p + r * 128, 0, 128);
+                    for (int b = 0; b < 4; ++b) sf[(r % 32) * 16 + (r / 32) * 4 + b] = 127;
+                }
+            }
+        }
+    });
+    return DSUF_OK;
+}
+
 int32_t dsuf_pack_fp4_weight(const uint8_t* codes, const uint8_t* scales, int32_t n, int32_t k, int32_t gate_up, uint8_t* out) {
     if (!codes || !scales || !out || n <= 0 || k <= 0 || k % 128) return DSUF_E_BADARG;
     if (gate_up && n % 16) return DSUF_E_BADARG;

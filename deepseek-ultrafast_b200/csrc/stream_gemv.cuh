@@ -49,6 +49,7 @@ struct StreamArgs {
     float alpha;
     float swiglu_limit;
     int whole_items;  // dense: give every CTA whole row tiles (no stream-K partials) when that costs no extra wave
+    int swiglu;       // dense: 1 = the weight holds interleaved gate / up rows and the epilogue is SwiGLU (bf16 [m][n/2] out)
     int out_f32;      // dense: 1 = fp32 output instead of bf16 (GemvOpts.out_f32, crates/engine/src/ops.rs:165-193)
     int n_split;      // dense: > 0 = weight rows >= n_split go to out2 (row stride ldo2) at column row - n_split (GemvOpts.split)
     void* out2;

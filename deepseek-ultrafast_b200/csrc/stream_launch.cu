@@ -97,15 +97,26 @@ static void fill_common(dsuf_ctx* ctx, StreamArgs& a, const dsuf_weight* w) {
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,
                         void* out, int ldo, float alpha, void* workspace, int* counters_at, const dsuf_gemm_opts* opts) {
     DSUF_REQUIRE(ctx, w->d.fmt == DSUF_FMT_FP8 && w->d.n_experts == 1, "dsuf_gemm_fp8: weight is not a dense FP8 weight");
-    const int n_first = (opts && opts->n_split > 0) ? opts->n_split : w->d.n;   // columns that go to `out`
+    const int n_first = (opts && opts->epilogue == DSUF_EPI_SWIGLU) ? w->d.n / 2 : (opts && opts->n_split > 0) ? opts->n_split : w->d.n;   // columns of `out`
     DSUF_REQUIRE(ctx, ldo >= n_first, "dsuf_gemm_fp8: ldo %d < %d output columns", ldo, n_first);
     DSUF_REQUIRE(ctx, xq && xs && out, "dsuf_gemm_fp8: null pointer");
+    DSUF_REQUIRE(ctx, !w->d.gate_up || (opts && opts->epilogue == DSUF_EPI_SWIGLU),
+                 "dsuf_gemm_fp8: a gate/up-interleaved weight is only meaningful with the SwiGLU epilogue (dsuf_gemm_fp8_ex)");
     StreamArgs a;
     fill_common(ctx, a, w);
     if (opts) {
         DSUF_REQUIRE(ctx, opts->n_split >= 0 && opts->n_split < w->d.n, "dsuf_gemm_fp8_ex: n_split (%d) must be in 0..n-1", opts->n_split);
         DSUF_REQUIRE(ctx, opts->n_split == 0 || (opts->out2 && opts->ldo2 >= w->d.n - opts->n_split),
                      "dsuf_gemm_fp8_ex: n_split needs out2 with ldo2 >= n - n_split");
+        DSUF_REQUIRE(ctx, opts->epilogue == DSUF_EPI_STORE || opts->epilogue == DSUF_EPI_SWIGLU, "dsuf_gemm_fp8_ex: unknown epilogue %d", opts->epilogue);
+        if (opts->epilogue == DSUF_EPI_SWIGLU) {
+            DSUF_REQUIRE(ctx, w->d.gate_up && w->d.mode == DSUF_MODE_MX, "dsuf_gemm_fp8_ex: the SwiGLU epilogue needs an MX weight packed with dsuf_pack_fp8_weight_gate_up");
+            DSUF_REQUIRE(ctx, ctx->use_tc, "dsuf_gemm_fp8_ex: the SwiGLU epilogue runs on the tcgen05 path only");
+            DSUF_REQUIRE(ctx, opts->alpha == 1.0f && !opts->out_f32 && opts->n_split == 0, "dsuf_gemm_fp8_ex: the SwiGLU epilogue takes alpha = 1, bf16 output, no split");
+            DSUF_REQUIRE(ctx, ldo >= w->d.n / 2, "dsuf_gemm_fp8_ex: ldo %d < n / 2 = %d activation columns", ldo, w->d.n / 2);
+            a.swiglu = 1;
+            a.swiglu_limit = opts->swiglu_limit;
+        }
         a.out_f32 = opts->out_f32 ? 1 : 0;
         a.n_split = opts->n_split;
         a.out2 = (void*)opts->out2;
@@ -114,7 +125,6 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     }
     if (ctx->use_tc && m > 64) {
         // prefill-size M: 128-token tiles x pairs of weight row tiles (tc_prefill.cuh); needs no workspace
-        DSUF_REQUIRE(ctx, (w->rt & 1) == 0, "dsuf_gemm_fp8: more than 64 token rows need an even number of 128-row weight tiles, got %d", w->rt);
         const bool ds = w->d.mode != DSUF_MODE_MX;
         int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, m, ds ? 64 : 128);
         if (rc) return rc;
@@ -199,7 +209,7 @@ int launch_stream_moe(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, 
     StreamArgs a;
     fill_common(ctx, a, w);
     const int nt8 = plan->tile_rows / 8;
-    const bool prefill_pairs = ctx->use_tc && plan->tile_rows == 128 && (w->rt & 1) == 0;
+    const bool prefill_pairs = ctx->use_tc && plan->tile_rows == 128;
     int rc = encode_x_map(ctx, &a.tm_x, xq, w->d.k, plan->p, plan->tile_rows);
     if (rc) return rc;
     a.xscale = xs;

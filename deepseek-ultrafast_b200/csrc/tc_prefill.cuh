@@ -76,7 +76,9 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x, c = blockIdx.x;
-    const int RT = a.RT, KT = a.KT, RP = RT >> 1;  // row-tile pairs per expert (RT is even: checked by the launcher)
+    // row-tile pairs per expert; with an odd number of row tiles the last pair's second half streams the last tile once
+    // more (its outputs are dropped): one step in RT of the weight bytes read twice instead of a second kernel
+    const int RT = a.RT, KT = a.KT, RP = (RT + 1) >> 1;
     bool dead = false;  // set by the first expired wait: nothing is waited for again, the loops stay finite
 
     if (warp == 1) {
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                 const int4 sl = slot_of(slot);
                 if (sl.z <= 0) continue;  // second half of a slot with at most NTOK rows: every role skips it
                 const int xrow0 = sl.y;
-                int tile = (int)((((long long)sl.x * RT) + 2 * rp + j) * KT);
+                int tile = (int)((((long long)sl.x * RT) + min(2 * rp + j, RT - 1)) * KT);
                 const uint8_t* sf_src = a.wtiles + (size_t)tile * a.rec_bytes + a.codes_bytes;
                 for (int kt = 0; kt < KT; ++kt, ++n) {
                     if (n >= S && !dead && !mbar_wait(&empty_bar[s], ph ^ 1, a.status, KID_TCP, 1 + j)) dead = true;
@@ -289,7 +291,7 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                 for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
                 for (int kt = 0; kt < KT; ++kt, ++n) {
                     // DS weights: the tile's fp32 128x128 block scale, fetched before the wait
-                    const float wds = WMX ? 1.0f : __ldg(a.wscale_ds + (size_t)rt * KT + kt);
+                    const float wds = WMX ? 1.0f : __ldg(a.wscale_ds + (size_t)min(rt, RT - 1) * KT + kt);
                     const int g = 2 * n + ga, ai = g % 3;
                     if (!dead && !mbar_wait(&tfull_bar[ai * 2 + ga], (uint32_t)((g / 6) & 1), a.status, KID_TCP, 5)) dead = true;
                     tc_fence_after();
@@ -323,7 +325,8 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                 rw0 = (cb + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + lane) : 0.f;
                 if (CPT > 32) rw1 = (cb + 32 + lane < cnt) ? __ldg(a.row_w + xrow0 + cb + 32 + lane) : 0.f;
             }
-            if (EPI == EPI_W13) {
+            if (EPI == EPI_W13 || (EPI == EPI_DENSE && a.swiglu)) {
+                // (EPI_DENSE with the SwiGLU option: the FP8 shared expert's gate/up weight, no routing weight)
                 // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group); after the
                 // exchange the gate lane finishes column j, the up lane column j + 1.
                 // SwiGLU as crates/kernels/cu/gemv.cu:470-483: bf16 rounds, optional clamp, routing weight folded in
@@ -335,8 +338,8 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                     const float o0 = __shfl_xor_sync(0xffffffffu, acc[j], 8);
                     const float o1 = __shfl_xor_sync(0xffffffffu, acc[j + 1], 8);
                     const int col = is_gate ? j : j + 1;
-                    const float rw = __shfl_sync(0xffffffffu, j < 32 ? rw0 : rw1, col & 31);
-                    if (cb + col < cnt) {
+                    const float rw = EPI == EPI_W13 ? __shfl_sync(0xffffffffu, j < 32 ? rw0 : rw1, col & 31) : 1.0f;
+                    if (cb + col < cnt && rt < RT) {   // (rt == RT: the repeated tile of an odd row-tile count)
                         const int row = xrow0 + cb + col;
                         float gt = bf16_round(is_gate ? acc[j] : o1), up = bf16_round(is_gate ? o0 : acc[j + 1]);
                         if (L > 0.f) { up = fminf(fmaxf(up, -L), L); gt = fminf(gt, L); }

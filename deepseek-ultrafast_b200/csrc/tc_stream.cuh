@@ -583,9 +583,28 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                     }
                     if (do_store) {
                         const int row = rt * 128 + r;
+                        if (a.swiglu) {
+                            // gate / up rows interleaved 8 + 8 per 16-row group: lanes l and l^8 exchange, as in the expert
+                            // epilogue below, without a routing weight (the shared expert applies to every token)
+                            bf16* ocol = (bf16*)a.out + rt * 64 + (r >> 4) * 8 + (r & 7);
+                            const float L = a.swiglu_limit;
+                            const bool is_gate = (r & 8) == 0;
 #pragma unroll
-                        for (int j = 0; j < NC; ++j)
-                            if (cb + j < cnt && row < a.n_rows) dense_store(a, cb + j, row, acc[j] * a.alpha);
+                            for (int j = 0; j < NC; j += 2) {
+                                const float o0 = __shfl_xor_sync(0xffffffffu, acc[j], 8);
+                                const float o1 = __shfl_xor_sync(0xffffffffu, acc[j + 1], 8);
+                                const int col = is_gate ? j : j + 1;
+                                if (cb + col < cnt && row < a.n_rows) {
+                                    float gt = bf16_round(is_gate ? acc[j] : o1), up = bf16_round(is_gate ? o0 : acc[j + 1]);
+                                    if (L > 0.f) { up = fminf(fmaxf(up, -L), L); gt = fminf(gt, L); }
+                                    ocol[(size_t)(cb + col) * a.ldo] = __float2bfloat16(gt / (1.0f + expf(-gt)) * up);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < NC; ++j)
+                                if (cb + j < cnt && row < a.n_rows) dense_store(a, cb + j, row, acc[j] * a.alpha);
+                        }
                     }
                 } else if (EPI == EPI_W13) {
                     // lanes l and l^8 hold a gate row and its up row (rows 0..7 / 8..15 of every 16-row group);

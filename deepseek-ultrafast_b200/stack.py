@@ -63,7 +63,7 @@ class LayerStack:
         ctx, w = self.ctx, self.dense[l]
         act_quant(ctx, w.mode, x, self.xq, self.xs)
         T = x.shape[0]
-        if ctx.tcgen05 and (T <= 64 or (w.n // 128) % 2 == 0):
+        if ctx.tcgen05:
             return gemm_fp8(ctx, w, self.xq, self.xs, T, out)   # one launch: decode kernel up to 64 rows, prefill kernel above
         slab = 64 if ctx.tcgen05 else 16
         for r0 in range(0, T, slab):
@@ -86,7 +86,7 @@ class LayerStack:
         cfg = self.cfg
         slab = 64 if self.ctx.tcgen05 else 16
         slabs = (cfg.tokens + slab - 1) // slab
-        if self.ctx.tcgen05 and (cfg.tokens <= 64 or (cfg.hidden // 128) % 2 == 0):
+        if self.ctx.tcgen05:
             slabs = 1
         # act_quant + dense slabs + front end (router + plan + gather/quant: 1 launch up to 1024 pairs, else 1 + 3 + 1)
         # + w13 + quant + w2 + unpermute

@@ -98,6 +98,11 @@ int32_t dsuf_quant_fp4_weight_host(const uint16_t* w, int32_t n, int32_t k, uint
  * n is padded up to a multiple of 128 with zero rows; k must be a multiple of 128. */
 size_t dsuf_packed_bytes(int32_t fmt, int32_t mode, int32_t n, int32_t k);
 int32_t dsuf_pack_fp8_weight(int32_t mode, const uint8_t* codes, const void* scales, int32_t n, int32_t k, uint8_t* out);
+/* The FP8 shared expert's gate/up weight (the w1 / w3 merge of Loader::layer, weights.rs:447-470, tile_fp8_k64 in
+ * crates/model/src/formats.rs:120-143): MX codes [2*inter][k] with gate rows first, then up rows, and their 32x32 UE8M0
+ * scales, packed with the same 8 + 8 gate / up row interleave as the FP4 experts, for dsuf_gemm_fp8_ex with the SwiGLU
+ * epilogue (set dsuf_weight_desc.gate_up).  n % 64 == 0. */
+int32_t dsuf_pack_fp8_weight_gate_up(const uint8_t* codes, const uint8_t* scales, int32_t n, int32_t k, uint8_t* out);
 /* gate_up != 0: codes/scales are [2*inter][k] with gate rows first, then up rows (n = 2*inter); rows are
  * interleaved per 16-row group as 8 gate + the 8 matching up rows (the reference interleaves 32+32 per
  * 64-row quad, packing.rs:237-241) so the SwiGLU epilogue finds both halves in one thread. */
@@ -182,8 +187,7 @@ int32_t dsuf_workspace_init(dsuf_ctx* ctx, void* stream, uint64_t workspace, siz
  * out[m][n] (bf16, row stride ldo) = alpha * W . dequant(xq, xs).  Activations come pre-quantized from
  * dsuf_act_quant_fp8 in the weight's geometry.  Token rows per call: 1..16 on the mma.sync decode path; on the
  * tcgen05 path 1..64 take the weight-streaming kernel (one pass over W, uses the workspace) and any m > 64 takes the
- * prefill kernel (128-token tiles x pairs of 128-row weight tiles; n/128 must be even; the workspace is not
- * touched and may be 0). */
+ * prefill kernel (128-token tiles x pairs of 128-row weight tiles; the workspace is not touched and may be 0). */
 int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
                       int32_t ldo, float alpha, uint64_t workspace);
 
@@ -192,15 +196,21 @@ int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_
  *   out_f32  1 = fp32 output (out / out2 are float buffers) instead of bf16 (GemvOpts.out_f32; cu/gemv.cu:510-517)
  *   n_split  > 0 = weight rows [n_split, n) are written to out2 (row stride ldo2) at column row - n_split, rows
  *            [0, n_split) to out (GemvOpts.split: one launch for two projections merged along n, e.g. Loader::fp8_merged)
- * The SwiGLU / AtomicAdd / sqrt-softplus / Partial epilogue kinds of the reference's dense GEMV and its fused RoPE are
- * not offered (the expert GEMMs have their own SwiGLU epilogue). */
+ * The AtomicAdd / sqrt-softplus / Partial epilogue kinds of the reference's dense GEMV and its fused RoPE are not offered. */
 typedef struct {
     float alpha;
     int32_t out_f32;
     int32_t n_split;
     int32_t ldo2;
     uint64_t out2;
+    int32_t epilogue;      /* DSUF_EPI_STORE or DSUF_EPI_SWIGLU */
+    float swiglu_limit;    /* SwiGLU: clamp as cu/gemv.cu:470-483 when > 0 */
 } dsuf_gemm_opts;
+/* Epilogue::Store / Epilogue::SwiGlu (crates/engine/src/ops.rs:137-144).  SWIGLU: the weight holds gate and up rows
+ * (packed by dsuf_pack_fp8_weight_gate_up, MX scales, tcgen05 path) and out receives bf16 [m][n/2] =
+ * bf16(silu(bf16 gate) * bf16 up), the reference's shared-expert gate/up projection (gemm_tc with Epilogue::SwiGlu,
+ * model.rs:3081-3084; cu/tcgemm.cu:89-110); alpha must be 1, out_f32 0, n_split 0. */
+enum { DSUF_EPI_STORE = 0, DSUF_EPI_SWIGLU = 1 };
 /* dsuf_gemm_fp8 with options; same kernels, any number of token rows. */
 int32_t dsuf_gemm_fp8_ex(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
                          int32_t ldo, const dsuf_gemm_opts* opts, uint64_t workspace);

@@ -158,16 +158,14 @@ def test_dense_gemv_cluster_k_split(pkg, ctx, mode, n, k, m):
     assert rel(a.float().cpu().numpy(), b.float().cpu().numpy()) < 2e-3
 
 
-def test_dense_gemm_prefill_rejects_odd_row_tile_count(pkg, ctx):
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("n,k,m", [(384, 256, 100), (128, 512, 65), (640, 1024, 300)])
+def test_dense_gemm_prefill_odd_number_of_row_tiles(pkg, ctx, mode, n, k, m):
+    """The prefill kernel walks weight row tiles in pairs; with an odd number of them (3, 1, 5) the last pair's second
+    half repeats the last tile and its outputs are dropped."""
     if not ctx.tcgen05:
         pytest.skip("tcgen05 path only")
-    g = seeded(5)
-    xt, _ = randn_bf16(g, 100, 256)
-    _, wn = randn_bf16(g, 384, 256, std=0.02)
-    wq, ws = oracle.quant_fp8_weight(1, wn)
-    w = pkg.Weight.dense_fp8(ctx, 1, wq, ws)
-    with pytest.raises(pkg.DsufError):
-        pkg.gemv(ctx, w, xt.cuda())
+    _dense_case(pkg, ctx, mode, n, k, m, seed=n + k + m)
 
 
 @pytest.mark.parametrize("mode", [0, 1])
@@ -197,6 +195,35 @@ def test_dense_gemv_options_fp32_output_and_column_split(pkg, ctx, mode, n, k, m
         with pytest.raises(pkg.DsufError):
             pkg.gemm_fp8_ex(ctx, w, xq, xs, m, n_split=n)          # nothing left for the second output
     assert ctx.status().code == 0
+
+
+@pytest.mark.parametrize("m,limit", [(5, 0.0), (64, 0.0), (200, 0.0), (16, 0.04)])
+def test_fp8_shared_expert_gate_up_with_swiglu_epilogue(pkg, ctx, m, limit):
+    """The FP8 shared expert's gate/up projection: one dense FP8 (MX) GEMM over interleaved gate / up rows with the SwiGLU
+    epilogue (gemm_tc with Epilogue::SwiGlu, model.rs:3081-3084), decode (m <= 64: cluster K-split / stream-K) and prefill
+    kernels, against the oracle's GEMM followed by bf16(silu(bf16 gate) * bf16 up) with the optional clamp."""
+    if not ctx.tcgen05:
+        pytest.skip("the SwiGLU epilogue on dense weights is offered on the tcgen05 path")
+    inter, k = 256, 1024
+    g = seeded(300 + m)
+    xt, xn = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, 2 * inter, k, std=0.05)
+    wq, ws = oracle.quant_fp8_weight(oracle.MODE_MX, wn)
+    W = pkg.Weight.dense_fp8_gate_up(ctx, wq, ws)
+    xq, xs = pkg.act_quant(ctx, pkg.MODE_MX, xt.cuda())
+    act = pkg.gemm_fp8_swiglu(ctx, W, xq, xs, m, swiglu_limit=limit)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    xqo, xso = oracle.act_quant(oracle.MODE_MX, xn)
+    _, f = oracle.gemm_fp8(oracle.MODE_MX, wq, ws, xqo, xso)
+    b = lambda a: oracle.bf16_to_f32(oracle.f32_to_bf16(a))
+    gt, up = b(f[:, :inter]), b(f[:, inter:])
+    if limit > 0:
+        up, gt = np.clip(up, -limit, limit), np.minimum(gt, limit)
+    want = b(gt / (1.0 + np.exp(-gt)) * up)
+    assert rel(act.float().cpu().numpy(), want) < TOL
+    with pytest.raises(pkg.DsufError, match="SwiGLU"):
+        pkg.gemm_fp8(ctx, W, xq, xs, m)        # a plain store would hand out interleaved rows
 
 
 def test_dense_gemv_linearity_and_alpha(pkg, ctx):
@@ -418,8 +445,8 @@ def test_moe_layer_prefill_tiles_of_128_rows(pkg, ctx, act_mode, T, E, K):
 
 @pytest.mark.parametrize("act_mode", [0, 1])
 def test_moe_layer_prefill_odd_number_of_row_tiles(pkg, ctx, act_mode):
-    """The prefill kernel pairs weight row tiles; the down projection of a 384-wide model has 3 row tiles and takes the
-    single-tile kernel instead (the gate/up projection, 2 row tiles x 3 K tiles, still takes the paired one)."""
+    """The prefill kernel pairs weight row tiles; the down projection of a 384-wide model has 3 row tiles: its last pair
+    repeats the third tile and drops the repeated outputs (the gate/up projection has 2 row tiles x 3 K tiles)."""
     if not ctx.tcgen05:
         pytest.skip("128-row plans run on the tcgen05 path only")
     _moe_case(pkg, ctx, act_mode, T=300, H=384, I=128, E=4, K=2, tile_rows=128, seed=11)
