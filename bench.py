@@ -45,7 +45,8 @@ def peaks():
 
 def workload_config(tokens, world, eager=False):
     """The `config` object of the JSON line; both arms print the same keys."""
-    return {"workload": "cfg4: 4 layers x (FP8 7168x7168 dense + 256-expert top-8 MXFP4 MoE), %d-token decode step" % tokens,
+    leg = "decode step" if tokens <= 1024 else "prefill"
+    return {"workload": "cfg4: 4 layers x (FP8 7168x7168 dense + 256-expert top-8 MXFP4 MoE), %d-token %s" % (tokens, leg),
             "tokens": tokens, "hidden": H, "experts": E, "topk": TOPK, "inter": I, "layers": LAYERS,
             "parallelism": "ep%d" % world, "step_launch": "eager" if eager else "cuda_graph",
             "l2": "weights read per step (>= 6 GB per GPU) exceed the 126 MB L2"}
@@ -562,7 +563,7 @@ def run_ours(args):
                 "ncu dram__bytes_read+write of the 64-expert small case (profiles/tc_stream_kernel_fp4_w13_decode_small_case.md), "
                 "per active expert, times this launch's active experts (traffic grows with the experts streamed)"}
     result = {
-        "metric": METRIC, "value": round(T / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if T <= 1024 else "moe_layer_stack_prefill_tokens_per_s", "value": round(T / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp8_e4m3 x {fp8_e4m3, mxfp4_e2m1}, fp32 accumulate", "data": "synthetic",
         "config": workload_config(T, world, args.no_graph),
@@ -572,6 +573,9 @@ def run_ours(args):
         "roofline": roofline, "clocks": clocks, "device_status": st.code,
         "exchange": stack.exchange_path() if world > 1 else "none (one GPU)",
     }
+    if T > 1024:
+        result["stack_tflops"] = round(LAYERS * (2.0 * T * H * H + 6.0 * T * TOPK * I * H) / (ms * 1e-3) / 1e12, 1)
+        result["roofline"]["note"] = "prefill-size batch: the HBM figure of the gate/up kernel is not its bound; see stack_tflops"
     if world > 1:
         result["exchange_fallback_reason"] = stack.peer_error
         result["parity_rel_err"] = parity
@@ -687,6 +691,74 @@ def small_case(args):
                       "active_experts": int(torch.unique(ids).numel()), "device_status": int(ctx.status().code)}))
 
 
+def exchange_bench(args):
+    """The expert-parallel exchanges alone, under torch.distributed.run: this library's peer-memory kernels (gather of
+    column slices = dispatch, all-reduce, combine fused with the unpermute) beside NCCL's all-gather / all-reduce on the
+    same [64][7168] bf16 rows, each as a CUDA graph of 20 calls replayed 10 times; microseconds per call (max over
+    ranks) and the bytes a rank pulls over NVLink per call."""
+    import datetime
+    import torch
+    import torch.distributed as dist
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=120))
+    pkg = load_package()
+    ctx = pkg.Ctx(local)
+    ctx.set_wait_budget_us(500000)
+    T = args.tokens
+    peer = pkg.PeerAllReduce(ctx, dist, rank, world)
+    bufs = [peer.buffer((T, H)) for _ in range(2)]
+    for b in bufs:
+        b.copy_(torch.randn(T, H, device="cuda").bfloat16())
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    plan = pkg.MoePlan(ctx, T, TOPK, E // world, 8)
+    owner = torch.randint(0, world, (T, TOPK), generator=torch.Generator(device="cuda").manual_seed(7), device="cuda")
+    rows_of = torch.arange(T * TOPK, device="cuda", dtype=torch.int32).view(T, TOPK)
+    plan.pair_row.copy_(torch.where(owner == rank, rows_of, torch.full_like(rows_of, -1)).view(-1))
+    yrows = torch.randn(T * TOPK, H, device="cuda")
+    nccl_buf = torch.randn(T, H, device="cuda").bfloat16()
+    sl = H // world
+    parts = [torch.empty(T, sl, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    mine = nccl_buf[:, rank * sl:(rank + 1) * sl].contiguous()
+    row_bytes = T * H * 2
+    ops = {
+        "peer_gather_cols (dispatch)": (lambda i: peer.gather_cols(bufs[i & 1], out), row_bytes * (world - 1) // world),
+        "peer_allreduce": (lambda i: peer(bufs[i & 1], out), row_bytes * (world - 1)),
+        "peer_combine (unpermute + all-reduce)": (lambda i: peer.combine(plan, yrows, None, bufs[i & 1], out), row_bytes * (world - 1)),
+        "nccl all_gather (column slices)": (lambda i: dist.all_gather(parts, mine), row_bytes * (world - 1) // world),
+        "nccl all_reduce": (lambda i: dist.all_reduce(nccl_buf), None),
+    }
+    res = {}
+    for name, (fn, pulled) in ops.items():
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(4):
+                fn(i)
+            side.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(20):
+                    fn(i)
+        torch.cuda.current_stream().wait_stream(side)
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = time_events(torch, graph.replay, 10, 3) / 20
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res[name] = {"us_per_call": round(float(t.item()) * 1e3, 2), "bytes_pulled_per_rank": pulled}
+        del graph
+        dist.barrier()
+    st = ctx.status()
+    if rank == 0:
+        print(json.dumps({"exchange_bench": res, "world": world, "rows": T, "row_elems": H, "device_status": st.code}))
+    sys.stdout.flush()
+    torch.cuda.synchronize()
+    dist.barrier()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -703,6 +775,7 @@ def main():
     ap.add_argument("--skip-ref-kernels", action="store_true", help="leave out the reference's own kernels (oracle/_ref) timed beside ours")
     ap.add_argument("--skip-parity", action="store_true", help="N > 1: leave out the one-layer comparison with the single-GPU stack")
     ap.add_argument("--no-sustain", dest="sustain", action="store_false", help="leave out the second timed region of >= 1 s")
+    ap.add_argument("--exchange-bench", action="store_true", help="under torch.distributed.run: time the peer-memory exchange kernels beside NCCL and exit")
     ap.add_argument("--small-case", default=None, choices=["decode", "prefill"],
                     help="run a few launches of a small case (a few GB on the device) and exit: the case the ncu captures use")
     ap.add_argument("--case-mode", default="ds", choices=["ds", "mx"], help="scale geometry of --small-case")
@@ -712,7 +785,9 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=16384)
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the dominant kernel, if captured")
     args = ap.parse_args()
-    if args.small_case:
+    if args.exchange_bench:
+        exchange_bench(args)
+    elif args.small_case:
         small_case(args)
     elif args.impl == "reference":
         run_reference(args)

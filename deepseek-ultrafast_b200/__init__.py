@@ -476,6 +476,7 @@ class PeerAllReduce:
         self.flag_ptrs = (C.c_uint64 * world)(*[int(p) for p in h.buffer_ptrs])
         self.state = t.zeros(2, dtype=t.int32, device=ctx.device)
         self.data_ptrs = {}
+        self.stages = {}
         t.cuda.synchronize()
         dist.barrier()   # every rank's flag block is zero before anyone announces
 
@@ -486,11 +487,33 @@ class PeerAllReduce:
         self.data_ptrs[buf.data_ptr()] = (C.c_uint64 * self.world)(*[int(p) for p in h.buffer_ptrs])
         return buf
 
+    TWO_SHOT_BYTES = 8 << 20   # from here on a rank sums only its own 1/W of the elements and the sums are gathered
+
     def __call__(self, partial, out):
         ptrs = self.data_ptrs[partial.data_ptr()]
+        n = partial.numel()
+        stage = self.stages.get(partial.data_ptr())
+        if stage is not None and n * 2 >= self.TWO_SHOT_BYTES and n % (8 * self.world) == 0:
+            # Large messages (prefill-size batches): reduce-scatter + all-gather with the same two kernels.  Rank r sums
+            # elements [r n/W, (r+1) n/W) of every partial into its slice of `stage` (a second mapped buffer), then every
+            # rank gathers the slices: 2 (W-1)/W n elements pulled per rank instead of (W-1) n -- the large-M shape of the
+            # reference's comm_push2 (crates/kernels/cu/comm.cu:323-542).
+            sl = n // self.world
+            off = self.rank * sl * 2
+            sub = (C.c_uint64 * self.world)(*[int(p) + off for p in ptrs])
+            self.ctx.check(lib().dsuf_ep_allreduce_bf16(self.ctx.h, self.ctx.stream(), sub, self.flag_ptrs, self.rank, self.world, sl,
+                                                        self.state.data_ptr(), stage.data_ptr() + off))
+            sptrs = self.data_ptrs[stage.data_ptr()]
+            self.ctx.check(lib().dsuf_ep_allgather_cols_bf16(self.ctx.h, self.ctx.stream(), sptrs, self.flag_ptrs, self.rank, self.world,
+                                                             1, n, self.state.data_ptr(), out.data_ptr()))
+            return out
         self.ctx.check(lib().dsuf_ep_allreduce_bf16(self.ctx.h, self.ctx.stream(), ptrs, self.flag_ptrs, self.rank, self.world,
-                                                    partial.numel(), self.state.data_ptr(), out.data_ptr()))
+                                                    n, self.state.data_ptr(), out.data_ptr()))
         return out
+
+    def stage_for(self, partial):
+        """Registers a second mapped buffer of the same shape for the two-shot all-reduce of ``partial``."""
+        self.stages[partial.data_ptr()] = self.buffer(tuple(partial.shape))
 
     def gather_cols(self, buf, out):
         """dsuf_ep_allgather_cols_bf16: every rank wrote its column slice of ``buf`` (a buffer from ``buffer``); ``out``

@@ -106,9 +106,11 @@ class _KernelCompute:
         n0, n1 = s.nslice
         act_quant(ctx, w.mode, x_all, s.xq, s.xs)
         T = x_all.shape[0]
-        slab = 64 if ctx.tcgen05 else 16
-        for r0 in range(0, T, slab):
-            m = min(slab, T - r0)
+        if ctx.tcgen05:
+            gemm_fp8(ctx, w, s.xq, s.xs, T, s.partial[:, n0:n1])   # decode kernel up to 64 rows, prefill kernel above
+            return s.partial
+        for r0 in range(0, T, 16):
+            m = min(16, T - r0)
             gemm_fp8(ctx, w, s.xq[r0:r0 + m], s.xs[r0:r0 + m], m, s.partial[r0:r0 + m, n0:n1])
         return s.partial
 
@@ -147,6 +149,9 @@ class EpLayerStack:
         self.t0, self.t1 = ep.shard_bounds(T, world, rank)
         n_loc, nloc_d = e_hi - self.e_lo, self.nslice[1] - self.nslice[0]
         self.dense, self.moe, self.logits = [], [], []
+        # decode: 8-row slots; prefill-size batches (tens of rows per expert and more): 128-row tiles (tcgen05 path only)
+        tile_rows = 128 if ctx.tcgen05 and T * cfg.topk >= 32 * E else 8
+        self.large = tile_rows == 128
         for l in range(cfg.layers):
             # the shards of ONE set of random-init weights (the seeds of LayerStack): the dense weight's rows of this rank's
             # output columns and the experts at their global ids, so the W-rank result is comparable with the single-GPU one
@@ -157,7 +162,7 @@ class EpLayerStack:
             w2 = synth.fp4_experts(t, n_loc, H, I, cfg.std, base + 3, False, dev, first_expert=self.e_lo)
             W13 = Weight.experts_fp4_packed(ctx, w13, 2 * I, H, n_loc, True)
             W2 = Weight.experts_fp4_packed(ctx, w2, H, I, n_loc, False)
-            self.moe.append(MoeLayer(ctx, W13, W2, T, cfg.topk, cfg.act_mode, e_lo=self.e_lo, tile_rows=8))
+            self.moe.append(MoeLayer(ctx, W13, W2, T, cfg.topk, cfg.act_mode, e_lo=self.e_lo, tile_rows=tile_rows))
             g = t.Generator(device=dev).manual_seed(cfg.seed + 1000 * l + 4)   # same logits on every rank
             self.logits.append(t.randn(T, E, generator=g, device=dev, dtype=t.float32))
         blk = 32 if cfg.dense_mode == MODE_MX else 128
@@ -189,7 +194,12 @@ class EpLayerStack:
             self.xch.peer = self.peer
             for buf in [self.partial] + self.y_part:
                 self.xch.peer_out[buf.data_ptr()] = t.empty((T, H), dtype=t.bfloat16, device=dev)
-            self.fuse_combine = os.environ.get("DSUF_EP_FUSE_COMBINE", "1") != "0"
+            # prefill-size batches: unpermute, then the two-shot all-reduce (reduce-scatter + gather) over a second mapped
+            # buffer per partial; decode-size batches: the one-shot combine fused with the unpermute
+            self.fuse_combine = os.environ.get("DSUF_EP_FUSE_COMBINE", "1") != "0" and not self.large
+            if self.large:
+                for buf in self.y_part:
+                    self.peer.stage_for(buf)
             if self.fuse_combine:
                 for buf in self.y_part:
                     self.xch.reduced.add(self.xch.peer_out[buf.data_ptr()].data_ptr())
@@ -223,10 +233,9 @@ class EpLayerStack:
 
     def count_launches(self):
         cfg = self.cfg
-        slab = 64 if self.ctx.tcgen05 else 16
-        slabs = (cfg.tokens + slab - 1) // slab
+        slabs = 1 if self.ctx.tcgen05 else (cfg.tokens + 15) // 16
         front = 1 if cfg.tokens * cfg.topk <= 1024 else 5
         # this library's exchange kernels (NCCL's kernels are not counted): the gather of the dense slices, and the combine
         # that either follows the unpermute as an all-reduce or replaces it
-        ar = 0 if self.peer is None else 1 if self.fuse_combine else 2
+        ar = 0 if self.peer is None else 1 if self.fuse_combine else 3 if self.large else 2
         return cfg.layers * (1 + slabs + front + 1 + 1 + 1 + 1 + ar)
