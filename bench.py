@@ -31,8 +31,8 @@ from __graft_entry__ import load_package  # noqa: E402
 H, I, E, TOPK, LAYERS = 7168, 2048, 256, 8, 4
 DENSE_SHAPES = [(4096, 7168), (7168, 2048), (18432, 7168), (7168, 16384)]
 METRIC = "moe_layer_stack_decode_tokens_per_s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch in the ncu small case, divided by its 59 active experts
-NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT = (921.251584e6 + 3.779072e6) / 59
+# dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch in the ncu small case, divided by its 55 active experts
+NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT = (858.861568e6 + 3.328e6) / 55
 
 
 def peaks():
@@ -560,7 +560,7 @@ def run_ours(args):
                 "algorithmic_bytes_per_launch": int(algo_w13),
                 "traffic": args.traffic if args.traffic is not None else int(e_act * NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT),
                 "traffic_source": "given on the command line" if args.traffic is not None else
-                "ncu dram__bytes_read+write of the 64-expert small case (profiles/tc_stream_kernel_fp4_w13_decode_small_case.md), "
+                "ncu dram__bytes_read+write of the 64-expert small case (profiles/tc_stream_kernel_decode_small_case.md), "
                 "per active expert, times this launch's active experts (traffic grows with the experts streamed)"}
     result = {
         "metric": METRIC if T <= 1024 else "moe_layer_stack_prefill_tokens_per_s", "value": round(T / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,

@@ -166,6 +166,11 @@ DSUF_DEV uint32_t cluster_cta_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+DSUF_DEV uint32_t cluster_num_ctas() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
 // Hardware barrier over every thread of every CTA of the cluster; shared-memory writes made before it are visible to
 // the other CTAs' distributed-shared-memory reads after it.  Whole warps must call it together.
 DSUF_DEV void cluster_barrier() {
@@ -178,6 +183,12 @@ DSUF_DEV float ld_cluster_f32(const float* my_smem_ptr, uint32_t rank) {
     float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+DSUF_DEV uint32_t ld_cluster_u32(const void* my_smem_ptr, uint32_t rank) {
+    uint32_t remote, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_ptr)), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
     return v;
 }
 DSUF_DEV void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }

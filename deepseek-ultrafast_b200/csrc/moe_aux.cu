@@ -68,11 +68,12 @@ DSUF_DEV void route_one_token(int score_fn, const float* s, const float* bias, i
         unsigned long long best = cand[0];
 #pragma unroll
         for (int i = 1; i < ROUTE_MAX_PER_LANE; ++i) best = cand[i] > best ? cand[i] : best;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
-            best = other > best ? other : best;
-        }
+        // warp maximum of the 64-bit words in two 32-bit hardware reductions: the best score first, then the best
+        // (complemented) id among the lanes that hold that score
+        const unsigned hi = (unsigned)(best >> 32);
+        const unsigned top_hi = __reduce_max_sync(0xffffffffu, hi);
+        const unsigned top_lo = __reduce_max_sync(0xffffffffu, hi == top_hi ? (unsigned)best : 0u);
+        best = ((unsigned long long)top_hi << 32) | top_lo;
         const int picked = (int)(0xffffffffu - (unsigned)(best & 0xffffffffull));  // every lane holds the same word
         // the owner lane retires the candidate and publishes its unbiased score
         float wv = 0.f;
@@ -240,12 +241,12 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_place_kernel(const PlanArgs a
 // pass.  Same result as the three-phase path, bit for bit (the order inside an expert is the pair order either way).
 // `write` = this CTA stores the plan to global memory; `s_pair_row` (optional, shared) receives pair_row as well.
 struct PlanSmem {
-    unsigned short warp_hist[32][PLAN_MAX_EXP];
+    alignas(16) unsigned short warp_hist[32][PLAN_MAX_EXP];
     int off[PLAN_MAX_EXP + 1], wa[32], wb[32];
 };
 DSUF_DEV void plan_small_body(const PlanArgs& a, PlanSmem& sm, bool write, int* s_pair_row) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    for (int i = tid; i < 32 * PLAN_MAX_EXP; i += PLAN_BLOCK) (&sm.warp_hist[0][0])[i] = 0;
+    for (int i = tid; i < 32 * PLAN_MAX_EXP / 8; i += PLAN_BLOCK) ((uint4*)&sm.warp_hist[0][0])[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
     int e = -1;
     if (tid < a.p) {
@@ -305,9 +306,10 @@ __global__ void __launch_bounds__(PLAN_BLOCK) plan_small_kernel(const PlanArgs a
 
 // Decode front end in ONE launch: router, permute plan and gather + quant for batches of at most 1024 (token, expert)
 // pairs -- the counterpart of the routing the reference runs inside its decode MoE launch (route_plan,
-// cu/gemv.cu:715-776).  Every CTA routes all tokens and builds the whole plan in shared memory (64 x 256 scores and
-// 512 pairs at the decode size: microseconds, and no second and third launch); CTA 0 stores ids, weights and the plan;
-// CTA b quantizes token rows b, b + gridDim.x, ... and writes each to its top-k permuted rows.
+// cu/gemv.cu:715-776).  The CTAs of a cluster of 8 route the tokens between them (one token per warp) and read one
+// another's picks through distributed shared memory; every CTA then builds the whole plan in its own shared memory
+// (512 pairs at the decode size: no second and third launch); CTA 0 stores ids, weights and the plan; CTA b quantizes
+// token rows b, b + gridDim.x, ... and writes each to its top-k permuted rows.
 struct FrontArgs {
     PlanArgs plan;          // ids / w point at the routing outputs in global memory (written by CTA 0)
     const float* scores;    // [t][n_exp_all]
@@ -331,10 +333,25 @@ __global__ void __launch_bounds__(PLAN_BLOCK) moe_front_kernel(const FrontArgs f
     __shared__ float s_w[PLAN_BLOCK];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool first = blockIdx.x == 0;
-    for (int tok = warp; tok < f.t; tok += PLAN_BLOCK / 32)
+    // the CTAs of a cluster share the routing: CTA r routes tokens r, r + cs, ... (one per warp) and the others read its
+    // picks through distributed shared memory; every CTA then holds all picks and builds the (same) plan by itself
+    const int cs = (int)cluster_num_ctas(), crank = (int)cluster_cta_rank();
+    for (int tok = crank + cs * warp; tok < f.t; tok += cs * (PLAN_BLOCK / 32))
         route_one_token(f.score_fn, f.scores + (size_t)tok * f.n_exp_all, f.bias, f.n_exp_all, f.topk, f.route_scale, lane,
                         s_ids + tok * f.topk, s_w + tok * f.topk);
-    __syncthreads();
+    if (cs > 1) {
+        cluster_barrier();
+        if (tid < f.plan.p) {
+            const int owner = (tid / f.topk) % cs;
+            if (owner != crank) {
+                s_ids[tid] = (int)ld_cluster_u32(s_ids + tid, owner);
+                s_w[tid] = ld_cluster_f32(s_w + tid, owner);
+            }
+        }
+        cluster_barrier();   // no CTA goes on (and none exits) while a peer still reads its picks
+    } else {
+        __syncthreads();
+    }
     if (first && tid < f.plan.p) {
         f.ids_out[tid] = s_ids[tid];
         f.w_out[tid] = s_w[tid];
@@ -408,9 +425,11 @@ int launch_front(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* 
     a.status = ctx->dev_status;
     f.scores = scores; f.bias = bias; f.score_fn = score_fn; f.t = t; f.n_exp_all = n_exp_all; f.topk = topk; f.route_scale = route_scale;
     f.ids_out = ids; f.w_out = w; f.x = (const bf16*)x; f.ldx = ldx; f.h = h; f.xq = (uint8_t*)xq; f.xs = xs;
-    const int grid = t < ctx->sm_count ? t : ctx->sm_count;
-    if (mode == DSUF_MODE_MX) return launch(ctx, stream, moe_front_kernel<DSUF_MODE_MX>, dim3(grid), dim3(PLAN_BLOCK), 0, f);
-    return launch(ctx, stream, moe_front_kernel<DSUF_MODE_DS>, dim3(grid), dim3(PLAN_BLOCK), 0, f);
+    const int cs = t >= 8 ? 8 : 1;
+    int grid = t < ctx->sm_count ? t : ctx->sm_count;
+    grid = grid / cs * cs;   // whole clusters; the quantizer strides over the tokens by the grid size
+    if (mode == DSUF_MODE_MX) return launch_cluster(ctx, stream, moe_front_kernel<DSUF_MODE_MX>, dim3(grid), dim3(PLAN_BLOCK), 0, cs, f);
+    return launch_cluster(ctx, stream, moe_front_kernel<DSUF_MODE_DS>, dim3(grid), dim3(PLAN_BLOCK), 0, cs, f);
 }
 
 // ---------------------------------------------------------------- unpermute / combine

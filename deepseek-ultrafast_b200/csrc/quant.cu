@@ -29,73 +29,57 @@ struct QuantArgs {
     int approx_rsqrt;     // pre-normalisation: 1 = the reference's rsqrtf (approximate instruction), 0 = correctly rounded 1/sqrt
 };
 
-// ITERS: 2048-element chunks of a row per CTA.  One for decode-size inputs (as many CTAs as possible: the kernel is a
-// few microseconds of latency); four, with all four 16-byte loads of a thread issued before the first is used, where the
-// rows number in the thousands and the kernel is bound by the bytes it keeps in flight.
-template <int MODE, int ITERS>
+template <int MODE>
 __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
     pdl_wait();
     pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
     const int row = blockIdx.x;
-    uint4 raw[ITERS], wraw[ITERS];
+    const int k0 = (blockIdx.y * 256 + threadIdx.x) * 8;
+    const bool live = k0 < a.k;
+    float v[8];
+    if (live) {
+        const uint4 raw = *(const uint4*)(a.x + (size_t)row * a.ldx + k0);
+        const bf16* h = (const bf16*)&raw;
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int k0 = ((blockIdx.y * ITERS + it) * 256 + threadIdx.x) * 8;
-        if (k0 < a.k) {
-            raw[it] = *(const uint4*)(a.x + (size_t)row * a.ldx + k0);
-            if (a.norm_w) wraw[it] = *(const uint4*)(a.norm_w + k0);
+        for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(h[e]);
+        if (a.norm_w) {
+            // tc_quant_rows with pw (cu/tcgemm.cu:316-320): v = bf16(w * (x * rs)), every product rounded on its own.
+            // rs by correctly rounded sqrt and division by default (the reference's rsqrtf is a 2-ulp approximation).
+            // With approx_rsqrt the same instruction is used and the codes are the reference kernel's on the same GPU.
+            const float ms = __fadd_rn(__fdiv_rn(a.sumsq[row], (float)a.k), a.eps);
+            const float rs = a.approx_rsqrt ? rsqrtf(ms) : __fdiv_rn(1.0f, __fsqrt_rn(ms));
+            const uint4 wraw = *(const uint4*)(a.norm_w + k0);
+            const bf16* hw = (const bf16*)&wraw;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = bf16_round(__fmul_rn(__bfloat162float(hw[e]), __fmul_rn(v[e], rs)));
         }
-    }
-    float rs = 1.0f;
-    if (a.norm_w) {
-        // tc_quant_rows with pw (cu/tcgemm.cu:316-320): v = bf16(w * (x * rs)), every product rounded on its own.
-        // rs by correctly rounded sqrt and division by default (the reference's rsqrtf is a 2-ulp approximation).
-        // With approx_rsqrt the same instruction is used and the codes are the reference kernel's on the same GPU.
-        const float ms = __fadd_rn(__fdiv_rn(a.sumsq[row], (float)a.k), a.eps);
-        rs = a.approx_rsqrt ? rsqrtf(ms) : __fdiv_rn(1.0f, __fsqrt_rn(ms));
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = 0.f;
     }
     constexpr int LANES = MODE == DSUF_MODE_MX ? 4 : 16;  // lanes sharing one scale block
+    float sc;
+    uint2 out;
+    quant8<MODE>(v, out, sc);
+    if (!live) return;
     const bool writes_scale = (threadIdx.x & (LANES - 1)) == 0;
     const int nfan = a.fanout > 0 ? a.fanout : 1;
-#pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int k0 = ((blockIdx.y * ITERS + it) * 256 + threadIdx.x) * 8;
-        const bool live = k0 < a.k;   // k % 128 == 0: a scale block is live or dead as a whole
-        float v[8];
-        if (live) {
-            const bf16* h = (const bf16*)&raw[it];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = __bfloat162float(h[e]);
-            if (a.norm_w) {
-                const bf16* hw = (const bf16*)&wraw[it];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = bf16_round(__fmul_rn(__bfloat162float(hw[e]), __fmul_rn(v[e], rs)));
-            }
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = 0.f;
-        }
-        float sc;
-        uint2 out;
-        quant8<MODE>(v, out, sc);   // every lane takes part in the block's amax
-        if (!live) continue;
-        for (int j = 0; j < nfan; ++j) {
-            const int dst = a.fanout > 0 ? a.pair_row[(size_t)row * a.fanout + j] : row;
-            if (dst < 0) continue;
-            *(uint2*)(a.q + (size_t)dst * a.k + k0) = out;
-            if (writes_scale) {
-                if (MODE == DSUF_MODE_MX) {
-                    const int kb = k0 >> 5;
-                    const uint8_t b = (uint8_t)(__float_as_uint(sc) >> 23);
-                    if (a.sf_atoms) {
-                        const int r = dst & 127;
-                        ((uint8_t*)a.scales)[((size_t)(dst >> 7) * (a.k >> 7) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = b;
-                    } else {
-                        ((uint8_t*)a.scales)[(size_t)dst * (a.k >> 5) + kb] = b;
-                    }
+    for (int j = 0; j < nfan; ++j) {
+        const int dst = a.fanout > 0 ? a.pair_row[(size_t)row * a.fanout + j] : row;
+        if (dst < 0) continue;
+        *(uint2*)(a.q + (size_t)dst * a.k + k0) = out;
+        if (writes_scale) {
+            if (MODE == DSUF_MODE_MX) {
+                const int kb = k0 >> 5;
+                const uint8_t b = (uint8_t)(__float_as_uint(sc) >> 23);
+                if (a.sf_atoms) {
+                    const int r = dst & 127;
+                    ((uint8_t*)a.scales)[((size_t)(dst >> 7) * (a.k >> 7) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = b;
                 } else {
-                    ((float*)a.scales)[(size_t)dst * (a.k >> 7) + (k0 >> 7)] = sc;
+                    ((uint8_t*)a.scales)[(size_t)dst * (a.k >> 5) + kb] = b;
                 }
+            } else {
+                ((float*)a.scales)[(size_t)dst * (a.k >> 7) + (k0 >> 7)] = sc;
             }
         }
     }
@@ -131,14 +115,10 @@ int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x
                      void* scales, const int* pair_row, int fanout, int sf_atoms, const void* norm_w, const float* sumsq, float eps) {
     QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, sf_atoms, (const bf16*)norm_w, sumsq, eps, ctx->prenorm_approx};
     if (rows_in == 0) return DSUF_OK;
-    if (rows_in >= 1024) {
-        dim3 grid(rows_in, (k + 8191) / 8192);
-        if (mode == DSUF_MODE_MX) return launch(ctx, stream, act_quant_kernel<DSUF_MODE_MX, 4>, grid, dim3(256), 0, a);
-        return launch(ctx, stream, act_quant_kernel<DSUF_MODE_DS, 4>, grid, dim3(256), 0, a);
-    }
     dim3 grid(rows_in, (k + 2047) / 2048);
-    if (mode == DSUF_MODE_MX) return launch(ctx, stream, act_quant_kernel<DSUF_MODE_MX, 1>, grid, dim3(256), 0, a);
-    return launch(ctx, stream, act_quant_kernel<DSUF_MODE_DS, 1>, grid, dim3(256), 0, a);
+    if (mode == DSUF_MODE_MX)
+        return launch(ctx, stream, act_quant_kernel<DSUF_MODE_MX>, grid, dim3(256), 0, a);
+    return launch(ctx, stream, act_quant_kernel<DSUF_MODE_DS>, grid, dim3(256), 0, a);
 }
 
 }  // namespace dsuf
