@@ -15,6 +15,7 @@ import numpy as np
 MODE_MX, MODE_DS = 0, 1
 FMT_FP8, FMT_FP4 = 0, 1
 SCORE_IDENTITY, SCORE_SOFTMAX, SCORE_SQRT_SOFTPLUS = 0, 1, 2
+EPI_STORE, EPI_SWIGLU, EPI_SQRT_SOFTPLUS = 0, 1, 2   # dsuf_gemm_opts.epilogue
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libdsuf_qmm.so")
@@ -89,6 +90,9 @@ ABI = {
                                                 C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
     "dsuf_ep_combine_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                          C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
+    "dsuf_ep_combine_quant_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
+                                               C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.c_int32, C.c_int32, C.c_uint64, C.c_uint64,
+                                               C.c_int32, C.c_uint64, C.c_uint64]),
     "dsuf_act_quant_fp8": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_int32,
                                        C.c_uint64, C.c_uint64]),
     "dsuf_gemm_workspace_bytes": (C.c_size_t, [C.c_void_p]),
@@ -420,23 +424,26 @@ def gemm_fp8_swiglu(ctx, w, xq, xs, m, out=None, swiglu_limit=0.0):
     t = ctx.torch
     if out is None:
         out = t.empty((m, w.n // 2), dtype=t.bfloat16, device=xq.device)
-    o = GemmOpts(1.0, 0, 0, 0, 0, 1, swiglu_limit)
+    o = GemmOpts(1.0, 0, 0, 0, 0, EPI_SWIGLU, swiglu_limit)
     ctx.check(lib().dsuf_gemm_fp8_ex(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0), C.byref(o),
                                      ctx.workspace.data_ptr()))
     return out
 
 
-def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None):
+def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None, sqrt_softplus=False):
     """dsuf_gemm_fp8_ex = ops::gemv with GemvOpts {alpha, out_f32, split} (ops.rs:165-193): fp32 or bf16 output, and with
-    ``n_split`` > 0 the weight rows from n_split on go to a second tensor.  Returns out, or (out, out2)."""
+    ``n_split`` > 0 the weight rows from n_split on go to a second tensor.  ``sqrt_softplus``: the router-gate epilogue
+    (Epilogue::SqrtSoftplus), fp32 scores.  Returns out, or (out, out2)."""
     t = ctx.torch
+    out_f32 = out_f32 or sqrt_softplus
     dt = t.float32 if out_f32 else t.bfloat16
     n1 = n_split if n_split > 0 else w.n
     if out is None:
         out = t.empty((m, n1), dtype=dt, device=xq.device)
     if n_split > 0 and out2 is None:
         out2 = t.empty((m, w.n - n_split), dtype=dt, device=xq.device)
-    o = GemmOpts(alpha, int(bool(out_f32)), n_split, out2.stride(0) if out2 is not None else 0, out2.data_ptr() if out2 is not None else 0, 0, 0.0)
+    o = GemmOpts(alpha, int(bool(out_f32)), n_split, out2.stride(0) if out2 is not None else 0, out2.data_ptr() if out2 is not None else 0,
+                 EPI_SQRT_SOFTPLUS if sqrt_softplus else EPI_STORE, 0.0)
     ctx.check(lib().dsuf_gemm_fp8_ex(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0), C.byref(o),
                                      ctx.workspace.data_ptr()))
     return (out, out2) if n_split > 0 else out
@@ -524,13 +531,16 @@ class PeerAllReduce:
                                                          rows, cols, self.state.data_ptr(), out.data_ptr()))
         return out
 
-    def combine(self, plan, yrows, shared, partial, out):
-        """dsuf_ep_combine_bf16: the local sum of every token's expert rows and its exchange in one kernel."""
+    def combine(self, plan, yrows, shared, partial, out, quant=None):
+        """dsuf_ep_combine_bf16: the local sum of every token's expert rows and its exchange in one kernel.
+        ``quant`` = (mode, xq, xs): also leave ``out`` quantized for the next projection (dsuf_ep_combine_quant_bf16)."""
         tok, h = out.shape
         ptrs = self.data_ptrs[partial.data_ptr()]
-        self.ctx.check(lib().dsuf_ep_combine_bf16(self.ctx.h, self.ctx.stream(), plan.pair_row.data_ptr(), yrows.data_ptr(),
-                                                  shared.data_ptr() if shared is not None else 0, tok, plan.topk, h, ptrs,
-                                                  self.flag_ptrs, self.rank, self.world, self.state.data_ptr(), out.data_ptr()))
+        mode, xq, xs = quant if quant is not None else (MODE_DS, None, None)
+        self.ctx.check(lib().dsuf_ep_combine_quant_bf16(self.ctx.h, self.ctx.stream(), plan.pair_row.data_ptr(), yrows.data_ptr(),
+                                                        shared.data_ptr() if shared is not None else 0, tok, plan.topk, h, ptrs,
+                                                        self.flag_ptrs, self.rank, self.world, self.state.data_ptr(), out.data_ptr(),
+                                                        mode, xq.data_ptr() if xq is not None else 0, xs.data_ptr() if xs is not None else 0))
         return out
 
 

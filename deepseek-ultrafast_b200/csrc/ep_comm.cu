@@ -13,6 +13,7 @@
 // DEVERR_WAIT_TIMEOUT in the context's status word and finish with an incomplete sum instead of hanging.
 // The only peer accesses are plain ld / st on peer pointers.
 #include "internal.h"
+#include "quant_core.cuh"
 
 namespace dsuf {
 
@@ -30,6 +31,9 @@ struct EpcArgs {
     int rank, world;
     int gather_vec, row_vec;           // all-gather of column slices: 16-byte vectors per slice / per row (0: all-reduce)
     long long wait_ticks;              // clock64 budget of the wait for the peers' announcements
+    uint8_t* q_out;                    // optional: FP8 codes of `out` (the next GEMM's activation operand), [n_elems]
+    void* q_scales;                    //           their block scales, row-major (MX u8 per 32, DS f32 per 128 elements)
+    int q_mode;                        //           DSUF_MODE_MX / DSUF_MODE_DS
     uint32_t* state;                   // local: [0] calls completed (the epoch lives on the device so that a captured
                                        // graph advances it on every replay), [1] CTAs finished in this call
 };
@@ -65,6 +69,63 @@ DSUF_DEV void exchange_wait(const EpcArgs& a, const uint32_t* f, uint32_t epoch,
     }
 }
 
+// out[i] = sum over the ranks, in rank order, of vector i of every rank's partial (fp32 adds, one rounding to bf16: all
+// ranks round the same sum).  Peer latency, not bandwidth, bounds this step, so a thread's loads of two rounds
+// (2 x world 16-byte vectors) are all issued before the first add.  With q_out set the rounded sums are also quantized
+// to FP8 exactly as dsuf_act_quant_fp8 would quantize `out` (a scale block is 4 or 16 neighbouring threads of a warp).
+DSUF_DEV void sum_vec(const EpcArgs& a, const uint4 (&v)[EPC_MAX_WORLD], long long i, bool live, int lane) {
+    float s[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s[e] = 0.f;
+#pragma unroll
+    for (int r = 0; r < EPC_MAX_WORLD; ++r)
+        if (r < a.world) {
+            const bf16* h = (const bf16*)&v[r];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[e] += __bfloat162float(h[e]);
+        }
+    uint4 o;
+    bf16* ho = (bf16*)&o;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16(live ? s[e] : 0.f);
+    if (live) *(uint4*)(a.out + i * 8) = o;
+    if (a.q_out) {   // (uniform over the grid)
+        float q[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q[e] = __bfloat162float(ho[e]);
+        uint2 codes;
+        float sc;
+        if (a.q_mode == DSUF_MODE_MX) {
+            quant8<DSUF_MODE_MX>(q, codes, sc);
+            if (live && (lane & 3) == 0) ((uint8_t*)a.q_scales)[i >> 2] = (uint8_t)(__float_as_uint(sc) >> 23);
+        } else {
+            quant8<DSUF_MODE_DS>(q, codes, sc);
+            if (live && (lane & 15) == 0) ((float*)a.q_scales)[i >> 4] = sc;
+        }
+        if (live) *(uint2*)(a.q_out + i * 8) = codes;
+    }
+}
+
+DSUF_DEV void sum_over_ranks(const EpcArgs& a, int b, int tid) {
+    const int lane = tid & 31;
+    const long long stride = (long long)gridDim.x * EPC_THREADS;
+    // whole warps run every round (the quantizer shuffles): the bound is on the warp's first vector
+    for (long long w0 = (long long)b * EPC_THREADS + (tid & ~31); w0 < a.n_vec; w0 += 2 * stride) {
+        const long long i0 = w0 + lane, i1 = i0 + stride;
+        const bool live0 = i0 < a.n_vec, live1 = i1 < a.n_vec, round1 = w0 + stride < a.n_vec;
+        uint4 v0[EPC_MAX_WORLD], v1[EPC_MAX_WORLD];
+#pragma unroll
+        for (int r = 0; r < EPC_MAX_WORLD; ++r) {
+            v0[r] = make_uint4(0, 0, 0, 0);
+            v1[r] = make_uint4(0, 0, 0, 0);
+            if (r < a.world && live0) v0[r] = ld_relaxed_sys_v4(a.data[r] + i0);
+            if (r < a.world && live1) v1[r] = ld_relaxed_sys_v4(a.data[r] + i1);
+        }
+        sum_vec(a, v0, i0, live0, lane);
+        if (round1) sum_vec(a, v1, i1, live1, lane);
+    }
+}
+
 __global__ void __launch_bounds__(EPC_THREADS) ep_allreduce_kernel(const EpcArgs a) {
     pdl_wait();
     pdl_launch_dependents();
@@ -82,34 +143,15 @@ __global__ void __launch_bounds__(EPC_THREADS) ep_allreduce_kernel(const EpcArgs
     }
     __syncthreads();
     // ---- sum in rank order; all of an element's loads are issued before the first add (peer latency, not bandwidth,
-    //      bounds this kernel) ----
+    //      bounds this kernel: sum_over_ranks) ----
     if (a.gather_vec) {
         // all-gather of column slices: every element has one owner (the rank that computed that column range)
         for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
             const int owner = (int)((i % a.row_vec) / a.gather_vec);
             *(uint4*)(a.out + i * 8) = ld_relaxed_sys_v4(a.data[owner] + i);
         }
-    } else
-    for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
-        uint4 v[EPC_MAX_WORLD];
-#pragma unroll
-        for (int r = 0; r < EPC_MAX_WORLD; ++r)
-            if (r < a.world) v[r] = ld_relaxed_sys_v4(a.data[r] + i);
-        float s[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) s[e] = 0.f;
-#pragma unroll
-        for (int r = 0; r < EPC_MAX_WORLD; ++r)
-            if (r < a.world) {
-                const bf16* h = (const bf16*)&v[r];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) s[e] += __bfloat162float(h[e]);
-            }
-        uint4 o;
-        bf16* ho = (bf16*)&o;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16(s[e]);
-        *(uint4*)(a.out + i * 8) = o;
+    } else {
+        sum_over_ranks(a, b, tid);
     }
     // ---- the last CTA to finish closes the call: the next call (stream-ordered behind this grid) sees epoch + 1 ----
     __syncthreads();
@@ -180,27 +222,7 @@ __global__ void __launch_bounds__(EPC_THREADS) ep_combine_kernel(const EpCombine
         exchange_wait(a, f, epoch, t0, 16 + tid);
     }
     __syncthreads();
-    for (long long i = (long long)b * EPC_THREADS + tid; i < a.n_vec; i += (long long)gridDim.x * EPC_THREADS) {
-        uint4 v[EPC_MAX_WORLD];
-#pragma unroll
-        for (int r = 0; r < EPC_MAX_WORLD; ++r)
-            if (r < a.world) v[r] = ld_relaxed_sys_v4(a.data[r] + i);
-        float s[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) s[e] = 0.f;
-#pragma unroll
-        for (int r = 0; r < EPC_MAX_WORLD; ++r)
-            if (r < a.world) {
-                const bf16* h = (const bf16*)&v[r];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) s[e] += __bfloat162float(h[e]);
-            }
-        uint4 o;
-        bf16* ho = (bf16*)&o;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ho[e] = __float2bfloat16(s[e]);
-        *(uint4*)(a.out + i * 8) = o;
-    }
+    sum_over_ranks(a, b, tid);
     __syncthreads();
     if (tid == 0) {
         __threadfence();
@@ -267,7 +289,18 @@ extern "C" int32_t dsuf_ep_allgather_cols_bf16(dsuf_ctx* ctx, void* stream, cons
 extern "C" int32_t dsuf_ep_combine_bf16(dsuf_ctx* ctx, void* stream, uint64_t pair_row, uint64_t yrows, uint64_t shared, int32_t t,
                                         int32_t topk, int32_t h, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
                                         int32_t world, uint64_t state, uint64_t out) {
+    return dsuf_ep_combine_quant_bf16(ctx, stream, pair_row, yrows, shared, t, topk, h, peer_data, peer_flags, rank, world, state, out,
+                                      DSUF_MODE_DS, 0, 0);
+}
+
+extern "C" int32_t dsuf_ep_combine_quant_bf16(dsuf_ctx* ctx, void* stream, uint64_t pair_row, uint64_t yrows, uint64_t shared, int32_t t,
+                                              int32_t topk, int32_t h, const uint64_t* peer_data, const uint64_t* peer_flags,
+                                              int32_t rank, int32_t world, uint64_t state, uint64_t out, int32_t mode, uint64_t xq,
+                                              uint64_t xs) {
     if (!ctx) return DSUF_E_BADARG;
+    DSUF_REQUIRE(ctx, (xq == 0) == (xs == 0), "ep_combine_quant: xq and xs go together");
+    DSUF_REQUIRE(ctx, !xq || ((mode == DSUF_MODE_MX || mode == DSUF_MODE_DS) && h % 128 == 0 && (xq & 7) == 0 && (xs & 3) == 0),
+                 "ep_combine_quant: mode MX/DS, h a multiple of 128, xq 8-byte and xs 4-byte aligned");
     DSUF_REQUIRE(ctx, t >= 0 && topk >= 1 && topk <= 16 && h > 0 && h % 8 == 0, "ep_combine: t >= 0, topk in 1..16, h a multiple of 8");
     DSUF_REQUIRE(ctx, pair_row && yrows && (yrows & 15) == 0 && (shared & 15) == 0, "ep_combine: null or misaligned pointer");
     EpCombineArgs p;
@@ -279,6 +312,9 @@ extern "C" int32_t dsuf_ep_combine_bf16(dsuf_ctx* ctx, void* stream, uint64_t pa
     p.partial = (bf16*)peer_data[rank];
     p.topk = topk;
     p.h = h;
+    p.c.q_out = (uint8_t*)xq;
+    p.c.q_scales = (void*)xs;
+    p.c.q_mode = mode;
     if (t == 0) return DSUF_OK;
     return launch(ctx, (cudaStream_t)stream, ep_combine_kernel, dim3(EPC_CTAS), dim3(EPC_THREADS), 0, p);
 }

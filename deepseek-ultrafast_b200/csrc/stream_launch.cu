@@ -108,7 +108,8 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
         DSUF_REQUIRE(ctx, opts->n_split >= 0 && opts->n_split < w->d.n, "dsuf_gemm_fp8_ex: n_split (%d) must be in 0..n-1", opts->n_split);
         DSUF_REQUIRE(ctx, opts->n_split == 0 || (opts->out2 && opts->ldo2 >= w->d.n - opts->n_split),
                      "dsuf_gemm_fp8_ex: n_split needs out2 with ldo2 >= n - n_split");
-        DSUF_REQUIRE(ctx, opts->epilogue == DSUF_EPI_STORE || opts->epilogue == DSUF_EPI_SWIGLU, "dsuf_gemm_fp8_ex: unknown epilogue %d", opts->epilogue);
+        DSUF_REQUIRE(ctx, opts->epilogue == DSUF_EPI_STORE || opts->epilogue == DSUF_EPI_SWIGLU || opts->epilogue == DSUF_EPI_SQRT_SOFTPLUS,
+                     "dsuf_gemm_fp8_ex: unknown epilogue %d", opts->epilogue);
         if (opts->epilogue == DSUF_EPI_SWIGLU) {
             DSUF_REQUIRE(ctx, w->d.gate_up && w->d.mode == DSUF_MODE_MX, "dsuf_gemm_fp8_ex: the SwiGLU epilogue needs an MX weight packed with dsuf_pack_fp8_weight_gate_up");
             DSUF_REQUIRE(ctx, ctx->use_tc, "dsuf_gemm_fp8_ex: the SwiGLU epilogue runs on the tcgen05 path only");
@@ -117,7 +118,8 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
             a.swiglu = 1;
             a.swiglu_limit = opts->swiglu_limit;
         }
-        a.out_f32 = opts->out_f32 ? 1 : 0;
+        a.ssp = opts->epilogue == DSUF_EPI_SQRT_SOFTPLUS ? 1 : 0;
+        a.out_f32 = (opts->out_f32 || a.ssp) ? 1 : 0;
         a.n_split = opts->n_split;
         a.out2 = (void*)opts->out2;
         a.ldo2 = opts->ldo2;
@@ -165,19 +167,22 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
     if (tot < grid) grid = (int)tot;
     // Stream-K balances to one tile but pays a partial-sum exchange per split row tile (a few microseconds on a kernel
     // of tens); whole row tiles per CTA are preferred when they need no more tile-steps than that.
-    const long long fix = 6 / pair;   // the stream-K exchange of partial sums costs about six 16 KB tile steps
+    // the stream-K exchange of partial sums through global memory (fence, counter, re-read by the last CTA of a row tile)
+    // measured 5-6 us on kernels of 12-16: as much as ten ring steps of two tiles
+    const long long fix = 20 / pair;
     const long long steps_streamk = (tot + grid - 1) / grid + fix, steps_whole = (long long)((w->rt + grid - 1) / grid) * kt;
     a.whole_items = steps_whole <= steps_streamk ? 1 : 0;
     const bool mx = w->d.mode == DSUF_MODE_MX;
     int cluster = 1;
     if (ctx->use_tc && ctx->use_kslices) {
-        // Weights with few row tiles: one row tile per cluster, K cut into 1, 2 or 4 slices that are summed through
-        // distributed shared memory (~1.5 us) instead of through global partials (~4 us on a kernel of 10).  Cost in tile
-        // steps of a CTA's stream; taken when no worse than the other two decompositions.
+        // Weights with few row tiles: one row tile per cluster, K cut into 1, 2, 4 or 8 slices that are summed through
+        // distributed shared memory (~1 us) instead of through global partials.  Cost in ring steps of a CTA's stream;
+        // taken when better than the other two decompositions.
         const long long steps_other = a.whole_items ? steps_whole : steps_streamk;
         long long best = steps_other;
-        for (int cs : {1, 2, 4}) {
-            if ((long long)w->rt * cs > grid || kt < cs) continue;
+        for (int cs : {1, 2, 4, 8}) {
+            // (clusters of 8 fit twice into a GPC of 16-20 SMs at one CTA per SM: 16 of them at most run at once)
+            if ((long long)w->rt * cs > (cs == 8 ? 128 : grid) || kt < cs) continue;
             const long long steps = (kt + cs - 1) / cs + (cs > 1 ? (pair == 2 ? 2 : 3) : 0);
             if (steps < best) { best = steps; cluster = cs; a.kslices = cs; }
         }

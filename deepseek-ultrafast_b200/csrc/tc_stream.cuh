@@ -136,7 +136,8 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
     // ---- this CTA's span of the global tile sequence (see stream_gemv.cuh) ----
     long long beg, end;
     // cluster K-split (dense weights with few row tiles): cluster r owns row tile r, its CTA j the K tiles
-    // [j KT / cs, (j + 1) KT / cs); the partial sums meet in CTA 0 of the cluster through distributed shared memory
+    // [j KT / cs, (j + 1) KT / cs); the partial sums meet through distributed shared memory, every CTA of the cluster
+    // summing and storing its share of the token columns
     const int ksl = EPI == EPI_DENSE ? a.kslices : 0;
     const int krank = ksl > 1 ? (int)cluster_cta_rank() : 0;
     bool cluster_done = false;  // this warp has been through the two cluster barriers of the reduce
@@ -535,21 +536,63 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                     bool do_store = whole;
                     if (ksl > 1) {
                         // This CTA's only item.  Every CTA parks its partial in its own ring (all of its MMAs have completed
-                        // and nothing is in flight into the ring any more), the cluster meets, CTA 0 adds the others' in
-                        // rank order and stores, and the cluster meets again before anyone's shared memory goes away.
+                        // and nothing is in flight into the ring any more), the cluster meets, the partials are summed in rank
+                        // order and stored, and the cluster meets again before anyone's shared memory goes away.
                         float* park = (float*)ring + (size_t)cb * 128 + etid;
 #pragma unroll
                         for (int j = 0; j < NC; ++j) park[(size_t)j * 128] = acc[j];
                         cluster_barrier();
-                        if (krank == 0) {
-                            for (int pr = 1; pr < ksl; ++pr) {
+                        // The token columns are dealt in contiguous blocks to the CTAs of the cluster: each sums its block
+                        // over all ranks (rank order: the same sum on every run) and stores it, so the remote reads of the
+                        // reduce run on all CTAs at once.  Eight columns at a time: their loads from every rank are in
+                        // flight together, then the eight stores.
+                        const int cols_per = NC / ksl < 2 ? 2 : NC / ksl;   // (a SwiGLU pair stays in one CTA)
+                        const int jbeg = krank * cols_per, jend = jbeg + cols_per < NC ? jbeg + cols_per : NC;
+                        uint32_t rbase[8];
 #pragma unroll
-                                for (int j = 0; j < NC; ++j) acc[j] += ld_cluster_f32(park + (size_t)j * 128, (uint32_t)pr);
+                        for (int pr = 0; pr < 8; ++pr)
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbase[pr]) : "r"(smem_u32(park)), "r"(pr < ksl ? pr : 0));
+                        const int row = rt * 128 + r;
+                        for (int jc = jbeg; jc < jend; jc += 8) {
+                            float sum[8];
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) sum[u] = 0.f;
+#pragma unroll
+                            for (int pr = 0; pr < 8; ++pr) {
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    if (pr < ksl && jc + u < jend) {
+                                        float v;
+                                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(rbase[pr] + (uint32_t)(jc + u) * 512u) : "memory");
+                                        sum[u] += v;
+                                    }
+                                }
+                            }
+                            if (a.swiglu) {
+                                // as the single-CTA SwiGLU store below: lanes l and l^8 hold a gate row and its up row
+                                bf16* ocol = (bf16*)a.out + rt * 64 + (r >> 4) * 8 + (r & 7);
+                                const float L = a.swiglu_limit;
+                                const bool is_gate = (r & 8) == 0;
+#pragma unroll
+                                for (int u = 0; u < 8; u += 2) {
+                                    const float o0 = __shfl_xor_sync(0xffffffffu, sum[u], 8);
+                                    const float o1 = __shfl_xor_sync(0xffffffffu, sum[u + 1], 8);
+                                    const int col = jc + (is_gate ? u : u + 1);
+                                    if (jc + u < jend && cb + col < cnt && row < a.n_rows) {
+                                        float gt = bf16_round(is_gate ? sum[u] : o1), up = bf16_round(is_gate ? o0 : sum[u + 1]);
+                                        if (L > 0.f) { up = fminf(fmaxf(up, -L), L); gt = fminf(gt, L); }
+                                        ocol[(size_t)(cb + col) * a.ldo] = __float2bfloat16(gt / (1.0f + expf(-gt)) * up);
+                                    }
+                                }
+                            } else {
+#pragma unroll
+                                for (int u = 0; u < 8; ++u)
+                                    if (jc + u < jend && cb + jc + u < cnt && row < a.n_rows) dense_store(a, cb + jc + u, row, sum[u] * a.alpha);
                             }
                         }
                         cluster_barrier();
                         cluster_done = true;
-                        do_store = krank == 0;
+                        do_store = false;   // stored above
                     } else if (!whole) {
                         const int slot = (q == beg / KT) ? 0 : 1;
                         float* pw = a.partial + ((size_t)(c * 2 + slot) * 64 + cb) * 128 + etid;

@@ -17,6 +17,10 @@ Sharding the projection by output columns instead of by K (what the reference's 
 projections, crates/engine/src/weights.rs:384-395) makes the first exchange a gather instead of a sum -- an eighth of
 the bytes on eight ranks -- and the sharded h equal to the unsharded one bit for bit.
 Routing is evaluated redundantly on every rank from the gathered rows (64 x 256 scores).
+At decode sizes the stack REPLICATES the dense projection instead (``dense_replicated``): 51 MB of FP8 weights stream from
+this GPU's HBM in less time than one hand-shake over NVLink takes (~8 us against ~13 us), every rank computes the
+identical h, and the layer is left with a single exchange (the combine).  Prefill-size batches keep the output-sharded
+projection and its gather, where the GEMM time, not the latency, is what counts.
 The reference has no expert parallelism (tensor parallel + its own push all-reduce,
 crates/kernels/cu/comm.cu:134-279); this exchange is this library's design.  On GPUs both exchanges run as this
 library's own one-shot kernels over NVLink peer memory (csrc/ep_comm.cu) when torch's symmetric memory can map the
@@ -83,10 +87,13 @@ def shard_bounds(total, world, rank):
 
 def ep_layer_forward(xch, compute, x_all):
     """One layer on one rank; x_all [T][H] holds ALL token rows (identical on every rank).  ``compute`` provides
-         dense_slice(x_all) -> h [T][H] with this rank's column slice filled in (all tokens; overwritten in place)
+         dense_slice(x_all) -> h [T][H] with this rank's column slice filled in (all tokens; overwritten in place);
+                               with ``compute.dense_replicated`` set, the whole h (every rank holds the whole dense
+                               weight and the gather is skipped)
          route(h_all) -> (ids [T][k], w [T][k])
          experts_partial(h_all, ids, w) -> y partial [T][H] over this rank's experts only (overwritten in place)
     Returns y [T][H], again identical on every rank."""
-    h_all = xch.all_gather_cols(compute.dense_slice(x_all))
+    h = compute.dense_slice(x_all)
+    h_all = h if getattr(compute, "dense_replicated", False) else xch.all_gather_cols(h)
     ids, w = compute.route(h_all)
     return xch.all_reduce(compute.experts_partial(h_all, ids, w))

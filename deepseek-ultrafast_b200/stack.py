@@ -99,12 +99,15 @@ class _KernelCompute:
 
     def __init__(self, stack, l):
         self.s, self.l = stack, l
+        self.dense_replicated = stack.dense_replicated
 
     def dense_slice(self, x_all):
         s, w = self.s, self.s.dense[self.l]
         ctx = s.ctx
         n0, n1 = s.nslice
-        act_quant(ctx, w.mode, x_all, s.xq, s.xs)
+        if s.prequantized is not x_all:   # (the previous layer's combine may have left x_all quantized in s.xq / s.xs)
+            act_quant(ctx, w.mode, x_all, s.xq, s.xs)
+        s.prequantized = None
         T = x_all.shape[0]
         if ctx.tcgen05:
             gemm_fp8(ctx, w, s.xq, s.xs, T, s.partial[:, n0:n1])   # decode kernel up to 64 rows, prefill kernel above
@@ -127,8 +130,14 @@ class _KernelCompute:
         if s.peer is not None and s.fuse_combine:
             # one kernel: local sum of the top-k rows into the mapped partial buffer, hand-shake, sum over the ranks
             out = s.xch.peer_out[part.data_ptr()]
-            return s.moe[self.l].forward(h_all, ids_all, w_all, part, route=route,
-                                         combine=lambda plan, yrows, shared: s.peer.combine(plan, yrows, shared, part, out))
+            # the result is the next layer's input: the combine leaves it quantized for that layer's dense projection
+            quant = (s.cfg.dense_mode, s.xq, s.xs) if s.fuse_quant and self.l + 1 < s.cfg.layers else None
+
+            def combine(plan, yrows, shared):
+                y = s.peer.combine(plan, yrows, shared, part, out, quant=quant)
+                s.prequantized = y if quant is not None else None
+                return y
+            return s.moe[self.l].forward(h_all, ids_all, w_all, part, route=route, combine=combine)
         return s.moe[self.l].forward(h_all, ids_all, w_all, part, route=route)
 
 
@@ -142,16 +151,20 @@ class EpLayerStack:
         self.ctx, self.cfg, self.rank, self.world = ctx, cfg, rank, world
         self.xch = ep.Exchange(dist, rank, world)
         H, I, E, T = cfg.hidden, cfg.inter, cfg.n_experts, cfg.tokens
-        self.nslice = ep.shard_bounds(H, world, rank)   # this rank's output columns of the dense projection
+        # decode: 8-row slots; prefill-size batches (tens of rows per expert and more): 128-row tiles (tcgen05 path only)
+        tile_rows = 128 if ctx.tcgen05 and T * cfg.topk >= 32 * E else 8
+        self.large = tile_rows == 128
+        # decode-size batches: every rank holds the whole dense weight and computes the whole h (one exchange per layer
+        # less, see ep.py); DSUF_EP_DENSE=shard keeps the output-sharded projection + gather at every size
+        self.dense_replicated = world > 1 and not self.large and os.environ.get("DSUF_EP_DENSE", "replicate") != "shard"
+        # this rank's output columns of the dense projection
+        self.nslice = (0, H) if self.dense_replicated else ep.shard_bounds(H, world, rank)
         if (self.nslice[1] - self.nslice[0]) % 128:
             raise ValueError("hidden / world must be a multiple of 128")
         self.e_lo, e_hi = ep.shard_bounds(E, world, rank)
         self.t0, self.t1 = ep.shard_bounds(T, world, rank)
         n_loc, nloc_d = e_hi - self.e_lo, self.nslice[1] - self.nslice[0]
         self.dense, self.moe, self.logits = [], [], []
-        # decode: 8-row slots; prefill-size batches (tens of rows per expert and more): 128-row tiles (tcgen05 path only)
-        tile_rows = 128 if ctx.tcgen05 and T * cfg.topk >= 32 * E else 8
-        self.large = tile_rows == 128
         for l in range(cfg.layers):
             # the shards of ONE set of random-init weights (the seeds of LayerStack): the dense weight's rows of this rank's
             # output columns and the experts at their global ids, so the W-rank result is comparable with the single-GPU one
@@ -206,6 +219,8 @@ class EpLayerStack:
         else:
             self.partial = t.empty((T, H), dtype=t.bfloat16, device=dev)
             self.y_part = [t.empty((T, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
+        self.prequantized = None   # the tensor whose FP8 codes / scales self.xq / self.xs currently hold, if any
+        self.fuse_quant = os.environ.get("DSUF_EP_FUSE_QUANT", "1") != "0"
         self.x_all = t.empty((T, H), dtype=t.bfloat16, device=dev)
         self.ids = t.empty((T, cfg.topk), dtype=t.int32, device=dev)
         self.w = t.empty((T, cfg.topk), dtype=t.float32, device=dev)
@@ -226,6 +241,7 @@ class EpLayerStack:
         default all)."""
         from . import ep
         cur = self.xch.all_gather_rows(self.x_all, x_local)
+        self.prequantized = None
         for l in range(self.cfg.layers if layers is None else layers):
             self.moe[l].events = events
             cur = ep.ep_layer_forward(self.xch, self.compute[l], cur)
@@ -235,7 +251,12 @@ class EpLayerStack:
         cfg = self.cfg
         slabs = 1 if self.ctx.tcgen05 else (cfg.tokens + 15) // 16
         front = 1 if cfg.tokens * cfg.topk <= 1024 else 5
-        # this library's exchange kernels (NCCL's kernels are not counted): the gather of the dense slices, and the combine
-        # that either follows the unpermute as an all-reduce or replaces it
-        ar = 0 if self.peer is None else 1 if self.fuse_combine else 3 if self.large else 2
-        return cfg.layers * (1 + slabs + front + 1 + 1 + 1 + 1 + ar)
+        # this library's exchange kernels (NCCL's kernels are not counted): the gather of the dense slices (none when the
+        # projection is replicated), and the combine that either replaces the unpermute (one fused kernel) or follows it as
+        # an all-reduce (one kernel; two -- reduce-scatter and gather -- for prefill-size batches)
+        unperm = 0 if self.peer is not None and self.fuse_combine else 1
+        xchg = 0 if self.peer is None else 2 if self.large and not self.fuse_combine else 1
+        gather = 1 if self.peer is not None and not self.dense_replicated else 0
+        # the fused combine leaves its result quantized: only the first layer quantizes its dense input by itself
+        quants = 1 if self.peer is not None and self.fuse_combine and self.fuse_quant else cfg.layers
+        return cfg.layers * (slabs + front + 1 + 1 + 1 + unperm + xchg + gather) + quants

@@ -196,21 +196,24 @@ int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_
  *   out_f32  1 = fp32 output (out / out2 are float buffers) instead of bf16 (GemvOpts.out_f32; cu/gemv.cu:510-517)
  *   n_split  > 0 = weight rows [n_split, n) are written to out2 (row stride ldo2) at column row - n_split, rows
  *            [0, n_split) to out (GemvOpts.split: one launch for two projections merged along n, e.g. Loader::fp8_merged)
- * The AtomicAdd / sqrt-softplus / Partial epilogue kinds of the reference's dense GEMV and its fused RoPE are not offered. */
+ * The AtomicAdd / Partial epilogue kinds of the reference's dense GEMV and its fused RoPE are not offered. */
 typedef struct {
     float alpha;
     int32_t out_f32;
     int32_t n_split;
     int32_t ldo2;
     uint64_t out2;
-    int32_t epilogue;      /* DSUF_EPI_STORE or DSUF_EPI_SWIGLU */
+    int32_t epilogue;      /* DSUF_EPI_STORE, DSUF_EPI_SWIGLU or DSUF_EPI_SQRT_SOFTPLUS */
     float swiglu_limit;    /* SwiGLU: clamp as cu/gemv.cu:470-483 when > 0 */
 } dsuf_gemm_opts;
 /* Epilogue::Store / Epilogue::SwiGlu (crates/engine/src/ops.rs:137-144).  SWIGLU: the weight holds gate and up rows
  * (packed by dsuf_pack_fp8_weight_gate_up, MX scales, tcgen05 path) and out receives bf16 [m][n/2] =
  * bf16(silu(bf16 gate) * bf16 up), the reference's shared-expert gate/up projection (gemm_tc with Epilogue::SwiGlu,
- * model.rs:3081-3084; cu/tcgemm.cu:89-110); alpha must be 1, out_f32 0, n_split 0. */
-enum { DSUF_EPI_STORE = 0, DSUF_EPI_SWIGLU = 1 };
+ * model.rs:3081-3084; cu/tcgemm.cu:89-110); alpha must be 1, out_f32 0, n_split 0.
+ * SQRT_SOFTPLUS: the router-gate projection (ops::gemv with Epilogue::SqrtSoftplus, model.rs:3094; cu/gemv.cu:523):
+ * fp32 out[m][n] = sqrt(softplus(alpha * dot)) (sqrt(x) itself above 20, cu/common.cuh:17-24), i.e. the scores
+ * dsuf_moe_route_tokens takes with DSUF_SCORE_IDENTITY; out is always fp32 (out_f32 is implied), n_split works as for STORE. */
+enum { DSUF_EPI_STORE = 0, DSUF_EPI_SWIGLU = 1, DSUF_EPI_SQRT_SOFTPLUS = 2 };
 /* dsuf_gemm_fp8 with options; same kernels, any number of token rows. */
 int32_t dsuf_gemm_fp8_ex(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
                          int32_t ldo, const dsuf_gemm_opts* opts, uint64_t workspace);
@@ -340,6 +343,13 @@ int32_t dsuf_ep_allgather_cols_bf16(dsuf_ctx* ctx, void* stream, const uint64_t*
 int32_t dsuf_ep_combine_bf16(dsuf_ctx* ctx, void* stream, uint64_t pair_row, uint64_t yrows, uint64_t shared, int32_t t,
                              int32_t topk, int32_t h, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
                              int32_t world, uint64_t state, uint64_t out);
+/* dsuf_ep_combine_bf16 that also leaves the result quantized for the next projection: xq [t][h] FP8 codes and xs block
+ * scales (mode MX: u8 [t][h/32], DS: f32 [t][h/128]) equal to dsuf_act_quant_fp8(mode, out) bit for bit, so the layer that
+ * follows starts at its GEMM.  The counterpart of the activation staging the reference's decode GEMVs run on their input
+ * (quant_blocks8, cu/quantblocks.cuh:7-57) moved into the producer.  xq = xs = 0: plain combine.  h % 128 == 0. */
+int32_t dsuf_ep_combine_quant_bf16(dsuf_ctx* ctx, void* stream, uint64_t pair_row, uint64_t yrows, uint64_t shared, int32_t t,
+                                   int32_t topk, int32_t h, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
+                                   int32_t world, uint64_t state, uint64_t out, int32_t mode, uint64_t xq, uint64_t xs);
 
 #ifdef __cplusplus
 }

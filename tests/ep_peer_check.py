@@ -58,6 +58,18 @@ def main():
         ar.combine(plan, yrows, None, bufs[it & 1], out)
         torch.cuda.synchronize()
         ok = ok and bool(((out.float() - ref).abs() <= mag * 2.0 ** -7 + 1e-5).all()) and ctx.status().code == 0
+    # the same with the result left quantized for the next projection: codes and scales of act_quant(out), bit for bit
+    for mode in (pkg.MODE_DS, pkg.MODE_MX):
+        blk = 128 if mode == pkg.MODE_DS else 32
+        xq = torch.zeros(tokens, width, dtype=torch.uint8, device="cuda")
+        xs = torch.zeros(tokens, width // blk, dtype=torch.float32 if mode == pkg.MODE_DS else torch.uint8, device="cuda")
+        ar.combine(plan, yrows, None, bufs[0], out, quant=(mode, xq, xs))
+        torch.cuda.synchronize()
+        rq, rs = pkg.act_quant(ctx, mode, out)
+        torch.cuda.synchronize()
+        ok = ok and bool(((out.float() - ref).abs() <= mag * 2.0 ** -7 + 1e-5).all()) and ctx.status().code == 0
+        ok = ok and bool((xq == rq).all()) and bool((xs.view(torch.uint8) == rs.view(torch.uint8)).all())
+        dist.barrier()      # (bufs[0] is rewritten by the next round only after every rank has read it)
     # all-gather of column slices: rank r fills its own columns, everybody ends up with the same full rows, bit for bit
     gg = torch.Generator(device="cuda").manual_seed(4242)      # same on every rank
     full = torch.randn(rows, width, generator=gg, device="cuda").bfloat16()

@@ -1,5 +1,6 @@
 """Expert-parallel exchange on CPU: two gloo ranks run ep.ep_layer_forward with the oracle as the compute steps and must
-reproduce the single-rank layer (output-sharded dense + all-gather = dispatch, expert shards, all-reduce = combine)."""
+reproduce the single-rank layer (output-sharded dense + all-gather = dispatch, or the replicated dense projection of the
+decode sizes; expert shards; all-reduce = combine)."""
 import os
 import socket
 import sys
@@ -28,13 +29,14 @@ def _inputs():
 
 
 class OracleCompute:
-    def __init__(self, inp, rank, world):
+    def __init__(self, inp, rank, world, dense_replicated=False):
         import oracle
         from __graft_entry__ import load_package
         import importlib
         self.o, self.inp, self.rank, self.world = oracle, inp, rank, world
         ep = importlib.import_module(load_package().__name__ + ".ep")
-        self.n0, self.n1 = ep.shard_bounds(H, world, rank)
+        self.dense_replicated = dense_replicated    # every rank computes the whole h; the layer skips the gather
+        self.n0, self.n1 = (0, H) if dense_replicated else ep.shard_bounds(H, world, rank)
         self.e0, self.e1 = ep.shard_bounds(E, world, rank)
         self.t0, self.t1 = ep.shard_bounds(T, world, rank)
         self.wq, self.ws = oracle.quant_fp8_weight(oracle.MODE_DS, np.ascontiguousarray(inp["wd"][self.n0:self.n1]))
@@ -58,7 +60,7 @@ class OracleCompute:
         return torch.from_numpy(r["y_bf16"].view(np.int16)).view(torch.bfloat16)
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, dense_replicated=False):
     sys.path.insert(0, ROOT)
     import importlib
     import torch.distributed as dist
@@ -69,7 +71,7 @@ def _worker(rank, world, port, out_dir):
     inp = _inputs()
     xch = ep.Exchange(dist, rank, world)
     t0, t1 = ep.shard_bounds(T, world, rank)
-    comp = OracleCompute(inp, rank, world)
+    comp = OracleCompute(inp, rank, world, dense_replicated)
     x_all = xch.all_gather_rows(torch.empty(T, H, dtype=torch.bfloat16), inp["x"][t0:t1].contiguous())
     y = ep.ep_layer_forward(xch, comp, x_all)
     torch.save((comp.h.clone(), y.clone()), os.path.join(out_dir, f"y{rank}.pt"))
@@ -77,7 +79,8 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-def test_two_rank_layer_equals_single_rank(tmp_path):
+@pytest.mark.parametrize("dense_replicated", [False, True])
+def test_two_rank_layer_equals_single_rank(tmp_path, dense_replicated):
     sys.path.insert(0, ROOT)
     import importlib
     from __graft_entry__ import load_package
@@ -89,7 +92,7 @@ def test_two_rank_layer_equals_single_rank(tmp_path):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, str(tmp_path), dense_replicated), nprocs=2, join=True)
     parts = [torch.load(os.path.join(tmp_path, f"y{r}.pt")) for r in range(2)]
     h2, y2 = parts[0][0], parts[0][1].float()
     assert (parts[1][0] == h2).all() and (parts[1][1].float() == y2).all()   # every rank holds the same full rows

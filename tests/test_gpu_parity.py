@@ -194,6 +194,11 @@ def test_dense_gemv_options_fp32_output_and_column_split(pkg, ctx, mode, n, k, m
         assert torch.equal(af, f32[:, :split]) and torch.equal(bf, f32[:, split:])
         with pytest.raises(pkg.DsufError):
             pkg.gemm_fp8_ex(ctx, w, xq, xs, m, n_split=n)          # nothing left for the second output
+    # the router-gate epilogue: sqrt(softplus(.)) of the fp32 result, in fp32 (what the router takes as ready scores)
+    ssp = pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, sqrt_softplus=True)
+    torch.cuda.synchronize()
+    want = torch.sqrt(torch.where(f32 > 20, f32, torch.log1p(torch.exp(f32))))
+    assert ssp.dtype == torch.float32 and torch.allclose(ssp, want, rtol=1e-5, atol=1e-6)
     assert ctx.status().code == 0
 
 
