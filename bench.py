@@ -235,6 +235,27 @@ def dense_sweep(pkg, ctx, torch, hbm_peak, quick):
     return out
 
 
+def lm_head_bench(pkg, ctx, torch, hbm_peak, vocab=129280):
+    """The output head (bf16 [vocab][7168] weight, 1.85 GB: larger than L2, read once per call) at 1 and 8 token rows,
+    with the sampling records on; microseconds per call and the weight bytes per second."""
+    g = torch.Generator(device="cuda").manual_seed(99)
+    w = (torch.randn(vocab, H, generator=g, device="cuda") * 0.02).bfloat16()
+    out = {"vocab": vocab, "k": H, "weight_bytes": vocab * H * 2, "cases": []}
+    for m in (1, 8):
+        x = torch.randn(m, H, generator=g, device="cuda").bfloat16()
+        logits = torch.empty(m, vocab, dtype=torch.float32, device="cuda")
+        rec = torch.zeros(m, vocab // 64, 20, dtype=torch.float32, device="cuda")
+        ms = time_events(torch, lambda: pkg.lm_head(ctx, w, x, out=logits, temperature=0.8, records=rec), 10, 3)
+        ms_plain = time_events(torch, lambda: pkg.lm_head(ctx, w, x, out=logits), 10, 3)
+        gbs = vocab * H * 2 / (ms * 1e-3) / 1e9
+        out["cases"].append({"m": m, "us": round(ms * 1e3, 1), "us_without_records": round(ms_plain * 1e3, 1), "gbs": round(gbs, 1),
+                             "frac_of_measured_hbm": round(gbs / hbm_peak, 3), "frac_of_8tbs": round(gbs / 8000.0, 3)})
+    out["device_status"] = int(ctx.status().code)
+    del w
+    torch.cuda.empty_cache()
+    return out
+
+
 def _graph_us(torch, launches, reps=10):
     """Microseconds per launch of a list of callables captured into one CUDA graph and replayed (GPU time, not launch rate)."""
     side = torch.cuda.Stream()
@@ -630,6 +651,8 @@ def run_ours(args):
                                    "routing": "softmax of N(0,1) logits, top-8 (near-uniform expert load)",
                                    "launches_per_layer": pstack.count_launches() // LAYERS, "device_status": int(ctx.status().code)}
         del pstack, xp
+    if world == 1 and not args.skip_sub and not args.quick:
+        result["lm_head"] = lm_head_bench(pkg, ctx, torch, hbm_peak)
     if world == 1 and not args.skip_sub and not args.skip_ref_kernels:
         try:
             result["reference_kernels"] = reference_kernels(pkg, ctx, torch, hbm_peak, args.quick)

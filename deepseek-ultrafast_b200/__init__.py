@@ -44,6 +44,10 @@ class GemmOpts(C.Structure):
                 ("epilogue", C.c_int32), ("swiglu_limit", C.c_float)]
 
 
+class SamplingOpts(C.Structure):
+    _fields_ = [("records", C.c_uint64), ("temperature", C.c_float), ("valid_rows", C.c_int32), ("id_offset", C.c_int32)]
+
+
 class TensorInfo(C.Structure):
     _fields_ = [("dtype", C.c_char * 16), ("rank", C.c_int32), ("shape", C.c_int64 * 8), ("data", C.c_void_p), ("nbytes", C.c_size_t)]
 
@@ -103,6 +107,8 @@ ABI = {
                                      C.c_int32, C.POINTER(GemmOpts), C.c_uint64]),
     "dsuf_gemm_fp8_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_int32, C.c_uint64,
                                          C.c_int32, C.c_float]),
+    "dsuf_lm_head_bf16": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int32, C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_float,
+                                      C.c_uint64, C.c_int32, C.POINTER(SamplingOpts)]),
     "dsuf_probe_tensor_rate": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_double)]),
     "dsuf_moe_route": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_uint64, C.c_uint64, C.c_int32, C.c_int32,
                                    C.c_int32, C.c_float, C.c_uint64, C.c_uint64]),
@@ -542,6 +548,25 @@ class PeerAllReduce:
                                                         self.flag_ptrs, self.rank, self.world, self.state.data_ptr(), out.data_ptr(),
                                                         mode, xq.data_ptr() if xq is not None else 0, xs.data_ptr() if xs is not None else 0))
         return out
+
+
+def lm_head(ctx, w, x, alpha=1.0, out=None, temperature=None, valid_rows=0, id_offset=0, records=None):
+    """dsuf_lm_head_bf16 = the output head, ops::gemv with GemvOpts {persist, out_f32, samp_rec} (crates/engine/src/ops.rs:165-193):
+    fp32 logits [m][n] of bf16 token rows x [m][k] (m <= 16) against the row-major bf16 weight w [n][k].  With a
+    ``temperature`` the per-quad sampling records float [m][n/64][20] are written too; returns (logits, records)."""
+    t = ctx.torch
+    n, k = w.shape
+    m = x.shape[0]
+    if out is None:
+        out = t.empty((m, n), dtype=t.float32, device=x.device)
+    sp = None
+    if temperature is not None:
+        if records is None:
+            records = t.zeros((m, n // 64, 20), dtype=t.float32, device=x.device)
+        sp = SamplingOpts(records.data_ptr(), float(temperature), int(valid_rows), int(id_offset))
+    ctx.check(lib().dsuf_lm_head_bf16(ctx.h, ctx.stream(), w.data_ptr(), n, k, x.data_ptr(), x.stride(0), m, alpha, out.data_ptr(),
+                                      out.stride(0), C.byref(sp) if sp is not None else None))
+    return (out, records) if temperature is not None else out
 
 
 def probe_tensor_rate(ctx, n_cols=128, a_is_e2m1=False, iters=20000, reps=5):

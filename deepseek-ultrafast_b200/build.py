@@ -11,7 +11,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdsuf_qmm.so")
-SOURCES = ["abi.cu", "quant.cu", "moe_aux.cu", "stream_launch.cu", "noalloc.cu", "ep_comm.cu", "peak_probe.cu", "pack.cc", "loader.cc"]
+SOURCES = ["abi.cu", "quant.cu", "moe_aux.cu", "stream_launch.cu", "noalloc.cu", "ep_comm.cu", "peak_probe.cu", "lm_head.cu", "pack.cc", "loader.cc"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
          "-Xptxas", "-v", "--expt-relaxed-constexpr", "-ccbin", "/usr/bin/g++"] + os.environ.get("DSUF_EXTRA_NVCC_FLAGS", "").split()

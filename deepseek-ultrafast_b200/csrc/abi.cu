@@ -42,6 +42,7 @@ int32_t dsuf_ctx_create(int32_t device, dsuf_ctx** out) {
     if (e != cudaSuccess) { delete ctx; return (int32_t)e; }
     cudaMemset(ctx->dev_status, 0, sizeof(DevStatus));
     int rc = stream_setup(ctx);
+    if (!rc) rc = lm_head_setup(ctx);
     if (rc) { cudaFree(ctx->dev_status); delete ctx; return rc; }
     *out = ctx;
     return DSUF_OK;

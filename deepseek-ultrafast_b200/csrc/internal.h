@@ -117,6 +117,7 @@ int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float*
 int launch_unpermute(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
                      int t, int topk, int h, void* out, int ldo);
 int stream_setup(dsuf_ctx* ctx);
+int lm_head_setup(dsuf_ctx* ctx);
 int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, long long rows, int box_rows);
 
 }  // namespace dsuf

@@ -351,6 +351,24 @@ int32_t dsuf_ep_combine_quant_bf16(dsuf_ctx* ctx, void* stream, uint64_t pair_ro
                                    int32_t topk, int32_t h, const uint64_t* peer_data, const uint64_t* peer_flags, int32_t rank,
                                    int32_t world, uint64_t state, uint64_t out, int32_t mode, uint64_t xq, uint64_t xs);
 
+/* ---- output head.  Replaces the persistent bf16 GEMV with sampling records, gemv_bf16_persist_p4
+ * (crates/kernels/cu/gemv.cu:542-689; ops::gemv with GemvOpts {persist, samp_rec, out_f32}, ops.rs:165-193). ----
+ * out fp32 [m][ldo] = alpha * x [m][ldx] (bf16) . w [n][k]^T (bf16, ROW-MAJOR as in the checkpoint: no host re-tiling,
+ * where the reference streams weights re-tiled by tile_bf16), m <= 16, k % 8 == 0.  With `sp` and sp->records != 0 the
+ * kernel also writes, per token and per quad of 64 vocabulary rows, the 20-float record the reference's sampler merges
+ * (cu/gemv.cu:651-688): [0] max z, [1] sum exp(z - max), [2] the 9th largest z, [3..10] the 8 largest z (descending),
+ * [11..18] their ids as int bits (ties: lower id first), [19] unused; z = logit / temperature for rows < valid_rows
+ * (0: all n) and -inf above, id = row + id_offset (a vocabulary shard's first row).  records: float
+ * [m][n / 64][20]; n % 64 == 0. */
+typedef struct {
+    uint64_t records;
+    float temperature;
+    int32_t valid_rows;
+    int32_t id_offset;
+} dsuf_sampling_opts;
+int32_t dsuf_lm_head_bf16(dsuf_ctx* ctx, void* stream, uint64_t w, int32_t n, int32_t k, uint64_t x, int32_t ldx, int32_t m,
+                          float alpha, uint64_t out, int32_t ldo, const dsuf_sampling_opts* sp);
+
 #ifdef __cplusplus
 }
 #endif

@@ -229,6 +229,42 @@ def dequant_fp4(codes, s):
     return v * np.repeat(sf, 32, axis=1)
 
 
+def lm_head(w_bf16, x_bf16, alpha=1.0):
+    """Output-head logits fp32 [m][n] = alpha * x . w^T over bf16 operands with fp32 accumulation
+    (gemv_bf16_persist_body, crates/kernels/cu/gemv.cu:542-650; the accumulation order inside a row is the kernel's own,
+    so comparisons carry a tolerance)."""
+    return (matmul_f32(bf16_to_f32(w_bf16), bf16_to_f32(x_bf16)) * np.float32(alpha)).astype(np.float32)
+
+
+def sampling_records(logits, temperature, valid_rows=0, id_offset=0):
+    """Per (token, quad of 64 vocabulary rows) the 20-float record of crates/kernels/cu/gemv.cu:651-688:
+    [0] max z, [1] sum exp(z - max), [2] 9th largest z, [3..10] the 8 largest z (descending), [11..18] their ids as int
+    bits (equal values: lower id first), [19] 0; z = logit * (1 / temperature) in fp32 for rows < valid_rows (0: all),
+    -inf above; id = row + id_offset.  Plain loops over quads: small inputs only."""
+    logits = np.asarray(logits, np.float32)
+    m, n = logits.shape
+    assert n % 64 == 0
+    vloc = valid_rows if valid_rows > 0 else n
+    inv_t = np.float32(1.0) / np.float32(temperature)
+    rec = np.zeros((m, n // 64, 20), np.float32)
+    ids_view = rec.view(np.int32)
+    for t in range(m):
+        for q in range(n // 64):
+            rows = np.arange(q * 64, q * 64 + 64)
+            z = np.where(rows < vloc, logits[t, rows] * inv_t, np.float32(-np.inf)).astype(np.float32)
+            order = np.lexsort((rows, -z.astype(np.float64)))     # by z descending, then by id ascending
+            top = order[:9]
+            zmax = z[top[0]]
+            rec[t, q, 0] = zmax
+            with np.errstate(invalid="ignore"):
+                e = np.where(np.isneginf(z), np.float32(0), np.exp((z - zmax).astype(np.float32), dtype=np.float32))
+            rec[t, q, 1] = np.float32(e.astype(np.float64).sum())
+            rec[t, q, 2] = z[top[8]]
+            rec[t, q, 3:11] = z[top[:8]]
+            ids_view[t, q, 11:19] = rows[top[:8]] + id_offset
+    return rec
+
+
 def num_threads():
     return lib().dsufo_num_threads()
 

@@ -662,3 +662,36 @@ def test_moe_layer_prefill_benchmark_shapes_sampled_tokens(pkg, ctx, act_mode):
     ids_l = np.vectorize(remap.get)(ids_n[sample]).astype(np.int32)
     ref = oracle.moe_layer(act_mode, xn[sample], ids_l, rw_n[sample], np.stack(c13), np.stack(s13), np.stack(c2), np.stack(s2))
     assert rel(got[sample], ref["y_f32"]) < TOL
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,k,m", [(1280, 512, 1), (320, 7168, 5), (2048 + 64, 1024 + 64, 16), (129280 // 10, 7168, 8)])
+def test_lm_head_logits_and_sampling_records(pkg, ctx, n, k, m):
+    """The output head: fp32 logits against the oracle (bf16 products are exact in fp32; the kernel's accumulation order is
+    its own: 2e-3 of the row norm), and the per-quad sampling records against the oracle's selection applied to the
+    kernel's own logits: maxima, top-8 values, ids and the 9th value bit for bit, the exponential sums to 1e-5.  Shapes:
+    a ragged last row tile (n % 128 = 64), K that is not a multiple of a ring stage, a duplicated weight row (a tie)."""
+    g = seeded(n + k + m)
+    xt, xn = randn_bf16(g, m, k)
+    wt, wn = randn_bf16(g, n, k, std=0.05)
+    wt[n // 2 + 3] = wt[n // 2 + 1]            # equal logits inside one quad: the lower id must come first
+    wn = wt.view(torch.uint16).numpy()
+    want = oracle.lm_head(wn, xn, alpha=0.75)
+    valid = n - 40
+    logits, rec = pkg.lm_head(ctx, wt.cuda(), xt.cuda(), alpha=0.75, temperature=0.7, valid_rows=valid, id_offset=5000)
+    plain = pkg.lm_head(ctx, wt.cuda(), xt.cuda(), alpha=0.75)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    got = logits.cpu().numpy()
+    assert np.array_equal(got, plain.cpu().numpy())
+    scale = np.linalg.norm(want, axis=1, keepdims=True) / np.sqrt(n)
+    assert np.abs(got - want).max() <= 2e-3 * scale.max() + 1e-6, np.abs(got - want).max()
+    ref = oracle.sampling_records(got, 0.7, valid_rows=valid, id_offset=5000)
+    r = rec.cpu().numpy()
+    assert np.array_equal(r[..., 0], ref[..., 0]) and np.array_equal(r[..., 2:11], ref[..., 2:11])
+    assert np.array_equal(r.view(np.int32)[..., 11:19], ref.view(np.int32)[..., 11:19])
+    assert np.allclose(r[..., 1], ref[..., 1], rtol=1e-5, atol=1e-6)
+    t_ids = r.view(np.int32)[0, (n // 2 + 1) // 64, 11:19]
+    if (n // 2 + 1) in (t_ids - 5000):        # the tie made the top 8: its twin follows it directly
+        i = list(t_ids - 5000).index(n // 2 + 1)
+        assert i == 7 or t_ids[i + 1] - 5000 == n // 2 + 3

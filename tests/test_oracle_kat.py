@@ -196,3 +196,20 @@ def test_row_sumsq_and_prenorm_quant():
         q0, s0 = oracle.act_quant(mode, vb)
         q1, s1 = oracle.act_quant_prenorm(mode, xb, wb, ss, float(eps))
         assert (q0 == q1).all() and (s0 == s1).all()
+
+
+def test_sampling_records_known_answers():
+    """The per-quad record of the output head (crates/kernels/cu/gemv.cu:651-688) on inputs whose answer is known:
+    an ascending ramp, a tie (lower id first), rows masked by valid_rows, and the id offset of a vocabulary shard."""
+    z = np.arange(128, dtype=np.float32)[None, :].copy()
+    z[0, 70] = z[0, 127]                      # a tie inside the second quad: id 70 comes before id 127
+    rec = oracle.sampling_records(z, temperature=2.0, valid_rows=120, id_offset=1000)
+    ids = rec.view(np.int32)
+    assert rec.shape == (1, 2, 20)
+    assert rec[0, 0, 0] == 31.5 and np.array_equal(rec[0, 0, 3:11], np.arange(63, 55, -1) / 2.0) and rec[0, 0, 2] == 27.5
+    assert np.array_equal(ids[0, 0, 11:19], 1000 + np.arange(63, 55, -1))
+    assert abs(rec[0, 0, 1] - np.exp((np.arange(64) - 63) / 2.0).sum()) < 1e-4
+    # second quad: rows 120..127 are masked (-inf), so the maximum is the tie's value at id 70 only
+    assert rec[0, 1, 0] == 63.5 and ids[0, 1, 11] == 1070 and rec[0, 1, 4] == 119 / 2.0 and ids[0, 1, 12] == 1119
+    lg = oracle.lm_head(oracle.f32_to_bf16(np.eye(64, 32, dtype=np.float32)), oracle.f32_to_bf16(np.ones((2, 32), np.float32)), alpha=0.5)
+    assert lg.shape == (2, 64) and np.array_equal(lg[0, :32], np.full(32, 0.5, np.float32)) and not lg[:, 32:].any()
