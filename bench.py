@@ -32,7 +32,7 @@ H, I, E, TOPK, LAYERS = 7168, 2048, 256, 8, 4
 DENSE_SHAPES = [(4096, 7168), (7168, 2048), (18432, 7168), (7168, 16384)]
 METRIC = "moe_layer_stack_decode_tokens_per_s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch in the ncu small case, divided by its 55 active experts
-NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT = (858.861568e6 + 3.328e6) / 55
+NCU_W13_DRAM_BYTES_PER_ACTIVE_EXPERT = (858.861312e6 + 4.27136e6) / 55
 
 
 def peaks():
@@ -676,6 +676,7 @@ def small_case(args):
     decode : one dense FP8 GEMV (18432 x 7168 and 7168 x 2048, --case-m token rows) and one decode expert layer
              (default 64 experts of the benchmark shape, 16 tokens, top-8: ~59 active experts, 0.92 GB of gate/up weights),
              each run twice.
+    lmhead : the output head over 32320 x 7168 bf16 weights (463 MB), 8 token rows, sampling records on, run twice.
     prefill: one expert layer on 128-row plans (default 8 experts, 2048 tokens, top-8) and one dense 7168 x 7168 GEMM over
              the same tokens, each run twice."""
     import torch
@@ -686,6 +687,17 @@ def small_case(args):
     mode = pkg.MODE_MX if args.case_mode == "mx" else pkg.MODE_DS
     ctx = pkg.Ctx(0, pdl=args.pdl)
     dev = ctx.device
+    if args.small_case == "lmhead":
+        # the output head on a quarter of the vocabulary (32320 x 7168 bf16 = 463 MB: larger than L2), 8 token rows, records on
+        n = args.case_experts or 32320
+        g = torch.Generator(device=dev).manual_seed(99)
+        w = (torch.randn(n, H, generator=g, device=dev) * 0.02).bfloat16()
+        x = torch.randn(8, H, generator=g, device=dev).bfloat16()
+        for _ in range(2):
+            logits, rec = pkg.lm_head(ctx, w, x, temperature=0.8)
+        torch.cuda.synchronize()
+        print(json.dumps({"small_case": "lmhead", "vocab_rows": n, "weight_bytes": n * H * 2, "device_status": int(ctx.status().code)}))
+        return
     prefill = args.small_case == "prefill"
     n_exp = args.case_experts or (8 if prefill else 64)
     tokens = args.case_tokens or (2048 if prefill else 16)
@@ -799,7 +811,7 @@ def main():
     ap.add_argument("--skip-parity", action="store_true", help="N > 1: leave out the one-layer comparison with the single-GPU stack")
     ap.add_argument("--no-sustain", dest="sustain", action="store_false", help="leave out the second timed region of >= 1 s")
     ap.add_argument("--exchange-bench", action="store_true", help="under torch.distributed.run: time the peer-memory exchange kernels beside NCCL and exit")
-    ap.add_argument("--small-case", default=None, choices=["decode", "prefill"],
+    ap.add_argument("--small-case", default=None, choices=["decode", "prefill", "lmhead"],
                     help="run a few launches of a small case (a few GB on the device) and exit: the case the ncu captures use")
     ap.add_argument("--case-mode", default="ds", choices=["ds", "mx"], help="scale geometry of --small-case")
     ap.add_argument("--case-experts", type=int, default=None)

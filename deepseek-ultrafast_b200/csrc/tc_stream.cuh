@@ -542,6 +542,19 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
 #pragma unroll
                         for (int j = 0; j < NC; ++j) park[(size_t)j * 128] = acc[j];
                         cluster_barrier();
+                        if (NC * ksl <= 32) {
+                            // few columns and few slices: CTA 0 adds the others' partials (all NC loads of a peer in flight
+                            // together) and stores; measured ~1 us faster than spreading so little work over the cluster
+                            if (krank == 0) {
+                                for (int pr = 1; pr < ksl; ++pr) {
+#pragma unroll
+                                    for (int j = 0; j < NC; ++j) acc[j] += ld_cluster_f32(park + (size_t)j * 128, (uint32_t)pr);
+                                }
+                            }
+                            cluster_barrier();
+                            cluster_done = true;
+                            do_store = krank == 0;
+                        } else {
                         // The token columns are dealt in contiguous blocks to the CTAs of the cluster: each sums its block
                         // over all ranks (rank order: the same sum on every run) and stores it, so the remote reads of the
                         // reduce run on all CTAs at once.  Eight columns at a time: their loads from every rank are in
@@ -593,6 +606,7 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                         cluster_barrier();
                         cluster_done = true;
                         do_store = false;   // stored above
+                        }
                     } else if (!whole) {
                         const int slot = (q == beg / KT) ? 0 : 1;
                         float* pw = a.partial + ((size_t)(c * 2 + slot) * 64 + cb) * 128 + etid;

@@ -491,3 +491,121 @@ def tc_gemv_fp8(tw, x, out=None, alpha=1.0, pdl=False):
     launch(f, (tw.n // 128, cs, 1), 128, smem, [p], cluster=(1, cs, 1), pdl=pdl)
     _KEEP.append((tw, x, out))
     return out
+
+
+# ------------------------------------------------------------------------------------------------ prefill expert GEMMs
+class TmParams(C.Structure):       # crates/engine/src/ops.rs:1511-1534, mirror of cu/tcmoe.cu:137-160
+    _fields_ = [("w", C.c_uint64), ("w_stride", C.c_uint64), ("k", C.c_int32), ("rt", C.c_int32), ("tb", C.c_uint64), ("sfb", C.c_uint64),
+                ("tiles", C.c_uint64), ("ntiles", C.c_uint64), ("row_pair", C.c_uint64), ("row_w", C.c_uint64), ("aq", C.c_uint64),
+                ("asf", C.c_uint64), ("ldaq", C.c_int32), ("akt", C.c_int32), ("limit", C.c_float), ("nq", C.c_int32), ("out", C.c_uint64),
+                ("ldo", C.c_int32), ("flags", C.c_int32), ("sf_off", C.c_uint64)]
+
+
+assert C.sizeof(TmParams) == 128
+TM_SMEM = 4 * 16384 + 2 * (16 * 2080 + 4096) + 3 * 8 * 2176 + 40 * 512 + 2 * 32 * 33 * 4 + 1024   # crates/engine/src/ops.rs:1543
+FP4_STEP = 2048 + 128                                                                             # crates/model/src/formats.rs:145
+
+
+def tile_fp4(codes, scales):
+    """tile_fp4 (crates/model/src/formats.rs:147-180): e2m1 codes u8 [n][k/2] (low nibble = even k) and UE8M0 scales u8
+    [n][k/32] -> the image the mma.sync / prefill expert kernels stream: per 64-row quad and 64-K step 2048 bytes of
+    codes (4 row groups x 32 lanes x 16 bytes; lane (g, t) holds, for j in 0..4, the bytes of rows {g, g+8} at K bytes
+    {8j + t, 8j + 4 + t} of the step) followed by 128 bytes of scales (row group x g x {row g: 2 scales, row g+8: 2})."""
+    w = np.ascontiguousarray(codes, np.uint8)
+    s = np.ascontiguousarray(scales, np.uint8)
+    n, kh = w.shape
+    k = kh * 2
+    require(n % 64 == 0 and k % 64 == 0 and s.shape == (n, k // 32), "tile_fp4 needs n % 64 == 0, k % 64 == 0, one scale per 32")
+    steps = k // 64
+    # byte column of a row = ks*32 + j*8 + half*4 + t;  row = q*64 + rg*16 + h*8 + g
+    w8 = w.reshape(n // 64, 4, 2, 8, steps, 4, 2, 4)                        # [q][rg][h][g][ks][j][half][t]
+    cw = np.ascontiguousarray(w8.transpose(0, 4, 1, 3, 7, 5, 2, 6))         # [q][ks][rg][g][t][j][h][half]
+    s6 = s.reshape(n // 64, 4, 2, 8, steps, 2)                              # [q][rg][h][g][ks][c]
+    cs = np.ascontiguousarray(s6.transpose(0, 4, 1, 3, 2, 5))               # [q][ks][rg][g][h][c]
+    out = np.empty((n // 64, steps, FP4_STEP), np.uint8)
+    out[:, :, :2048] = cw.reshape(n // 64, steps, 2048)
+    out[:, :, 2048:] = cs.reshape(n // 64, steps, 128)
+    return out.reshape(-1)
+
+
+def interleave_gate_up(gate, up):
+    """The row order of an expert's w13 image (crates/model/src/packing.rs:237-241): within each 64-row quad, rows 0-31 are
+    gate rows 32q..32q+31 and rows 32-63 the matching up rows.  gate / up: [inter][...] -> [2*inter][...]."""
+    inter = gate.shape[0]
+    require(inter % 32 == 0 and up.shape == gate.shape, "inter % 32 == 0")
+    g = gate.reshape(inter // 32, 32, -1)
+    u = up.reshape(inter // 32, 32, -1)
+    return np.ascontiguousarray(np.concatenate([g, u], axis=1)).reshape(2 * inter, -1)
+
+
+def _maps8(base_tensor, cols, rows):
+    """The eight activation tensor maps of PrefillMoe (crates/engine/src/model.rs:864-871): box rows 16, 32, ..., 128 over
+    the same u8 [rows][cols] image, 128 bytes apart in one device allocation."""
+    import torch
+    require(base_tensor.data_ptr() % 16 == 0 and cols % 128 == 0, "activation image alignment")
+    host = np.zeros(8 * 128, np.uint8)
+    for nb in range(1, 9):
+        _check(lib().refk_tmap_u8_sw128(host[(nb - 1) * 128:].ctypes.data_as(C.c_void_p), base_tensor.data_ptr(), cols, rows, cols, 16 * nb))
+    dev = torch.from_numpy(host).cuda()
+    require(dev.data_ptr() % 64 == 0, "tensor maps must be 64-byte aligned in device memory")
+    return dev
+
+
+class MoeFp4Weights:
+    """Per-expert tile_fp4 images of the gate/up (interleaved) and down projections of ``n_exp`` experts, as
+    expert_shard_impl builds them for one tensor-parallel rank holding everything (packing.rs:209-254, tp = 1)."""
+
+    def __init__(self, w13_codes, w13_scales, w2_codes, w2_scales):
+        import torch
+        e, n13, kh = w13_codes.shape
+        self.n_exp, self.inter, self.dim = e, n13 // 2, kh * 2
+        require(w2_codes.shape == (e, self.dim, self.inter // 2), "w2 codes [e][dim][inter/2]")
+        require(self.dim % 128 == 0 and self.inter % 128 == 0, "this harness takes dim % 128 == 0 and inter % 128 == 0 (no K padding)")
+        inter = self.inter
+        img13 = [tile_fp4(interleave_gate_up(w13_codes[i, :inter], w13_codes[i, inter:]), interleave_gate_up(w13_scales[i, :inter], w13_scales[i, inter:]))
+                 for i in range(e)]
+        img2 = [tile_fp4(w2_codes[i], w2_scales[i]) for i in range(e)]
+        self.w13 = torch.from_numpy(np.stack(img13)).cuda()
+        self.w2 = torch.from_numpy(np.stack(img2)).cuda()
+        self.w13_stride, self.w2_stride = self.w13.shape[1], self.w2.shape[1]
+
+
+def tc_moe(weights, plan, xq, sf, swiglu_limit=0.0):
+    """tc_moe_w13 then tc_moe_w2 as Rank::ffn_prefill launches them (crates/engine/src/model.rs:3125-3166, the path without
+    the row-major expert image): grid = SM count, 512 threads, TM_SMEM bytes.  xq / sf: moe_gather_quant's outputs.
+    Returns (aq u8 [rows + 128][ldaq] in kpos32 order, asf atoms, ypair f32 [pairs][dim])."""
+    import torch
+    dim, inter = weights.dim, weights.inter
+    rows, slack = plan.p, plan.p + 128
+    require(xq.shape == (slack, dim) and xq.dtype == torch.uint8, "xq is moe_gather_quant's [rows + 128][dim] image")
+    # the kernel keeps the activation scale atoms of all K tiles of a token tile in 40 slots (cu/tcmoe.cu:171)
+    require(dim // 128 <= 40 and inter // 128 <= 40, "K <= 5120 (SFB_MAX = 40 scale atoms per token tile)")
+    require((2 * inter) % 64 == 0 and inter % 64 == 0, "model.rs:854: (2 * inter) % 64 == 0 && kpad % 64 == 0")
+    ntile_cap = rows // 128 + plan.n_exp
+    require(ntile_cap <= 1024, "tile list (TM_MAX_TILES)")
+    ldaq, akt = inter, inter // 128                       # kpad = inter: model.rs:860-861
+    dev = xq.device
+    aq = torch.zeros(slack, ldaq, dtype=torch.uint8, device=dev)
+    asf = torch.zeros(ntile_cap * akt * 512, dtype=torch.uint8, device=dev)
+    ypair = torch.zeros(rows, dim, dtype=torch.float32, device=dev)
+    tb13, tb2 = _maps8(xq, dim, slack), _maps8(aq, ldaq, slack)
+    sms = sm_count()
+    p13 = TmParams(weights.w13.data_ptr(), weights.w13_stride, dim, (2 * inter + 127) // 128, tb13.data_ptr(), sf.data_ptr(), plan.tiles.data_ptr(),
+                   plan.ntiles.data_ptr(), plan.row_pair.data_ptr(), plan.row_w.data_ptr(), aq.data_ptr(), asf.data_ptr(), ldaq, akt,
+                   float(swiglu_limit), 2 * inter // 64, 0, 0, 0, 0)
+    p2 = TmParams(weights.w2.data_ptr(), weights.w2_stride, inter, dim // 128, tb2.data_ptr(), asf.data_ptr(), plan.tiles.data_ptr(),
+                  plan.ntiles.data_ptr(), plan.row_pair.data_ptr(), plan.row_w.data_ptr(), aq.data_ptr(), asf.data_ptr(), ldaq, akt,
+                  float(swiglu_limit), dim // 64, ypair.data_ptr(), dim, 0, 0)
+    launch(function("tcmoe", "tc_moe_w13", smem=TM_SMEM), (sms,), 512, TM_SMEM, [p13])
+    launch(function("tcmoe", "tc_moe_w2", smem=TM_SMEM), (sms,), 512, TM_SMEM, [p2])
+    _KEEP.append((weights, plan, xq, sf, tb13, tb2))
+    return aq, asf, ypair
+
+
+def unpermute_k32(codes_rows):
+    """Inverse of the kpos32 order inside every 32-K block: u8 [rows][k] as moe_gather_quant / tc_moe_w13 store them ->
+    natural K order."""
+    a = np.asarray(codes_rows, np.uint8)
+    rows, k = a.shape
+    pos = np.array([kpos32(j) for j in range(32)])
+    return np.ascontiguousarray(a.reshape(rows, k // 32, 32)[:, :, pos]).reshape(rows, k)

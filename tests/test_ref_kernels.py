@@ -234,3 +234,81 @@ def test_tc_gemv_fp8_pins_the_oracle_and_matches_the_library(pkg, tc_only, n, k,
     _, ref = oracle.gemm_fp8(oracle.MODE_MX, wq, ws, xq, xs)
     got_r, got_l = out_r.float().cpu().numpy(), out_l.float().cpu().numpy()
     assert rel(ref, got_r) < TOL and rel(got_l, got_r) < TOL
+
+
+def test_tc_moe_w13_w2_pin_the_oracle_and_match_the_library(pkg, tc_only):
+    """tc_moe_w13 / tc_moe_w2 (cu/tcmoe.cu:184-588), the reference's tcgen05 prefill expert GEMMs, launched after its own
+    moe_perm and moe_gather_quant.  Each kernel is checked on the reference's OWN inputs:
+      * gate/up + SwiGLU + re-quantization: the FP8 codes and UE8M0 scales it writes against the oracle's grouped FP4 GEMM
+        + SwiGLU (bf16 rounds, routing weight folded in) + 1x32 quantizer on the same quantized token rows (a handful of
+        codes may differ: the device's and the host's expf round a few bf16 values apart);
+      * down projection: its fp32 pair rows against the oracle's GEMM on the reference's re-quantized activations;
+      * and this library's grouped kernels (dsuf_moe_w13_swiglu, dsuf_act_quant_fp8, dsuf_moe_w2 on 128-row plans, MX
+        geometry) on the same token codes, pair by pair.
+    This pins the expert-GEMM half of the oracle by the reference's kernel, as the dense half is pinned above."""
+    ctx = tc_only
+    t, e, k, dim, inter = 300, 8, 4, 1024, 512
+    g = seeded(77)
+    logits = torch.randn(t, e, generator=g)
+    ids_n, w_n = oracle.route(1, logits.numpy(), None, k)
+    ids, w = torch.from_numpy(ids_n).cuda(), torch.from_numpy(w_n).cuda()
+    xt, _ = randn_bf16(g, t, dim)
+    pw = torch.ones(dim, dtype=torch.bfloat16)
+    w13 = (torch.randn(e, 2 * inter, dim, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    w2 = (torch.randn(e, dim, inter, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    q13 = [oracle.quant_fp4_weight(w13[i]) for i in range(e)]
+    q2 = [oracle.quant_fp4_weight(w2[i]) for i in range(e)]
+    c13, s13 = np.stack([a for a, _ in q13]), np.stack([b for _, b in q13])
+    c2, s2 = np.stack([a for a, _ in q2]), np.stack([b for _, b in q2])
+    # ---- the reference's chain ----
+    plan_r = rk.PrefillPlan(ids, w, e)
+    xq, sf = rk.moe_gather_quant(xt.cuda(), pw.cuda(), 1e-6, plan_r)
+    wts = rk.MoeFp4Weights(c13, s13, c2, s2)
+    aq, asf, ypair = rk.tc_moe(wts, plan_r, xq, sf)
+    rk.synchronize()
+    p = t * k
+    nt = int(plan_r.ntiles.cpu()[0])
+    tiles = plan_r.tiles.cpu().numpy()[:nt]
+    rp_r, rw_r = plan_r.row_pair.cpu().numpy(), plan_r.row_w.cpu().numpy()
+    rt_r = plan_r.row_tile.cpu().numpy()
+    tile_of, idx_of = rt_r >> 8, rt_r & 255
+    xq_nat = rk.unpermute_k32(xq.cpu().numpy()[:p])
+    xs_rows = rk.sf_atoms_to_rows(sf.cpu().numpy()[:nt * (dim // 128) * 512], nt * 128, dim)[tile_of * 128 + idx_of]
+    aq_nat = rk.unpermute_k32(aq.cpu().numpy()[:p])
+    as_rows = rk.sf_atoms_to_rows(asf.cpu().numpy()[:nt * (inter // 128) * 512], nt * 128, inter)[tile_of * 128 + idx_of]
+    yp = ypair.cpu().numpy()
+    lut = oracle.e4m3_lut()
+    bad_codes = bad_scales = 0
+    act_ref = np.zeros((p, inter), np.float32)
+    for ex, row0, cnt, _ in tiles:
+        rows = np.arange(row0, row0 + cnt)
+        gu = oracle.gemm_fp4(oracle.MODE_MX, c13[ex], s13[ex], xq_nat[rows], xs_rows[rows])
+        gt = oracle.bf16_to_f32(oracle.f32_to_bf16(gu[:, :inter]))
+        up = oracle.bf16_to_f32(oracle.f32_to_bf16(gu[:, inter:]))
+        a16 = oracle.f32_to_bf16((gt / (np.float32(1) + np.exp(-gt, dtype=np.float32)) * up * rw_r[rows, None]).astype(np.float32))
+        qc, qs = oracle.act_quant(oracle.MODE_MX, a16)
+        bad_codes += int((qc != aq_nat[rows]).sum())
+        bad_scales += int((qs != as_rows[rows]).sum())
+        act_ref[rows] = lut[aq_nat[rows]] * np.repeat((as_rows[rows].astype(np.uint32) << 23).view(np.float32), 32, axis=1)
+        assert rel(act_ref[rows], oracle.bf16_to_f32(a16)) < 0.04          # e4m3 re-quantization error of the same values
+        y = oracle.gemm_fp4(oracle.MODE_MX, c2[ex], s2[ex], aq_nat[rows], as_rows[rows])
+        assert rel(yp[rp_r[rows]], y) < 1e-4                               # same codes, fp32 accumulation order only
+    assert bad_scales <= p * (inter // 32) // 1000 and bad_codes <= p * inter // 500, (bad_codes, bad_scales)
+    # ---- this library's kernels on the same token codes ----
+    plan = pkg.MoePlan(ctx, t, k, e, 128)
+    pkg.moe_perm(ctx, plan, ids, w)
+    pr_l, pr_r = plan.pair_row.cpu().numpy(), plan_r.pair_row.cpu().numpy()
+    xq_l, xs_l = np.zeros((p, dim), np.uint8), np.zeros((p, dim // 32), np.uint8)
+    xq_l[pr_l], xs_l[pr_l] = xq_nat[pr_r], xs_rows[pr_r]
+    W13 = pkg.Weight.experts_fp4(ctx, c13, s13, True)
+    W2 = pkg.Weight.experts_fp4(ctx, c2, s2, False)
+    act = torch.zeros(p, inter, dtype=torch.bfloat16, device="cuda")
+    pkg.moe_w13_swiglu(ctx, W13, pkg.MODE_MX, plan, torch.from_numpy(xq_l).cuda(), torch.from_numpy(xs_l).cuda(), act, 0.0)
+    aq_l, as_l = pkg.act_quant(ctx, pkg.MODE_MX, act)
+    yrows = torch.zeros(p, dim, dtype=torch.float32, device="cuda")
+    pkg.moe_w2(ctx, W2, pkg.MODE_MX, plan, aq_l, as_l, yrows)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    aq_ln, as_ln = aq_l.cpu().numpy(), as_l.cpu().numpy()
+    assert int((aq_ln[pr_l] != aq_nat[pr_r]).sum()) <= p * inter // 500 and int((as_ln[pr_l] != as_rows[pr_r]).sum()) <= p * (inter // 32) // 1000
+    assert rel(yrows.cpu().numpy()[pr_l], yp[np.arange(p)]) < TOL
