@@ -336,9 +336,49 @@ def reference_kernels(pkg, ctx, torch, hbm_peak, quick):
                             "reference_tflops": round(flops / ms_ref / 1e9, 1), "reference_tc_quant_rows_ms": round(ms_ref_q, 4),
                             "ours_ms": round(ms_ours, 4), "ours_tflops": round(flops / ms_ours / 1e9, 1), "ours_act_quant_ms": round(ms_ours_q, 4),
                             "speedup_gemm": round(ms_ref / ms_ours, 2), "speedup_quant": round(ms_ref_q / ms_ours_q, 2)}
-    out["notes"].append("tc_moe_w13 / tc_moe_w2 (the reference's prefill expert GEMMs) keep the scale atoms of all K tiles of a token tile in 40 "
-                        "shared-memory slots (cu/tcmoe.cu:171, SFB_MAX): K <= 5120, so the gate/up GEMM cannot run at hidden 7168; the fused decode "
-                        "MoE entries and comm.cu spin on global memory without a bound and are not launched on a shared GPU")
+    # prefill expert GEMMs: tc_moe_w13 + tc_moe_w2 at the largest hidden size the reference's gate/up kernel takes (it keeps
+    # the scale atoms of all K tiles of a token tile in 40 shared-memory slots, cu/tcmoe.cu:171: K <= 5120)
+    dm, it_, ne, tk = 5120, I, 32, 2048
+    rng = np.random.default_rng(11)
+    c13 = rng.integers(0, 256, (ne, 2 * it_, dm // 2), dtype=np.uint8)
+    s13 = rng.integers(118, 122, (ne, 2 * it_, dm // 32), dtype=np.uint8)
+    c2 = rng.integers(0, 256, (ne, dm, it_ // 2), dtype=np.uint8)
+    s2 = rng.integers(118, 122, (ne, dm, it_ // 32), dtype=np.uint8)
+    xm = torch.randn(tk, dm, device=ctx.device).bfloat16()
+    ids, wr = pkg.moe_route_tokens(ctx, pkg.SCORE_SOFTMAX, torch.randn(tk, ne, device=ctx.device), None, TOPK)
+    plan_r = rk.PrefillPlan(ids, wr, ne)
+    xq_r, sf_r = rk.moe_gather_quant(xm, torch.ones(dm, dtype=torch.bfloat16, device=ctx.device), 1e-6, plan_r)
+    wts = rk.MoeFp4Weights(c13, s13, c2, s2)
+    bufs = rk.tc_moe(wts, plan_r, xq_r, sf_r)
+    ms_ref_moe = time_events(torch, lambda: rk.tc_moe(wts, plan_r, xq_r, sf_r, out=bufs), 5, 2)
+    rk.synchronize()
+    plan_l = pkg.MoePlan(ctx, tk, TOPK, ne, 128)
+    pkg.moe_perm(ctx, plan_l, ids, wr)
+    W13 = pkg.Weight.experts_fp4(ctx, c13, s13, True)
+    W2 = pkg.Weight.experts_fp4(ctx, c2, s2, False)
+    pr = tk * TOPK
+    xq_l = torch.empty(pr, dm, dtype=torch.uint8, device=ctx.device)
+    xs_l = torch.empty(pr, dm // 32, dtype=torch.uint8, device=ctx.device)
+    pkg.moe_gather_quant(ctx, pkg.MODE_MX, plan_l, xm, xq_l, xs_l)
+    act = torch.empty(pr, it_, dtype=torch.bfloat16, device=ctx.device)
+    aq_l = torch.empty(pr, it_, dtype=torch.uint8, device=ctx.device)
+    as_l = torch.empty(pr, it_ // 32, dtype=torch.uint8, device=ctx.device)
+    yr = torch.empty(pr, dm, dtype=torch.float32, device=ctx.device)
+
+    def ours_moe():
+        pkg.moe_w13_swiglu(ctx, W13, pkg.MODE_MX, plan_l, xq_l, xs_l, act, 0.0)
+        pkg.act_quant(ctx, pkg.MODE_MX, act, aq_l, as_l)
+        pkg.moe_w2(ctx, W2, pkg.MODE_MX, plan_l, aq_l, as_l, yr)
+    ms_ours_moe = time_events(torch, ours_moe, 5, 2)
+    fl = 6.0 * pr * it_ * dm
+    out["prefill_moe"] = {"hidden": dm, "inter": it_, "experts": ne, "tokens": tk, "pairs": pr, "reference_kernels": "tc_moe_w13 + tc_moe_w2",
+                          "reference_ms": round(ms_ref_moe, 4), "reference_tflops": round(fl / ms_ref_moe / 1e9, 1),
+                          "ours_ms_w13_quant_w2": round(ms_ours_moe, 4), "ours_tflops": round(fl / ms_ours_moe / 1e9, 1),
+                          "speedup": round(ms_ref_moe / ms_ours_moe, 2)}
+    del wts, W13, W2, bufs
+    out["notes"].append("tc_moe_w13 (the reference's prefill gate/up GEMM) keeps the scale atoms of all K tiles of a token tile in 40 "
+                        "shared-memory slots (cu/tcmoe.cu:171, SFB_MAX): K <= 5120, so it cannot run at hidden 7168 and is timed at 5120; the fused "
+                        "decode MoE entries and comm.cu spin on global memory without a bound and are not launched on a shared GPU")
     out["device_status"] = int(ctx.status().code)
     return out
 

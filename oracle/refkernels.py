@@ -543,11 +543,15 @@ def _maps8(base_tensor, cols, rows):
     the same u8 [rows][cols] image, 128 bytes apart in one device allocation."""
     import torch
     require(base_tensor.data_ptr() % 16 == 0 and cols % 128 == 0, "activation image alignment")
+    key = ("maps8", base_tensor.data_ptr(), cols, rows)
+    if key in _TMAPS:
+        return _TMAPS[key]
     host = np.zeros(8 * 128, np.uint8)
     for nb in range(1, 9):
         _check(lib().refk_tmap_u8_sw128(host[(nb - 1) * 128:].ctypes.data_as(C.c_void_p), base_tensor.data_ptr(), cols, rows, cols, 16 * nb))
     dev = torch.from_numpy(host).cuda()
     require(dev.data_ptr() % 64 == 0, "tensor maps must be 64-byte aligned in device memory")
+    _TMAPS[key] = dev
     return dev
 
 
@@ -570,10 +574,11 @@ class MoeFp4Weights:
         self.w13_stride, self.w2_stride = self.w13.shape[1], self.w2.shape[1]
 
 
-def tc_moe(weights, plan, xq, sf, swiglu_limit=0.0):
+def tc_moe(weights, plan, xq, sf, swiglu_limit=0.0, out=None):
     """tc_moe_w13 then tc_moe_w2 as Rank::ffn_prefill launches them (crates/engine/src/model.rs:3125-3166, the path without
     the row-major expert image): grid = SM count, 512 threads, TM_SMEM bytes.  xq / sf: moe_gather_quant's outputs.
-    Returns (aq u8 [rows + 128][ldaq] in kpos32 order, asf atoms, ypair f32 [pairs][dim])."""
+    Returns (aq u8 [rows + 128][ldaq] in kpos32 order, asf atoms, ypair f32 [pairs][dim]); ``out``: the same three buffers
+    from an earlier call, reused (timing loops)."""
     import torch
     dim, inter = weights.dim, weights.inter
     rows, slack = plan.p, plan.p + 128
@@ -585,9 +590,13 @@ def tc_moe(weights, plan, xq, sf, swiglu_limit=0.0):
     require(ntile_cap <= 1024, "tile list (TM_MAX_TILES)")
     ldaq, akt = inter, inter // 128                       # kpad = inter: model.rs:860-861
     dev = xq.device
-    aq = torch.zeros(slack, ldaq, dtype=torch.uint8, device=dev)
-    asf = torch.zeros(ntile_cap * akt * 512, dtype=torch.uint8, device=dev)
-    ypair = torch.zeros(rows, dim, dtype=torch.float32, device=dev)
+    if out is not None:
+        aq, asf, ypair = out
+        require(aq.shape == (slack, ldaq) and asf.numel() == ntile_cap * akt * 512 and ypair.shape == (rows, dim), "reused output buffers")
+    else:
+        aq = torch.zeros(slack, ldaq, dtype=torch.uint8, device=dev)
+        asf = torch.zeros(ntile_cap * akt * 512, dtype=torch.uint8, device=dev)
+        ypair = torch.zeros(rows, dim, dtype=torch.float32, device=dev)
     tb13, tb2 = _maps8(xq, dim, slack), _maps8(aq, ldaq, slack)
     sms = sm_count()
     p13 = TmParams(weights.w13.data_ptr(), weights.w13_stride, dim, (2 * inter + 127) // 128, tb13.data_ptr(), sf.data_ptr(), plan.tiles.data_ptr(),

@@ -63,3 +63,35 @@ def test_scale_atoms_follow_the_reference_formula():
             assert a[((r // 128) * kt + kb // 4) * 512 + (r % 128 % 32) * 16 + (r % 128 // 32) * 4 + kb % 4] == s[r, kb]
     assert (rk.sf_atoms_to_rows(a, n, k) == s).all()
     assert sorted(rk.kpos32(j) for j in range(32)) == list(range(32))
+
+
+def test_tile_fp4_and_gate_up_interleave_follow_the_reference_formulas():
+    """tile_fp4 (crates/model/src/formats.rs:147-180) restated with array operations against the formula evaluated byte by
+    byte, the w13 row interleave of packing.rs:237-241, the inverse kpos32 order and the size of TmParams (ops.rs:1511-1534)."""
+    n, k = 128, 192
+    rng = np.random.default_rng(5)
+    w = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    s = rng.integers(0, 256, (n, k // 32), dtype=np.uint8)
+    got = rk.tile_fp4(w, s)
+    steps, step_b = k // 64, rk.FP4_STEP
+    assert got.size == (n // 64) * steps * step_b
+    for rg, ks, lane, j in [(0, 0, 0, 0), (3, 2, 17, 1), (5, 1, 31, 3), (7, 2, 9, 2), (4, 0, 22, 0)]:
+        g, t = lane // 4, lane % 4
+        r0, r1 = rg * 16 + g, rg * 16 + g + 8
+        o = ((rg // 4) * steps + ks) * step_b + (rg % 4) * 512 + lane * 16 + j * 4
+        kb = ks * 64 + j * 16                       # in elements; two per byte
+        want = [w[r0, (kb + 2 * t) // 2], w[r0, (kb + 8 + 2 * t) // 2], w[r1, (kb + 2 * t) // 2], w[r1, (kb + 8 + 2 * t) // 2]]
+        assert got[o:o + 4].tolist() == want
+        so = ((rg // 4) * steps + ks) * step_b + 2048 + (rg % 4) * 32 + g * 4
+        assert got[so:so + 4].tolist() == [s[r0, ks * 2], s[r0, ks * 2 + 1], s[r1, ks * 2], s[r1, ks * 2 + 1]]
+    gate = np.arange(64 * 3, dtype=np.uint8).reshape(64, 3)
+    up = gate + 100
+    il = rk.interleave_gate_up(gate, up)
+    assert il.shape == (128, 3) and (il[:32] == gate[:32]).all() and (il[32:64] == up[:32]).all() and (il[64:96] == gate[32:]).all()
+    rows = rng.integers(0, 256, (3, 64), dtype=np.uint8)
+    perm = np.empty_like(rows)
+    for kk in range(64):
+        perm[:, (kk // 32) * 32 + rk.kpos32(kk % 32)] = rows[:, kk]
+    assert (rk.unpermute_k32(perm) == rows).all()
+    import ctypes
+    assert ctypes.sizeof(rk.TmParams) == 128 and rk.TM_SMEM == 222464
