@@ -172,7 +172,7 @@ int32_t dsuf_act_quant_fp8(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_t x
     if (m == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, x && q_out && scale_out, "act_quant: null pointer");
     DSUF_REQUIRE(ctx, (x & 15) == 0 && (q_out & 7) == 0, "act_quant: x must be 16-byte and q_out 8-byte aligned");
-    return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, m, k, (void*)q_out, (void*)scale_out, nullptr, 0, 0);
+    return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, m, k, (void*)q_out, (void*)scale_out, nullptr, 0);
 }
 
 int32_t dsuf_row_sumsq(dsuf_ctx* ctx, void* stream, uint64_t x, int32_t ldx, int32_t m, int32_t k, uint64_t sumsq_out) {
@@ -193,7 +193,7 @@ int32_t dsuf_act_quant_fp8_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode, ui
     if (m == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, x && q_out && scale_out && norm_w && sumsq, "act_quant_prenorm: null pointer");
     DSUF_REQUIRE(ctx, (x & 15) == 0 && (norm_w & 15) == 0 && (q_out & 7) == 0, "act_quant_prenorm: x and norm_w must be 16-byte, q_out 8-byte aligned");
-    return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, m, k, (void*)q_out, (void*)scale_out, nullptr, 0, 0,
+    return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, m, k, (void*)q_out, (void*)scale_out, nullptr, 0,
                             (const void*)norm_w, (const float*)sumsq, eps);
 }
 
@@ -267,7 +267,7 @@ int32_t dsuf_moe_gather_quant(dsuf_ctx* ctx, void* stream, int32_t mode, uint64_
     if (t == 0) return DSUF_OK;
     DSUF_REQUIRE(ctx, x && xq_out && xs_out && (x & 15) == 0 && (xq_out & 15) == 0, "gather_quant: null or misaligned pointer");
     return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, t, h, (void*)xq_out, (void*)xs_out,
-                            (const int*)plan->pair_row, topk, 0);
+                            (const int*)plan->pair_row, topk);
 }
 
 int32_t dsuf_moe_route_plan_gather(dsuf_ctx* ctx, void* stream, int32_t score_fn, uint64_t scores, uint64_t bias, int32_t t,
@@ -304,7 +304,7 @@ int32_t dsuf_moe_gather_quant_prenorm(dsuf_ctx* ctx, void* stream, int32_t mode,
     DSUF_REQUIRE(ctx, x && xq_out && xs_out && norm_w && sumsq && (x & 15) == 0 && (xq_out & 15) == 0 && (norm_w & 15) == 0,
                  "gather_quant_prenorm: null or misaligned pointer");
     return launch_act_quant(ctx, (cudaStream_t)stream, mode, (const void*)x, ldx, t, h, (void*)xq_out, (void*)xs_out,
-                            (const int*)plan->pair_row, topk, 0, (const void*)norm_w, (const float*)sumsq, eps);
+                            (const int*)plan->pair_row, topk, (const void*)norm_w, (const float*)sumsq, eps);
 }
 
 int32_t dsuf_moe_w13_swiglu(dsuf_ctx* ctx, void* stream, const dsuf_weight* w13, int32_t act_mode, const dsuf_moe_plan* plan,

@@ -29,6 +29,11 @@ struct dsuf_ctx {
     long long xchg_wait_ticks;     // clock64 budget of the peer-exchange kernels' waits (dsuf_ctx_set_wait_budget_us)
     dsuf::DevStatus* dev_status;   // device word written by a kernel whose bounded wait expired
     dsuf_encode_tiled_fn encode_tiled;
+    // activation tensor maps already encoded, by (base, row bytes, rows, box rows): a layer calls with the same buffers
+    // step after step, so the driver call is paid once per buffer, not once per launch (a context serves one host thread)
+    struct XMapEntry { const void* base; int k_bytes; long long rows; int box_rows; CUtensorMap tm; };
+    XMapEntry xmaps[32];
+    unsigned xmap_next;
     char err[512];
 };
 
@@ -101,7 +106,7 @@ int launch(dsuf_ctx* ctx, cudaStream_t stream, void (*kernel)(KArgs...), dim3 gr
 
 // per-file launchers
 int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
-                     void* scales, const int* pair_row, int fanout, int sf_atoms, const void* norm_w = nullptr,
+                     void* scales, const int* pair_row, int fanout, const void* norm_w = nullptr,
                      const float* sumsq = nullptr, float eps = 0.f);
 int launch_row_sumsq(dsuf_ctx* ctx, cudaStream_t stream, const void* x, int ldx, int m, int k, float* out);
 int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w, const void* xq, const void* xs, int m,

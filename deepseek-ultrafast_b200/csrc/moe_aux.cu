@@ -75,12 +75,13 @@ DSUF_DEV void route_one_token(int score_fn, const float* s, const float* bias, i
         const unsigned top_lo = __reduce_max_sync(0xffffffffu, hi == top_hi ? (unsigned)best : 0u);
         best = ((unsigned long long)top_hi << 32) | top_lo;
         const int picked = (int)(0xffffffffu - (unsigned)(best & 0xffffffffull));  // every lane holds the same word
-        // the owner lane retires the candidate and publishes its unbiased score
-        float wv = 0.f;
+        // exactly one lane holds the winning word: it retires the candidate, and an OR over the warp hands everybody the bits
+        // of its unbiased score (all other lanes contribute zero)
+        unsigned wbits = 0u;
 #pragma unroll
         for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
-            if (cand[i] == best) { wv = sc[i]; cand[i] = 0ull; }
-        wv = __shfl_sync(0xffffffffu, wv, picked & 31);
+            if (cand[i] == best) { wbits = __float_as_uint(sc[i]); cand[i] = 0ull; }
+        const float wv = __uint_as_float(__reduce_or_sync(0xffffffffu, wbits));
         wsum += wv;
         if (lane == j) { myw = wv; myid = picked; }
     }

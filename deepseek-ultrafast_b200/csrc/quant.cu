@@ -19,10 +19,9 @@ struct QuantArgs {
     const bf16* x;        // [rows_in][ldx]
     int ldx, rows_in, k;
     uint8_t* q;           // [rows_out][k]
-    void* scales;         // MX: u8 [rows_out][k/32] (or 512-byte atoms), DS: f32 [rows_out][k/128]
+    void* scales;         // MX: u8 [rows_out][k/32], DS: f32 [rows_out][k/128]
     const int* pair_row;  // scatter form: destination rows of token t are pair_row[t*fanout + j] (<0: skipped)
     int fanout;           // 0: plain (row r -> row r)
-    int sf_atoms;         // MX only: write scales into 128-row x 128-K atoms instead of row-major
     const bf16* norm_w;   // RMS pre-normalisation weights [k], or null
     const float* sumsq;   // pre-normalisation: sum of squares of every input row (row_sumsq_kernel)
     float eps;
@@ -72,12 +71,7 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
             if (MODE == DSUF_MODE_MX) {
                 const int kb = k0 >> 5;
                 const uint8_t b = (uint8_t)(__float_as_uint(sc) >> 23);
-                if (a.sf_atoms) {
-                    const int r = dst & 127;
-                    ((uint8_t*)a.scales)[((size_t)(dst >> 7) * (a.k >> 7) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = b;
-                } else {
-                    ((uint8_t*)a.scales)[(size_t)dst * (a.k >> 5) + kb] = b;
-                }
+                ((uint8_t*)a.scales)[(size_t)dst * (a.k >> 5) + kb] = b;
             } else {
                 ((float*)a.scales)[(size_t)dst * (a.k >> 7) + (k0 >> 7)] = sc;
             }
@@ -112,8 +106,8 @@ int launch_row_sumsq(dsuf_ctx* ctx, cudaStream_t stream, const void* x, int ldx,
 }
 
 int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x, int ldx, int rows_in, int k, void* q,
-                     void* scales, const int* pair_row, int fanout, int sf_atoms, const void* norm_w, const float* sumsq, float eps) {
-    QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, sf_atoms, (const bf16*)norm_w, sumsq, eps, ctx->prenorm_approx};
+                     void* scales, const int* pair_row, int fanout, const void* norm_w, const float* sumsq, float eps) {
+    QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, (const bf16*)norm_w, sumsq, eps, ctx->prenorm_approx};
     if (rows_in == 0) return DSUF_OK;
     dim3 grid(rows_in, (k + 2047) / 2048);
     if (mode == DSUF_MODE_MX)

@@ -15,6 +15,11 @@ constexpr size_t WS_PARTIAL_BYTES = (size_t)WS_MAX_CTAS * 2 * 64 * 128 * sizeof(
 constexpr size_t WS_BYTES = WS_PARTIAL_BYTES + WS_MAX_ROW_TILES * sizeof(int);
 
 int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, long long rows, int box_rows) {
+    for (const auto& e : ctx->xmaps)
+        if (e.base == base && e.k_bytes == k_bytes && e.rows == rows && e.box_rows == box_rows) {
+            *tm = e.tm;
+            return DSUF_OK;
+        }
     cuuint64_t dims[2] = {(cuuint64_t)k_bytes, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)k_bytes};
     cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
@@ -23,6 +28,8 @@ int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, 
                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ctx, DSUF_E_BADARG, "cuTensorMapEncodeTiled(activations) failed: %d", (int)r);
+    auto& slot = ctx->xmaps[ctx->xmap_next++ % (sizeof(ctx->xmaps) / sizeof(ctx->xmaps[0]))];
+    slot.base = base; slot.k_bytes = k_bytes; slot.rows = rows; slot.box_rows = box_rows; slot.tm = *tm;
     return DSUF_OK;
 }
 
