@@ -228,6 +228,24 @@ DSUF_DEV void mma_e4m3(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Packed fp32 arithmetic (two lanes per instruction, each rounded like the scalar fma.rn / mul.rn): halves the
+// instruction count of the per-tile fp32 promotion.  The 64-bit operands are register pairs; the packing moves cost
+// nothing when the allocator keeps the halves adjacent (accumulators and tensor-memory read-backs come in such pairs).
+DSUF_DEV unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+DSUF_DEV void fma_f32x2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    unsigned long long d = pack_f32x2(d0, d1);
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(pack_f32x2(a0, a1)), "l"(pack_f32x2(b0, b1)));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
+DSUF_DEV void mul_f32x2(float& d0, float& d1, float b0, float b1) {
+    unsigned long long d = pack_f32x2(d0, d1);
+    asm("mul.rn.f32x2 %0, %0, %1;" : "+l"(d) : "l"(pack_f32x2(b0, b1)));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d0), "=f"(d1) : "l"(d));
+}
 DSUF_DEV float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
 
 // Row permutation inside an 8-row group that makes 8-byte shared loads from 128-byte swizzled rows conflict free:

@@ -257,10 +257,10 @@ using namespace dsuf;
 extern "C" int32_t dsuf_lm_head_bf16(dsuf_ctx* ctx, void* stream, uint64_t w, int32_t n, int32_t k, uint64_t x, int32_t ldx, int32_t m,
                                      float alpha, uint64_t out, int32_t ldo, const dsuf_sampling_opts* sp) {
     if (!ctx) return DSUF_E_BADARG;
+    if (m == 0) return DSUF_OK;   // an empty batch: nothing to launch (and no pointer to look at)
     DSUF_REQUIRE(ctx, w && x && out && (w & 15) == 0 && (x & 15) == 0 && (out & 3) == 0, "lm_head: null or misaligned pointer");
     DSUF_REQUIRE(ctx, n > 0 && k > 0 && k % 8 == 0 && ldx >= k && ldx % 8 == 0, "lm_head: k and ldx must be multiples of 8, ldx >= k");
-    DSUF_REQUIRE(ctx, m >= 0 && m <= LH_NTOK && ldo >= n, "lm_head: 0..%d token rows, ldo >= n", LH_NTOK);
-    if (m == 0) return DSUF_OK;
+    DSUF_REQUIRE(ctx, m > 0 && m <= LH_NTOK && ldo >= n, "lm_head: 0..%d token rows, ldo >= n", LH_NTOK);
     LmHeadArgs a;
     memset(&a, 0, sizeof(a));
     int rc = encode_bf16_rows(ctx, &a.tm_w, (const void*)w, k, k, n, 128);

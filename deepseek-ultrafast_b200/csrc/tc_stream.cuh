@@ -493,13 +493,21 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                             for (int pp = 0; pp < PAIR; ++pp) {
 #pragma unroll
                                 for (int j = 0; j < CH; j += 4) {
-                                    const float4 t4 = *(const float4*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * (pp * N + cb + c0 + j));
+                                    float4 t4 = *(const float4*)(s_xs + (gidx & (XR - 1)) * XSE + 4 * (pp * N + cb + c0 + j));
                                     const float* vv = (PAIR == 2 && pp == 1) ? v1 : v;
                                     const float wds = wdsp[pp];
-                                    acc[c0 + j] = fmaf(vv[j], wds * t4.x, acc[c0 + j]);
-                                    acc[c0 + j + 1] = fmaf(vv[j + 1], wds * t4.y, acc[c0 + j + 1]);
-                                    acc[c0 + j + 2] = fmaf(vv[j + 2], wds * t4.z, acc[c0 + j + 2]);
-                                    acc[c0 + j + 3] = fmaf(vv[j + 3], wds * t4.w, acc[c0 + j + 3]);
+                                    if constexpr (N >= 32) {
+                                        // wide token tiles: two columns per instruction (packed fp32, same roundings)
+                                        mul_f32x2(t4.x, t4.y, wds, wds);
+                                        mul_f32x2(t4.z, t4.w, wds, wds);
+                                        fma_f32x2(acc[c0 + j], acc[c0 + j + 1], vv[j], vv[j + 1], t4.x, t4.y);
+                                        fma_f32x2(acc[c0 + j + 2], acc[c0 + j + 3], vv[j + 2], vv[j + 3], t4.z, t4.w);
+                                    } else {
+                                        acc[c0 + j] = fmaf(vv[j], wds * t4.x, acc[c0 + j]);
+                                        acc[c0 + j + 1] = fmaf(vv[j + 1], wds * t4.y, acc[c0 + j + 1]);
+                                        acc[c0 + j + 2] = fmaf(vv[j + 2], wds * t4.z, acc[c0 + j + 2]);
+                                        acc[c0 + j + 3] = fmaf(vv[j + 3], wds * t4.w, acc[c0 + j + 3]);
+                                    }
                                 }
                             }
                         } else {

@@ -695,3 +695,20 @@ def test_lm_head_logits_and_sampling_records(pkg, ctx, n, k, m):
     if (n // 2 + 1) in (t_ids - 5000):        # the tie made the top 8: its twin follows it directly
         i = list(t_ids - 5000).index(n // 2 + 1)
         assert i == 7 or t_ids[i + 1] - 5000 == n // 2 + 3
+
+
+@pytest.mark.gpu
+def test_lm_head_rejects_bad_arguments_and_takes_an_empty_batch(pkg, ctx):
+    """More than 16 token rows, records over a vocabulary that is not a multiple of 64, a zero temperature: refused on the
+    host with a message, nothing is launched; zero token rows: a no-op."""
+    w = torch.zeros(192, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(pkg.DsufError):
+        pkg.lm_head(ctx, w, torch.zeros(17, 256, dtype=torch.bfloat16, device="cuda"))
+    x = torch.zeros(2, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(pkg.DsufError):
+        pkg.lm_head(ctx, w[:160], x, temperature=1.0, records=torch.zeros(2, 3, 20, device="cuda"))
+    with pytest.raises(pkg.DsufError):
+        pkg.lm_head(ctx, w, x, temperature=0.0)
+    out = pkg.lm_head(ctx, w, x[:0])
+    torch.cuda.synchronize()
+    assert out.shape == (0, 192) and ctx.status().code == 0
