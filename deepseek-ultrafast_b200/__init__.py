@@ -127,6 +127,8 @@ ABI = {
                                 C.c_uint64, C.c_uint64]),
     "dsuf_moe_unpermute": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(PlanStruct), C.c_uint64, C.c_uint64, C.c_int32,
                                        C.c_int32, C.c_int32, C.c_uint64, C.c_int32]),
+    "dsuf_moe_unpermute_quant": (C.c_int32, [C.c_void_p, C.c_void_p, C.POINTER(PlanStruct), C.c_uint64, C.c_uint64, C.c_int32, C.c_int32,
+                                             C.c_int32, C.c_uint64, C.c_int32, C.c_int32, C.c_uint64, C.c_uint64]),
 }
 
 
@@ -657,10 +659,17 @@ def moe_w2(ctx, w2, act_mode, plan, act_q, act_s, yrows):
                                 yrows.data_ptr()))
 
 
-def moe_unpermute(ctx, plan, yrows, out, shared=None):
+def moe_unpermute(ctx, plan, yrows, out, shared=None, quant=None):
+    """dsuf_moe_unpermute; with ``quant`` = (mode, xq, xs) the result is also left quantized for the next projection
+    (dsuf_moe_unpermute_quant: codes and scales of act_quant(out), bit for bit)."""
     tok, h = out.shape
-    ctx.check(lib().dsuf_moe_unpermute(ctx.h, ctx.stream(), C.byref(plan.c), yrows.data_ptr(),
-                                       shared.data_ptr() if shared is not None else 0, tok, plan.topk, h, out.data_ptr(),
+    sh = shared.data_ptr() if shared is not None else 0
+    if quant is not None:
+        mode, xq, xs = quant
+        ctx.check(lib().dsuf_moe_unpermute_quant(ctx.h, ctx.stream(), C.byref(plan.c), yrows.data_ptr(), sh, tok, plan.topk, h,
+                                                 out.data_ptr(), out.stride(0), mode, xq.data_ptr(), xs.data_ptr()))
+        return
+    ctx.check(lib().dsuf_moe_unpermute(ctx.h, ctx.stream(), C.byref(plan.c), yrows.data_ptr(), sh, tok, plan.topk, h, out.data_ptr(),
                                        out.stride(0)))
 
 
@@ -689,12 +698,13 @@ class MoeLayer:
         self.act_s = t.zeros((p, self.inter // blk), dtype=sdt, device=dev)
         self.yrows = t.zeros((p, self.h), dtype=t.float32, device=dev)
 
-    def forward(self, x, ids, w, out, shared=None, events=None, combine=None, route=None):
+    def forward(self, x, ids, w, out, shared=None, events=None, combine=None, route=None, out_quant=None):
         """``events``: optional list; (start, end) CUDA events around the gate/up kernel are appended (bench timing).
         ``combine``: optional callable (plan, yrows, shared) -> tensor that replaces the local unpermute (the
         expert-parallel stack passes the kernel that sums locally and across ranks in one launch).
         ``route``: optional (score_fn, scores [t][experts], bias, route_scale): the router runs here and writes ``ids`` / ``w``;
-        decode-size batches (at most 1024 pairs) take one launch for router + plan + gather/quant."""
+        decode-size batches (at most 1024 pairs) take one launch for router + plan + gather/quant.
+        ``out_quant``: optional (mode, xq, xs): the unpermute also leaves ``out`` quantized for the next projection."""
         ctx, plan = self.ctx, self.plan
         if events is None:
             events = getattr(self, "events", None)
@@ -721,5 +731,5 @@ class MoeLayer:
         moe_w2(ctx, self.w2, self.act_mode, plan, self.act_q, self.act_s, self.yrows)
         if combine is not None:
             return combine(plan, self.yrows, shared)
-        moe_unpermute(ctx, plan, self.yrows, out, shared)
+        moe_unpermute(ctx, plan, self.yrows, out, shared, quant=out_quant)
         return out

@@ -341,4 +341,19 @@ int32_t dsuf_moe_unpermute(dsuf_ctx* ctx, void* stream, const dsuf_moe_plan* pla
     return launch_unpermute(ctx, (cudaStream_t)stream, plan, (const float*)yrows, (const void*)shared, t, topk, h, (void*)out, ldo);
 }
 
+int32_t dsuf_moe_unpermute_quant(dsuf_ctx* ctx, void* stream, const dsuf_moe_plan* plan, uint64_t yrows, uint64_t shared, int32_t t,
+                                 int32_t topk, int32_t h, uint64_t out, int32_t ldo, int32_t mode, uint64_t xq, uint64_t xs) {
+    if (!ctx) return DSUF_E_BADARG;
+    int rc = check_plan(ctx, plan);
+    if (rc) return rc;
+    DSUF_REQUIRE(ctx, topk >= 1 && topk <= 16 && (long long)t * topk == plan->p, "unpermute_quant: t*topk != plan.p");
+    DSUF_REQUIRE(ctx, mode == DSUF_MODE_MX || mode == DSUF_MODE_DS, "unpermute_quant: mode");
+    DSUF_REQUIRE(ctx, h > 0 && h % 128 == 0 && ldo >= h && ldo % 8 == 0, "unpermute_quant: h must be a multiple of 128, ldo of 8");
+    if (t == 0) return DSUF_OK;
+    DSUF_REQUIRE(ctx, yrows && out && xq && xs && (yrows & 15) == 0 && (out & 15) == 0 && (shared & 15) == 0 && (xq & 7) == 0 && (xs & 3) == 0,
+                 "unpermute_quant: null or misaligned pointer");
+    return launch_unpermute_quant(ctx, (cudaStream_t)stream, plan, (const float*)yrows, (const void*)shared, t, topk, h, (void*)out, ldo, mode,
+                                  (void*)xq, (void*)xs);
+}
+
 }  // extern "C"

@@ -121,6 +121,8 @@ int launch_front(dsuf_ctx* ctx, cudaStream_t stream, int score_fn, const float* 
 int launch_plan(dsuf_ctx* ctx, cudaStream_t stream, const int* ids, const float* w, int e_lo, const dsuf_moe_plan* plan);
 int launch_unpermute(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
                      int t, int topk, int h, void* out, int ldo);
+int launch_unpermute_quant(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
+                           int t, int topk, int h, void* out, int ldo, int mode, void* q_out, void* s_out);
 int stream_setup(dsuf_ctx* ctx);
 int lm_head_setup(dsuf_ctx* ctx);
 int encode_x_map(dsuf_ctx* ctx, CUtensorMap* tm, const void* base, int k_bytes, long long rows, int box_rows);

@@ -464,6 +464,70 @@ __global__ void __launch_bounds__(256) unpermute_kernel(const int* pair_row, con
     }
 }
 
+// The same sum, eight columns per thread, with the result also quantized for the next projection (the quantizer's step:
+// quant_core.cuh): one launch instead of unpermute + act_quant between two layers.
+template <int MODE>
+__global__ void __launch_bounds__(256) unpermute_quant_kernel(const int* pair_row, const float* yrows, const bf16* shared, int topk,
+                                                              int h, bf16* out, int ldo, uint8_t* q_out, void* s_out) {
+    pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+    const int tok = blockIdx.x;
+    __shared__ int rows[16];
+    if (threadIdx.x < topk) rows[threadIdx.x] = pair_row[(size_t)tok * topk + threadIdx.x];
+    __syncthreads();
+    const int c = (blockIdx.y * 256 + threadIdx.x) * 8;
+    const bool live = c < h;      // h % 128 == 0: a scale block is live or dead as a whole
+    float s[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s[e] = 0.f;
+    if (live) {
+        for (int j = 0; j < topk; ++j) {
+            const int r = rows[j];
+            if (r < 0) continue;
+            const float4 v0 = __ldcs((const float4*)(yrows + (size_t)r * h + c));
+            const float4 v1 = __ldcs((const float4*)(yrows + (size_t)r * h + c + 4));
+            s[0] += v0.x; s[1] += v0.y; s[2] += v0.z; s[3] += v0.w;
+            s[4] += v1.x; s[5] += v1.y; s[6] += v1.z; s[7] += v1.w;
+        }
+        if (shared) {
+            const uint4 raw = *(const uint4*)(shared + (size_t)tok * h + c);
+            const bf16* sh = (const bf16*)&raw;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[e] += __bfloat162float(sh[e]);
+        }
+    }
+    uint4 o;
+    bf16* ob = (bf16*)&o;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        ob[e] = __float2bfloat16(s[e]);
+        v[e] = __bfloat162float(ob[e]);      // the quantizer sees the bf16 row the next layer would read
+    }
+    uint2 codes;
+    float sc;
+    quant8<MODE>(v, codes, sc);   // every lane takes part in the block's amax
+    if (!live) return;
+    *(uint4*)(out + (size_t)tok * ldo + c) = o;
+    *(uint2*)(q_out + (size_t)tok * h + c) = codes;
+    if (MODE == DSUF_MODE_MX) {
+        if ((threadIdx.x & 3) == 0) ((uint8_t*)s_out)[(size_t)tok * (h >> 5) + (c >> 5)] = (uint8_t)(__float_as_uint(sc) >> 23);
+    } else {
+        if ((threadIdx.x & 15) == 0) ((float*)s_out)[(size_t)tok * (h >> 7) + (c >> 7)] = sc;
+    }
+}
+
+int launch_unpermute_quant(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
+                           int t, int topk, int h, void* out, int ldo, int mode, void* q_out, void* s_out) {
+    if (t == 0) return DSUF_OK;
+    const dim3 grid(t, (h + 2047) / 2048);
+    if (mode == DSUF_MODE_MX)
+        return launch(ctx, stream, unpermute_quant_kernel<DSUF_MODE_MX>, grid, dim3(256), 0, (const int*)plan->pair_row, yrows,
+                      (const bf16*)shared, topk, h, (bf16*)out, ldo, (uint8_t*)q_out, s_out);
+    return launch(ctx, stream, unpermute_quant_kernel<DSUF_MODE_DS>, grid, dim3(256), 0, (const int*)plan->pair_row, yrows,
+                  (const bf16*)shared, topk, h, (bf16*)out, ldo, (uint8_t*)q_out, s_out);
+}
+
 int launch_unpermute(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_moe_plan* plan, const float* yrows, const void* shared,
                      int t, int topk, int h, void* out, int ldo) {
     if (t == 0) return DSUF_OK;

@@ -57,11 +57,14 @@ class LayerStack:
         self.y = [t.empty((cfg.tokens, H), dtype=t.bfloat16, device=dev) for _ in range(2)]
         self.ids = t.empty((cfg.tokens, cfg.topk), dtype=t.int32, device=dev)
         self.w = t.empty((cfg.tokens, cfg.topk), dtype=t.float32, device=dev)
+        self.fuse_quant = H % 128 == 0 and os.environ.get("DSUF_FUSE_QUANT", "1") != "0"
 
-    def dense_forward(self, l, x, out):
-        """x bf16 [T][H] -> out bf16 [T][H]; processed in slabs of the decode kernel's row limit (64 tcgen05, 16 mma.sync)."""
+    def dense_forward(self, l, x, out, prequantized=False):
+        """x bf16 [T][H] -> out bf16 [T][H]; processed in slabs of the decode kernel's row limit (64 tcgen05, 16 mma.sync).
+        ``prequantized``: self.xq / self.xs already hold x's codes and scales (the previous layer's unpermute wrote them)."""
         ctx, w = self.ctx, self.dense[l]
-        act_quant(ctx, w.mode, x, self.xq, self.xs)
+        if not prequantized:
+            act_quant(ctx, w.mode, x, self.xq, self.xs)
         T = x.shape[0]
         if ctx.tcgen05:
             return gemm_fp8(ctx, w, self.xq, self.xs, T, out)   # one launch: decode kernel up to 64 rows, prefill kernel above
@@ -74,11 +77,14 @@ class LayerStack:
     def forward(self, x, events=None, layers=None):
         cfg = self.cfg
         cur = x
-        for l in range(cfg.layers if layers is None else layers):
-            self.dense_forward(l, cur, self.h)
+        n_layers = cfg.layers if layers is None else layers
+        for l in range(n_layers):
+            self.dense_forward(l, cur, self.h, prequantized=l > 0 and self.fuse_quant)
             out = self.y[l & 1]
-            # router inside the layer: decode-size batches take one launch for router + plan + gather/quant
-            self.moe[l].forward(self.h, self.ids, self.w, out, events=events, route=(SCORE_SOFTMAX, self.logits[l], None, 1.0))
+            # router inside the layer: decode-size batches take one launch for router + plan + gather/quant; the unpermute
+            # leaves its result quantized for the next layer's projection
+            oq = (cfg.dense_mode, self.xq, self.xs) if self.fuse_quant and l + 1 < n_layers else None
+            self.moe[l].forward(self.h, self.ids, self.w, out, events=events, route=(SCORE_SOFTMAX, self.logits[l], None, 1.0), out_quant=oq)
             cur = out
         return cur
 
@@ -91,7 +97,8 @@ class LayerStack:
         # act_quant + dense slabs + front end (router + plan + gather/quant: 1 launch up to 1024 pairs, else 1 + 3 + 1)
         # + w13 + quant + w2 + unpermute
         front = 1 if cfg.tokens * cfg.topk <= 1024 else 5
-        return cfg.layers * (1 + slabs + front + 1 + 1 + 1 + 1)
+        quants = 1 if self.fuse_quant else cfg.layers     # only the first layer quantizes its input by itself
+        return cfg.layers * (slabs + front + 1 + 1 + 1 + 1) + quants
 
 
 class _KernelCompute:

@@ -308,6 +308,12 @@ int32_t dsuf_moe_w2(dsuf_ctx* ctx, void* stream, const dsuf_weight* w2, int32_t 
  * out[t] = bf16(sum_j yrows[pair_row[t*topk+j]] (+ shared[t])), rows with pair_row < 0 skipped. */
 int32_t dsuf_moe_unpermute(dsuf_ctx* ctx, void* stream, const dsuf_moe_plan* plan, uint64_t yrows, uint64_t shared, int32_t t,
                            int32_t topk, int32_t h, uint64_t out, int32_t ldo);
+/* dsuf_moe_unpermute that also leaves its result quantized for the next projection: xq [t][h] FP8 codes and xs block
+ * scales (mode MX: u8 [t][h/32], DS: f32 [t][h/128]) equal to dsuf_act_quant_fp8(mode, out) bit for bit -- the activation
+ * staging the reference's next GEMV would run on these rows (quant_blocks8, cu/quantblocks.cuh:7-57) done by the producer.
+ * h % 128 == 0, out and shared 16-byte aligned. */
+int32_t dsuf_moe_unpermute_quant(dsuf_ctx* ctx, void* stream, const dsuf_moe_plan* plan, uint64_t yrows, uint64_t shared, int32_t t,
+                                 int32_t topk, int32_t h, uint64_t out, int32_t ldo, int32_t mode, uint64_t xq, uint64_t xs);
 
 /* ---- expert-parallel exchange over NVLink peer memory ----
  * One-shot all-reduce of bf16 rows: out[i] = bf16(sum over ranks r = 0..world-1, in that order, of peer_data[r][i]).

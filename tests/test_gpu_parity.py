@@ -712,3 +712,31 @@ def test_lm_head_rejects_bad_arguments_and_takes_an_empty_batch(pkg, ctx):
     out = pkg.lm_head(ctx, w, x[:0])
     torch.cuda.synchronize()
     assert out.shape == (0, 192) and ctx.status().code == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("t,topk,h,with_shared", [(64, 8, 7168, False), (5, 2, 256, True), (130, 4, 1024, True)])
+def test_unpermute_that_also_quantizes_equals_unpermute_then_act_quant(pkg, ctx, mode, t, topk, h, with_shared):
+    """dsuf_moe_unpermute_quant: the bf16 rows of dsuf_moe_unpermute and the codes / scales of dsuf_act_quant_fp8 on those
+    rows, all bit for bit, with pairs that live on another rank (row < 0) and the optional shared-expert rows."""
+    g = seeded(t * topk + h + mode)
+    p = t * topk
+    plan = pkg.MoePlan(ctx, t, topk, 8, 8)
+    rows = torch.randperm(p, generator=g).to(torch.int32)
+    rows[::7] = -1
+    plan.pair_row.copy_(rows.cuda())
+    yrows = torch.randn(p, h, generator=g).cuda()
+    shared = torch.randn(t, h, generator=g).bfloat16().cuda() if with_shared else None
+    ref = torch.empty(t, h, dtype=torch.bfloat16, device="cuda")
+    pkg.moe_unpermute(ctx, plan, yrows, ref, shared)
+    rq, rs = pkg.act_quant(ctx, mode, ref)
+    out = torch.zeros_like(ref)
+    blk = 32 if mode == pkg.MODE_MX else 128
+    xq = torch.zeros(t, h, dtype=torch.uint8, device="cuda")
+    xs = torch.zeros(t, h // blk, dtype=torch.uint8 if mode == pkg.MODE_MX else torch.float32, device="cuda")
+    pkg.moe_unpermute(ctx, plan, yrows, out, shared, quant=(mode, xq, xs))
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0
+    assert torch.equal(out.view(torch.uint16), ref.view(torch.uint16))
+    assert torch.equal(xq, rq) and torch.equal(xs.view(torch.uint8), rs.view(torch.uint8))
