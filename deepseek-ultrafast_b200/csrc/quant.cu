@@ -79,6 +79,62 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const QuantArgs a) {
     }
 }
 
+// Large inputs (thousands of rows, no scatter, no pre-normalisation): one CTA per row, one whole 32-element block per
+// thread -- four independent 16-byte loads in flight per thread and, in the MX geometry, no shuffle at all (a DS scale
+// block is four neighbouring threads).  Same arithmetic as quant8, so codes and scales are bit-identical to the kernel
+// above.
+template <int MODE>
+__global__ void __launch_bounds__(256) act_quant_rows_kernel(const bf16* x, int ldx, int k, uint8_t* q, void* scales) {
+    pdl_wait();
+    pdl_launch_dependents();  // dependents still wait for this grid to finish; only their prologues overlap
+    const int row = blockIdx.x, nkb = k >> 5;
+    // (k % 128 == 0: the four threads of a DS block are live or dead together, and all in one warp)
+    for (int kb0 = 0; kb0 < nkb; kb0 += 256) {
+        const int kb = kb0 + threadIdx.x;
+        const bool live = kb < nkb;
+        float v[32];
+        if (live) {
+            const bf16* xr = x + (size_t)row * ldx + kb * 32;
+            uint4 raw[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) raw[j] = *(const uint4*)(xr + 8 * j);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bf16* h = (const bf16*)&raw[j];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[8 * j + e] = __bfloat162float(h[e]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        uint32_t w[8];
+        if (MODE == DSUF_MODE_MX) {
+            const float sc = round_scale_pow2(fmaxf(amax, 1e-4f), 1.0f / 448.0f);
+            const float inv = __uint_as_float(0x7f000000u - __float_as_uint(sc));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) w[j] = f32x4_to_e4m3x4(v[4 * j] * inv, v[4 * j + 1] * inv, v[4 * j + 2] * inv, v[4 * j + 3] * inv);
+            if (live) ((uint8_t*)scales)[(size_t)row * nkb + kb] = (uint8_t)(__float_as_uint(sc) >> 23);
+        } else {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const float sc = amax == 0.f ? 1.0f : __fdiv_rn(amax, 448.0f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                w[j] = f32x4_to_e4m3x4(__fdiv_rn(v[4 * j], sc), __fdiv_rn(v[4 * j + 1], sc), __fdiv_rn(v[4 * j + 2], sc), __fdiv_rn(v[4 * j + 3], sc));
+            if (live && (threadIdx.x & 3) == 0) ((float*)scales)[(size_t)row * (nkb >> 2) + (kb >> 2)] = sc;
+        }
+        if (live) {
+            uint4* o = (uint4*)(q + (size_t)row * k + kb * 32);
+            o[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            o[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+    }
+}
+
 // tc_row_sumsq (cu/tcgemm.cu:341-355), same summation order: one warp per row, lane l takes k = 8 l + 256 i + e.
 __global__ void __launch_bounds__(256) row_sumsq_kernel(const bf16* x, int ldx, int m, int k, float* out) {
     pdl_wait();
@@ -109,6 +165,13 @@ int launch_act_quant(dsuf_ctx* ctx, cudaStream_t stream, int mode, const void* x
                      void* scales, const int* pair_row, int fanout, const void* norm_w, const float* sumsq, float eps) {
     QuantArgs a{(const bf16*)x, ldx, rows_in, k, (uint8_t*)q, scales, pair_row, fanout, (const bf16*)norm_w, sumsq, eps, ctx->prenorm_approx};
     if (rows_in == 0) return DSUF_OK;
+    // (rows of at least 6144 elements keep three quarters of the CTA's 256 threads busy; the 2048-wide SwiGLU output of
+    // the expert layer does not: there the kernel above is several times faster)
+    if (rows_in >= 1024 && k >= 6144 && !pair_row && !norm_w && ((uintptr_t)q & 15) == 0 && k % 128 == 0) {
+        if (mode == DSUF_MODE_MX)
+            return launch(ctx, stream, act_quant_rows_kernel<DSUF_MODE_MX>, dim3(rows_in), dim3(256), 0, (const bf16*)x, ldx, k, (uint8_t*)q, scales);
+        return launch(ctx, stream, act_quant_rows_kernel<DSUF_MODE_DS>, dim3(rows_in), dim3(256), 0, (const bf16*)x, ldx, k, (uint8_t*)q, scales);
+    }
     dim3 grid(rows_in, (k + 2047) / 2048);
     if (mode == DSUF_MODE_MX)
         return launch(ctx, stream, act_quant_kernel<DSUF_MODE_MX>, grid, dim3(256), 0, a);

@@ -20,7 +20,8 @@ def rel(a, b):
 
 # ------------------------------------------------------------------ activation quantizer
 @pytest.mark.parametrize("mode", [0, 1])
-@pytest.mark.parametrize("m,k,ld", [(4, 2048, 2048), (16, 7168, 7168), (1, 128, 128), (3, 384, 512), (64, 2048, 2048)])
+@pytest.mark.parametrize("m,k,ld", [(4, 2048, 2048), (16, 7168, 7168), (1, 128, 128), (3, 384, 512), (64, 2048, 2048),
+                                    (1500, 7168, 7168), (1024, 384, 512), (2100, 8320, 8320)])   # >= 1024 rows of >= 6144: the kernel for large inputs
 def test_act_quant_bit_exact(pkg, ctx, mode, m, k, ld):
     g = seeded(10 + m + k)
     xt, _ = randn_bf16(g, m, ld)
