@@ -43,12 +43,12 @@ def peaks():
     return 6650.0, "fallback"
 
 
-def workload_config(tokens, world, eager=False):
+def workload_config(tokens, world, eager=False, pdl=True):
     """The `config` object of the JSON line; both arms print the same keys."""
     leg = "decode step" if tokens <= 1024 else "prefill"
     return {"workload": "cfg4: 4 layers x (FP8 7168x7168 dense + 256-expert top-8 MXFP4 MoE), %d-token %s" % (tokens, leg),
             "tokens": tokens, "hidden": H, "experts": E, "topk": TOPK, "inter": I, "layers": LAYERS,
-            "parallelism": "ep%d" % world, "step_launch": "eager" if eager else "cuda_graph",
+            "parallelism": "ep%d" % world, "step_launch": "eager" if eager else "cuda_graph", "pdl": bool(pdl),
             "l2": "weights read per step (>= 6 GB per GPU) exceed the 126 MB L2"}
 
 
@@ -168,7 +168,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(vals),
         "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * float(np.median(dts)), "step_is": "one timed pass over the bounded sample (cpu_baseline.sample); value extrapolates it to the 64-token, 4-layer step", "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp8_e4m3 x {fp8_e4m3, mxfp4_e2m1}, fp32 accumulate", "data": "synthetic",
-        "config": workload_config(64, args.gpus),
+        "config": workload_config(64, args.gpus, pdl=args.pdl),
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": nthreads, "kind": "port", "sample": cpu_sample_text(len(vals), float(np.median(dts)))},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -274,7 +274,7 @@ def _graph_us(torch, launches, reps=10):
     return ms * 1e3
 
 
-def reference_kernels(pkg, ctx, torch, hbm_peak, quick):
+def reference_kernels(pkg, ctx, torch, hbm_peak, quick, use_pdl=False):
     """The reference's own sm_100a kernels (compiled from its sources into oracle/_ref, launched with its own geometry by
     oracle/refkernels.py) timed on this GPU beside this library's kernels on the same codes, in the reference's (MX) scale
     geometry, which is the only one the reference implements.  Decode GEMVs rotate over enough weight copies to defeat L2."""
@@ -301,14 +301,14 @@ def reference_kernels(pkg, ctx, torch, hbm_peak, quick):
             o = torch.empty(m, n, dtype=torch.bfloat16, device=ctx.device)
             xq, xs = pkg.act_quant(ctx, pkg.MODE_MX, x)
             geo = rk.gemv_geometry(n, k, m, ctx.sm_count)
-            us_ref = _graph_us(torch, [lambda w=w: rk.gemv_fp8(w, x, o) for w in ref_w])
+            us_ref = _graph_us(torch, [lambda w=w: rk.gemv_fp8(w, x, o, pdl=use_pdl) for w in ref_w])
             us_ours = _graph_us(torch, [lambda w=w: (pkg.act_quant(ctx, pkg.MODE_MX, x, xq, xs), pkg.gemm_fp8(ctx, w, xq, xs, m, o)) for w in ours_w])
             algo = wbytes + 2 * m * k + 2 * m * n
             row = {"n": n, "k": k, "m": m, "reference_kernel": geo["kernel"], "reference_cluster": geo["cs"], "reference_us": round(us_ref, 2),
                    "reference_gbs": round(algo / us_ref / 1e3, 1), "ours_us_with_act_quant": round(us_ours, 2),
                    "ours_gbs": round(algo / us_ours / 1e3, 1), "speedup": round(us_ref / us_ours, 2)}
             if tc_w is not None and m <= 8:
-                us_tc = _graph_us(torch, [lambda w=w: rk.tc_gemv_fp8(w, x, o) for w in tc_w])
+                us_tc = _graph_us(torch, [lambda w=w: rk.tc_gemv_fp8(w, x, o, pdl=use_pdl) for w in tc_w])
                 row["reference_tc_gemv_fp8_us"] = round(us_tc, 2)
                 row["speedup_vs_tc_gemv_fp8"] = round(us_tc / us_ours, 2)
             out["decode_gemv"].append(row)
@@ -627,7 +627,7 @@ def run_ours(args):
         "metric": METRIC if T <= 1024 else "moe_layer_stack_prefill_tokens_per_s", "value": round(T / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "fp8_e4m3 x {fp8_e4m3, mxfp4_e2m1}, fp32 accumulate", "data": "synthetic",
-        "config": workload_config(T, world, args.no_graph),
+        "config": workload_config(T, world, args.no_graph, pdl=args.pdl),
         "e2e": {"value": round(T / (ms_e2e * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": t_local * H * 2 * world,
                 "d2h_bytes_per_step": t_local * H * 2 * world, "ms_per_step": round(ms_e2e, 4)},
         "gpu_launches": stack.count_launches() * args.steps,
@@ -695,7 +695,7 @@ def run_ours(args):
         result["lm_head"] = lm_head_bench(pkg, ctx, torch, hbm_peak)
     if world == 1 and not args.skip_sub and not args.skip_ref_kernels:
         try:
-            result["reference_kernels"] = reference_kernels(pkg, ctx, torch, hbm_peak, args.quick)
+            result["reference_kernels"] = reference_kernels(pkg, ctx, torch, hbm_peak, args.quick, use_pdl=args.pdl)
         except Exception as ex:  # noqa: BLE001 - the comparison must not take the benchmark line down with it
             result["reference_kernels"] = {"unavailable": f"{type(ex).__name__}: {ex}"}
     if world == 1 and not args.skip_cpu:
@@ -841,7 +841,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=64)
-    ap.add_argument("--pdl", action="store_true")
+    ap.add_argument("--no-pdl", dest="pdl", action="store_false",
+                    help="launch without programmatic dependent launch (default: on, as the reference's GemvOpts.pdl)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--act-mode", default="ds", choices=["ds", "mx"], help="scale geometry: ds = 1x128 fp32 (benchmark configs), mx = 1x32 UE8M0 (reference semantics)")
     ap.add_argument("--quick", action="store_true", help="shorter GEMV sweep")

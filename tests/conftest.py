@@ -24,7 +24,9 @@ def ctx(pkg, request):
     import torch
     if not torch.cuda.is_available():
         pytest.skip("no GPU")
-    c = pkg.Ctx(0, tcgen05=request.param == "tcgen05")
+    # DSUF_TEST_PDL=1 runs the whole suite with programmatic dependent launch on (every kernel waits for its predecessor
+    # with griddepcontrol.wait before it reads anything, so the results must not change)
+    c = pkg.Ctx(0, tcgen05=request.param == "tcgen05", pdl=os.environ.get("DSUF_TEST_PDL", "0") == "1")
     yield c
     c.close()
 

@@ -741,3 +741,40 @@ def test_unpermute_that_also_quantizes_equals_unpermute_then_act_quant(pkg, ctx,
     assert ctx.status().code == 0
     assert torch.equal(out.view(torch.uint16), ref.view(torch.uint16))
     assert torch.equal(xq, rq) and torch.equal(xs.view(torch.uint8), rs.view(torch.uint8))
+
+
+@pytest.mark.gpu
+def test_programmatic_dependent_launch_changes_no_result(pkg):
+    """The same chain of launches (quantizer -> dense GEMV -> decode expert layer with the fused front end) with and
+    without programmatic dependent launch: bitwise equal (each kernel's griddepcontrol.wait precedes its first read of a
+    predecessor's output)."""
+    g = seeded(321)
+    H, I, E, K, T = 512, 256, 8, 2, 12
+    xt, _ = randn_bf16(g, T, H)
+    _, wn = randn_bf16(g, H, H, std=0.05)
+    wq, ws = oracle.quant_fp8_weight(1, wn)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    q13 = [oracle.quant_fp4_weight(w13[e]) for e in range(E)]
+    q2 = [oracle.quant_fp4_weight(w2[e]) for e in range(E)]
+    logits = torch.randn(T, E, generator=g).cuda()
+    outs = []
+    for pdl in (False, True):
+        c = pkg.Ctx(0, pdl=pdl)
+        wd = pkg.Weight.dense_fp8(c, 1, wq, ws)
+        W13 = pkg.Weight.experts_fp4(c, np.stack([a for a, _ in q13]), np.stack([b for _, b in q13]), True)
+        W2 = pkg.Weight.experts_fp4(c, np.stack([a for a, _ in q2]), np.stack([b for _, b in q2]), False)
+        layer = pkg.MoeLayer(c, W13, W2, T, K, 1, tile_rows=8)
+        ids = torch.empty(T, K, dtype=torch.int32, device="cuda")
+        wts = torch.empty(T, K, dtype=torch.float32, device="cuda")
+        y = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+        for _ in range(3):
+            xq, xs = pkg.act_quant(c, 1, xt.cuda())
+            h = pkg.gemm_fp8(c, wd, xq, xs, T)
+            layer.forward(h, ids, wts, y, route=(pkg.SCORE_SOFTMAX, logits, None, 1.0))
+        torch.cuda.synchronize()
+        assert c.status().code == 0
+        outs.append((h.clone(), y.clone(), ids.clone()))
+        c.close()
+    assert torch.equal(outs[0][0].view(torch.uint16), outs[1][0].view(torch.uint16))
+    assert torch.equal(outs[0][1].view(torch.uint16), outs[1][1].view(torch.uint16)) and torch.equal(outs[0][2], outs[1][2])
