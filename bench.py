@@ -841,8 +841,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=64)
-    ap.add_argument("--no-pdl", dest="pdl", action="store_false",
-                    help="launch without programmatic dependent launch (default: on, as the reference's GemvOpts.pdl)")
+    ap.add_argument("--pdl", dest="pdl", action="store_true", default=None,
+                    help="programmatic dependent launch (as the reference's GemvOpts.pdl); default: on for one GPU, where it "
+                         "takes ~0.9 us off the small GEMVs, off for several, where the step measured 1-2 %% slower with it")
+    ap.add_argument("--no-pdl", dest="pdl", action="store_false")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--act-mode", default="ds", choices=["ds", "mx"], help="scale geometry: ds = 1x128 fp32 (benchmark configs), mx = 1x32 UE8M0 (reference semantics)")
     ap.add_argument("--quick", action="store_true", help="shorter GEMV sweep")
@@ -861,6 +863,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=16384)
     ap.add_argument("--traffic", type=float, default=None, help="ncu dram bytes per launch of the dominant kernel, if captured")
     args = ap.parse_args()
+    if args.pdl is None:
+        args.pdl = int(os.environ.get("WORLD_SIZE", "1")) == 1
     if args.exchange_bench:
         exchange_bench(args)
     elif args.small_case:
