@@ -45,8 +45,22 @@ def moe_small(mode):
     return dict(ids=ids, w=rw, y=r["y_bf16"], c13_sum=np.array([c13.astype(np.uint64).sum()]), s13=s13[0, :4])
 
 
+def lm_head_small():
+    """Output head: 4 token rows against a bf16 [256][512] weight, seed 2, alpha 0.5, temperature 0.8, the last 20 rows
+    masked, ids offset 1000: the logits' row sums (fp64 of the fp32 values, rounded to 1e-3), and of the per-quad sampling
+    records the parts that do not depend on the accumulation order of a dot product: the ids of the 8 largest."""
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(4, 512, generator=g).bfloat16().view(torch.uint16).numpy()
+    w = (torch.randn(256, 512, generator=g) * 0.05).bfloat16().view(torch.uint16).numpy()
+    logits = oracle.lm_head(w, x, alpha=0.5)
+    rec = oracle.sampling_records(logits, 0.8, valid_rows=236, id_offset=1000)
+    return dict(row_sums=np.round(logits.astype(np.float64).sum(axis=1), 3), top_ids=rec.view(np.int32)[..., 11:19].copy(),
+                zmax=np.round(rec[..., 0].astype(np.float64), 3))
+
+
 if __name__ == "__main__":
     for mode, name in ((oracle.MODE_MX, "mx"), (oracle.MODE_DS, "ds")):
         np.savez_compressed(os.path.join(HERE, f"config0_{name}.npz"), **config0(mode))
         np.savez_compressed(os.path.join(HERE, f"moe_small_{name}.npz"), **moe_small(mode))
+    np.savez_compressed(os.path.join(HERE, "lm_head_small.npz"), **lm_head_small())
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))

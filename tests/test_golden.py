@@ -71,3 +71,27 @@ def test_cuda_path_matches_golden_moe(pkg, ctx, mode, name):
     want = oracle.bf16_to_f32(gold["y"])
     got = y.float().cpu().numpy()
     assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-2
+
+
+def test_oracle_reproduces_golden_lm_head():
+    gold = np.load(os.path.join(HERE, "lm_head_small.npz"))
+    now = make_golden.lm_head_small()
+    assert set(gold.files) == set(now)
+    for k in gold.files:
+        assert np.array_equal(gold[k], now[k]), k
+
+
+@pytest.mark.gpu
+def test_cuda_path_matches_golden_lm_head(pkg, ctx):
+    """dsuf_lm_head_bf16 against the committed vectors: the ids of the 8 largest logits of every quad exactly (the seeded
+    case has no near-ties), row sums and maxima within the rounding the fixture stores."""
+    gold = np.load(os.path.join(HERE, "lm_head_small.npz"))
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(4, 512, generator=g).bfloat16()
+    w = (torch.randn(256, 512, generator=g) * 0.05).bfloat16()
+    logits, rec = pkg.lm_head(ctx, w.cuda(), x.cuda(), alpha=0.5, temperature=0.8, valid_rows=236, id_offset=1000)
+    torch.cuda.synchronize()
+    r = rec.cpu().numpy()
+    assert np.array_equal(r.view(np.int32)[..., 11:19], gold["top_ids"])
+    assert np.abs(logits.cpu().numpy().astype(np.float64).sum(axis=1) - gold["row_sums"]).max() < 5e-3
+    assert np.abs(r[..., 0].astype(np.float64) - gold["zmax"]).max() < 2e-3
