@@ -15,7 +15,7 @@ import numpy as np
 MODE_MX, MODE_DS = 0, 1
 FMT_FP8, FMT_FP4 = 0, 1
 SCORE_IDENTITY, SCORE_SOFTMAX, SCORE_SQRT_SOFTPLUS = 0, 1, 2
-EPI_STORE, EPI_SWIGLU, EPI_SQRT_SOFTPLUS = 0, 1, 2   # dsuf_gemm_opts.epilogue
+EPI_STORE, EPI_SWIGLU, EPI_SQRT_SOFTPLUS, EPI_ACCUMULATE = 0, 1, 2, 3   # dsuf_gemm_opts.epilogue
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libdsuf_qmm.so")
@@ -438,12 +438,12 @@ def gemm_fp8_swiglu(ctx, w, xq, xs, m, out=None, swiglu_limit=0.0):
     return out
 
 
-def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None, sqrt_softplus=False):
+def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None, sqrt_softplus=False, accumulate=False):
     """dsuf_gemm_fp8_ex = ops::gemv with GemvOpts {alpha, out_f32, split} (ops.rs:165-193): fp32 or bf16 output, and with
     ``n_split`` > 0 the weight rows from n_split on go to a second tensor.  ``sqrt_softplus``: the router-gate epilogue
-    (Epilogue::SqrtSoftplus), fp32 scores.  Returns out, or (out, out2)."""
+    (Epilogue::SqrtSoftplus), fp32 scores.  ``accumulate``: fp32 ``out`` += result (deterministic).  Returns out, or (out, out2)."""
     t = ctx.torch
-    out_f32 = out_f32 or sqrt_softplus
+    out_f32 = out_f32 or sqrt_softplus or accumulate
     dt = t.float32 if out_f32 else t.bfloat16
     n1 = n_split if n_split > 0 else w.n
     if out is None:
@@ -451,7 +451,7 @@ def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None
     if n_split > 0 and out2 is None:
         out2 = t.empty((m, w.n - n_split), dtype=dt, device=xq.device)
     o = GemmOpts(alpha, int(bool(out_f32)), n_split, out2.stride(0) if out2 is not None else 0, out2.data_ptr() if out2 is not None else 0,
-                 EPI_SQRT_SOFTPLUS if sqrt_softplus else EPI_STORE, 0.0)
+                 EPI_SQRT_SOFTPLUS if sqrt_softplus else EPI_ACCUMULATE if accumulate else EPI_STORE, 0.0)
     ctx.check(lib().dsuf_gemm_fp8_ex(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0), C.byref(o),
                                      ctx.workspace.data_ptr()))
     return (out, out2) if n_split > 0 else out

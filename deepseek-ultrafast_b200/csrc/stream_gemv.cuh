@@ -51,6 +51,7 @@ struct StreamArgs {
     int whole_items;  // dense: give every CTA whole row tiles (no stream-K partials) when that costs no extra wave
     int swiglu;       // dense: 1 = the weight holds interleaved gate / up rows and the epilogue is SwiGLU (bf16 [m][n/2] out)
     int out_f32;      // dense: 1 = fp32 output instead of bf16 (GemvOpts.out_f32, crates/engine/src/ops.rs:165-193)
+    int accumulate;   // dense: 1 = fp32 out += v instead of out = v (each element is written by one thread of the launch)
     int ssp;          // dense: 1 = store sqrt(softplus(v)) (the router-gate epilogue, crates/kernels/cu/gemv.cu:523); fp32 output
     int n_split;      // dense: > 0 = weight rows >= n_split go to out2 (row stride ldo2) at column row - n_split (GemvOpts.split)
     void* out2;
@@ -66,7 +67,8 @@ DSUF_DEV void dense_store(const StreamArgs& a, int tok, int row, float v) {
     int ld = a.ldo, col = row;
     if (a.n_split > 0 && row >= a.n_split) { ob = a.out2; ld = a.ldo2; col = row - a.n_split; }
     if (a.ssp) v = sqrtf(v > 20.f ? v : log1pf(expf(v)));
-    if (a.out_f32) ((float*)ob)[(size_t)tok * ld + col] = v;
+    if (a.accumulate) ((float*)ob)[(size_t)tok * ld + col] += v;
+    else if (a.out_f32) ((float*)ob)[(size_t)tok * ld + col] = v;
     else ((__nv_bfloat16*)ob)[(size_t)tok * ld + col] = __float2bfloat16(v);
 }
 

@@ -115,7 +115,8 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
         DSUF_REQUIRE(ctx, opts->n_split >= 0 && opts->n_split < w->d.n, "dsuf_gemm_fp8_ex: n_split (%d) must be in 0..n-1", opts->n_split);
         DSUF_REQUIRE(ctx, opts->n_split == 0 || (opts->out2 && opts->ldo2 >= w->d.n - opts->n_split),
                      "dsuf_gemm_fp8_ex: n_split needs out2 with ldo2 >= n - n_split");
-        DSUF_REQUIRE(ctx, opts->epilogue == DSUF_EPI_STORE || opts->epilogue == DSUF_EPI_SWIGLU || opts->epilogue == DSUF_EPI_SQRT_SOFTPLUS,
+        DSUF_REQUIRE(ctx, opts->epilogue == DSUF_EPI_STORE || opts->epilogue == DSUF_EPI_SWIGLU || opts->epilogue == DSUF_EPI_SQRT_SOFTPLUS ||
+                              opts->epilogue == DSUF_EPI_ACCUMULATE,
                      "dsuf_gemm_fp8_ex: unknown epilogue %d", opts->epilogue);
         if (opts->epilogue == DSUF_EPI_SWIGLU) {
             DSUF_REQUIRE(ctx, w->d.gate_up && w->d.mode == DSUF_MODE_MX, "dsuf_gemm_fp8_ex: the SwiGLU epilogue needs an MX weight packed with dsuf_pack_fp8_weight_gate_up");
@@ -126,7 +127,8 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
             a.swiglu_limit = opts->swiglu_limit;
         }
         a.ssp = opts->epilogue == DSUF_EPI_SQRT_SOFTPLUS ? 1 : 0;
-        a.out_f32 = (opts->out_f32 || a.ssp) ? 1 : 0;
+        a.accumulate = opts->epilogue == DSUF_EPI_ACCUMULATE ? 1 : 0;
+        a.out_f32 = (opts->out_f32 || a.ssp || a.accumulate) ? 1 : 0;
         a.n_split = opts->n_split;
         a.out2 = (void*)opts->out2;
         a.ldo2 = opts->ldo2;

@@ -196,14 +196,15 @@ int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_
  *   out_f32  1 = fp32 output (out / out2 are float buffers) instead of bf16 (GemvOpts.out_f32; cu/gemv.cu:510-517)
  *   n_split  > 0 = weight rows [n_split, n) are written to out2 (row stride ldo2) at column row - n_split, rows
  *            [0, n_split) to out (GemvOpts.split: one launch for two projections merged along n, e.g. Loader::fp8_merged)
- * The AtomicAdd / Partial epilogue kinds of the reference's dense GEMV and its fused RoPE are not offered. */
+ * The Partial epilogue kind of the reference's dense GEMV (its K-split across launches; here the K reduction is inside the
+ * launch) and its fused RoPE are not offered. */
 typedef struct {
     float alpha;
     int32_t out_f32;
     int32_t n_split;
     int32_t ldo2;
     uint64_t out2;
-    int32_t epilogue;      /* DSUF_EPI_STORE, DSUF_EPI_SWIGLU or DSUF_EPI_SQRT_SOFTPLUS */
+    int32_t epilogue;      /* DSUF_EPI_STORE, _SWIGLU, _SQRT_SOFTPLUS or _ACCUMULATE */
     float swiglu_limit;    /* SwiGLU: clamp as cu/gemv.cu:470-483 when > 0 */
 } dsuf_gemm_opts;
 /* Epilogue::Store / Epilogue::SwiGlu (crates/engine/src/ops.rs:137-144).  SWIGLU: the weight holds gate and up rows
@@ -212,8 +213,11 @@ typedef struct {
  * model.rs:3081-3084; cu/tcgemm.cu:89-110); alpha must be 1, out_f32 0, n_split 0.
  * SQRT_SOFTPLUS: the router-gate projection (ops::gemv with Epilogue::SqrtSoftplus, model.rs:3094; cu/gemv.cu:523):
  * fp32 out[m][n] = sqrt(softplus(alpha * dot)) (sqrt(x) itself above 20, cu/common.cuh:17-24), i.e. the scores
- * dsuf_moe_route_tokens takes with DSUF_SCORE_IDENTITY; out is always fp32 (out_f32 is implied), n_split works as for STORE. */
-enum { DSUF_EPI_STORE = 0, DSUF_EPI_SWIGLU = 1, DSUF_EPI_SQRT_SOFTPLUS = 2 };
+ * dsuf_moe_route_tokens takes with DSUF_SCORE_IDENTITY; out is always fp32 (out_f32 is implied), n_split works as for STORE.
+ * ACCUMULATE: fp32 out[m][n] += alpha * dot -- what the reference's Epilogue::AtomicAdd is used for on dense weights
+ * (several projections summed into one fp32 buffer, cu/gemv.cu:489-491), without atomics: every output element is written
+ * by exactly one thread of the launch after the K reduction, so the sum is deterministic; out is fp32 (out_f32 implied). */
+enum { DSUF_EPI_STORE = 0, DSUF_EPI_SWIGLU = 1, DSUF_EPI_SQRT_SOFTPLUS = 2, DSUF_EPI_ACCUMULATE = 3 };
 /* dsuf_gemm_fp8 with options; same kernels, any number of token rows. */
 int32_t dsuf_gemm_fp8_ex(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_t xq, uint64_t xs, int32_t m, uint64_t out,
                          int32_t ldo, const dsuf_gemm_opts* opts, uint64_t workspace);

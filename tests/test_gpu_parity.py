@@ -200,6 +200,12 @@ def test_dense_gemv_options_fp32_output_and_column_split(pkg, ctx, mode, n, k, m
     torch.cuda.synchronize()
     want = torch.sqrt(torch.where(f32 > 20, f32, torch.log1p(torch.exp(f32))))
     assert ssp.dtype == torch.float32 and torch.allclose(ssp, want, rtol=1e-5, atol=1e-6)
+    # accumulate: fp32 out += result, every element written once per launch: two launches give exactly base + 2 * f32
+    accum = torch.full_like(f32, 0.25)
+    pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, out=accum, accumulate=True)
+    pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, out=accum, accumulate=True)
+    torch.cuda.synchronize()
+    assert torch.equal(accum, (torch.full_like(f32, 0.25) + f32) + f32)
     assert ctx.status().code == 0
 
 
