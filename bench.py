@@ -376,6 +376,49 @@ def reference_kernels(pkg, ctx, torch, hbm_peak, quick, use_pdl=False):
                           "ours_ms_w13_quant_w2": round(ms_ours_moe, 4), "ours_tflops": round(fl / ms_ours_moe / 1e9, 1),
                           "speedup": round(ms_ref_moe / ms_ours_moe, 2)}
     del wts, W13, W2, bufs
+    # the decode-size batch (64 tokens, top-8): the reference's decode path takes at most 16 rows (MAX_M,
+    # crates/model/src/limits.rs:1; its MoE kernels 97 slots, cu/gemv.cu:9), so a 64-token step takes Rank::ffn_prefill
+    # (model.rs:3063): the same tc_moe_w13 / tc_moe_w2, with 128-row tiles that hold a handful of rows each; ours runs its
+    # decode kernels on 8-row slots.  128 experts, hidden 5120 (the largest the reference's gate/up kernel takes).
+    ne2, tk2 = 128, 64
+    c13 = rng.integers(0, 256, (ne2, 2 * it_, dm // 2), dtype=np.uint8)
+    s13 = rng.integers(118, 122, (ne2, 2 * it_, dm // 32), dtype=np.uint8)
+    c2 = rng.integers(0, 256, (ne2, dm, it_ // 2), dtype=np.uint8)
+    s2 = rng.integers(118, 122, (ne2, dm, it_ // 32), dtype=np.uint8)
+    xm2 = torch.randn(tk2, dm, device=ctx.device).bfloat16()
+    ids2, wr2 = pkg.moe_route_tokens(ctx, pkg.SCORE_SOFTMAX, torch.randn(tk2, ne2, device=ctx.device), None, TOPK)
+    plan_r2 = rk.PrefillPlan(ids2, wr2, ne2)
+    xq_r2, sf_r2 = rk.moe_gather_quant(xm2, torch.ones(dm, dtype=torch.bfloat16, device=ctx.device), 1e-6, plan_r2)
+    wts2 = rk.MoeFp4Weights(c13, s13, c2, s2)
+    bufs2 = rk.tc_moe(wts2, plan_r2, xq_r2, sf_r2)
+    ms_ref_dec = time_events(torch, lambda: rk.tc_moe(wts2, plan_r2, xq_r2, sf_r2, out=bufs2), 10, 3)
+    rk.synchronize()
+    W13d = pkg.Weight.experts_fp4(ctx, c13, s13, True)
+    W2d = pkg.Weight.experts_fp4(ctx, c2, s2, False)
+    plan_d = pkg.MoePlan(ctx, tk2, TOPK, ne2, 8)
+    pkg.moe_perm(ctx, plan_d, ids2, wr2)
+    pr2 = tk2 * TOPK
+    xq_d = torch.empty(pr2, dm, dtype=torch.uint8, device=ctx.device)
+    xs_d = torch.empty(pr2, dm // 32, dtype=torch.uint8, device=ctx.device)
+    pkg.moe_gather_quant(ctx, pkg.MODE_MX, plan_d, xm2, xq_d, xs_d)
+    act_d = torch.empty(pr2, it_, dtype=torch.bfloat16, device=ctx.device)
+    aq_d = torch.empty(pr2, it_, dtype=torch.uint8, device=ctx.device)
+    as_d = torch.empty(pr2, it_ // 32, dtype=torch.uint8, device=ctx.device)
+    yr_d = torch.empty(pr2, dm, dtype=torch.float32, device=ctx.device)
+
+    def ours_dec():
+        pkg.moe_w13_swiglu(ctx, W13d, pkg.MODE_MX, plan_d, xq_d, xs_d, act_d, 0.0)
+        pkg.act_quant(ctx, pkg.MODE_MX, act_d, aq_d, as_d)
+        pkg.moe_w2(ctx, W2d, pkg.MODE_MX, plan_d, aq_d, as_d, yr_d)
+    ms_ours_dec = time_events(torch, ours_dec, 10, 3)
+    act_exp = int(torch.unique(ids2).numel())
+    wbytes = act_exp * (2 * it_ * dm // 2 + 2 * it_ * dm // 32 + dm * it_ // 2 + dm * it_ // 32)
+    out["decode_moe"] = {"hidden": dm, "inter": it_, "experts": ne2, "active_experts": act_exp, "tokens": tk2,
+                         "reference_kernels": "tc_moe_w13 + tc_moe_w2 (more than MAX_M = 16 rows: the reference's prefill path)",
+                         "reference_ms": round(ms_ref_dec, 4), "reference_gbs": round(wbytes / ms_ref_dec / 1e6, 1),
+                         "ours_ms_w13_quant_w2": round(ms_ours_dec, 4), "ours_gbs": round(wbytes / ms_ours_dec / 1e6, 1),
+                         "speedup": round(ms_ref_dec / ms_ours_dec, 2)}
+    del wts2, W13d, W2d, bufs2
     out["notes"].append("tc_moe_w13 (the reference's prefill gate/up GEMM) keeps the scale atoms of all K tiles of a token tile in 40 "
                         "shared-memory slots (cu/tcmoe.cu:171, SFB_MAX): K <= 5120, so it cannot run at hidden 7168 and is timed at 5120; the fused "
                         "decode MoE entries and comm.cu spin on global memory without a bound and are not launched on a shared GPU")
