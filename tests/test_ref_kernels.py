@@ -236,17 +236,20 @@ def test_tc_gemv_fp8_pins_the_oracle_and_matches_the_library(pkg, tc_only, n, k,
     assert rel(ref, got_r) < TOL and rel(got_l, got_r) < TOL
 
 
-def test_tc_moe_w13_w2_pin_the_oracle_and_match_the_library(pkg, tc_only):
+@pytest.mark.parametrize("tile_rows", [128, 8])
+def test_tc_moe_w13_w2_pin_the_oracle_and_match_the_library(pkg, ctx, tile_rows):
     """tc_moe_w13 / tc_moe_w2 (cu/tcmoe.cu:184-588), the reference's tcgen05 prefill expert GEMMs, launched after its own
     moe_perm and moe_gather_quant.  Each kernel is checked on the reference's OWN inputs:
       * gate/up + SwiGLU + re-quantization: the FP8 codes and UE8M0 scales it writes against the oracle's grouped FP4 GEMM
         + SwiGLU (bf16 rounds, routing weight folded in) + 1x32 quantizer on the same quantized token rows (a handful of
         codes may differ: the device's and the host's expf round a few bf16 values apart);
       * down projection: its fp32 pair rows against the oracle's GEMM on the reference's re-quantized activations;
-      * and this library's grouped kernels (dsuf_moe_w13_swiglu, dsuf_act_quant_fp8, dsuf_moe_w2 on 128-row plans, MX
-        geometry) on the same token codes, pair by pair.
-    This pins the expert-GEMM half of the oracle by the reference's kernel, as the dense half is pinned above."""
-    ctx = tc_only
+      * and this library's grouped kernels (dsuf_moe_w13_swiglu, dsuf_act_quant_fp8, dsuf_moe_w2, MX geometry) on the same
+        token codes, pair by pair: the prefill kernels on a 128-row plan and the decode kernels on 8-row slots.
+    This pins the expert-GEMM half of the oracle by the reference's kernel, as the dense half is pinned above.  The 8-row
+    case runs on both decode paths (tcgen05 and mma.sync streaming kernels)."""
+    if not ctx.tcgen05 and tile_rows == 128:
+        pytest.skip("128-row plans run on the tcgen05 path only")
     t, e, k, dim, inter = 300, 8, 4, 1024, 512
     g = seeded(77)
     logits = torch.randn(t, e, generator=g)
@@ -295,7 +298,7 @@ def test_tc_moe_w13_w2_pin_the_oracle_and_match_the_library(pkg, tc_only):
         assert rel(yp[rp_r[rows]], y) < 1e-4                               # same codes, fp32 accumulation order only
     assert bad_scales <= p * (inter // 32) // 1000 and bad_codes <= p * inter // 500, (bad_codes, bad_scales)
     # ---- this library's kernels on the same token codes ----
-    plan = pkg.MoePlan(ctx, t, k, e, 128)
+    plan = pkg.MoePlan(ctx, t, k, e, tile_rows)
     pkg.moe_perm(ctx, plan, ids, w)
     pr_l, pr_r = plan.pair_row.cpu().numpy(), plan_r.pair_row.cpu().numpy()
     xq_l, xs_l = np.zeros((p, dim), np.uint8), np.zeros((p, dim // 32), np.uint8)
