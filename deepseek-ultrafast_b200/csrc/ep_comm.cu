@@ -1,5 +1,6 @@
-// One-shot all-reduce of bf16 activation rows over NVLink peer memory, for the two per-layer exchanges of the
-// expert-parallel stack (the sum of the K-sharded dense partials and the sum of the per-rank expert outputs).
+// Exchanges of bf16 activation rows over NVLink peer memory for the expert-parallel stack: a one-shot all-reduce, the
+// combine (this rank's sum of every token's expert rows, then the all-reduce, optionally leaving the result quantized for
+// the next projection) and an all-gather of column slices (an output-sharded projection's dispatch).
 //
 // Replaces comm_push / comm_push2_body / nv_contrib (crates/kernels/cu/comm.cu:134-279, 355-375, 559-584): the
 // reference pushes partial rows into every peer and sums what arrived.  Here every rank leaves its partial where the
@@ -9,8 +10,9 @@
 // (64 tokens x 7168) that is 7 peer reads of 0.9 MB per rank: latency-, not bandwidth-bound, which is why it is one
 // kernel with one hand-shake instead of a ring or a tree.
 //
-// Every wait is bounded (dsuf_ctx_set_wait_budget_us, default common.cuh WAIT_BUDGET_TICKS): a rank that never announces makes the others record
-// DEVERR_WAIT_TIMEOUT in the context's status word and finish with an incomplete sum instead of hanging.
+// Every wait is bounded (dsuf_ctx_set_wait_budget_us, default common.cuh WAIT_BUDGET_TICKS): a rank that never announces
+// makes the others record DEVERR_WAIT_TIMEOUT in the context's status word and finish with an incomplete sum instead of
+// hanging; a peer more than one call ahead is reported as DEVERR_EPOCH_DRIFT.
 // The only peer accesses are plain ld / st on peer pointers.
 #include "internal.h"
 #include "quant_core.cuh"
