@@ -360,11 +360,13 @@ def test_gather_quant_prenorm_rows_equal_plain_prenorm_quant(pkg, ctx, mode):
 
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("t,e,k,h,e_lo,n_loc,tile", [(64, 256, 8, 7168, 0, 256, 8), (64, 256, 8, 1024, 32, 32, 8), (1, 8, 2, 128, 0, 8, 8),
-                                                     (100, 16, 3, 512, 0, 16, 16), (128, 256, 8, 256, 0, 256, 8), (40, 384, 6, 8320, 128, 128, 8)])
+                                                     (100, 16, 3, 512, 0, 16, 16), (128, 256, 8, 256, 0, 256, 8), (40, 384, 6, 8320, 128, 128, 8),
+                                                     (7, 16, 2, 256, 0, 16, 8), (9, 16, 2, 256, 0, 16, 8), (150, 32, 4, 256, 0, 32, 8)])
 def test_fused_decode_front_end_equals_the_separate_kernels(pkg, ctx, mode, t, e, k, h, e_lo, n_loc, tile):
     """Router + permute plan + gather/quant in one launch (at most 1024 pairs) against the three separate entries: routing,
     every plan array and the quantized permuted rows bit for bit; expert-parallel shards (pairs of other ranks' experts
-    dropped) and a hidden size above one 8192-element pass included."""
+    dropped), a hidden size above one 8192-element pass, and token counts around the cluster size of the shared routing
+    (7: no cluster; 9: one cluster of 8 CTAs for 9 tokens; 150: more tokens than CTAs) included."""
     g = seeded(t + e + h)
     xt, _ = randn_bf16(g, t, h)
     logits = torch.randn(t, e, generator=g).cuda()
