@@ -41,7 +41,8 @@ class PlanStruct(C.Structure):
 
 class GemmOpts(C.Structure):
     _fields_ = [("alpha", C.c_float), ("out_f32", C.c_int32), ("n_split", C.c_int32), ("ldo2", C.c_int32), ("out2", C.c_uint64),
-                ("epilogue", C.c_int32), ("swiglu_limit", C.c_float)]
+                ("epilogue", C.c_int32), ("swiglu_limit", C.c_float), ("rope_cos", C.c_uint64), ("rope_sin", C.c_uint64),
+                ("rope_pos", C.c_uint64), ("rope_head", C.c_int32), ("rope_off", C.c_int32)]
 
 
 class SamplingOpts(C.Structure):
@@ -438,10 +439,12 @@ def gemm_fp8_swiglu(ctx, w, xq, xs, m, out=None, swiglu_limit=0.0):
     return out
 
 
-def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None, sqrt_softplus=False, accumulate=False):
+def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None, out2=None, sqrt_softplus=False, accumulate=False,
+                rope=None):
     """dsuf_gemm_fp8_ex = ops::gemv with GemvOpts {alpha, out_f32, split} (ops.rs:165-193): fp32 or bf16 output, and with
     ``n_split`` > 0 the weight rows from n_split on go to a second tensor.  ``sqrt_softplus``: the router-gate epilogue
-    (Epilogue::SqrtSoftplus), fp32 scores.  ``accumulate``: fp32 ``out`` += result (deterministic).  Returns out, or (out, out2)."""
+    (Epilogue::SqrtSoftplus), fp32 scores.  ``accumulate``: fp32 ``out`` += result (deterministic).  ``rope`` = (cos f32 [pos][32], sin, pos int32 [1] on the device,
+    head, off): the fused rotary embedding of GemvOpts.rope on the first output.  Returns out, or (out, out2)."""
     t = ctx.torch
     out_f32 = out_f32 or sqrt_softplus or accumulate
     dt = t.float32 if out_f32 else t.bfloat16
@@ -452,6 +455,9 @@ def gemm_fp8_ex(ctx, w, xq, xs, m, alpha=1.0, out_f32=False, n_split=0, out=None
         out2 = t.empty((m, w.n - n_split), dtype=dt, device=xq.device)
     o = GemmOpts(alpha, int(bool(out_f32)), n_split, out2.stride(0) if out2 is not None else 0, out2.data_ptr() if out2 is not None else 0,
                  EPI_SQRT_SOFTPLUS if sqrt_softplus else EPI_ACCUMULATE if accumulate else EPI_STORE, 0.0)
+    if rope is not None:
+        cos, sin, pos, head, off = rope
+        o.rope_cos, o.rope_sin, o.rope_pos, o.rope_head, o.rope_off = cos.data_ptr(), sin.data_ptr(), pos.data_ptr(), int(head), int(off)
     ctx.check(lib().dsuf_gemm_fp8_ex(ctx.h, ctx.stream(), w.h, xq.data_ptr(), xs.data_ptr(), m, out.data_ptr(), out.stride(0), C.byref(o),
                                      ctx.workspace.data_ptr()))
     return (out, out2) if n_split > 0 else out

@@ -56,6 +56,10 @@ struct StreamArgs {
     int n_split;      // dense: > 0 = weight rows >= n_split go to out2 (row stride ldo2) at column row - n_split (GemvOpts.split)
     void* out2;
     int ldo2;
+    const float* rope_cos;   // dense, tcgen05 kernels: rotary tables [position][32] (null: no rotation), GemvOpts.rope
+    const float* rope_sin;
+    const int* rope_pos;     // device int: position of token row 0 (row m sits at rope_pos[0] + m)
+    int rope_head, rope_off; // rows r with (r % rope_head) >= rope_off are rotated in (even, odd) pairs
     int kslices;      // dense, tcgen05 kernel: > 0 = one row tile per cluster of `kslices` CTAs, each taking a slice of K;
                       // the slices are summed through distributed shared memory (no global partials)
 };
@@ -70,6 +74,23 @@ DSUF_DEV void dense_store(const StreamArgs& a, int tok, int row, float v) {
     if (a.accumulate) ((float*)ob)[(size_t)tok * ld + col] += v;
     else if (a.out_f32) ((float*)ob)[(size_t)tok * ld + col] = v;
     else ((__nv_bfloat16*)ob)[(size_t)tok * ld + col] = __float2bfloat16(v);
+}
+
+// The same store with the reference's fused rotary embedding (crates/kernels/cu/gemv.cu:508-516): rows of the first output
+// whose position inside their head is at least rope_off are rotated in (even, odd) pairs with the token's cos / sin,
+// operands rounded to bf16 first, one fma per output as the reference writes them; every other row is stored as usual.
+// `v` is this row's value, `partner` the value of row ^ 1 (the neighbouring lane).  bf16 output.
+DSUF_DEV void dense_store_rope(const StreamArgs& a, int tok, int row, float v, float partner) {
+    const int hd = row % a.rope_head;
+    if ((a.n_split > 0 && row >= a.n_split) || hd < a.rope_off) {
+        dense_store(a, tok, row, v);
+        return;
+    }
+    const float x = __bfloat162float(__float2bfloat16(v)), y = __bfloat162float(__float2bfloat16(partner));
+    const int pos = a.rope_pos[0] + tok, f = (hd - a.rope_off) >> 1;
+    const float c = a.rope_cos[(size_t)pos * 32 + f], sn = a.rope_sin[(size_t)pos * 32 + f];
+    const float o = (row & 1) ? __fmaf_rn(y, sn, __fmul_rn(x, c)) : __fmaf_rn(x, c, -__fmul_rn(y, sn));
+    ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + row] = __float2bfloat16(o);
 }
 
 template <int FMT>

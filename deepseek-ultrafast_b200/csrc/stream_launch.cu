@@ -127,6 +127,19 @@ int launch_stream_dense(dsuf_ctx* ctx, cudaStream_t stream, const dsuf_weight* w
             a.swiglu_limit = opts->swiglu_limit;
         }
         a.ssp = opts->epilogue == DSUF_EPI_SQRT_SOFTPLUS ? 1 : 0;
+        if (opts->rope_cos) {
+            DSUF_REQUIRE(ctx, ctx->use_tc && opts->epilogue == DSUF_EPI_STORE && !opts->out_f32, "dsuf_gemm_fp8_ex: the fused rotary embedding needs the tcgen05 path, the store epilogue and bf16 output");
+            DSUF_REQUIRE(ctx, opts->rope_sin && opts->rope_pos && (opts->rope_cos & 3) == 0 && (opts->rope_sin & 3) == 0 && (opts->rope_pos & 3) == 0,
+                         "dsuf_gemm_fp8_ex: rope tables / position null or misaligned");
+            DSUF_REQUIRE(ctx, opts->rope_head >= 2 && opts->rope_head % 2 == 0 && opts->rope_off >= 0 && opts->rope_off % 2 == 0 &&
+                              opts->rope_off < opts->rope_head && opts->rope_head - opts->rope_off <= 64 && w->d.n % 2 == 0 && opts->n_split % 2 == 0,
+                         "dsuf_gemm_fp8_ex: rope_head / rope_off must be even, 0 <= rope_off < rope_head, at most 64 rotated rows per head");
+            a.rope_cos = (const float*)opts->rope_cos;
+            a.rope_sin = (const float*)opts->rope_sin;
+            a.rope_pos = (const int*)opts->rope_pos;
+            a.rope_head = opts->rope_head;
+            a.rope_off = opts->rope_off;
+        }
         a.accumulate = opts->epilogue == DSUF_EPI_ACCUMULATE ? 1 : 0;
         a.out_f32 = (opts->out_f32 || a.ssp || a.accumulate) ? 1 : 0;
         a.n_split = opts->n_split;

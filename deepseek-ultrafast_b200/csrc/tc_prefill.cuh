@@ -354,7 +354,16 @@ __global__ void __launch_bounds__(TcpCfgT<NTOK>::THREADS, 1) tc_prefill_kernel(c
                 const int col = rt * 128 + r;
 #pragma unroll
                 for (int j = 0; j < CPT; ++j)
-                    if (cb + j < cnt && col < a.n_rows) dense_store(a, xrow0 + cb + j, col, acc[j] * a.alpha);
+                {
+                    const float v = acc[j] * a.alpha;
+                    const bool mine = cb + j < cnt && col < a.n_rows;
+                    if (a.rope_cos) {
+                        const float pv = __shfl_xor_sync(0xffffffffu, v, 1);   // row ^ 1 is the neighbouring lane
+                        if (mine) dense_store_rope(a, xrow0 + cb + j, col, v, pv);
+                    } else if (mine) {
+                        dense_store(a, xrow0 + cb + j, col, v);
+                    }
+                }
             } else {
                 float* o = (float*)a.out;
                 const int col = rt * 128 + r;

@@ -607,8 +607,16 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                                 }
                             } else {
 #pragma unroll
-                                for (int u = 0; u < 8; ++u)
-                                    if (jc + u < jend && cb + jc + u < cnt && row < a.n_rows) dense_store(a, cb + jc + u, row, sum[u] * a.alpha);
+                                for (int u = 0; u < 8; ++u) {
+                                    const float v = sum[u] * a.alpha;
+                                    const bool mine = jc + u < jend && cb + jc + u < cnt && row < a.n_rows;
+                                    if (a.rope_cos) {
+                                        const float pv = __shfl_xor_sync(0xffffffffu, v, 1);   // row ^ 1 is the neighbouring lane
+                                        if (mine) dense_store_rope(a, cb + jc + u, row, v, pv);
+                                    } else if (mine) {
+                                        dense_store(a, cb + jc + u, row, v);
+                                    }
+                                }
                             }
                         }
                         cluster_barrier();
@@ -667,8 +675,16 @@ __global__ void __launch_bounds__(TcCfg<N, PAIR>::THREADS, 1) tc_stream_kernel(c
                             }
                         } else {
 #pragma unroll
-                            for (int j = 0; j < NC; ++j)
-                                if (cb + j < cnt && row < a.n_rows) dense_store(a, cb + j, row, acc[j] * a.alpha);
+                            for (int j = 0; j < NC; ++j) {
+                                const float v = acc[j] * a.alpha;
+                                const bool mine = cb + j < cnt && row < a.n_rows;
+                                if (a.rope_cos) {
+                                    const float pv = __shfl_xor_sync(0xffffffffu, v, 1);   // row ^ 1 is the neighbouring lane
+                                    if (mine) dense_store_rope(a, cb + j, row, v, pv);
+                                } else if (mine) {
+                                    dense_store(a, cb + j, row, v);
+                                }
+                            }
                         }
                     }
                 } else if (EPI == EPI_W13) {

@@ -197,7 +197,7 @@ int32_t dsuf_gemm_fp8(dsuf_ctx* ctx, void* stream, const dsuf_weight* w, uint64_
  *   n_split  > 0 = weight rows [n_split, n) are written to out2 (row stride ldo2) at column row - n_split, rows
  *            [0, n_split) to out (GemvOpts.split: one launch for two projections merged along n, e.g. Loader::fp8_merged)
  * The Partial epilogue kind of the reference's dense GEMV (its K-split across launches; here the K reduction is inside the
- * launch) and its fused RoPE are not offered. */
+ * launch) and the FP4 index-query branch of its fused RoPE (iq_head) are not offered. */
 typedef struct {
     float alpha;
     int32_t out_f32;
@@ -206,6 +206,15 @@ typedef struct {
     uint64_t out2;
     int32_t epilogue;      /* DSUF_EPI_STORE, _SWIGLU, _SQRT_SOFTPLUS or _ACCUMULATE */
     float swiglu_limit;    /* SwiGLU: clamp as cu/gemv.cu:470-483 when > 0 */
+    /* Fused rotary embedding (GemvOpts.rope, ops.rs:165-193; cu/gemv.cu:508-516), STORE epilogue, bf16 output, tcgen05
+     * path: rope_cos / rope_sin f32 [positions][32], rope_pos a DEVICE int (token row m sits at position rope_pos[0] + m);
+     * output rows r of the first output (r < n_split when split) with (r % rope_head) >= rope_off are rotated in
+     * (even, odd) pairs.  rope_cos = 0: no rotation. */
+    uint64_t rope_cos;
+    uint64_t rope_sin;
+    uint64_t rope_pos;
+    int32_t rope_head;
+    int32_t rope_off;
 } dsuf_gemm_opts;
 /* Epilogue::Store / Epilogue::SwiGlu (crates/engine/src/ops.rs:137-144).  SWIGLU: the weight holds gate and up rows
  * (packed by dsuf_pack_fp8_weight_gate_up, MX scales, tcgen05 path) and out receives bf16 [m][n/2] =

@@ -229,6 +229,28 @@ def dequant_fp4(codes, s):
     return v * np.repeat(sf, 32, axis=1)
 
 
+def rope_rows(v_f32, cos, sin, pos0, head, off, n_first=None):
+    """The fused rotary embedding of the reference's GEMV epilogue (crates/kernels/cu/gemv.cu:508-516) applied to fp32
+    results v [m][n]: columns r < n_first (default: all) with (r % head) >= off are rotated in (even, odd) pairs:
+    a = bf16(v[r]), b = bf16(v[r+1]); out[r] = fma(a, c, -(b*s)), out[r+1] = fma(a, s, b*c) with c / s =
+    cos / sin[pos0 + token][((r % head) - off) / 2]; fp32 in, bf16-rounded fp32 out (every column rounded to bf16)."""
+    v = np.asarray(v_f32, np.float32)
+    m, n = v.shape
+    n_first = n if n_first is None else n_first
+    out = bf16_to_f32(f32_to_bf16(v)).astype(np.float32)
+    r = np.arange(0, n_first, 2)
+    sel = r[(r % head) >= off]
+    f = ((sel % head) - off) // 2
+    for t in range(m):
+        a, b = out[t, sel].astype(np.float64), out[t, sel + 1].astype(np.float64)
+        c, s_ = cos[pos0 + t, f].astype(np.float64), sin[pos0 + t, f].astype(np.float64)
+        bs, bc = (b * s_).astype(np.float32).astype(np.float64), (b * c).astype(np.float32).astype(np.float64)
+        o0, o1 = (a * c - bs).astype(np.float32), (a * s_ + bc).astype(np.float32)
+        out[t, sel] = bf16_to_f32(f32_to_bf16(o0))
+        out[t, sel + 1] = bf16_to_f32(f32_to_bf16(o1))
+    return out
+
+
 def lm_head(w_bf16, x_bf16, alpha=1.0):
     """Output-head logits fp32 [m][n] = alpha * x . w^T over bf16 operands with fp32 accumulation
     (gemv_bf16_persist_body, crates/kernels/cu/gemv.cu:542-650; the accumulation order inside a row is the kernel's own,

@@ -786,3 +786,41 @@ def test_programmatic_dependent_launch_changes_no_result(pkg):
         c.close()
     assert torch.equal(outs[0][0].view(torch.uint16), outs[1][0].view(torch.uint16))
     assert torch.equal(outs[0][1].view(torch.uint16), outs[1][1].view(torch.uint16)) and torch.equal(outs[0][2], outs[1][2])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("n,k,m,head,off,split", [(512, 1024, 5, 128, 64, 0), (1024, 512, 64, 192, 128, 768), (768, 2048, 200, 64, 0, 0), (7168, 2048, 2, 128, 64, 0)])
+def test_dense_gemv_fused_rotary_embedding(pkg, ctx, mode, n, k, m, head, off, split):
+    """GemvOpts.rope on the dense kernels (decode stream-K / cluster split / prefill tiles): the rotated bf16 output against
+    the oracle's rotation (crates/kernels/cu/gemv.cu:508-516) of the kernel's own fp32 result -- at most one bf16 step apart
+    (the host evaluates the fma in double) -- with heads whose first rows are not rotated, a column split whose second
+    output is stored unrotated, and a position offset read from device memory."""
+    if not ctx.tcgen05:
+        pytest.skip("tcgen05 path only")
+    g = seeded(n + k + m + head)
+    xt, _ = randn_bf16(g, m, k)
+    _, wn = randn_bf16(g, n, k, std=0.02)
+    wq, ws = oracle.quant_fp8_weight(mode, wn)
+    w = pkg.Weight.dense_fp8(ctx, mode, wq, ws)
+    xq, xs = pkg.act_quant(ctx, mode, xt.cuda())
+    pos0 = 37
+    ang = torch.rand(pos0 + m, 32, generator=g) * 6.28
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+    f32 = pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, out_f32=True)
+    rope = (cos.cuda(), sin.cuda(), pos, head, off)
+    if split:
+        a, b = pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, n_split=split, rope=rope)
+        got = torch.cat([a, b], dim=1)
+    else:
+        got = pkg.gemm_fp8_ex(ctx, w, xq, xs, m, alpha=0.5, rope=rope)
+    torch.cuda.synchronize()
+    assert ctx.status().code == 0 and got.dtype == torch.bfloat16
+    want = oracle.rope_rows(f32.cpu().numpy(), cos.numpy(), sin.numpy(), pos0, head, off, n_first=split or None)
+    gf = got.float().cpu().numpy()
+    assert np.abs(gf - want).max() <= np.abs(want).max() * 2.0 ** -7
+    assert (gf == want).mean() > 0.99
+    cols = np.arange(n)
+    plain = ((cols % head) < off) | ((cols >= split) if split else False)
+    assert np.array_equal(gf[:, plain], oracle.bf16_to_f32(oracle.f32_to_bf16(f32.cpu().numpy()))[:, plain])   # unrotated columns: the plain store
